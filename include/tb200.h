@@ -1,0 +1,115 @@
+/*
+ * tb200 — C ABI of the sm_100a kernels behind the PCVR inference hot path.
+ *
+ * Conventions shared by every entry point:
+ *   - plain C types only; all data pointers are DEVICE pointers owned by the caller and
+ *     kept alive until the stream has passed the call;
+ *   - the work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream); no entry point synchronises, allocates device memory or
+ *     takes ownership of anything unless its comment says so;
+ *   - the return value is 0 on success, a negative TB200_ERR_* code for a rejected
+ *     argument (nothing was launched), or a positive cudaError_t from the launch;
+ *   - tensors are dense row-major unless strides are passed explicitly.
+ *
+ * Each declaration names the reference operator it stands behind
+ * (paths are relative to the reference project's root).
+ */
+#ifndef TB200_H_
+#define TB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------------------- */
+#define TB200_OK 0
+#define TB200_ERR_NULL (-1)        /* a required pointer is NULL */
+#define TB200_ERR_DTYPE (-2)       /* unknown / unsupported element or index type */
+#define TB200_ERR_SHAPE (-3)       /* a size is negative, zero where it must not be, or too large */
+#define TB200_ERR_ALIGN (-4)       /* a pointer or stride breaks the kernel's alignment rule */
+#define TB200_ERR_UNSUPPORTED (-5) /* valid request that this build has no kernel for */
+#define TB200_ERR_DEVICE (-6)      /* current device is not compute capability 10.x */
+#define TB200_ERR_DRIVER (-7)      /* a driver entry point (tensor-map encode) is unavailable or failed */
+
+/* ---- element / index type codes ------------------------------------------------------- */
+#define TB200_F32 0
+#define TB200_F16 1
+#define TB200_BF16 2
+#define TB200_I32 0
+#define TB200_I64 1
+
+/* Human-readable text for a status code returned by this library (never NULL). */
+const char* tb200_strerror(int code);
+
+/* Library ABI version; bumped when a signature changes. */
+int tb200_abi_version(void);
+
+/* 1 if the CURRENT device can run these kernels (compute capability 10.x), else 0.
+ * Mirrors the availability probes the reference dispatchers consult before choosing an
+ * accelerated backend (src/taac2026/infrastructure/accelerators/tilelang_runtime.py,
+ * triton_runtime.py). */
+int tb200_device_ok(void);
+
+/* Number of kernel launches enqueued by this library in this process so far. */
+int64_t tb200_launch_count(void);
+
+/* ---- (b) normalisation ------------------------------------------------------------------
+ * y[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * gamma          (fp32 accumulation)
+ * Replaces the accelerated branches of `rms_norm`
+ * (src/taac2026/infrastructure/accelerators/normalization/rms_norm.py:377-401; oracle
+ * `_torch_rms_norm` :71-73).  x, y: [rows, cols] contiguous, gamma: [cols], all of
+ * `dtype`.  rows may be 0.  Any cols >= 1 is accepted; rows whose byte length is a multiple
+ * of 16 with 16-byte aligned bases take the TMA-staged kernel. */
+int tb200_rmsnorm_fwd(const void* x, const void* gamma, void* y, int64_t rows, int32_t cols, float eps, int dtype,
+                      void* stream);
+
+/* y[r, :] = (x[r, :] - mean) * rsqrt(var + eps) * gamma + beta, two-pass centred variance in fp32.
+ * Replaces the accelerated branch of `layer_norm`
+ * (src/taac2026/infrastructure/accelerators/normalization/layer_norm.py:261-280; oracle
+ * `_torch_layer_norm` :65-66). */
+int tb200_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int32_t cols,
+                        float eps, int dtype, void* stream);
+
+/* ---- (a) sparse-field embedding gather / pool ---------------------------------------------
+ * out[b, :] = mean over hot h of table[ids[b, h], :] for ids in (0, vocab_rows); ids equal to 0
+ * (padding) or outside the table are skipped; an empty bag gives zeros.  fp32 sum in hot order,
+ * one true division by the count, then rounding to `dtype`.  A bag of one id is a bit-exact row copy.
+ * Replaces `embedding_bag_mean`
+ * (src/taac2026/infrastructure/accelerators/embedding/embedding_bag.py:439-467; oracle
+ * `_torch_embedding_bag_mean` :82-83 and the CUDA kernel
+ * embedding/kernels/cuembed_embedding_bag_mean.cu:19-47).
+ * table: [vocab_rows, dim]; ids: [batch, bag] of `ids_dtype`; out: [batch, dim]. */
+int tb200_bag_mean_fwd(const void* table, int64_t vocab_rows, int32_t dim, const void* ids, int ids_dtype,
+                       int64_t batch, int32_t bag, void* out, int dtype, void* stream);
+
+/* All sparse fields of one entity in a single launch: the fused form of the per-field Python
+ * loop in `FeatureEmbeddingBank.forward`
+ * (src/taac2026/infrastructure/modeling/embeddings.py:137-173), including its
+ * `.clamp(min=0, max=vocab)` of the raw ids.
+ * tables: device array of n_fields table base pointers, each [rows[f], dim] of `dtype`;
+ * rows, offsets, lengths: device arrays [n_fields] (table row count; first column and bag size
+ * of the field inside one row of `ids`); ids: [batch, ids_cols] of `ids_dtype`;
+ * out: [batch, n_fields, dim].  max_bag = max(lengths) (host value, sizes the id staging). */
+int tb200_fields_bag_mean_fwd(const void* const* tables, const int64_t* rows, const int32_t* offsets,
+                              const int32_t* lengths, int32_t n_fields, int32_t max_bag, int32_t dim, const void* ids,
+                              int ids_dtype, int64_t batch, int32_t ids_cols, void* out, int dtype, void* stream);
+
+/* out[i, out_col0 : out_col0 + dim] = table[clamp(id_i, 0, vocab_rows - 1), :]   (bit-exact copy)
+ * for i in [0, n), with id_i = ids[(i / seq_len) * ids_batch_stride + (i % seq_len)].
+ * The `nn.Embedding` gather of `SequenceTokenizer.forward` fused with its id clamp and with the
+ * `torch.cat` over features (src/taac2026/infrastructure/modeling/tokenizers.py:156-176): for feature f
+ * of a [B, F, L] id tensor pass ids + f * L, seq_len = L, ids_batch_stride = F * L, n = B * L, and
+ * out_col0 = f * dim inside output rows of out_stride = F * dim elements.  A flat id vector is
+ * seq_len = n, ids_batch_stride = 0.
+ * dim, out_col0 and out_stride times sizeof(dtype) must be multiples of 16; table and out 16-byte aligned. */
+int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t dim, const void* ids, int ids_dtype, int64_t n,
+                      int64_t seq_len, int64_t ids_batch_stride, void* out, int64_t out_stride, int32_t out_col0,
+                      int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TB200_H_ */
