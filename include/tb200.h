@@ -108,6 +108,29 @@ int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t dim, const 
                       int64_t seq_len, int64_t ids_batch_stride, void* out, int64_t out_stride, int32_t out_col0,
                       int dtype, void* stream);
 
+/* ---- (c) varlen masked attention forward ----------------------------------------------------
+ * o[b, h, q, :] = softmax_k(scale * <q[b, h, q, :], k[b, h, k, :]> over visible k) . v[b, h, k, :]
+ * with fp32 softmax statistics and accumulation.  Key k is visible to query q of sample b iff
+ *     (k < seq_len[b]  or  k >= ns_start)  and  k < Lk  and  (not causal or k <= q).
+ * With padded_query_self, queries in [seq_len[b], ns_start) return v[b, h, q, :] (needs Lq == Lk);
+ * a query without any visible key returns zeros.  The mask is never materialised.
+ * Replaces the inference branch of `flash_attention`
+ * (src/taac2026/infrastructure/accelerators/attention/flash_attention.py:871-919; mask planner
+ * :149-198 -> (seq_len, causal, padded_query_self); self fallback :201-209; kernel
+ * attention/kernels/tilelang.py:36-138; oracle `_torch_flash_attention` :552-570).  ns_start extends
+ * the planner's two mask families to OneTrans's [sequence | always-valid NS tokens] layout
+ * (experiments/onetrans/model.py:325-330); ns_start >= Lk means no such suffix.
+ * strides: 12 host values, in elements: (batch, head, row) for q, k, v, o; the head dim is contiguous
+ * and every stride a multiple of 8.  seq_len: device int32[B] or NULL (all keys valid).
+ * cu_rows: device int32[B + 1] or NULL; when given, the batch is packed along the row axis: sample b
+ * owns rows [cu_rows[b], cu_rows[b+1]) (batch strides and seq_len unused, every key valid, Lq and Lk
+ * are upper bounds of any sample's row count).
+ * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.  kernel: 0 = automatic choice. */
+int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
+                   int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len, const int32_t* cu_rows,
+                   int32_t ns_start, int32_t causal, int32_t padded_query_self, float scale, int dtype,
+                   int32_t kernel, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

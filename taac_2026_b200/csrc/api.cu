@@ -24,6 +24,7 @@ const DeviceInfo& device_info() {
     }
     std::call_once(g_once[dev], [dev]() {
         DeviceInfo d;
+        d.index = dev;
         cudaDeviceProp p;
         if (cudaGetDeviceProperties(&p, dev) == cudaSuccess) {
             d.sm_count = p.multiProcessorCount;

@@ -1,0 +1,40 @@
+// C-ABI entry of the attention forward: argument checks and kernel selection.
+#include "attn_common.cuh"
+#include "tb200_common.cuh"
+
+namespace tb200 {
+int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cudaStream_t stream);
+}  // namespace tb200
+
+extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
+                              int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len,
+                              const int32_t* cu_rows, int32_t ns_start, int32_t causal, int32_t padded_query_self,
+                              float scale, int dtype, int32_t kernel, void* stream) {
+    using namespace tb200;
+    if (B < 0 || H < 1 || Lq < 0 || Lk < 0 || D < 1) return TB200_ERR_SHAPE;
+    if (B == 0 || Lq == 0) return TB200_OK;
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || strides == nullptr) return TB200_ERR_NULL;
+    if (dtype != TB200_BF16 && dtype != TB200_F16) return TB200_ERR_DTYPE;
+    if (D != 32 && D != 64 && D != 128) return TB200_ERR_UNSUPPORTED;
+    if (padded_query_self && cu_rows == nullptr && Lq != Lk) return TB200_ERR_SHAPE;
+    if (ns_start < 0) return TB200_ERR_SHAPE;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return TB200_ERR_ALIGN;
+    for (int i = 0; i < 12; ++i)
+        if (strides[i] % 8 != 0) return TB200_ERR_ALIGN;  // every row must start on a 16-byte boundary
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    AttnArgs a{};
+    a.q = q; a.k = k; a.v = v; a.o = o;
+    a.q_sb = strides[0]; a.q_sh = strides[1]; a.q_sl = strides[2];
+    a.k_sb = strides[3]; a.k_sh = strides[4]; a.k_sl = strides[5];
+    a.v_sb = strides[6]; a.v_sh = strides[7]; a.v_sl = strides[8];
+    a.o_sb = strides[9]; a.o_sh = strides[10]; a.o_sl = strides[11];
+    a.seq_len = seq_len;
+    a.cu_rows = cu_rows;
+    a.B = B; a.H = H; a.Lq = Lq; a.Lk = Lk;
+    a.ns_start = ns_start > Lk ? Lk : ns_start;
+    a.causal = causal != 0;
+    a.padded_query_self = padded_query_self != 0;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    (void)kernel;
+    return attn_mma_forward(a, D, dtype, Lq, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,338 @@
+// Varlen masked attention forward, broad-coverage kernel (head_dim 32 / 64 / 128, bf16 / fp16,
+// any strides, padded or packed batches).  Online softmax in registers, fp32 accumulation,
+// warp-level mma.sync m16n8k16 tiles fed by cp.async double buffering.  KV tiles that hold no
+// visible key for the query tile are skipped, and query tiles that lie wholly inside the padded
+// region only copy their value rows.  The tcgen05 kernel covers the head_dim-64 bf16 hot shape;
+// this one covers everything else.
+#include "attn_common.cuh"
+#include "tb200_common.cuh"
+
+namespace tb200 {
+void count_launch();
+
+namespace {
+
+constexpr int kBM = 64;  // query rows per CTA (16 per warp)
+constexpr int kBN = 64;  // keys per tile
+constexpr int kThreads = 128;
+
+template <int D>
+__device__ __forceinline__ int swz(int row, int chunk) {  // element offset of a 16-byte chunk
+    constexpr int CH = D / 8;
+    if (CH >= 8) return row * D + ((chunk ^ (row & 7)) << 3);
+    if (CH == 4) return row * D + ((chunk ^ ((row >> 1) & 3)) << 3);
+    return row * D + ((chunk ^ ((row >> 2) & 1)) << 3);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int bytes = pred ? 16 : 0;  // src-size 0 -> zero fill
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                        uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// rows [row0, row0 + 64) of a [*, D] strided matrix -> swizzled shared tile; rows >= n_rows are zero
+template <typename T, int D>
+__device__ __forceinline__ void load_tile(T* smem, const T* gmem, int64_t stride_l, int row0, int n_rows, int tid) {
+    constexpr int CH = D / 8;
+    for (int i = tid; i < kBN * CH; i += kThreads) {
+        const int r = i / CH;
+        const int c = i - r * CH;
+        const bool ok = row0 + r < n_rows;
+        const T* src = gmem + static_cast<int64_t>(ok ? row0 + r : 0) * stride_l + c * 8;
+        cp_async16(smem + swz<D>(r, c), src, ok);
+    }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    T* sQ = reinterpret_cast<T*>(smem_raw);
+    T* sK = sQ + kBM * D;       // 2 stages
+    T* sV = sK + 2 * kBN * D;   // 2 stages
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int b = blockIdx.z;
+    const int h = blockIdx.y;
+    const int m0 = blockIdx.x * kBM;
+
+    int lq = a.Lq, lk = a.Lk;
+    int64_t row_base = 0;
+    if (a.cu_rows != nullptr) {
+        row_base = a.cu_rows[b];
+        lq = lk = a.cu_rows[b + 1] - static_cast<int32_t>(row_base);
+    }
+    if (m0 >= lq) return;
+    const bool packed = a.cu_rows != nullptr;
+    const T* q = static_cast<const T*>(a.q) + (packed ? row_base * a.q_sl : b * a.q_sb) + h * a.q_sh;
+    const T* k = static_cast<const T*>(a.k) + (packed ? row_base * a.k_sl : b * a.k_sb) + h * a.k_sh;
+    const T* v = static_cast<const T*>(a.v) + (packed ? row_base * a.v_sl : b * a.v_sb) + h * a.v_sh;
+    T* o = static_cast<T*>(a.o) + (packed ? row_base * a.o_sl : b * a.o_sb) + h * a.o_sh;
+
+    const int valid_len = (a.seq_len != nullptr && !packed) ? min(max(a.seq_len[b], 0), lk) : lk;
+    const int ns_start = packed ? lk : min(a.ns_start, lk);
+    const bool causal = a.causal != 0;
+    const bool self_rows = a.padded_query_self != 0;
+    const int m_end = min(m0 + kBM, lq);
+    // queries in [valid_len, ns_start) are padded; they return their value row
+    const bool tile_all_padded = self_rows && m0 >= valid_len && m_end <= ns_start;
+
+    float acc_o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc_o[j][e] = 0.f;
+    float row_m[2] = {-INFINITY, -INFINITY};
+    float row_l[2] = {0.f, 0.f};
+
+    if (!tile_all_padded) {
+        // key tiles that can hold a visible key for this query tile
+        const int kv_end = causal ? min(lk, m_end) : lk;
+        const int n_tiles = (kv_end + kBN - 1) / kBN;
+        auto tile_live = [&](int n) {
+            const int n0 = n * kBN;
+            return n0 < valid_len || n0 + kBN > ns_start;
+        };
+        int first = 0;
+        while (first < n_tiles && !tile_live(first)) ++first;
+
+        load_tile<T, D>(sQ, q, a.q_sl, m0, lq, tid);
+        if (first < n_tiles) {
+            load_tile<T, D>(sK, k, a.k_sl, first * kBN, lk, tid);
+            load_tile<T, D>(sV, v, a.v_sl, first * kBN, lk, tid);
+        }
+        cp_async_commit();
+
+        uint32_t qf[D / 16][4];
+        bool q_loaded = false;
+        int stage = 0;
+        for (int n = first; n < n_tiles;) {
+            int next = n + 1;
+            while (next < n_tiles && !tile_live(next)) ++next;
+            if (next < n_tiles) {
+                load_tile<T, D>(sK + (stage ^ 1) * kBN * D, k, a.k_sl, next * kBN, lk, tid);
+                load_tile<T, D>(sV + (stage ^ 1) * kBN * D, v, a.v_sl, next * kBN, lk, tid);
+            }
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+
+            if (!q_loaded) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    ldsm_x4(qf[kk], sQ + swz<D>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+                q_loaded = true;
+            }
+            const T* cK = sK + stage * kBN * D;
+            const T* cV = sV + stage * kBN * D;
+
+            // S = Q K^T
+            float s[kBN / 8][4];
+#pragma unroll
+            for (int j = 0; j < kBN / 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+                for (int jp = 0; jp < kBN / 16; ++jp) {
+                    uint32_t kb[4];
+                    const int mi = lane >> 3;
+                    ldsm_x4(kb, cK + swz<D>(jp * 16 + (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
+                    mma16816<T>(s[2 * jp], qf[kk], kb[0], kb[1]);
+                    mma16816<T>(s[2 * jp + 1], qf[kk], kb[2], kb[3]);
+                }
+            }
+
+            // mask (only tiles that touch a boundary)
+            const int n0 = n * kBN;
+            const bool full = (n0 + kBN <= valid_len || n0 >= ns_start) && n0 + kBN <= lk && (!causal || n0 + kBN - 1 <= m0);
+            if (!full) {
+#pragma unroll
+                for (int j = 0; j < kBN / 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int r = m0 + warp * 16 + g + ((e >> 1) << 3);
+                        const int c = n0 + j * 8 + 2 * t + (e & 1);
+                        if (!attn_visible(r, c, valid_len, ns_start, lk, causal)) s[j][e] = -INFINITY;
+                    }
+            }
+
+            // online softmax (rows g and g + 8 of this warp's 16)
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                float mx = row_m[hr];
+#pragma unroll
+                for (int j = 0; j < kBN / 8; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * hr], s[j][2 * hr + 1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_use = mx == -INFINITY ? 0.f : mx;
+                const float corr = exp2f((row_m[hr] - m_use) * a.scale_log2);  // exp2(-inf) = 0 on the first tile
+                row_m[hr] = mx;
+                float sum = 0.f;
+                const float ms = m_use * a.scale_log2;
+#pragma unroll
+                for (int j = 0; j < kBN / 8; ++j) {
+                    const float p0 = exp2f(fmaf(s[j][2 * hr], a.scale_log2, -ms));
+                    const float p1 = exp2f(fmaf(s[j][2 * hr + 1], a.scale_log2, -ms));
+                    s[j][2 * hr] = p0;
+                    s[j][2 * hr + 1] = p1;
+                    sum += p0 + p1;
+                }
+                row_l[hr] = row_l[hr] * corr + sum;
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j) {
+                    acc_o[j][2 * hr] *= corr;
+                    acc_o[j][2 * hr + 1] *= corr;
+                }
+            }
+
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < kBN / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack2<T>(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack2<T>(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int jp = 0; jp < D / 16; ++jp) {
+                    uint32_t vb[4];
+                    const int mi = lane >> 3;
+                    ldsm_x4_t(vb, cV + swz<D>(kk * 16 + (mi & 1) * 8 + (lane & 7), jp * 2 + (mi >> 1)));
+                    mma16816<T>(acc_o[2 * jp], pa, vb[0], vb[1]);
+                    mma16816<T>(acc_o[2 * jp + 1], pa, vb[2], vb[3]);
+                }
+            }
+            __syncthreads();  // everyone is done with this stage before it is refilled
+            stage ^= 1;
+            n = next;
+        }
+        cp_async_wait<0>();
+
+        // normalise; rows without a visible key stay zero
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            float l = row_l[hr];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+            for (int j = 0; j < D / 8; ++j) {
+                acc_o[j][2 * hr] *= inv;
+                acc_o[j][2 * hr + 1] *= inv;
+            }
+        }
+        __syncthreads();
+        // stage the output tile in the Q buffer for 16-byte stores
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            const int r0 = warp * 16 + g;
+            *reinterpret_cast<uint32_t*>(sQ + swz<D>(r0, j) + 2 * t) = pack2<T>(acc_o[j][0], acc_o[j][1]);
+            *reinterpret_cast<uint32_t*>(sQ + swz<D>(r0 + 8, j) + 2 * t) = pack2<T>(acc_o[j][2], acc_o[j][3]);
+        }
+        __syncthreads();
+    }
+
+    constexpr int CH = D / 8;
+    for (int i = tid; i < kBM * CH; i += kThreads) {
+        const int r = i / CH;
+        const int c = i - r * CH;
+        const int row = m0 + r;
+        if (row >= lq) continue;
+        uint4 val;
+        if (self_rows && row >= valid_len && row < ns_start) {
+            val = *reinterpret_cast<const uint4*>(v + static_cast<int64_t>(row) * a.v_sl + c * 8);
+        } else {
+            val = *reinterpret_cast<const uint4*>(sQ + swz<D>(r, c));
+        }
+        *reinterpret_cast<uint4*>(o + static_cast<int64_t>(row) * a.o_sl + c * 8) = val;
+    }
+}
+
+template <typename T, int D>
+int launch(const AttnArgs& a, int max_lq, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(kBM + 4 * kBN) * D * sizeof(T);
+    const DeviceInfo& dev = device_info();
+    static bool attr_set[64] = {};
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(attn_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        attr_set[dev.index] = true;
+    }
+    dim3 grid((max_lq + kBM - 1) / kBM, a.H, a.B);
+    attn_mma_kernel<T, D><<<grid, kThreads, smem, stream>>>(a);
+    count_launch();
+    return launch_status();
+}
+
+}  // namespace
+
+// Entry used by the C ABI dispatcher in attn_api.cu.  max_lq bounds the query rows of any sample.
+int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cudaStream_t stream) {
+    if (dtype == TB200_BF16) {
+        if (head_dim == 32) return launch<__nv_bfloat16, 32>(a, max_lq, stream);
+        if (head_dim == 64) return launch<__nv_bfloat16, 64>(a, max_lq, stream);
+        if (head_dim == 128) return launch<__nv_bfloat16, 128>(a, max_lq, stream);
+    } else if (dtype == TB200_F16) {
+        if (head_dim == 32) return launch<__half, 32>(a, max_lq, stream);
+        if (head_dim == 64) return launch<__half, 64>(a, max_lq, stream);
+        if (head_dim == 128) return launch<__half, 128>(a, max_lq, stream);
+    }
+    return TB200_ERR_UNSUPPORTED;
+}
+
+}  // namespace tb200

@@ -17,147 +17,166 @@ void count_launch();
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kMaxThreads = 256;
+constexpr int kWarps = kMaxThreads / 32;
 constexpr int kStages = 4;
-constexpr int kTileBytes = 16384;
 
-template <typename T, bool LAYER, int CPL>
-__global__ void __launch_bounds__(kThreads)
+// Every warp owns a contiguous span of rows and a private 4-stage ring of small tiles
+// (a few rows, about 2 KB) with its own mbarriers: lane 0 issues the bulk loads and stores,
+// the warp normalises RU rows per lane group at a time (independent shuffle chains), and no
+// CTA-wide barrier is ever taken after start-up.  gamma / beta sit in shared memory.
+template <typename T, bool LAYER, int CPL, int RU>
+__global__ void __launch_bounds__(kMaxThreads, 3)
 norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
-                int64_t rows, int cols, float eps, int rows_per_tile, int lanes_per_row, int* __restrict__ status) {
+                int64_t rows, int cols, float eps, int lanes_per_row, int* __restrict__ status) {
     constexpr int N = Vec16<T>::N;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full_bar[kStages];
+    __shared__ uint64_t full_bar[kWarps][kStages];
 
     const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
     const int chunks = cols / N;  // 16-byte chunks per row
     const uint32_t row_bytes = static_cast<uint32_t>(chunks) * 16u;
-    const uint32_t tile_bytes = row_bytes * static_cast<uint32_t>(rows_per_tile);
-    const int64_t n_tiles = (rows + rows_per_tile - 1) / rows_per_tile;
-    const int64_t first = blockIdx.x;
-    const int64_t n_my = first < n_tiles ? (n_tiles - first + gridDim.x - 1) / gridDim.x : 0;
+    const int G = lanes_per_row;
+    const int ng = 32 / G;           // rows handled side by side by one warp instruction
+    const int tile_rows = ng * RU;   // rows per tile
+    const uint32_t tile_bytes = row_bytes * static_cast<uint32_t>(tile_rows);
+    uint8_t* ring = smem + static_cast<size_t>(warp) * kStages * tile_bytes;
+    uint4* gamma_s = reinterpret_cast<uint4*>(smem + static_cast<size_t>(kWarps) * kStages * tile_bytes);
+    uint4* beta_s = gamma_s + chunks;
 
-    if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
-        fence_mbar_init();
-    }
-    __syncthreads();
+    // contiguous, balanced row span of this warp
+    const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kWarps;
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+    const int64_t row_begin = (w * rows) / n_warps;
+    const int64_t row_end = ((w + 1) * rows) / n_warps;
+    const int64_t n_my = (row_end - row_begin + tile_rows - 1) / tile_rows;
 
-    auto tile_rows = [&](int64_t it) -> int {
-        const int64_t r0 = (first + it * gridDim.x) * rows_per_tile;
-        const int64_t left = rows - r0;
-        return left < rows_per_tile ? static_cast<int>(left) : rows_per_tile;
+    auto rows_in = [&](int64_t it) -> int {
+        const int64_t left = row_end - (row_begin + it * tile_rows);
+        return left < tile_rows ? static_cast<int>(left) : tile_rows;
     };
     auto issue_load = [&](int64_t it) {
         const int s = static_cast<int>(it % kStages);
-        const int64_t r0 = (first + it * gridDim.x) * rows_per_tile;
-        const uint32_t bytes = static_cast<uint32_t>(tile_rows(it)) * row_bytes;
-        mbar_expect_tx(&full_bar[s], bytes);
-        bulk_load(smem + static_cast<size_t>(s) * tile_bytes, reinterpret_cast<const uint8_t*>(x) + r0 * row_bytes,
-                  bytes, &full_bar[s]);
+        const uint32_t bytes = static_cast<uint32_t>(rows_in(it)) * row_bytes;
+        mbar_expect_tx(&full_bar[warp][s], bytes);
+        bulk_load(ring + static_cast<size_t>(s) * tile_bytes,
+                  reinterpret_cast<const uint8_t*>(x) + (row_begin + it * tile_rows) * row_bytes, bytes,
+                  &full_bar[warp][s]);
     };
 
-    if (tid == 0) {
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[warp][s], 1);
+        fence_mbar_init();
         for (int64_t it = 0; it < n_my && it < kStages; ++it) issue_load(it);
     }
-
-    const int G = lanes_per_row;
-    const int group = tid / G;
-    const int lane_g = tid % G;
-    const int n_groups = kThreads / G;
-
-    // gamma / beta for this lane's chunks stay in registers for the whole kernel
-    float g[CPL][N];
-    float b[CPL][N];
-#pragma unroll
-    for (int j = 0; j < CPL; ++j) {
-        const int c = lane_g + j * G;
-        if (c < chunks) {
-            Vec16<T>::unpack(reinterpret_cast<const uint4*>(gamma)[c], g[j]);
-            if (LAYER) Vec16<T>::unpack(reinterpret_cast<const uint4*>(beta)[c], b[j]);
-        } else {
-#pragma unroll
-            for (int e = 0; e < N; ++e) {
-                g[j][e] = 0.f;
-                b[j][e] = 0.f;
-            }
-        }
+    for (int c = tid; c < chunks; c += kMaxThreads) {
+        gamma_s[c] = reinterpret_cast<const uint4*>(gamma)[c];
+        if (LAYER) beta_s[c] = reinterpret_cast<const uint4*>(beta)[c];
     }
+    __syncthreads();
+
+    const int group = lane / G;
+    const int lane_g = lane % G;
     const float inv_cols = 1.0f / static_cast<float>(cols);
 
     for (int64_t it = 0; it < n_my; ++it) {
         const int s = static_cast<int>(it % kStages);
         const uint32_t parity = static_cast<uint32_t>((it / kStages) & 1);
-        const bool ok = mbar_wait(&full_bar[s], parity);
-        if (__syncthreads_or(!ok)) {
-            if (tid == 0 && status != nullptr) atomicExch(status, 1);
+        const int rows_here = rows_in(it);
+        uint4* tile = reinterpret_cast<uint4*>(ring + static_cast<size_t>(s) * tile_bytes);
+        const bool ok = mbar_wait(&full_bar[warp][s], parity);
+        if (__any_sync(0xffffffffu, !ok)) {  // a load never arrived: report and leave
+            if (lane == 0 && status != nullptr) atomicExch(status, 1);
             break;
         }
-        const int rows_here = tile_rows(it);
-        uint4* tile = reinterpret_cast<uint4*>(smem + static_cast<size_t>(s) * tile_bytes);
 
-        for (int r0 = 0; r0 < rows_here; r0 += n_groups) {
-            const int r = r0 + group;
-            const bool valid_row = r < rows_here;
-            uint4* rowp = tile + static_cast<size_t>(valid_row ? r : 0) * chunks;
-            float v[CPL][N];
-            float sum = 0.f;
-            float sq = 0.f;
+        float v[RU][CPL][N];
+        float sum[RU];
+        float sq[RU];
+        bool valid[RU];
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+            const int r = u * ng + group;
+            valid[u] = r < rows_here;
+            const uint4* rowp = tile + static_cast<size_t>(valid[u] ? r : 0) * chunks;
+            sum[u] = 0.f;
+            sq[u] = 0.f;
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
                 const int c = lane_g + j * G;
-                if (valid_row && c < chunks) {
-                    Vec16<T>::unpack(rowp[c], v[j]);
+                if (valid[u] && c < chunks) {
+                    Vec16<T>::unpack(rowp[c], v[u][j]);
                 } else {
 #pragma unroll
-                    for (int e = 0; e < N; ++e) v[j][e] = 0.f;
+                    for (int e = 0; e < N; ++e) v[u][j][e] = 0.f;
                 }
 #pragma unroll
                 for (int e = 0; e < N; ++e) {
-                    if (LAYER) sum += v[j][e];
-                    else sq = fmaf(v[j][e], v[j][e], sq);
+                    if (LAYER) sum[u] += v[u][j][e];
+                    else sq[u] = fmaf(v[u][j][e], v[u][j][e], sq[u]);
                 }
             }
-            float mean = 0.f;
-            if (LAYER) {
-                for (int o = G >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                mean = sum * inv_cols;
+        }
+        float mean[RU];
+        if (LAYER) {
+            for (int o = G >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < RU; ++u) sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], o);
+            }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                mean[u] = sum[u] * inv_cols;
 #pragma unroll
                 for (int j = 0; j < CPL; ++j) {
                     const int c = lane_g + j * G;
                     if (c < chunks) {
 #pragma unroll
                         for (int e = 0; e < N; ++e) {
-                            const float d = v[j][e] - mean;
-                            sq = fmaf(d, d, sq);
+                            const float d = v[u][j][e] - mean[u];
+                            sq[u] = fmaf(d, d, sq[u]);
                         }
                     }
                 }
             }
-            for (int o = G >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            const float inv = rsqrtf(sq * inv_cols + eps);
-            if (valid_row) {
+        } else {
 #pragma unroll
-                for (int j = 0; j < CPL; ++j) {
-                    const int c = lane_g + j * G;
-                    if (c < chunks) {
+            for (int u = 0; u < RU; ++u) mean[u] = 0.f;
+        }
+        for (int o = G >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < RU; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
+        }
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+            const int c = lane_g + j * G;
+            if (c < chunks) {
+                float g[N];
+                float b[N];
+                Vec16<T>::unpack(gamma_s[c], g);
+                if (LAYER) Vec16<T>::unpack(beta_s[c], b);
+#pragma unroll
+                for (int u = 0; u < RU; ++u) {
+                    if (valid[u]) {
+                        const float inv = rsqrtf(sq[u] * inv_cols + eps);
                         float o[N];
 #pragma unroll
                         for (int e = 0; e < N; ++e) {
-                            if (LAYER) o[e] = fmaf((v[j][e] - mean) * inv, g[j][e], b[j][e]);
-                            else o[e] = (v[j][e] * inv) * g[j][e];
+                            if (LAYER) o[e] = fmaf((v[u][j][e] - mean[u]) * inv, g[e], b[e]);
+                            else o[e] = (v[u][j][e] * inv) * g[e];
                         }
-                        rowp[c] = Vec16<T>::pack(o);
+                        tile[static_cast<size_t>(u * ng + group) * chunks + c] = Vec16<T>::pack(o);
                     }
                 }
             }
         }
 
         fence_proxy_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-            const int64_t r0g = (first + it * gridDim.x) * rows_per_tile;
-            bulk_store(reinterpret_cast<uint8_t*>(y) + r0g * row_bytes, tile, static_cast<uint32_t>(rows_here) * row_bytes);
+        __syncwarp();
+        if (lane == 0) {
+            bulk_store(reinterpret_cast<uint8_t*>(y) + (row_begin + it * tile_rows) * row_bytes, tile,
+                       static_cast<uint32_t>(rows_here) * row_bytes);
             bulk_commit();
             // The stage stored one iteration ago is free once its store has read shared memory.
             if (it >= 1 && it - 1 + kStages < n_my) {
@@ -165,18 +184,19 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                 issue_load(it - 1 + kStages);
             }
         }
+        __syncwarp();
     }
-    if (tid == 0) bulk_wait<0>();
+    if (lane == 0) bulk_wait<0>();
 }
 
 // Warp per row, scalar accesses, any cols / alignment.
 template <typename T, bool LAYER>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kMaxThreads)
 norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                     T* __restrict__ y, int64_t rows, int cols, float eps) {
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
-    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * kThreads) >> 5;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kMaxThreads + threadIdx.x) >> 5;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * kMaxThreads) >> 5;
     const float inv_cols = 1.0f / static_cast<float>(cols);
     for (int64_t r = warp; r < rows; r += n_warps) {
         const T* xr = x + r * cols;
@@ -205,35 +225,32 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     }
 }
 
-template <typename T, bool LAYER, int CPL>
+template <typename T, bool LAYER, int CPL, int RU>
 int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
                int lanes_per_row, cudaStream_t stream) {
     const int N = Vec16<T>::N;
     const int chunks = cols / N;
     const int row_bytes = chunks * 16;
-    const int n_groups = kThreads / lanes_per_row;
-    int rows_per_tile = kTileBytes / row_bytes;
-    if (rows_per_tile < 1) rows_per_tile = 1;
-    // a whole number of passes over the row groups keeps every group busy
-    if (rows_per_tile > n_groups) rows_per_tile -= rows_per_tile % n_groups;
-    const size_t tile_bytes = static_cast<size_t>(rows_per_tile) * row_bytes;
-    const size_t smem = tile_bytes * kStages;
+    const int tile_rows = (32 / lanes_per_row) * RU;
+    const size_t tile_bytes = static_cast<size_t>(tile_rows) * row_bytes;
+    const size_t smem = tile_bytes * kStages * kWarps + static_cast<size_t>(row_bytes) * 2;
     const DeviceInfo& dev = device_info();
-    static bool attr_set = false;  // per instantiation; idempotent
-    if (!attr_set) {
-        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        attr_set = true;
+    static bool attr_set[64] = {};
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024);
+        attr_set[dev.index] = true;
     }
-    const int64_t n_tiles = (rows + rows_per_tile - 1) / rows_per_tile;
-    int ctas_per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
+    int ctas_per_sm = static_cast<int>((220 * 1024) / (smem + 1024));
     if (ctas_per_sm > 4) ctas_per_sm = 4;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     int64_t grid = static_cast<int64_t>(dev.sm_count) * ctas_per_sm;
-    if (grid > n_tiles) grid = n_tiles;
+    const int64_t useful = (rows + static_cast<int64_t>(tile_rows) * kWarps - 1) / (static_cast<int64_t>(tile_rows) * kWarps);
+    if (grid > useful) grid = useful;
     if (grid < 1) grid = 1;
-    norm_tma_kernel<T, LAYER, CPL><<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(
+    norm_tma_kernel<T, LAYER, CPL, RU><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
-        cols, eps, rows_per_tile, lanes_per_row, nullptr);
+        cols, eps, lanes_per_row, nullptr);
     count_launch();
     return launch_status();
 }
@@ -243,23 +260,24 @@ int norm_dispatch(const void* x, const void* gamma, const void* beta, void* y, i
                   cudaStream_t stream) {
     const int N = Vec16<T>::N;
     const bool vec_ok = (cols % N == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) &&
-                        (!LAYER || aligned16(beta)) && (cols / N) <= 256 && (cols / N) * 16 <= kTileBytes;
+                        (!LAYER || aligned16(beta)) && (cols / N) <= 256;
     if (vec_ok) {
         const int chunks = cols / N;
         int G = 1;
         while (G < 32 && G < chunks) G <<= 1;  // lanes per row: power of two, <= 32
         const int cpl = (chunks + G - 1) / G;
-        if (cpl <= 1) return launch_tma<T, LAYER, 1>(x, gamma, beta, y, rows, cols, eps, G, stream);
-        if (cpl <= 2) return launch_tma<T, LAYER, 2>(x, gamma, beta, y, rows, cols, eps, G, stream);
-        if (cpl <= 4) return launch_tma<T, LAYER, 4>(x, gamma, beta, y, rows, cols, eps, G, stream);
-        return launch_tma<T, LAYER, 8>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        // RU rows per lane group and tile, so that a lane holds about 4 chunks whatever the row width
+        if (cpl <= 1) return launch_tma<T, LAYER, 1, 4>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        if (cpl <= 2) return launch_tma<T, LAYER, 2, 2>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        if (cpl <= 4) return launch_tma<T, LAYER, 4, 1>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        return launch_tma<T, LAYER, 8, 1>(x, gamma, beta, y, rows, cols, eps, G, stream);
     }
     const DeviceInfo& dev = device_info();
-    int64_t blocks = (rows + (kThreads / 32) - 1) / (kThreads / 32);
+    int64_t blocks = (rows + (kMaxThreads / 32) - 1) / (kMaxThreads / 32);
     const int64_t cap = static_cast<int64_t>(dev.sm_count) * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    norm_rowwarp_kernel<T, LAYER><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(
+    norm_rowwarp_kernel<T, LAYER><<<static_cast<unsigned>(blocks), kMaxThreads, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
         cols, eps);
     count_launch();

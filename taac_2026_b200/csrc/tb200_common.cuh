@@ -27,6 +27,7 @@ inline int launch_status() {
 }
 
 struct DeviceInfo {
+    int index = 0;
     int sm_count = 0;
     int cc_major = 0;
     int cc_minor = 0;

@@ -18,6 +18,8 @@ on the CPU: CPU tensors, a missing library or a non-sm_100 device raise ``Runtim
 from __future__ import annotations
 
 import ctypes
+import math
+from dataclasses import dataclass
 from typing import Literal
 
 import torch
@@ -346,9 +348,278 @@ def gather_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     return out.view(*ids.shape, weight.shape[1])
 
 
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+@dataclass(frozen=True, slots=True)
+class AttentionMaskPlan:
+    """A bool attention mask reduced to what the kernel needs (the counterpart of the
+    reference's `FlashAttentionMaskPlan`, accelerators/attention/flash_attention.py:60-64):
+    key k is visible to query q of sample b iff (k < seq_len[b] or k >= ns_start) and
+    (not causal or k <= q); with ``padded_query_self`` the queries in [seq_len[b], ns_start)
+    return their own value row."""
+
+    seq_len: torch.Tensor  # int32 [B]
+    ns_start: int
+    causal: bool
+    padded_query_self: bool
+
+
+def _prefix_suffix_lengths(
+    key_valid: torch.Tensor, known: torch.Tensor | None = None
+) -> tuple[torch.Tensor, int] | None:
+    """key_valid [B, T] -> (prefix length per sample, common suffix start), or None if some row is
+    not `valid prefix | padding | valid suffix`.  Rows with ``known == False`` carry no information
+    (their mask is the identity whatever their length): they are given length 0."""
+    batch, total = key_valid.shape
+    valid = key_valid.to(torch.int32)
+    lead = torch.cumprod(valid, dim=1).sum(dim=1)
+    trail = torch.cumprod(valid.flip(1), dim=1).sum(dim=1)
+    partial = lead < total
+    informative = partial if known is None else (partial & known)
+    ns = int(trail[informative].min().item()) if bool(informative.any()) else 0
+    ns_start = total - ns
+    if known is not None:
+        lead = torch.where(known, lead, torch.zeros_like(lead))
+        partial = partial | ~known
+    positions = torch.arange(total, device=key_valid.device).unsqueeze(0)
+    expected = (positions < lead.unsqueeze(1)) | (positions >= ns_start)
+    if known is not None:
+        key_valid = torch.where(known[:, None], key_valid, expected)
+    if not torch.equal(expected, key_valid):
+        return None
+    return torch.where(partial, lead, torch.full_like(lead, ns_start)).clamp_max(ns_start).to(torch.int32), ns_start
+
+
+def _structured_mask(seq_len: torch.Tensor, total: int, ns_start: int) -> torch.Tensor:
+    positions = torch.arange(total, device=seq_len.device)
+    key_valid = (positions[None, :] < seq_len[:, None]) | (positions[None, :] >= ns_start)
+    mask = key_valid[:, None, :] & (positions[None, :] <= positions[:, None])[None]
+    eye = torch.eye(total, dtype=torch.bool, device=seq_len.device)
+    return torch.where(~key_valid[:, :, None], eye[None], mask)
+
+
+def plan_attention_mask(
+    q: torch.Tensor, k: torch.Tensor, attn_mask: torch.Tensor | None, *, is_causal: bool
+) -> AttentionMaskPlan:
+    """Recognise the structured bool masks the models build and describe them by lengths.
+
+    Accepts what `_plan_tilelang_flash_attention_mask` accepts
+    (accelerators/attention/flash_attention.py:149-198) — no mask, a key mask shared by all
+    queries, or `causal_valid_attention_mask` of a prefix-valid padding mask — and, beyond it, the
+    same two forms when an always-valid suffix follows the padding (OneTrans's non-sequence tokens,
+    experiments/onetrans/model.py:325-330), which the reference planner rejects.
+    Like the reference it compares the full mask against the reconstruction (one device sync)."""
+    batch, heads, q_len, k_len = q.shape[0], q.shape[1], q.shape[2], k.shape[2]
+    if attn_mask is None:
+        seq_len = torch.full((batch,), k_len, dtype=torch.int32, device=q.device)
+        return AttentionMaskPlan(seq_len, k_len, bool(is_causal), False)
+    if attn_mask.dtype is not torch.bool:
+        raise RuntimeError("cuda flash_attention only supports structured bool attention masks")
+    if attn_mask.ndim != 4 or tuple(attn_mask.shape) != (batch, heads, q_len, k_len):
+        raise RuntimeError("cuda flash_attention only supports 4D bool masks matching (batch, heads, query_len, kv_len)")
+    head0 = attn_mask[:, 0]
+    if attn_mask.stride(1) != 0 and not torch.equal(attn_mask, attn_mask[:, :1].expand_as(attn_mask)):
+        raise RuntimeError("cuda flash_attention requires the bool attention mask to be shared across heads")
+
+    if q_len == 0 or k_len == 0:
+        return AttentionMaskPlan(torch.zeros(batch, dtype=torch.int32, device=q.device), k_len, bool(is_causal), False)
+    if torch.equal(head0, head0[:, :1, :].expand_as(head0)):  # one key mask for every query
+        lengths = _prefix_suffix_lengths(head0[:, 0, :])
+        if lengths is None:
+            raise RuntimeError("cuda flash_attention requires bool key masks to be a valid prefix plus an optional valid suffix")
+        return AttentionMaskPlan(lengths[0], lengths[1], bool(is_causal), False)
+
+    if q_len != k_len:
+        raise RuntimeError("cuda flash_attention only supports non-broadcast bool masks when query and key lengths match")
+    # causal-valid family: the last query row that sees two or more keys shows every valid key
+    counts = head0.sum(dim=-1)
+    multi = counts >= 2
+    positions = torch.arange(q_len, device=q.device)
+    last_multi = torch.where(multi, positions[None, :], torch.full_like(counts, -1)).max(dim=1).values
+    rows = head0[torch.arange(batch, device=q.device), last_multi.clamp_min(0)]
+    key_valid = torch.where((last_multi >= 0)[:, None], rows, torch.zeros_like(rows))
+    lengths = _prefix_suffix_lengths(key_valid, last_multi >= 0)
+    if lengths is None or not torch.equal(_structured_mask(lengths[0], q_len, lengths[1]), head0):
+        raise RuntimeError(
+            "cuda flash_attention only supports prefix(+suffix) key masks or causal_valid_attention_mask-style bool masks"
+        )
+    return AttentionMaskPlan(lengths[0], lengths[1], True, True)
+
+
+def _normalize_flash_attention_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("flash_attention expects q, k, and v with shape (batch, heads, seq_len, head_dim)")
+    if q.shape[0] != k.shape[0] or q.shape[0] != v.shape[0]:
+        raise ValueError("flash_attention requires matching batch dimensions")
+    if q.shape[1] != k.shape[1] or q.shape[1] != v.shape[1]:
+        raise ValueError("flash_attention requires matching head counts")
+    if k.shape[2] != v.shape[2]:
+        raise ValueError("flash_attention requires matching key and value sequence lengths")
+    if q.shape[3] != k.shape[3] or q.shape[3] != v.shape[3]:
+        raise ValueError("flash_attention requires matching head dimensions")
+    if len({q.dtype, k.dtype, v.dtype}) != 1:
+        raise ValueError("flash_attention requires tensors to share the same dtype")
+    return q, k, v
+
+
+def resolved_flash_attention_backend(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    backend: str = "cuda",
+    *,
+    attn_mask: torch.Tensor | None = None,
+    dropout_p: float = 0.0,
+    training: bool = False,
+    is_causal: bool = False,
+) -> str:
+    del attn_mask, is_causal
+    _normalize_flash_attention_inputs(q, k, v)
+    if backend != "cuda":
+        raise ValueError(f"unsupported flash_attention backend: {backend}")
+    if dropout_p < 0.0 or dropout_p >= 1.0:
+        raise RuntimeError("cuda flash_attention requires dropout_p to be in [0, 1)")
+    if dropout_p != 0.0 and not training:
+        raise RuntimeError("cuda flash_attention only supports dropout during training")
+    if training and dropout_p != 0.0:
+        raise RuntimeError("cuda flash_attention is a forward-only inference kernel and has no dropout")
+    _require_backend("flash_attention", backend)
+    _require_cuda_tensors("cuda flash_attention", q, k, v)
+    if q.dtype not in _DTYPE_CODES:
+        raise RuntimeError(f"cuda flash_attention does not support dtype {q.dtype}")
+    if q.shape[3] not in (32, 64, 128):
+        raise RuntimeError(f"cuda flash_attention supports head_dim 32, 64 or 128, got {q.shape[3]}")
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        raise RuntimeError("cuda flash_attention is forward-only; use the torch backend for training")
+    return "cuda"
+
+
+def _attn_strides(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
+    if layout == "bhld":
+        return t.stride(0), t.stride(1), t.stride(2)
+    return t.stride(0), t.stride(2), t.stride(1)  # "blhd"
+
+
+def _strided_ok(t: torch.Tensor) -> bool:
+    return t.stride(-1) == 1 and all(s % 8 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+
+
+def varlen_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    seq_len: torch.Tensor | None = None,
+    ns_start: int | None = None,
+    causal: bool = False,
+    padded_query_self: bool = False,
+    scale: float | None = None,
+    layout: str = "bhld",
+    cu_rows: torch.Tensor | None = None,
+    max_rows: int | None = None,
+    kernel: int = 0,
+) -> torch.Tensor:
+    """Masked attention forward with the mask given by lengths (never materialised).
+
+    ``layout="bhld"``: q, k, v are (B, H, L, D); ``"blhd"``: (B, L, H, D) — e.g. views of a fused QKV
+    projection, any strides whose rows are 16-byte aligned.  The result is a new contiguous tensor in
+    the same layout.  ``cu_rows`` (int32 [B + 1]) switches to a packed batch: q, k, v are
+    (rows, H, D) and sample b owns rows [cu_rows[b], cu_rows[b+1]); ``max_rows`` bounds any
+    sample's row count.  fp16 / bf16 only; see ``flash_attention`` for the fp32 policy."""
+    _require_backend("varlen_attention", "cuda")
+    _require_cuda_tensors("cuda varlen_attention", q, k, v, seq_len, cu_rows)
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError(f"cuda varlen_attention needs fp16 or bf16 q, k, v of one dtype, got {q.dtype}")
+    q = q if _strided_ok(q) else q.contiguous()
+    k = k if _strided_ok(k) else k.contiguous()
+    v = v if _strided_ok(v) else v.contiguous()
+    if cu_rows is not None:
+        if q.ndim != 3:
+            raise ValueError("packed varlen_attention expects (rows, heads, head_dim) tensors")
+        batch, heads, dim = cu_rows.shape[0] - 1, q.shape[1], q.shape[2]
+        if max_rows is None:
+            raise ValueError("packed varlen_attention needs max_rows")
+        lq = lk = int(max_rows)
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        strides = []
+        for t in (q, k, v, out):
+            strides += [0, t.stride(1), t.stride(0)]
+        cu = cu_rows.to(torch.int32).contiguous()
+    else:
+        if q.ndim != 4:
+            raise ValueError("varlen_attention expects 4D q, k, v")
+        if layout == "bhld":
+            batch, heads, lq, dim = q.shape
+            lk = k.shape[2]
+        elif layout == "blhd":
+            batch, lq, heads, dim = q.shape
+            lk = k.shape[1]
+        else:
+            raise ValueError(f"unknown layout {layout}")
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        strides = []
+        for t in (q, k, v, out):
+            strides += list(_attn_strides(t, layout))
+        cu = None
+    lens = None if seq_len is None else seq_len.to(torch.int32).contiguous()
+    if scale is None:
+        scale = 1.0 / math.sqrt(dim)
+    stride_arr = (ctypes.c_int64 * 12)(*strides)
+    with torch.cuda.device(q.device):
+        code = _lib.load().tb200_attn_fwd(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu),
+            lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)), float(scale),
+            _DTYPE_CODES[q.dtype], int(kernel), _stream_ptr(),
+        )
+    _lib.check(code, "cuda varlen_attention")
+    return out
+
+
+def flash_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    backend: str = "cuda",
+    attn_mask: torch.Tensor | None = None,
+    dropout_p: float = 0.0,
+    training: bool = False,
+    is_causal: bool = False,
+    block_m: int = 64,
+    block_n: int = 64,
+    num_stages: int = 1,
+    threads: int = 128,
+) -> torch.Tensor:
+    """`flash_attention(..., backend="cuda")`: (B, H, L, D) in, (B, H, L, D) out, inference only.
+
+    fp32 callers are computed in bf16 and cast back, the policy of the reference's accelerated
+    backend (accelerators/attention/flash_attention.py:249-252).  The tile-shape arguments are
+    accepted for signature compatibility; the kernel owns its tiling."""
+    del block_m, block_n, num_stages, threads
+    q, k, v = _normalize_flash_attention_inputs(q, k, v)
+    resolved_flash_attention_backend(
+        q, k, v, backend, attn_mask=attn_mask, dropout_p=dropout_p, training=training, is_causal=is_causal
+    )
+    plan = plan_attention_mask(q, k, attn_mask, is_causal=is_causal)
+    output_dtype = q.dtype
+    if output_dtype == torch.float32:
+        q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    out = varlen_attention(
+        q, k, v, seq_len=plan.seq_len, ns_start=plan.ns_start, causal=plan.causal,
+        padded_query_self=plan.padded_query_self, layout="bhld",
+    )
+    return out if out.dtype == output_dtype else out.to(output_dtype)
+
+
 __all__ = [
+    "AttentionMaskPlan",
     "CudaBackend",
     "FieldTables",
+    "flash_attention",
+    "plan_attention_mask",
+    "resolved_flash_attention_backend",
+    "varlen_attention",
     "cuda_available",
     "cuda_supported_floating_dtype",
     "embedding_bag_mean",
