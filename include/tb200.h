@@ -125,10 +125,13 @@ int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t dim, const 
  * cu_rows: device int32[B + 1] or NULL; when given, the batch is packed along the row axis: sample b
  * owns rows [cu_rows[b], cu_rows[b+1]) (batch strides and seq_len unused, every key valid, Lq and Lk
  * are upper bounds of any sample's row count).
+ * key_valid: device uint8[B, Lk] or NULL; when given it replaces the (seq_len, ns_start) rule by
+ * "key k is valid iff key_valid[b, k] != 0" for arbitrary padding patterns (several sequence domains
+ * with separators, experiments/onetrans/model.py:287-315); padded queries are the invalid positions.
  * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.  kernel: 0 = automatic choice. */
 int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
                    int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len, const int32_t* cu_rows,
-                   int32_t ns_start, int32_t causal, int32_t padded_query_self, float scale, int dtype,
+                   const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self, float scale, int dtype,
                    int32_t kernel, void* stream);
 
 #ifdef __cplusplus

@@ -36,7 +36,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "tb200_fields_bag_mean_fwd": (_INT, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _INT, _I64, _I32, _P, _INT, _P]),
     "tb200_attn_fwd": (
         _INT,
-        [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _I32, _I32, _I32, _F, _INT, _I32, _P],
+        [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _I32, _I32, _I32, _F, _INT, _I32, _P],
     ),
     "tb200_gather_rows": (_INT, [_P, _I64, _I32, _P, _INT, _I64, _I64, _I64, _P, _I64, _I32, _INT, _P]),
 }

@@ -8,7 +8,7 @@ int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cud
 
 extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
                               int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len,
-                              const int32_t* cu_rows, int32_t ns_start, int32_t causal, int32_t padded_query_self,
+                              const int32_t* cu_rows, const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self,
                               float scale, int dtype, int32_t kernel, void* stream) {
     using namespace tb200;
     if (B < 0 || H < 1 || Lq < 0 || Lk < 0 || D < 1) return TB200_ERR_SHAPE;
@@ -30,6 +30,7 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     a.o_sb = strides[9]; a.o_sh = strides[10]; a.o_sl = strides[11];
     a.seq_len = seq_len;
     a.cu_rows = cu_rows;
+    a.key_valid = key_valid;
     a.B = B; a.H = H; a.Lq = Lq; a.Lk = Lk;
     a.ns_start = ns_start > Lk ? Lk : ns_start;
     a.causal = causal != 0;

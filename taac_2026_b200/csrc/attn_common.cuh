@@ -19,6 +19,7 @@ struct AttnArgs {
     int64_t o_sb, o_sh, o_sl;
     const int32_t* seq_len;  // [B] valid-prefix length of the key axis, or nullptr = all valid
     const int32_t* cu_rows;  // [B + 1] or nullptr
+    const uint8_t* key_valid;  // [B, Lk] bytes (0 = padding) or nullptr; replaces seq_len / ns_start when given
     int32_t B, H, Lq, Lk;
     int32_t ns_start;           // keys >= ns_start are always valid (Lk = no such suffix)
     int32_t causal;             // key <= query (top-left aligned)

@@ -129,7 +129,8 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
     const bool self_rows = a.padded_query_self != 0;
     const int m_end = min(m0 + kBM, lq);
     // queries in [valid_len, ns_start) are padded; they return their value row
-    const bool tile_all_padded = self_rows && m0 >= valid_len && m_end <= ns_start;
+    const uint8_t* kvalid = (a.key_valid != nullptr && !packed) ? a.key_valid + static_cast<int64_t>(b) * lk : nullptr;
+    const bool tile_all_padded = kvalid == nullptr && self_rows && m0 >= valid_len && m_end <= ns_start;
 
     float acc_o[D / 8][4];
 #pragma unroll
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
         const int n_tiles = (kv_end + kBN - 1) / kBN;
         auto tile_live = [&](int n) {
             const int n0 = n * kBN;
-            return n0 < valid_len || n0 + kBN > ns_start;
+            return kvalid != nullptr || n0 < valid_len || n0 + kBN > ns_start;
         };
         int first = 0;
         while (first < n_tiles && !tile_live(first)) ++first;
@@ -201,7 +202,17 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
             // mask (only tiles that touch a boundary)
             const int n0 = n * kBN;
             const bool full = (n0 + kBN <= valid_len || n0 >= ns_start) && n0 + kBN <= lk && (!causal || n0 + kBN - 1 <= m0);
-            if (!full) {
+            if (kvalid != nullptr) {  // arbitrary key-padding pattern: one byte per key
+#pragma unroll
+                for (int j = 0; j < kBN / 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int r = m0 + warp * 16 + g + ((e >> 1) << 3);
+                        const int c = n0 + j * 8 + 2 * t + (e & 1);
+                        const bool vis = c < lk && kvalid[c] != 0 && (!causal || c <= r);
+                        if (!vis) s[j][e] = -INFINITY;
+                    }
+            } else if (!full) {
 #pragma unroll
                 for (int j = 0; j < kBN / 8; ++j)
 #pragma unroll
@@ -295,7 +306,8 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
         const int row = m0 + r;
         if (row >= lq) continue;
         uint4 val;
-        if (self_rows && row >= valid_len && row < ns_start) {
+        const bool padded_q = kvalid != nullptr ? kvalid[row] == 0 : (row >= valid_len && row < ns_start);
+        if (self_rows && padded_q) {
             val = *reinterpret_cast<const uint4*>(v + static_cast<int64_t>(row) * a.v_sl + c * 8);
         } else {
             val = *reinterpret_cast<const uint4*>(sQ + swz<D>(r, c));

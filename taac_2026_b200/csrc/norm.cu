@@ -43,8 +43,9 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     const int tile_rows = ng * RU;   // rows per tile
     const uint32_t tile_bytes = row_bytes * static_cast<uint32_t>(tile_rows);
     uint8_t* ring = smem + static_cast<size_t>(warp) * kStages * tile_bytes;
-    uint4* gamma_s = reinterpret_cast<uint4*>(smem + static_cast<size_t>(kWarps) * kStages * tile_bytes);
-    uint4* beta_s = gamma_s + chunks;
+    // gamma / beta as fp32: [N / 4][chunks] float4 each, so that a warp's float4 reads are contiguous
+    float2* gamma_s = reinterpret_cast<float2*>(smem + static_cast<size_t>(kWarps) * kStages * tile_bytes);
+    float2* beta_s = gamma_s + static_cast<size_t>(chunks) * (N / 2);
 
     // contiguous, balanced row span of this warp
     const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kWarps;
@@ -72,8 +73,15 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
         for (int64_t it = 0; it < n_my && it < kStages; ++it) issue_load(it);
     }
     for (int c = tid; c < chunks; c += kMaxThreads) {
-        gamma_s[c] = reinterpret_cast<const uint4*>(gamma)[c];
-        if (LAYER) beta_s[c] = reinterpret_cast<const uint4*>(beta)[c];
+        float2 f[N / 2];
+        Vec16<T>::unpack2(reinterpret_cast<const uint4*>(gamma)[c], f);
+#pragma unroll
+        for (int e = 0; e < N / 2; ++e) gamma_s[((e >> 1) * chunks + c) * 2 + (e & 1)] = f[e];
+        if (LAYER) {
+            Vec16<T>::unpack2(reinterpret_cast<const uint4*>(beta)[c], f);
+#pragma unroll
+            for (int e = 0; e < N / 2; ++e) beta_s[((e >> 1) * chunks + c) * 2 + (e & 1)] = f[e];
+        }
     }
     __syncthreads();
 
@@ -92,7 +100,8 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             break;
         }
 
-        float v[RU][CPL][N];
+        // packed fp32x2 arithmetic throughout: the kernel is issue-bound, not HBM-bound, otherwise
+        float2 v[RU][CPL][N / 2];
         float sum[RU];
         float sq[RU];
         bool valid[RU];
@@ -101,25 +110,25 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             const int r = u * ng + group;
             valid[u] = r < rows_here;
             const uint4* rowp = tile + static_cast<size_t>(valid[u] ? r : 0) * chunks;
-            sum[u] = 0.f;
-            sq[u] = 0.f;
+            float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
                 const int c = lane_g + j * G;
                 if (valid[u] && c < chunks) {
-                    Vec16<T>::unpack(rowp[c], v[u][j]);
+                    Vec16<T>::unpack2(rowp[c], v[u][j]);
                 } else {
 #pragma unroll
-                    for (int e = 0; e < N; ++e) v[u][j][e] = 0.f;
+                    for (int e = 0; e < N / 2; ++e) v[u][j][e] = make_float2(0.f, 0.f);
                 }
 #pragma unroll
-                for (int e = 0; e < N; ++e) {
-                    if (LAYER) sum[u] += v[u][j][e];
-                    else sq[u] = fmaf(v[u][j][e], v[u][j][e], sq[u]);
+                for (int e = 0; e < N / 2; ++e) {
+                    if (LAYER) acc = __fadd2_rn(acc, v[u][j][e]);
+                    else acc = __ffma2_rn(v[u][j][e], v[u][j][e], acc);
                 }
             }
+            sum[u] = acc.x + acc.y;
+            sq[u] = sum[u];
         }
-        float mean[RU];
         if (LAYER) {
             for (int o = G >> 1; o > 0; o >>= 1) {
 #pragma unroll
@@ -127,46 +136,60 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             }
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
-                mean[u] = sum[u] * inv_cols;
+                const float nm = -sum[u] * inv_cols;
+                const float2 nmean = make_float2(nm, nm);
+                float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int j = 0; j < CPL; ++j) {
                     const int c = lane_g + j * G;
                     if (c < chunks) {
 #pragma unroll
-                        for (int e = 0; e < N; ++e) {
-                            const float d = v[u][j][e] - mean[u];
-                            sq[u] = fmaf(d, d, sq[u]);
+                        for (int e = 0; e < N / 2; ++e) {
+                            v[u][j][e] = __fadd2_rn(v[u][j][e], nmean);  // keep the centred value
+                            acc = __ffma2_rn(v[u][j][e], v[u][j][e], acc);
                         }
                     }
                 }
+                sq[u] = acc.x + acc.y;
             }
-        } else {
-#pragma unroll
-            for (int u = 0; u < RU; ++u) mean[u] = 0.f;
         }
         for (int o = G >> 1; o > 0; o >>= 1) {
 #pragma unroll
             for (int u = 0; u < RU; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
         }
+        float2 inv[RU];
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+            const float i1 = rsqrtf(sq[u] * inv_cols + eps);
+            inv[u] = make_float2(i1, i1);
+        }
 #pragma unroll
         for (int j = 0; j < CPL; ++j) {
             const int c = lane_g + j * G;
             if (c < chunks) {
-                float g[N];
-                float b[N];
-                Vec16<T>::unpack(gamma_s[c], g);
-                if (LAYER) Vec16<T>::unpack(beta_s[c], b);
+                float2 g[N / 2];
+                float2 b[N / 2];
+#pragma unroll
+                for (int e = 0; e < N / 2; e += 2) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(&gamma_s[((e >> 1) * chunks + c) * 2]);
+                    g[e] = make_float2(g4.x, g4.y);
+                    g[e + 1] = make_float2(g4.z, g4.w);
+                    if (LAYER) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(&beta_s[((e >> 1) * chunks + c) * 2]);
+                        b[e] = make_float2(b4.x, b4.y);
+                        b[e + 1] = make_float2(b4.z, b4.w);
+                    }
+                }
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
                     if (valid[u]) {
-                        const float inv = rsqrtf(sq[u] * inv_cols + eps);
-                        float o[N];
+                        float2 o[N / 2];
 #pragma unroll
-                        for (int e = 0; e < N; ++e) {
-                            if (LAYER) o[e] = fmaf((v[u][j][e] - mean[u]) * inv, g[e], b[e]);
-                            else o[e] = (v[u][j][e] * inv) * g[e];
+                        for (int e = 0; e < N / 2; ++e) {
+                            if (LAYER) o[e] = __ffma2_rn(__fmul2_rn(v[u][j][e], inv[u]), g[e], b[e]);
+                            else o[e] = __fmul2_rn(__fmul2_rn(v[u][j][e], inv[u]), g[e]);
                         }
-                        tile[static_cast<size_t>(u * ng + group) * chunks + c] = Vec16<T>::pack(o);
+                        tile[static_cast<size_t>(u * ng + group) * chunks + c] = Vec16<T>::pack2(o);
                     }
                 }
             }
@@ -233,7 +256,7 @@ int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int6
     const int row_bytes = chunks * 16;
     const int tile_rows = (32 / lanes_per_row) * RU;
     const size_t tile_bytes = static_cast<size_t>(tile_rows) * row_bytes;
-    const size_t smem = tile_bytes * kStages * kWarps + static_cast<size_t>(row_bytes) * 2;
+    const size_t smem = tile_bytes * kStages * kWarps + static_cast<size_t>(cols) * sizeof(float) * 2;
     const DeviceInfo& dev = device_info();
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {

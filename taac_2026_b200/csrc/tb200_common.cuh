@@ -54,6 +54,14 @@ struct Vec16<float> {
     __device__ static uint4 pack(const float (&f)[4]) {
         return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
     }
+    __device__ static void unpack2(const uint4& v, float2 (&f)[2]) {
+        f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+        f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+    }
+    __device__ static uint4 pack2(const float2 (&f)[2]) {
+        return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x),
+                          __float_as_uint(f[1].y));
+    }
 };
 
 template <>
@@ -73,6 +81,20 @@ struct Vec16<__nv_bfloat16> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static void unpack2(const uint4& v, float2 (&f)[4]) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+    }
+    __device__ static uint4 pack2(const float2 (&f)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __float22bfloat162_rn(f[i]);
             w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
@@ -97,6 +119,20 @@ struct Vec16<__half> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static void unpack2(const uint4& v, float2 (&f)[4]) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    }
+    __device__ static uint4 pack2(const float2 (&f)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __float22half2_rn(f[i]);
             w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);

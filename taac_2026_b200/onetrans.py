@@ -1,0 +1,613 @@
+"""Inference engine for the OneTrans-style PCVR model on the ``cuda`` backend.
+
+``OneTransInference`` runs the forward of the reference's ``PCVROneTrans``
+(experiments/onetrans/model.py:110-359) from a plain ``state_dict`` (same parameter names),
+re-organised for a B200:
+
+* all sparse fields of an entity are pooled by ONE gather kernel (``ops.fields_bag_mean``)
+  instead of one ``F.embedding_bag`` launch per field (modeling/embeddings.py:137-173);
+* sequence ids are gathered straight into the concatenated ``[B, L, F * emb]`` layout
+  (``ops.sequence_gather``; modeling/tokenizers.py:156-176);
+* RMSNorm / LayerNorm are the fused TMA-staged kernels (``ops.rms_norm`` / ``ops.layer_norm``);
+* attention runs on strided views of the fused QKV projection with the mask described by
+  per-sample lengths — the ``[B, H, T, T]`` bool mask of ``causal_valid_attention_mask``
+  (modeling/sequence.py:119-127) is never built;
+* the per-NS-token projections and FFNs (model.py:60-67, :89-93) are batched matmuls;
+* duplicate-event removal and the sequence statistics share one stable sort
+  (modeling/sequence.py:141-198, modeling/time_features.py:49-105).
+
+Plain dense layers go through cuBLAS (``torch.nn.functional.linear``).  Everything runs on the
+GPU; there is no CPU path.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from taac_2026_b200 import ops
+from taac_2026_b200.inputs import OneTransSpec
+
+# Gap-time bucket edges in seconds (the constant table of modeling/time_features.py:16-28).
+_BUCKET_EDGES = (
+    [5 * i for i in range(1, 13)]
+    + [60 * i for i in range(2, 11)]
+    + [300 * i for i in range(3, 13)]
+    + [1800 * i for i in range(3, 13)]
+    + [10800 * i for i in range(3, 9)]
+    + [86400 * i for i in range(2, 8)]
+    + [1123200, 1641600, 2160000, 2592000, 4320000, 6048000, 7776000, 11664000, 15552000, 31536000]
+)
+
+
+def _table_kind(vocab: int, threshold: int, compress: bool) -> str:
+    """Which embedding table a feature owns (modeling/embeddings.py:99-127)."""
+    if int(vocab) <= 0:
+        return "none"
+    if threshold > 0 and int(vocab) > threshold:
+        return "compressed" if compress else "none"
+    return "table"
+
+
+def hash_compress_ids(values: torch.Tensor, num_buckets: int) -> torch.Tensor:
+    """Positive ids -> ((v - 1) mod buckets) + 1, everything else -> 0 (modeling/embeddings.py:74-79)."""
+    if num_buckets <= 0:
+        return torch.zeros_like(values)
+    hashed = torch.remainder(values.clamp_min(1) - 1, int(num_buckets)) + 1
+    return torch.where(values > 0, hashed, torch.zeros_like(values))
+
+
+def pyramid_keep_count(seq_tokens: int, layer: int, n_layers: int, num_ns: int) -> int:
+    """Sequence positions kept after block ``layer`` (experiments/onetrans/model.py:317-323)."""
+    if seq_tokens <= max(1, num_ns):
+        return seq_tokens
+    remaining = max(1, n_layers - layer)
+    target = max(1, num_ns)
+    decay = (target / seq_tokens) ** (1.0 / remaining)
+    return max(target, min(seq_tokens, math.ceil(seq_tokens * decay)))
+
+
+@dataclass
+class _Bank:
+    """Sparse fields of one entity, ready for the fused pooling kernel."""
+
+    fields: ops.FieldTables | None
+    n_fields: int
+    hashed: list[tuple[int, int, int]]  # (offset, length, buckets) of hashed high-cardinality fields
+
+
+class _SequenceSort:
+    """One lexicographic stable sort of a domain's events, shared by duplicate removal and the
+    statistics token.  An event is the tuple of all feature values at a position; it is active when
+    it lies inside the row's length and any feature is positive."""
+
+    def __init__(self, values: torch.Tensor, lengths: torch.Tensor) -> None:
+        batch, n_feat, max_len = values.shape
+        dev = values.device
+        self.raw_len = lengths.clamp(min=0, max=max_len).to(torch.long)
+        self.positions = torch.arange(max_len, device=dev)
+        self.active = (values > 0).any(dim=1) & (self.positions[None, :] < self.raw_len[:, None])
+        keys = torch.where(self.active[:, None, :], values, torch.full_like(values, -1))  # [B, F, L]
+        order = self.positions.expand(batch, -1).contiguous()
+        for f in range(n_feat - 1, -1, -1):  # least-significant feature first; every pass is stable
+            order = order.gather(1, torch.sort(keys[:, f].gather(1, order), dim=1, stable=True).indices)
+        sorted_keys = keys.gather(2, order[:, None, :].expand(-1, n_feat, -1))
+        differs = (sorted_keys[:, :, 1:] != sorted_keys[:, :, :-1]).any(dim=1)  # [B, L-1]
+        true_col = torch.ones(batch, 1, dtype=torch.bool, device=dev)
+        sorted_active = self.active.gather(1, order)
+        self.order = order
+        self.group_last = torch.cat([differs, true_col], dim=1) & sorted_active
+        self.group_first = torch.cat([true_col, differs], dim=1) & sorted_active
+
+
+def deduplicate_sequence_events(values: torch.Tensor, lengths: torch.Tensor, timestamps: torch.Tensor,
+                                sort: _SequenceSort | None = None):
+    """Keep the LAST occurrence of every distinct active event, in original order; rows that lose
+    nothing (or have raw length <= 1) are returned untouched, changed rows are compacted to the front
+    and zero-filled (modeling/sequence.py:141-198).  Integer work: bit-exact."""
+    batch, n_feat, max_len = values.shape
+    sort = sort or _SequenceSort(values, lengths)
+    keep = torch.zeros_like(sort.group_last).scatter_(1, sort.order, sort.group_last)
+    keep_count = keep.sum(dim=1)
+    changed = (keep_count != sort.raw_len) & (sort.raw_len > 1)
+    # stable compaction: the j-th kept position of a row moves to slot j
+    slot = torch.cumsum(keep.to(torch.long), dim=1) - 1
+    src = torch.zeros(batch, max_len, dtype=torch.long, device=values.device)
+    rows = torch.arange(batch, device=values.device)[:, None].expand(-1, max_len)
+    src.index_put_((rows[keep], slot[keep]), sort.positions.expand(batch, -1)[keep])
+    tail = (sort.positions[None, :] >= keep_count[:, None]) & changed[:, None]
+    new_values = values.gather(2, src[:, None, :].expand(-1, n_feat, -1)).masked_fill(tail[:, None, :], 0)
+    new_ts = timestamps.gather(1, src).masked_fill(tail, 0)
+    return (
+        torch.where(changed[:, None, None], new_values, values),
+        torch.where(changed, keep_count.to(lengths.dtype), lengths),
+        torch.where(changed[:, None], new_ts, timestamps),
+    )
+
+
+def sequence_time_buckets(timestamps: torch.Tensor, request_ts: torch.Tensor, edges: torch.Tensor) -> torch.Tensor:
+    """Gap bucket of every event: min(#edges < gap, 62) + 1, 0 for zero timestamps
+    (modeling/time_features.py:31-46)."""
+    if timestamps.shape[1] == 0:
+        return timestamps.new_zeros(timestamps.shape, dtype=torch.long)
+    gap = (request_ts[:, None] - timestamps).clamp_min(0)
+    bucket = torch.searchsorted(edges, gap).clamp_max(edges.numel() - 1) + 1
+    return torch.where(timestamps == 0, torch.zeros_like(bucket), bucket)
+
+
+def sequence_stats(values: torch.Tensor, lengths: torch.Tensor, timestamps: torch.Tensor, request_ts: torch.Tensor,
+                   edges: torch.Tensor, sort: _SequenceSort | None = None) -> torch.Tensor:
+    """[length, active, distinct, 1 - distinct / active, positive share, last gap bucket] in fp32,
+    zero rows without active events (modeling/time_features.py:49-105)."""
+    batch, n_feat, max_len = values.shape
+    stats = torch.zeros(batch, 6, dtype=torch.float32, device=values.device)
+    if n_feat <= 0:
+        return stats
+    sort = sort or _SequenceSort(values, lengths)
+    active = sort.active.sum(dim=1)
+    distinct = sort.group_first.sum(dim=1)
+    has = active > 0
+    positive = (values > 0).sum(dim=(1, 2))
+    share = positive / torch.maximum(sort.raw_len * n_feat, torch.ones_like(sort.raw_len))
+    buckets = sequence_time_buckets(timestamps, request_ts, edges)
+    last_bucket = buckets[torch.arange(batch, device=values.device), (sort.raw_len - 1).clamp_min(0)]
+    zero = torch.zeros(batch, dtype=torch.float32, device=values.device)
+    active_f = active.to(torch.float32)
+    stats[:, 0] = torch.where(has, sort.raw_len.to(torch.float32), zero)
+    stats[:, 1] = torch.where(has, active_f, zero)
+    stats[:, 2] = torch.where(has, distinct.to(torch.float32), zero)
+    stats[:, 3] = torch.where(has, 1.0 - distinct.to(torch.float32) / torch.maximum(active_f, torch.ones_like(active_f)), zero)
+    stats[:, 4] = torch.where(has, share.to(torch.float32), zero)
+    stats[:, 5] = torch.where(has & (sort.raw_len > 0), last_bucket.to(torch.float32), zero)
+    return stats
+
+
+class OneTransInference:
+    """Forward-only OneTrans on one GPU.
+
+    ``dtype`` is the activation / weight type of the dense path: ``torch.bfloat16`` (serving) or
+    ``torch.float32`` (score-parity runs; attention still computes in bf16, the reference's own policy
+    for fp32 callers of an accelerated backend, accelerators/attention/flash_attention.py:249-252).
+    """
+
+    def __init__(self, state_dict: dict[str, torch.Tensor], spec: OneTransSpec, *, device: torch.device | str = "cuda",
+                 dtype: torch.dtype = torch.bfloat16, attention_kernel: int = 0) -> None:
+        if not ops.cuda_available():
+            raise RuntimeError("OneTransInference needs the cuda backend (libtb200 + an sm_100 device)")
+        self.spec = spec
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.attention_kernel = attention_kernel
+        self.d = spec.d_model
+        heads = max(1, spec.num_heads)
+        if self.d % heads:  # choose_num_heads (modeling/sequence.py:70-78)
+            heads = next(h for h in range(min(heads, self.d), 0, -1) if self.d % h == 0)
+        self.heads = heads
+        self.head_dim = self.d // heads
+        if self.head_dim not in (32, 64, 128):
+            raise RuntimeError(f"cuda attention supports head_dim 32, 64 or 128, got {self.head_dim}")
+        self.domains = sorted(spec.seq_vocab_sizes)
+        self.n_blocks = max(1, spec.num_blocks)
+        self.seq_keep = max(1, int(spec.seq_top_k))
+        self.w = {k: v.to(self.device) for k, v in state_dict.items()}
+        self._edges = torch.tensor(_BUCKET_EDGES, dtype=torch.long, device=self.device)
+        self._cast_cache: dict[str, torch.Tensor] = {}
+
+        self.user_bank = self._make_bank("user_tokenizer.bank", spec.user_int_specs, compress=False)
+        self.item_bank = self._make_bank("item_tokenizer.bank", spec.item_int_specs, compress=True)
+        self.user_tokens = self._ns_token_count(spec.user_ns_tokens, spec.user_ns_groups, spec.user_int_specs)
+        self.item_tokens = self._ns_token_count(spec.item_ns_tokens, spec.item_ns_groups, spec.item_int_specs)
+        self.num_ns = (self.user_tokens + self.item_tokens + int(spec.user_dense_dim > 0) + int(spec.item_dense_dim > 0)
+                       + int(bool(self.domains)))
+        self.seq_tables: dict[str, list[tuple[str, torch.Tensor | None]]] = {}
+        for domain in self.domains:
+            entries: list[tuple[str, torch.Tensor | None]] = []
+            n_plain = n_comp = 0
+            for vocab in spec.seq_vocab_sizes[domain]:
+                kind = _table_kind(vocab, spec.emb_skip_threshold, True)
+                if kind == "table":
+                    entries.append((kind, self._table(f"sequence_tokenizers.{domain}.embeddings.{n_plain}.weight")))
+                    n_plain += 1
+                elif kind == "compressed":
+                    entries.append((kind, self._table(f"sequence_tokenizers.{domain}.compressed_embeddings.{n_comp}.weight")))
+                    n_comp += 1
+                else:
+                    entries.append((kind, None))
+            self.seq_tables[domain] = entries
+        self._prepare_blocks()
+        self._pos_cache: dict[int, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ weights
+    def _p(self, name: str) -> torch.Tensor:
+        """Parameter in the compute dtype (cast once)."""
+        t = self._cast_cache.get(name)
+        if t is None:
+            t = self.w[name].to(self.dtype).contiguous()
+            self._cast_cache[name] = t
+        return t
+
+    def _table(self, name: str) -> torch.Tensor:
+        return self._p(name)
+
+    @staticmethod
+    def _ns_token_count(n_tokens: int, groups: list[list[int]], specs) -> int:
+        groups = list(groups) or [[i] for i in range(len(specs))]
+        return int(n_tokens) if n_tokens > 0 else len(groups)
+
+    def _make_bank(self, prefix: str, specs, *, compress: bool) -> _Bank:
+        if not specs:
+            return _Bank(None, 0, [])
+        zero_table = torch.zeros(1, self.spec.emb_dim, dtype=self.dtype, device=self.device)
+        tables, hashed = [], []
+        n_plain = n_comp = 0
+        for vocab, offset, length in specs:
+            kind = _table_kind(vocab, self.spec.emb_skip_threshold, compress)
+            if kind == "table":
+                tables.append(self._table(f"{prefix}.embeddings.{n_plain}.weight"))
+                n_plain += 1
+            elif kind == "compressed":
+                table = self._table(f"{prefix}.compressed_embeddings.{n_comp}.weight")
+                tables.append(table)
+                hashed.append((offset, length, table.shape[0] - 1))
+                n_comp += 1
+            else:
+                tables.append(zero_table)  # every id clamps to the padding row -> zeros
+        fields = ops.FieldTables(tables, [s[1] for s in specs], [s[2] for s in specs])
+        return _Bank(fields, len(specs), hashed)
+
+    def _prepare_blocks(self) -> None:
+        """Stack the per-NS-token projections so that each block needs three batched matmuls."""
+        ns = self.num_ns
+        self.blocks = []
+        for layer in range(self.n_blocks):
+            p = f"blocks.{layer}"
+            blk = {"p": p}
+            if ns > 0:
+                def stack(fmt: str, kind: str) -> torch.Tensor:
+                    return torch.stack([self._p(fmt.format(i=i) + "." + kind) for i in range(ns)])
+
+                wq, wk, wv = (stack(p + f".attention.ns_{n}." + "{i}", "weight") for n in "qkv")
+                bq, bk, bv = (stack(p + f".attention.ns_{n}." + "{i}", "bias") for n in "qkv")
+                blk["ns_qkv_w"] = torch.cat([wq, wk, wv], dim=1).transpose(1, 2).contiguous()  # [ns, d, 3d]
+                blk["ns_qkv_b"] = torch.cat([bq, bk, bv], dim=1).unsqueeze(1)  # [ns, 1, 3d]
+                blk["ns_w1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "weight").transpose(1, 2).contiguous()
+                blk["ns_b1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "bias").unsqueeze(1)
+                blk["ns_w2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "weight").transpose(1, 2).contiguous()
+                blk["ns_b2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "bias").unsqueeze(1)
+            self.blocks.append(blk)
+
+    # ------------------------------------------------------------------ pieces
+    def _linear(self, x: torch.Tensor, prefix: str) -> torch.Tensor:
+        return F.linear(x, self._p(prefix + ".weight"), self._p(prefix + ".bias"))
+
+    def _layer_norm(self, x: torch.Tensor, prefix: str) -> torch.Tensor:
+        return ops.layer_norm(x, self._p(prefix + ".weight"), self._p(prefix + ".bias"), 1e-5)
+
+    def _bank_tokens(self, bank: _Bank, int_feats: torch.Tensor) -> torch.Tensor:
+        if bank.fields is None:
+            return torch.zeros(int_feats.shape[0], 0, self.spec.emb_dim, dtype=self.dtype, device=self.device)
+        if bank.hashed:
+            int_feats = int_feats.clone()
+            for offset, length, buckets in bank.hashed:
+                cols = int_feats[:, offset : offset + length]
+                int_feats[:, offset : offset + length] = hash_compress_ids(cols.clamp_min(0), buckets)
+        return ops.fields_bag_mean(bank.fields, int_feats)
+
+    def _ns_tokenizer(self, prefix: str, bank: _Bank, n_tokens: int, groups, int_feats, missing) -> torch.Tensor:
+        """`NonSequentialTokenizer.forward` (modeling/tokenizers.py:63-87)."""
+        batch = int_feats.shape[0]
+        feats = self._bank_tokens(bank, int_feats)
+        key = prefix + ".missing_embeddings"
+        if key in self.w and missing is not None and feats.shape[1] > 0:
+            m = missing[:, : feats.shape[1]].to(self.dtype)
+            feats = feats + m.unsqueeze(-1) * self._p(key)[: feats.shape[1]].unsqueeze(0)
+        if n_tokens <= 0:
+            return torch.zeros(batch, 0, self.d, dtype=self.dtype, device=self.device)
+        groups = [list(g) for g in groups] or [[i] for i in range(bank.n_fields)]
+        if self.spec.force_auto_split or n_tokens != len(groups):
+            flat = feats.reshape(batch, -1) if feats.shape[1] > 0 else torch.zeros(batch, 1, dtype=self.dtype, device=self.device)
+            h = F.silu(self._linear(flat, prefix + ".project.0"))
+            return self._layer_norm(h, prefix + ".project.2").view(batch, n_tokens, self.d)
+        grouped = []
+        for g in groups:
+            idx = [i for i in g if 0 <= i < feats.shape[1]]
+            grouped.append(feats[:, idx, :].mean(dim=1) if idx else torch.zeros(batch, self.spec.emb_dim, dtype=self.dtype, device=self.device))
+        return self._layer_norm(self._linear(torch.stack(grouped, dim=1), prefix + ".project.0"), prefix + ".project.1")
+
+    def _dense_token(self, prefix: str, dim: int, values: torch.Tensor, missing: torch.Tensor | None):
+        """`DenseTokenProjector.forward` (modeling/tokenizers.py:101-111)."""
+        if dim <= 0:
+            return None
+        values = values.to(self.dtype)
+        miss = torch.zeros_like(values) if missing is None else missing[:, : values.shape[1]].to(self.dtype)
+        h = F.silu(self._linear(torch.cat([values, miss], dim=-1), prefix + ".project.0"))
+        return self._layer_norm(h, prefix + ".project.2").unsqueeze(1)
+
+    def _sequence_tokens(self, domain: str, values: torch.Tensor, timestamps: torch.Tensor, request_ts: torch.Tensor):
+        """`SequenceTokenizer.forward` (modeling/tokenizers.py:156-190)."""
+        prefix = f"sequence_tokenizers.{domain}"
+        entries = self.seq_tables[domain]
+        batch, n_feat, length = values.shape
+        if any(kind == "compressed" for kind, _ in entries):
+            values = values.clone()
+            for f, (kind, table) in enumerate(entries):
+                if kind == "compressed":
+                    values[:, f] = hash_compress_ids(values[:, f].clamp_min(0), table.shape[0] - 1)
+        tables = [entries[f][1] if f < len(entries) else None for f in range(n_feat)]
+        if all(t is None for t in tables):
+            width = max(1, n_feat * self.spec.emb_dim) if n_feat else 1
+            token_input = torch.zeros(batch, length, width, dtype=self.dtype, device=self.device)
+        else:
+            token_input = ops.sequence_gather(tables, values)
+        h = F.silu(self._linear(token_input, prefix + ".project.0"))
+        tokens = self._layer_norm(h, prefix + ".project.2")
+        key = prefix + ".time_embedding.weight"
+        if key in self.w:
+            buckets = sequence_time_buckets(timestamps, request_ts, self._edges)
+            tokens = tokens + ops.gather_rows(self._p(key), buckets)
+        return tokens
+
+    def _positions(self, length: int) -> torch.Tensor:
+        """Sinusoidal table, computed in fp32 like the reference (modeling/sequence.py:130-138)."""
+        table = self._pos_cache.get(length)
+        if table is None:
+            pos = torch.arange(length, dtype=torch.float32, device=self.device).unsqueeze(1)
+            freq = torch.exp(torch.arange(0, self.d, 2, dtype=torch.float32, device=self.device) * (-math.log(10000.0) / self.d))
+            table = torch.zeros(length, self.d, device=self.device)
+            table[:, 0::2] = torch.sin(pos * freq)
+            table[:, 1::2] = torch.cos(pos * freq[: table[:, 1::2].shape[1]])
+            table = table.to(self.dtype)
+            self._pos_cache[length] = table
+        return table
+
+    def _tail_crop(self, tokens: torch.Tensor, lengths: torch.Tensor) -> torch.Tensor:
+        """Last ``seq_top_k`` valid positions of every row (experiments/onetrans/model.py:278-285)."""
+        keep = self.seq_keep
+        if tokens.shape[1] <= keep:
+            return tokens
+        start = (lengths - keep).clamp_min(0)
+        idx = (start[:, None] + torch.arange(keep, device=self.device)[None, :]).clamp_max(tokens.shape[1] - 1)
+        return tokens.gather(1, idx[:, :, None].expand(-1, -1, tokens.shape[-1]))
+
+    # ------------------------------------------------------------------ blocks
+    def _block(self, blk: dict, tokens: torch.Tensor, mask: dict, seq_count: int) -> torch.Tensor:
+        """`OneTransBlock.forward` (experiments/onetrans/model.py:97-107)."""
+        p = blk["p"]
+        batch, total, d = tokens.shape
+        ns_here = max(0, min(self.num_ns, total - seq_count))
+        x = ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
+        qkv = self._linear(x, p + ".attention.shared_qkv")  # [B, T, 3d]
+        if ns_here > 0:
+            x_ns = x[:, seq_count : seq_count + ns_here].transpose(0, 1)  # [ns, B, d]
+            qkv[:, seq_count : seq_count + ns_here] = torch.baddbmm(
+                blk["ns_qkv_b"][:ns_here], x_ns, blk["ns_qkv_w"][:ns_here]
+            ).transpose(0, 1)
+        q, k, v = (qkv[:, :, i * d : (i + 1) * d].unflatten(-1, (self.heads, self.head_dim)) for i in range(3))
+        if q.dtype == torch.float32:
+            q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        attn = ops.varlen_attention(q, k, v, causal=True, padded_query_self=True, layout="blhd",
+                                    kernel=self.attention_kernel, **mask)
+        attn = attn.view(batch, total, d).to(self.dtype)
+        tokens = tokens + self._linear(attn, p + ".attention.out")
+
+        x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
+        out = self._linear(F.silu(self._linear(x, p + ".ffn.shared.net.0")), p + ".ffn.shared.net.3")
+        if ns_here > 0:
+            x_ns = x[:, seq_count : seq_count + ns_here].transpose(0, 1)
+            h = F.silu(torch.baddbmm(blk["ns_b1"][:ns_here], x_ns, blk["ns_w1"][:ns_here]))
+            out[:, seq_count : seq_count + ns_here] = torch.baddbmm(blk["ns_b2"][:ns_here], h, blk["ns_w2"][:ns_here]).transpose(0, 1)
+        return tokens + out
+
+    # ------------------------------------------------------------------ forward
+    @torch.inference_mode()
+    def predict(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
+        """(logits [B, action_num], pooled embeddings [B, 2 d]) in fp32 — `PCVROneTrans.predict`."""
+        spec = self.spec
+        dev = self.device
+        batch = inputs.user.int_values.shape[0]
+        request_ts = inputs.request_timestamp
+
+        # ---- sequence stream (experiments/onetrans/model.py:287-315)
+        pieces, valid_parts, stat_vectors = [], [], []
+        single_len = None
+        for di, domain in enumerate(self.domains):
+            seq = inputs.sequences[domain]
+            sort = _SequenceSort(seq.values, seq.lengths)
+            stats = sequence_stats(seq.values, seq.lengths, seq.timestamps, request_ts, self._edges, sort)
+            # raw counts (up to the sequence length) do not survive bf16: this small projector stays fp32
+            h = F.silu(F.linear(stats, self.w["sequence_stats_projector.0.weight"].float(),
+                                self.w["sequence_stats_projector.0.bias"].float()))
+            stat_vectors.append(ops.layer_norm(h, self.w["sequence_stats_projector.2.weight"].float(),
+                                               self.w["sequence_stats_projector.2.bias"].float(), 1e-5))
+            values, lengths, ts = deduplicate_sequence_events(seq.values, seq.lengths, seq.timestamps, sort)
+            seq_len = lengths.clamp(min=0, max=values.shape[2])
+            tokens = self._sequence_tokens(domain, values, ts, request_ts)
+            tokens = self._tail_crop(tokens, seq_len)
+            seq_len = seq_len.clamp_max(tokens.shape[1])
+            tokens = tokens + self._positions(tokens.shape[1]).unsqueeze(0)
+            pieces.append(tokens)
+            valid_parts.append(torch.arange(tokens.shape[1], device=dev)[None, :] < seq_len[:, None])
+            single_len = seq_len
+            if di < len(self.domains) - 1:
+                pieces.append(self._p("separator_tokens")[di].view(1, 1, -1).expand(batch, -1, -1))
+                valid_parts.append(torch.ones(batch, 1, dtype=torch.bool, device=dev))
+        seq_tokens = torch.cat(pieces, dim=1) if pieces else torch.zeros(batch, 0, self.d, dtype=self.dtype, device=dev)
+        seq_count = seq_tokens.shape[1]
+
+        # ---- non-sequence tokens (:240-252)
+        parts = [self._ns_tokenizer("user_tokenizer", self.user_bank, self.user_tokens, spec.user_ns_groups,
+                                    inputs.user.int_values, inputs.user.int_missing_mask)]
+        tok = self._dense_token("user_dense", spec.user_dense_dim, inputs.user.dense_values, inputs.user.dense_missing_mask)
+        if tok is not None:
+            parts.append(tok)
+        parts.append(self._ns_tokenizer("item_tokenizer", self.item_bank, self.item_tokens, spec.item_ns_groups,
+                                        inputs.item.int_values, inputs.item.int_missing_mask))
+        tok = self._dense_token("item_dense", spec.item_dense_dim, inputs.item.dense_values, inputs.item.dense_missing_mask)
+        if tok is not None:
+            parts.append(tok)
+        if stat_vectors:
+            parts.append(torch.stack(stat_vectors, dim=1).mean(dim=1, keepdim=True).to(self.dtype))
+        ns_tokens = torch.cat(parts, dim=1)
+        tokens = torch.cat([seq_tokens, ns_tokens], dim=1)
+
+        # ---- mask description: one valid prefix (single domain) or a per-key validity map
+        structured = len(self.domains) <= 1
+        if structured:
+            base_len = single_len if single_len is not None else torch.zeros(batch, dtype=torch.long, device=dev)
+            valid_map = None
+        else:
+            base_len = None
+            valid_map = torch.cat(valid_parts + [torch.ones(batch, ns_tokens.shape[1], dtype=torch.bool, device=dev)], dim=1)
+        dropped = 0  # sequence positions removed from the front so far
+
+        for layer, blk in enumerate(self.blocks):
+            if structured:
+                mask = {"seq_len": (base_len - dropped).clamp(min=0, max=seq_count).to(torch.int32), "ns_start": seq_count}
+            else:
+                mask = {"key_valid": valid_map}
+            tokens = self._block(blk, tokens, mask, seq_count)
+            keep = pyramid_keep_count(seq_count, layer, self.n_blocks, self.num_ns)
+            if keep < seq_count:  # keep the LAST `keep` sequence positions (:340-348)
+                cut = seq_count - keep
+                tokens = tokens[:, cut:]
+                if valid_map is not None:
+                    valid_map = valid_map[:, cut:]
+                dropped += cut
+                seq_count = keep
+
+        tokens = ops.rms_norm(tokens.contiguous(), self._p("final_norm.weight"), 1e-6).float()
+        if structured:
+            seq_valid = torch.arange(seq_count, device=dev)[None, :] < (base_len - dropped).clamp(min=0)[:, None]
+        else:
+            seq_valid = valid_map[:, :seq_count]
+        if seq_count > 0:
+            wgt = seq_valid.to(torch.float32).unsqueeze(-1)
+            seq_summary = (tokens[:, :seq_count] * wgt).sum(dim=1) / wgt.sum(dim=1).clamp_min(1.0)
+        else:
+            seq_summary = torch.zeros(batch, self.d, device=dev)
+        ns_part = tokens[:, seq_count:]
+        ns_summary = ns_part.mean(dim=1) if ns_part.shape[1] > 0 else torch.zeros(batch, self.d, device=dev)
+        embeddings = torch.cat([seq_summary, ns_summary], dim=-1)
+        h = F.silu(F.linear(embeddings, self.w["classifier.0.weight"].float(), self.w["classifier.0.bias"].float()))
+        logits = F.linear(h, self.w["classifier.3.weight"].float(), self.w["classifier.3.bias"].float())
+        return logits, embeddings
+
+    @torch.inference_mode()
+    def scores(self, inputs) -> torch.Tensor:
+        """Sigmoid click-conversion probabilities [B] (fp32, on the device)."""
+        logits, _ = self.predict(inputs)
+        return torch.sigmoid(logits.float()).reshape(-1) if logits.shape[1] == 1 else torch.sigmoid(logits.float())
+
+
+def random_state_dict(spec: OneTransSpec, *, seed: int = 0, device: torch.device | str = "cpu",
+                      dtype: torch.dtype = torch.float32) -> dict[str, torch.Tensor]:
+    """Seeded random weights with the parameter names, shapes and init scales of the reference module
+    tree (xavier-normal tables with a zero padding row, modeling/embeddings.py:131-134; default
+    `nn.Linear` / `nn.LayerNorm` init).  Generated directly on ``device`` so that multi-GB tables never
+    touch the host.  The values are NOT the reference's seed-0 stream; golden-score checks use
+    state_dicts exported from the reference itself."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    sd: dict[str, torch.Tensor] = {}
+    d, emb = spec.d_model, spec.emb_dim
+
+    def table(name: str, rows: int, cols: int) -> None:
+        std = math.sqrt(2.0 / (rows + cols))
+        t = torch.empty(rows, cols, device=device, dtype=dtype).normal_(0.0, std, generator=g)
+        t[0].zero_()
+        sd[name] = t
+
+    def linear(name: str, fan_in: int, fan_out: int) -> None:
+        bound = 1.0 / math.sqrt(fan_in)
+        sd[name + ".weight"] = (torch.rand(fan_out, fan_in, device=device, generator=g, dtype=dtype) * 2 - 1) * bound
+        sd[name + ".bias"] = (torch.rand(fan_out, device=device, generator=g, dtype=dtype) * 2 - 1) * bound
+
+    def norm(name: str, dim: int, bias: bool = True) -> None:
+        sd[name + ".weight"] = torch.ones(dim, device=device, dtype=dtype)
+        if bias:
+            sd[name + ".bias"] = torch.zeros(dim, device=device, dtype=dtype)
+
+    def bank(prefix: str, specs, compress: bool) -> None:
+        n_plain = n_comp = 0
+        for vocab, _o, _l in specs:
+            kind = _table_kind(vocab, spec.emb_skip_threshold, compress)
+            if kind == "table":
+                table(f"{prefix}.embeddings.{n_plain}.weight", vocab + 1, emb)
+                n_plain += 1
+            elif kind == "compressed":
+                table(f"{prefix}.compressed_embeddings.{n_comp}.weight", spec.emb_skip_threshold + 1, emb)
+                n_comp += 1
+
+    def ns_tokenizer(prefix: str, specs, n_tokens: int, groups, compress: bool) -> int:
+        sd[prefix + ".missing_embeddings"] = torch.empty(len(specs), emb, device=device, dtype=dtype).normal_(0.0, 0.02, generator=g)
+        bank(prefix + ".bank", specs, compress)
+        groups = list(groups) or [[i] for i in range(len(specs))]
+        n_tok = int(n_tokens) if n_tokens > 0 else len(groups)
+        if spec.force_auto_split or n_tok != len(groups):
+            linear(prefix + ".project.0", max(1, len(specs) * emb), n_tok * d)
+            norm(prefix + ".project.2", n_tok * d)
+        else:
+            linear(prefix + ".project.0", emb, d)
+            norm(prefix + ".project.1", d)
+        return n_tok
+
+    n_domains = len(spec.seq_vocab_sizes)
+    sd["separator_tokens"] = torch.empty(max(1, n_domains - 1), d, device=device, dtype=dtype).normal_(0.0, 0.02, generator=g)
+    num_ns = ns_tokenizer("user_tokenizer", spec.user_int_specs, spec.user_ns_tokens, spec.user_ns_groups, False)
+    num_ns += ns_tokenizer("item_tokenizer", spec.item_int_specs, spec.item_ns_tokens, spec.item_ns_groups, True)
+    for name, dim in (("user_dense", spec.user_dense_dim), ("item_dense", spec.item_dense_dim)):
+        if dim > 0:
+            linear(name + ".project.0", dim * 2, d)
+            norm(name + ".project.2", d)
+            num_ns += 1
+    for domain in sorted(spec.seq_vocab_sizes):
+        prefix = f"sequence_tokenizers.{domain}"
+        n_plain = n_comp = 0
+        vocabs = spec.seq_vocab_sizes[domain]
+        for vocab in vocabs:
+            kind = _table_kind(vocab, spec.emb_skip_threshold, True)
+            if kind == "table":
+                table(f"{prefix}.embeddings.{n_plain}.weight", vocab + 1, emb)
+                n_plain += 1
+            elif kind == "compressed":
+                table(f"{prefix}.compressed_embeddings.{n_comp}.weight", spec.emb_skip_threshold + 1, emb)
+                n_comp += 1
+        linear(prefix + ".project.0", max(1, len(vocabs) * emb), d)
+        norm(prefix + ".project.2", d)
+        if spec.num_time_buckets > 0:
+            table(prefix + ".time_embedding.weight", spec.num_time_buckets, d)
+    num_ns += int(n_domains > 0)
+    linear("sequence_stats_projector.0", 6, d)
+    norm("sequence_stats_projector.2", d)
+    hidden = d * spec.hidden_mult
+    for layer in range(max(1, spec.num_blocks)):
+        p = f"blocks.{layer}"
+        norm(p + ".attn_norm", d, bias=False)
+        linear(p + ".attention.shared_qkv", d, 3 * d)
+        for n in "qkv":
+            for i in range(num_ns):
+                linear(f"{p}.attention.ns_{n}.{i}", d, d)
+        linear(p + ".attention.out", d, d)
+        norm(p + ".ffn_norm", d, bias=False)
+        linear(p + ".ffn.shared.net.0", d, hidden)
+        linear(p + ".ffn.shared.net.3", hidden, d)
+        for i in range(num_ns):
+            linear(f"{p}.ffn.ns_specific.{i}.net.0", d, hidden)
+            linear(f"{p}.ffn.ns_specific.{i}.net.3", hidden, d)
+    norm("final_norm", d, bias=False)
+    linear("classifier.0", 2 * d, d)
+    linear("classifier.3", d, spec.action_num)
+    return sd
+
+
+__all__ = [
+    "OneTransInference",
+    "deduplicate_sequence_events",
+    "hash_compress_ids",
+    "pyramid_keep_count",
+    "random_state_dict",
+    "sequence_stats",
+    "sequence_time_buckets",
+]

@@ -518,9 +518,13 @@ def varlen_attention(
     layout: str = "bhld",
     cu_rows: torch.Tensor | None = None,
     max_rows: int | None = None,
+    key_valid: torch.Tensor | None = None,
     kernel: int = 0,
 ) -> torch.Tensor:
     """Masked attention forward with the mask given by lengths (never materialised).
+
+    ``key_valid`` (bool / uint8 [B, Lk]) replaces ``seq_len`` / ``ns_start`` for padding patterns that
+    are not `valid prefix | padding | valid suffix`.
 
     ``layout="bhld"``: q, k, v are (B, H, L, D); ``"blhd"``: (B, L, H, D) — e.g. views of a fused QKV
     projection, any strides whose rows are 16-byte aligned.  The result is a new contiguous tensor in
@@ -563,12 +567,17 @@ def varlen_attention(
             strides += list(_attn_strides(t, layout))
         cu = None
     lens = None if seq_len is None else seq_len.to(torch.int32).contiguous()
+    kv = None
+    if key_valid is not None:
+        if cu_rows is not None or tuple(key_valid.shape) != (batch, lk):
+            raise ValueError("key_valid must have shape (batch, kv_len) and cannot be combined with cu_rows")
+        kv = key_valid.to(torch.uint8).contiguous()
     if scale is None:
         scale = 1.0 / math.sqrt(dim)
     stride_arr = (ctypes.c_int64 * 12)(*strides)
     with torch.cuda.device(q.device):
         code = _lib.load().tb200_attn_fwd(
-            _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu),
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu), _ptr(kv),
             lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)), float(scale),
             _DTYPE_CODES[q.dtype], int(kernel), _stream_ptr(),
         )

@@ -174,9 +174,9 @@ def make_onetrans(out: Path, root: Path, variant: str) -> None:
             seq={"seq_a": {"prefix": "seq_a", "ts_fid": 1, "features": [[1, 0], [2, 90]]}},
         )
         config = PCVRModelConfig(
-            d_model=32, emb_dim=16, num_blocks=2, num_heads=2, hidden_mult=4, dropout_rate=0.0,
+            d_model=64, emb_dim=16, num_blocks=2, num_heads=2, hidden_mult=4, dropout_rate=0.0,
             use_time_buckets=False, seq_top_k=40, emb_skip_threshold=0,
-            ns=PCVRNSConfig(grouping_strategy="singleton", tokenizer_type="rankmixer", user_tokens=5, item_tokens=2),
+            ns=PCVRNSConfig(grouping_strategy="singleton", tokenizer_type="rankmixer", user_tokens=2, item_tokens=1),
         )
         B, lens = 6, {"seq_a": (40, torch.tensor([40, 1, 17, 0, 33, 8]))}
     else:  # multi-id fields, two domains, time buckets, hashed high-cardinality tables, tail crop
@@ -192,7 +192,7 @@ def make_onetrans(out: Path, root: Path, variant: str) -> None:
             },
         )
         config = PCVRModelConfig(
-            d_model=24, emb_dim=8, num_blocks=3, num_heads=3, hidden_mult=2, dropout_rate=0.0,
+            d_model=64, emb_dim=8, num_blocks=3, num_heads=2, hidden_mult=2, dropout_rate=0.0,
             use_time_buckets=True, seq_top_k=10, emb_skip_threshold=100,
             ns=PCVRNSConfig(grouping_strategy="singleton", tokenizer_type="rankmixer", user_tokens=3, item_tokens=2),
         )
