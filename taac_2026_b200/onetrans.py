@@ -496,10 +496,18 @@ class OneTransInference:
         return logits, embeddings
 
     @torch.inference_mode()
-    def scores(self, inputs) -> torch.Tensor:
-        """Sigmoid click-conversion probabilities [B] (fp32, on the device)."""
-        logits, _ = self.predict(inputs)
-        return torch.sigmoid(logits.float()).reshape(-1) if logits.shape[1] == 1 else torch.sigmoid(logits.float())
+    def scores(self, inputs, micro_batch: int | None = None) -> torch.Tensor:
+        """Sigmoid conversion probabilities (fp32, on the device): [B] for one action, else [B, actions].
+        ``micro_batch`` bounds the rows that go through the network at once (samples are independent,
+        so the result does not depend on it); it caps activation memory at large batches."""
+        batch = inputs.user.int_values.shape[0]
+        if micro_batch is None or micro_batch >= batch:
+            logits, _ = self.predict(inputs)
+        else:
+            logits = torch.cat([self.predict(inputs.slice(lo, min(lo + micro_batch, batch)))[0]
+                                for lo in range(0, batch, micro_batch)])
+        probs = torch.sigmoid(logits.float())
+        return probs.reshape(-1) if probs.shape[1] == 1 else probs
 
 
 def random_state_dict(spec: OneTransSpec, *, seed: int = 0, device: torch.device | str = "cpu",

@@ -64,6 +64,36 @@ def _require_backend(operator_name: str, backend: str) -> None:
         raise RuntimeError("cuda backend requested but libtb200 or an sm_100 CUDA device is not available")
 
 
+# Optional per-launch timing: while a list is installed, every operator brackets its kernel launch
+# with CUDA events on the launching stream and appends (name, meta, start, end).  Used by the
+# benchmark to attribute time and roofline work to kernels inside a timed step; off by default.
+_TIMING: list | None = None
+
+
+def set_kernel_timing(sink: list | None) -> None:
+    global _TIMING
+    _TIMING = sink
+
+
+class _timed:
+    __slots__ = ("name", "meta", "start")
+
+    def __init__(self, name: str, **meta) -> None:
+        self.name, self.meta, self.start = name, meta, None
+
+    def __enter__(self):
+        if _TIMING is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        if self.start is not None and _TIMING is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            _TIMING.append((self.name, self.meta, self.start, end))
+
+
 def _stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -114,7 +144,7 @@ def rms_norm(
     matrix, normalized_weight, original_shape = _normalize_rms_norm_inputs(x, weight)
     resolved_rms_norm_backend(matrix, backend, eps=eps, block_rows=block_rows)
     out = torch.empty_like(matrix)
-    with torch.cuda.device(matrix.device):
+    with torch.cuda.device(matrix.device), _timed("rms_norm", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
         code = _lib.load().tb200_rmsnorm_fwd(
             _ptr(matrix), _ptr(normalized_weight), _ptr(out), matrix.shape[0], matrix.shape[1], float(eps),
             _DTYPE_CODES[matrix.dtype], _stream_ptr(),
@@ -167,7 +197,7 @@ def layer_norm(
     matrix, normalized_weight, normalized_bias, original_shape = _normalize_layer_norm_inputs(x, weight, bias)
     resolved_layer_norm_backend(matrix, backend, eps=eps, block_rows=block_rows)
     out = torch.empty_like(matrix)
-    with torch.cuda.device(matrix.device):
+    with torch.cuda.device(matrix.device), _timed("layer_norm", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
         code = _lib.load().tb200_layernorm_fwd(
             _ptr(matrix), _ptr(normalized_weight), _ptr(normalized_bias), _ptr(out), matrix.shape[0],
             matrix.shape[1], float(eps), _DTYPE_CODES[matrix.dtype], _stream_ptr(),
@@ -273,7 +303,7 @@ def fields_bag_mean(fields: FieldTables, int_feats: torch.Tensor) -> torch.Tenso
         raise RuntimeError(f"cuda fields_bag_mean requires int32 or int64 values, got {int_feats.dtype}")
     ids = int_feats.contiguous()
     out = torch.empty((ids.shape[0], fields.n_fields, fields.dim), dtype=fields.dtype, device=fields.device)
-    with torch.cuda.device(fields.device):
+    with torch.cuda.device(fields.device), _timed("fields_bag_mean", ids=ids, dim=fields.dim, esize=out.element_size(), n_fields=fields.n_fields):
         code = _lib.load().tb200_fields_bag_mean_fwd(
             _ptr(fields.ptrs), _ptr(fields.rows), _ptr(fields.offsets), _ptr(fields.lengths), fields.n_fields,
             fields.max_bag, fields.dim, _ptr(ids), _ID_CODES[ids.dtype], ids.shape[0], ids.shape[1], _ptr(out),
@@ -310,7 +340,7 @@ def sequence_gather(tables: list[torch.Tensor | None], sequence: torch.Tensor) -
         out = torch.empty((batch, length, n_feat * dim), dtype=first.dtype, device=first.device)
     lib = _lib.load()
     item = ids.element_size()
-    with torch.cuda.device(first.device):
+    with torch.cuda.device(first.device), _timed("sequence_gather", ids=ids, dim=dim, esize=out.element_size(), n_tables=len(live)):
         for f, table in enumerate(tables):
             if table is None:
                 continue
@@ -575,7 +605,9 @@ def varlen_attention(
     if scale is None:
         scale = 1.0 / math.sqrt(dim)
     stride_arr = (ctypes.c_int64 * 12)(*strides)
-    with torch.cuda.device(q.device):
+    with torch.cuda.device(q.device), _timed("attention", seq_len=lens, cu_rows=cu, key_valid=kv, batch=batch, heads=heads,
+                                             lq=lq, lk=lk, dim=dim, ns_start=lk if ns_start is None else int(ns_start),
+                                             causal=bool(causal), self_rows=bool(padded_query_self)):
         code = _lib.load().tb200_attn_fwd(
             _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu), _ptr(kv),
             lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)), float(scale),

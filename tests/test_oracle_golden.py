@@ -106,3 +106,18 @@ def test_onetrans_forward_matches_reference(name):
     torch.testing.assert_close(got_logits, logits, atol=2e-5, rtol=1e-4)
     scores = oracle_model.sigmoid_scores(got_logits)
     assert np.abs(scores - torch.sigmoid(logits).numpy()).max() < 1e-5
+
+
+@pytest.mark.parametrize("name", ["onetrans_a", "onetrans_b"])
+def test_vectorised_cpu_port_matches_reference(name):
+    """The multi-threaded CPU port that the benchmark times is held to the same golden outputs."""
+    from oracle import torch_cpu
+
+    sd, spec, inputs, logits, embeddings = load_onetrans_fixture(name)
+    got_logits, got_emb = torch_cpu.predict(sd, spec, inputs)
+    torch.testing.assert_close(got_emb, embeddings, atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(got_logits, logits, atol=2e-5, rtol=1e-4)
+    # bf16 tables (the serving configuration) only move the result by table rounding
+    sd16 = {k: (v.bfloat16() if "embeddings." in k and k.endswith(".weight") and "missing" not in k else v) for k, v in sd.items()}
+    lo, _ = torch_cpu.predict(sd16, spec, inputs)
+    assert (torch.sigmoid(lo) - torch.sigmoid(logits)).abs().max().item() < 5e-3
