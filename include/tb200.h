@@ -134,6 +134,31 @@ int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t
                    const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self, float scale, int dtype,
                    int32_t kernel, void* stream);
 
+/* ---- (d) FP8 e4m3 block-scaled FFN ---------------------------------------------------------
+ * The reference has no FP8 path: its FFNs are bf16/fp32 torch modules — the SiLU-gated
+ * `down(silu(gate) * value)` of experiments/tokenformer/model.py:118-128 and
+ * experiments/symbiosis/backbone.py:11-21, and OneTrans's ungated `Linear -> SiLU -> Linear`
+ * (experiments/onetrans/model.py:33-44).  These entry points compute the same layers with e4m3
+ * operands: activations carry one fp32 scale per 1 x 128 block of a row, weights one per
+ * 128 x 128 block, both scale = amax / 448 (1 where amax == 0), value = e4m3 * scale.
+ *
+ * x_bf16 [M, K] -> x_fp8 [M, K] e4m3, scales [M, K / 128].  K % 128 == 0. */
+int tb200_quant_act_1x128(const void* x_bf16, void* x_fp8, float* scales, int64_t M, int32_t K, void* stream);
+
+/* out = epilogue( dequant(a) @ dequant(b)^T ), a: [M, K] e4m3 with a_scales [M, K / 128],
+ * b: [N, K] e4m3 (a torch Linear weight) with b_scales [N / 128, K / 128]; fp32 accumulation,
+ * every 128-wide K block scaled by its own (a, b) scale pair.  N % 256 == 0, K % 128 == 0.
+ * mode 0 (SiLU-gated): b's rows are interleaved per 128-column hidden block t as
+ *        [gate rows of block t | value rows of block t]; out = e4m3 [M, N / 2] of silu(gate) * value,
+ *        out_scales [M, N / 256]; bias (optional, fp32 [N]) in the same interleaved order.
+ * mode 1 (SiLU):       out = e4m3 [M, N] of silu(acc + bias), out_scales [M, N / 128].
+ * mode 2 (linear):     out = bf16 [M, N] of acc + bias (+ residual bf16 [M, N]); out_scales unused.
+ * bias and residual may be NULL.  status_word: optional device int32 that the kernel sets to 1 if
+ * one of its bounded waits gave up (the output is then incomplete). */
+int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const void* b_fp8, const float* b_scales,
+                   const float* bias, const void* residual, void* out, float* out_scales, int64_t M, int32_t N,
+                   int32_t K, int32_t mode, int32_t* status_word, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

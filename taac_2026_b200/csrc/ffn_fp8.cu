@@ -1,0 +1,479 @@
+// FP8 (e4m3) block-scaled FFN for sm_100a: activation quantisation and the two GEMMs, with the
+// dequantisation scales, bias, SiLU / SiLU-gating and the re-quantisation of the hidden activation
+// fused into the GEMM epilogues.
+//
+// Scales are fp32 amax scales — one per 1 x 128 block of an activation row and one per 128 x 128
+// block of a weight — so every 128-wide K block has its own scale pair.  The tensor cores therefore
+// produce one partial product per K block in TMEM (tcgen05.mma kind::f8f6f4, 128 x 256 x 32 per
+// instruction, operands staged by TMA in 128-byte-swizzled shared memory), and the epilogue warps
+// promote it into fp32 register accumulators with the block's scale while the tensor cores already
+// work on the next K block (two TMEM accumulator buffers of 256 columns).
+//
+// Roles in a CTA of 320 threads (persistent, one CTA per SM, static round-robin over output tiles):
+//   warp 0      TMA producer: 4-stage ring of {A 128 x 128 B, B 256 x 128 B} tiles
+//   warp 1      MMA issuer (one elected lane), owner of the TMEM allocation
+//   warps 2..9  promotion + epilogue: each thread owns one output row and 128 of the 256 columns
+// Every wait on an mbarrier is bounded; a wait that gives up raises the status word and all roles
+// drain out through the same final barrier, where the TMEM allocation is released.
+#include <cuda_fp8.h>
+#include <cudaTypedefs.h>
+
+#include "tb200_common.cuh"
+#include "tb200_ptx.cuh"
+
+namespace tb200 {
+void count_launch();
+
+namespace {
+
+constexpr int kBM = 128;          // output rows per tile
+constexpr int kBN = 256;          // output columns per tile
+constexpr int kBK = 128;          // K bytes (= e4m3 elements) per stage: one 128-byte swizzle atom
+constexpr int kStages = 4;
+constexpr int kThreads = 320;
+constexpr int kEpiThreads = 256;
+constexpr uint32_t kABytes = kBM * kBK;  // 16 KB
+constexpr uint32_t kBBytes = kBN * kBK;  // 32 KB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kTmemCols = 512;      // two 256-column fp32 accumulator buffers
+
+enum Mode : int {
+    kSwiGLU = 0,  // columns = [128 gate | 128 up] of one hidden block -> fp8 hidden + 1x128 scales
+    kSiLU = 1,    // hidden = silu(acc + bias)                          -> fp8 hidden + 1x128 scales
+    kLinear = 2,  // y = acc + bias (+ residual)                        -> bf16
+};
+
+struct GemmArgs {
+    const float* sa;     // [M, K / 128] activation scales
+    const float* sb;     // [N / 128, K / 128] weight scales
+    const float* bias;   // [N] fp32 or nullptr (for kSwiGLU in the tile's interleaved column order)
+    const __nv_bfloat16* residual;  // [M, N] or nullptr (kLinear only)
+    void* out;           // kLinear: bf16 [M, N]; else e4m3 [M, N_hidden]
+    float* out_scale;    // [M, N_hidden / 128] (quantising modes)
+    int32_t* status;     // device word: set to 1 when a wait gave up (may be nullptr)
+    int64_t M;
+    int32_t N;           // GEMM columns (kSwiGLU: 2 * hidden)
+    int32_t K;
+    int32_t out_ld;      // row pitch of `out` in elements
+};
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// 64 fp32 -> 64 e4m3 bytes (as 16 words) with q = x * inv_scale, round-to-nearest, saturating
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[kStages];
+    __shared__ uint64_t empty_bar[kStages];
+    __shared__ uint64_t tmem_full[2];
+    __shared__ uint64_t tmem_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ float amax_xchg[2][kBM];
+    __shared__ int s_abort;
+
+    // stage tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int64_t m_tiles = (g.M + kBM - 1) / kBM;
+    const int n_tiles = g.N / kBN;
+    const int64_t total_tiles = m_tiles * n_tiles;
+    const int k_blocks = g.K / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], kEpiThreads);
+        }
+        s_abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = static_cast<int>(tile / n_tiles) * kBM;
+                const int n0 = static_cast<int>(tile % n_tiles) * kBN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_dst = smem + s * kStageBytes;
+                    mbar_expect_tx(&full_bar[s], kStageBytes);
+                    tma_load_2d(a_dst, &tmap_a, kb * kBK, m0, &full_bar[s]);
+                    tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, n0, &full_bar[s]);
+                }
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (g.status != nullptr) atomicExch(g.status, 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(0, 0, 0, 0, kBM, kBN);  // e4m3 x e4m3 -> f32, both K-major
+            uint32_t it = 0, acc_it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < k_blocks; ++kb, ++it, ++acc_it) {
+                    const uint32_t buf = acc_it & 1;
+                    const uint32_t aph = (acc_it >> 1) & 1;
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!mbar_wait(&tmem_empty[buf], aph ^ 1) || !mbar_wait(&full_bar[s], ph) ||
+                        *reinterpret_cast<volatile int*>(&s_abort)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+                    const uint32_t b_addr = a_addr + kABytes;
+                    const uint32_t d_tmem = tmem_base + buf * kBN;
+#pragma unroll
+                    for (int k = 0; k < kBK / 32; ++k) {
+                        const uint64_t da = umma_desc_sw128(a_addr + k * 32, 1024, 16);
+                        const uint64_t db = umma_desc_sw128(b_addr + k * 32, 1024, 16);
+                        mma_f8_ss(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
+                    tc_commit(&tmem_full[buf]);   // the partial product of this K block is complete
+                }
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (g.status != nullptr) atomicExch(g.status, 1);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- promotion + epilogue
+        const int et = threadIdx.x - 64;          // 0..255
+        const int half = et >> 7;                 // which 128-column half of the tile this thread serves
+        const int quarter = warp & 3;             // TMEM lanes [32 * quarter, +32) are visible to this warp
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        // this thread's two 64-column ranges inside the 256-column accumulator
+        const int col_a = MODE == kSwiGLU ? half * 64 : half * 128;
+        const int col_b = MODE == kSwiGLU ? 128 + half * 64 : half * 128 + 64;
+        const int kb_scales = g.K / kBK;
+        uint32_t acc_it = 0;
+        bool ok = true;
+
+        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int64_t m0 = (tile / n_tiles) * kBM;
+            const int n0 = static_cast<int>(tile % n_tiles) * kBN;
+            const int64_t row = m0 + row_in_tile;
+            const bool row_ok = row < g.M;
+            const float* sa_row = g.sa + (row_ok ? row : 0) * kb_scales;
+            const float* sb_a = g.sb + static_cast<int64_t>((n0 + col_a) / 128) * kb_scales;
+            const float* sb_b = g.sb + static_cast<int64_t>((n0 + col_b) / 128) * kb_scales;
+
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+
+            for (int kb = 0; kb < k_blocks; ++kb, ++acc_it) {
+                const uint32_t buf = acc_it & 1;
+                const uint32_t aph = (acc_it >> 1) & 1;
+                const float sa = row_ok ? sa_row[kb] : 0.f;
+                const float scale_a = sa * sb_a[kb];
+                const float scale_b = sa * sb_b[kb];
+                // all 256 epilogue threads wait for the same phase, so they pass or give up together
+                if (!mbar_wait(&tmem_full[buf], aph)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
+                uint32_t r0[32], r1[32];
+                tmem_ld_x32(t0 + col_a, r0);
+                tmem_ld_x32(t0 + col_a + 32, r1);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    acc[i] = fmaf(__uint_as_float(r0[i]), scale_a, acc[i]);
+                    acc[32 + i] = fmaf(__uint_as_float(r1[i]), scale_a, acc[32 + i]);
+                }
+                tmem_ld_x32(t0 + col_b, r0);
+                tmem_ld_x32(t0 + col_b + 32, r1);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale_b, acc[64 + i]);
+                    acc[96 + i] = fmaf(__uint_as_float(r1[i]), scale_b, acc[96 + i]);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&tmem_empty[buf]);
+            }
+            if (!ok) break;
+
+            // ------------------------------------------------------------ tile epilogue
+            if (MODE == kSwiGLU) {
+                // acc[0..63] = gate, acc[64..127] = up of hidden columns h0 + half * 64 + (0..63)
+                const int h0 = (n0 / kBN) * 128;
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    float gate = acc[i];
+                    float up = acc[64 + i];
+                    if (g.bias != nullptr) {
+                        gate += g.bias[n0 + col_a + i];
+                        up += g.bias[n0 + col_b + i];
+                    }
+                    const float h = silu(gate) * up;
+                    acc[i] = h;
+                    amax = fmaxf(amax, fabsf(h));
+                }
+                amax_xchg[half][row_in_tile] = amax;
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+                amax = fmaxf(amax, amax_xchg[half ^ 1][row_in_tile]);
+                const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+                const float inv = 1.0f / scale;
+                if (row_ok) {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + h0 + half * 64);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 w;
+                        w.x = pack_e4m3x4(acc[16 * c + 0] * inv, acc[16 * c + 1] * inv, acc[16 * c + 2] * inv, acc[16 * c + 3] * inv);
+                        w.y = pack_e4m3x4(acc[16 * c + 4] * inv, acc[16 * c + 5] * inv, acc[16 * c + 6] * inv, acc[16 * c + 7] * inv);
+                        w.z = pack_e4m3x4(acc[16 * c + 8] * inv, acc[16 * c + 9] * inv, acc[16 * c + 10] * inv, acc[16 * c + 11] * inv);
+                        w.w = pack_e4m3x4(acc[16 * c + 12] * inv, acc[16 * c + 13] * inv, acc[16 * c + 14] * inv, acc[16 * c + 15] * inv);
+                        dst[c] = w;
+                    }
+                    if (half == 0) g.out_scale[row * (g.N / 256) + n0 / kBN] = scale;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // amax_xchg is reused by the next tile
+            } else if (MODE == kSiLU) {
+                const int c0 = n0 + half * 128;
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    float v = acc[i];
+                    if (g.bias != nullptr) v += g.bias[c0 + i];
+                    v = silu(v);
+                    acc[i] = v;
+                    amax = fmaxf(amax, fabsf(v));
+                }
+                const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+                const float inv = 1.0f / scale;
+                if (row_ok) {
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + c0);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 w;
+                        w.x = pack_e4m3x4(acc[16 * c + 0] * inv, acc[16 * c + 1] * inv, acc[16 * c + 2] * inv, acc[16 * c + 3] * inv);
+                        w.y = pack_e4m3x4(acc[16 * c + 4] * inv, acc[16 * c + 5] * inv, acc[16 * c + 6] * inv, acc[16 * c + 7] * inv);
+                        w.z = pack_e4m3x4(acc[16 * c + 8] * inv, acc[16 * c + 9] * inv, acc[16 * c + 10] * inv, acc[16 * c + 11] * inv);
+                        w.w = pack_e4m3x4(acc[16 * c + 12] * inv, acc[16 * c + 13] * inv, acc[16 * c + 14] * inv, acc[16 * c + 15] * inv);
+                        dst[c] = w;
+                    }
+                    g.out_scale[row * (g.N / 128) + c0 / 128] = scale;
+                }
+            } else {
+                const int c0 = n0 + half * 128;
+                if (row_ok) {
+                    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + row * g.out_ld + c0;
+                    const __nv_bfloat16* res = g.residual != nullptr ? g.residual + row * g.out_ld + c0 : nullptr;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            v[e] = acc[8 * c + e];
+                            if (g.bias != nullptr) v[e] += g.bias[c0 + 8 * c + e];
+                        }
+                        if (res != nullptr) {
+                            float r[8];
+                            Vec16<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(res)[c], r);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] += r[e];
+                        }
+                        reinterpret_cast<uint4*>(dst)[c] = Vec16<__nv_bfloat16>::pack(v);
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            s_abort = 1;
+            if (g.status != nullptr) atomicExch(g.status, 1);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// activation quantisation: bf16 [M, K] -> e4m3 [M, K] + fp32 scales [M, K / 128]
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+quant_act_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __restrict__ scales, int64_t n_blocks) {
+    // 16 lanes x 8 values = one 1 x 128 block
+    const int64_t gthread = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    const int64_t block = gthread >> 4;
+    const int sub = threadIdx.x & 15;
+    const bool ok = block < n_blocks;
+    float f[8];
+    if (ok) {
+        Vec16<__nv_bfloat16>::unpack(x[block * 16 + sub], f);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+    const float inv = 1.0f / scale;
+    if (ok) {
+        uint2 w;
+        w.x = pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+        w.y = pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+        q[block * 16 + sub] = w;
+        if (sub == 0) scales[block] = scale;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return fn;
+}
+
+// [rows, k_bytes] row-major bytes, tiles of box_rows x 128 bytes, 128-byte swizzle, zero fill outside
+bool make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t k_bytes, uint64_t rows, uint64_t pitch_bytes,
+                     uint32_t box_rows) {
+    PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {k_bytes, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int MODE>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t stream) {
+    const DeviceInfo& dev = device_info();
+    const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
+    static bool attr_set[64] = {};
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(ffn_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        attr_set[dev.index] = true;
+    }
+    const int64_t tiles = ((g.M + kBM - 1) / kBM) * (g.N / kBN);
+    int64_t grid = dev.sm_count;
+    if (grid > tiles) grid = tiles;
+    ffn_gemm_kernel<MODE><<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(ta, tb, g);
+    count_launch();
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_quant_act_1x128(const void* x_bf16, void* x_fp8, float* scales, int64_t M, int32_t K,
+                                     void* stream) {
+    using namespace tb200;
+    if (M < 0 || K < 128 || K % 128 != 0) return TB200_ERR_SHAPE;
+    if (M == 0) return TB200_OK;
+    if (x_bf16 == nullptr || x_fp8 == nullptr || scales == nullptr) return TB200_ERR_NULL;
+    if (!aligned16(x_bf16) || !aligned16(x_fp8)) return TB200_ERR_ALIGN;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    const int64_t n_blocks = M * (K / 128);
+    const int64_t grid = (n_blocks * 16 + 255) / 256;
+    if (grid > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    quant_act_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x_bf16), static_cast<uint2*>(x_fp8), scales, n_blocks);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const void* b_fp8, const float* b_scales,
+                              const float* bias, const void* residual, void* out, float* out_scales, int64_t M,
+                              int32_t N, int32_t K, int32_t mode, int32_t* status_word, void* stream) {
+    using namespace tb200;
+    if (M < 0 || N < 256 || N % 256 != 0 || K < 128 || K % 128 != 0) return TB200_ERR_SHAPE;
+    if (mode < 0 || mode > 2) return TB200_ERR_UNSUPPORTED;
+    if (M == 0) return TB200_OK;
+    if (a_fp8 == nullptr || a_scales == nullptr || b_fp8 == nullptr || b_scales == nullptr || out == nullptr)
+        return TB200_ERR_NULL;
+    if (mode != kLinear && out_scales == nullptr) return TB200_ERR_NULL;
+    if (mode != kLinear && residual != nullptr) return TB200_ERR_UNSUPPORTED;
+    if (!aligned16(a_fp8) || !aligned16(b_fp8) || !aligned16(out) || (residual != nullptr && !aligned16(residual)))
+        return TB200_ERR_ALIGN;
+    if (M > 0x7FFFFF00ll) return TB200_ERR_SHAPE;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    CUtensorMap ta, tb;
+    if (!make_tmap_bytes(&ta, a_fp8, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), kBM) ||
+        !make_tmap_bytes(&tb, b_fp8, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), kBN))
+        return TB200_ERR_DRIVER;
+    GemmArgs g{};
+    g.sa = a_scales;
+    g.sb = b_scales;
+    g.bias = bias;
+    g.residual = static_cast<const __nv_bfloat16*>(residual);
+    g.out = out;
+    g.out_scale = out_scales;
+    g.status = status_word;
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.out_ld = mode == kSwiGLU ? N / 2 : N;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (mode == kSwiGLU) return launch_gemm<kSwiGLU>(ta, tb, g, s);
+    if (mode == kSiLU) return launch_gemm<kSiLU>(ta, tb, g, s);
+    return launch_gemm<kLinear>(ta, tb, g, s);
+}

@@ -653,8 +653,151 @@ def flash_attention(
     return out if out.dtype == output_dtype else out.to(output_dtype)
 
 
+# --------------------------------------------------------------------------------------------
+# FP8 block-scaled FFN
+# --------------------------------------------------------------------------------------------
+E4M3_MAX = 448.0
+
+
+def quantize_activation_1x128(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [..., K] -> (e4m3 [..., K], fp32 scales [..., K / 128]); scale = amax / 448 per 1 x 128 block."""
+    _require_backend("quantize_activation_1x128", "cuda")
+    _require_cuda_tensors("cuda quantize_activation_1x128", x)
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError(f"cuda quantize_activation_1x128 needs bf16 input, got {x.dtype}")
+    if x.shape[-1] % 128:
+        raise ValueError("quantize_activation_1x128 needs the last dimension to be a multiple of 128")
+    matrix = x.reshape(-1, x.shape[-1]).contiguous()
+    q = torch.empty(matrix.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty((matrix.shape[0], matrix.shape[1] // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device), _timed("quant_act", rows=matrix.shape[0], cols=matrix.shape[1]):
+        code = _lib.load().tb200_quant_act_1x128(_ptr(matrix), _ptr(q), _ptr(scales), matrix.shape[0], matrix.shape[1], _stream_ptr())
+    _lib.check(code, "cuda quantize_activation_1x128")
+    return q.view(*x.shape), scales.view(*x.shape[:-1], x.shape[-1] // 128)
+
+
+def quantize_weight_128x128(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """[N, K] weight -> (e4m3 [N, K], fp32 scales [N / 128, K / 128]); scale = amax / 448 per 128 x 128 block.
+    Done once at model load with tensor ops on the weight's own device."""
+    n, k = weight.shape
+    if n % 128 or k % 128:
+        raise ValueError("quantize_weight_128x128 needs both dimensions to be multiples of 128")
+    blocks = weight.float().view(n // 128, 128, k // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3))
+    scales = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    q = (blocks / scales[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.view(n, k).contiguous(), scales.contiguous()
+
+
+def fp8_gemm(
+    a: torch.Tensor,
+    a_scales: torch.Tensor,
+    b: torch.Tensor,
+    b_scales: torch.Tensor,
+    *,
+    mode: str,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    check: bool = False,
+):
+    """Block-scaled e4m3 GEMM ``a @ b^T`` with a fused epilogue (see ``tb200_fp8_gemm``):
+    ``mode="swiglu"`` / ``"silu"`` return (e4m3 hidden, fp32 1 x 128 scales), ``"linear"`` returns bf16.
+    ``check=True`` reads the kernel's status word back (one sync) and raises if a wait inside gave up."""
+    modes = {"swiglu": 0, "silu": 1, "linear": 2}
+    if mode not in modes:
+        raise ValueError(f"unknown fp8_gemm mode {mode}")
+    _require_backend("fp8_gemm", "cuda")
+    _require_cuda_tensors("cuda fp8_gemm", a, a_scales, b, b_scales, bias, residual)
+    if a.dtype != torch.float8_e4m3fn or b.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("cuda fp8_gemm needs float8_e4m3fn operands")
+    if a.ndim != 2 or b.ndim != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError("fp8_gemm expects a [M, K] and b [N, K]")
+    m, k = a.shape
+    n = b.shape[0]
+    if n % 256 or k % 128:
+        raise ValueError("fp8_gemm needs N % 256 == 0 and K % 128 == 0")
+    if tuple(a_scales.shape) != (m, k // 128) or tuple(b_scales.shape) != (n // 128, k // 128):
+        raise ValueError("fp8_gemm scale shapes must be [M, K / 128] and [N / 128, K / 128]")
+    a, b = a.contiguous(), b.contiguous()
+    a_scales, b_scales = a_scales.float().contiguous(), b_scales.float().contiguous()
+    bias_f = None if bias is None else bias.float().contiguous()
+    dev = a.device
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if check else None
+    if mode == "linear":
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        out_scales = None
+        res = None if residual is None else residual.to(torch.bfloat16).contiguous()
+        if res is not None and tuple(res.shape) != (m, n):
+            raise ValueError("fp8_gemm residual must be [M, N]")
+    else:
+        if residual is not None:
+            raise ValueError("fp8_gemm residual is only supported in linear mode")
+        hidden = n // 2 if mode == "swiglu" else n
+        out = torch.empty((m, hidden), dtype=torch.float8_e4m3fn, device=dev)
+        out_scales = torch.empty((m, hidden // 128), dtype=torch.float32, device=dev)
+        res = None
+    with torch.cuda.device(dev), _timed("fp8_gemm_" + mode, m=m, n=n, k=k):
+        code = _lib.load().tb200_fp8_gemm(
+            _ptr(a), _ptr(a_scales), _ptr(b), _ptr(b_scales), _ptr(bias_f), _ptr(res), _ptr(out), _ptr(out_scales),
+            m, n, k, modes[mode], _ptr(status), _stream_ptr(),
+        )
+    _lib.check(code, "cuda fp8_gemm")
+    if status is not None and int(status.item()) != 0:
+        raise RuntimeError("cuda fp8_gemm: a bounded wait inside the kernel gave up; the output is incomplete")
+    return out if mode == "linear" else (out, out_scales)
+
+
+class Fp8FfnWeights:
+    """e4m3 weights of one FFN, prepared once.
+
+    ``gated=True``: ``w_up`` is [2 * hidden, d]; the gate is its first half of rows (``gate_first``,
+    experiments/tokenformer/model.py:118-128) or its second (experiments/baseline/model.py:99-113);
+    rows are re-ordered per 128-wide hidden block as [gate block | value block] so that one output
+    tile holds matching gate and value columns.  ``gated=False``: ``w_up`` is [hidden, d] followed by
+    SiLU (experiments/onetrans/model.py:33-44)."""
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, *, gated: bool, gate_first: bool = True,
+                 b_up: torch.Tensor | None = None, b_down: torch.Tensor | None = None) -> None:
+        self.gated = gated
+        hidden = w_up.shape[0] // 2 if gated else w_up.shape[0]
+        if w_down.shape[1] != hidden:
+            raise ValueError("Fp8FfnWeights: w_down must be [d_out, hidden]")
+        if gated:
+            if hidden % 128:
+                raise ValueError("Fp8FfnWeights: hidden must be a multiple of 128")
+            gate, value = (w_up[:hidden], w_up[hidden:]) if gate_first else (w_up[hidden:], w_up[:hidden])
+            order = torch.stack([gate.view(hidden // 128, 128, -1), value.view(hidden // 128, 128, -1)], dim=1)
+            w_up = order.reshape(2 * hidden, -1)
+            if b_up is not None:
+                bg, bv = (b_up[:hidden], b_up[hidden:]) if gate_first else (b_up[hidden:], b_up[:hidden])
+                b_up = torch.stack([bg.view(-1, 128), bv.view(-1, 128)], dim=1).reshape(-1)
+        self.hidden = hidden
+        self.w_up, self.s_up = quantize_weight_128x128(w_up)
+        self.w_down, self.s_down = quantize_weight_128x128(w_down)
+        self.b_up = None if b_up is None else b_up.float().contiguous()
+        self.b_down = None if b_down is None else b_down.float().contiguous()
+
+
+def ffn_fp8(x: torch.Tensor, weights: Fp8FfnWeights, *, residual: torch.Tensor | None = None,
+            check: bool = False) -> torch.Tensor:
+    """bf16 [..., d] -> bf16 [..., d_out]: quantise, GEMM 1 with fused (gated) SiLU and re-quantisation,
+    GEMM 2 with fused bias / residual.  The hidden activation only ever exists in e4m3."""
+    shape = x.shape
+    xq, sx = quantize_activation_1x128(x.reshape(-1, shape[-1]))
+    h, sh = fp8_gemm(xq, sx, weights.w_up, weights.s_up, mode="swiglu" if weights.gated else "silu",
+                     bias=weights.b_up, check=check)
+    res = None if residual is None else residual.reshape(-1, weights.w_down.shape[0])
+    y = fp8_gemm(h, sh, weights.w_down, weights.s_down, mode="linear", bias=weights.b_down, residual=res, check=check)
+    return y.view(*shape[:-1], weights.w_down.shape[0])
+
+
 __all__ = [
     "AttentionMaskPlan",
+    "Fp8FfnWeights",
+    "ffn_fp8",
+    "fp8_gemm",
+    "quantize_activation_1x128",
+    "quantize_weight_128x128",
     "CudaBackend",
     "FieldTables",
     "flash_attention",
