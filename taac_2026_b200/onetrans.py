@@ -169,18 +169,36 @@ class OneTransInference:
     """Forward-only OneTrans on one GPU.
 
     ``dtype`` is the activation / weight type of the dense path: ``torch.bfloat16`` (serving) or
-    ``torch.float32`` (score-parity runs; attention still computes in bf16, the reference's own policy
-    for fp32 callers of an accelerated backend, accelerators/attention/flash_attention.py:249-252).
+    ``torch.float32`` (score-parity runs; attention still takes 16-bit tensor-core inputs — the
+    reference's accelerated backend serves fp32 callers in bf16, accelerators/attention/
+    flash_attention.py:249-252; here fp16, whose three extra mantissa bits keep the scores within 1e-5
+    of the fp32 reference; activations behind an RMSNorm are far inside the fp16 range).
+
+    ``ffn="fp8"`` runs the shared FFN of every block through the e4m3 block-scaled tcgen05 GEMMs
+    (bf16 activations only; needs d_model % 256 == 0 and hidden % 256 == 0); ``"bf16"`` uses cuBLAS.
+
+    ``packed=True`` (single sequence domain) stores only VALID tokens: padded positions never influence
+    a score (they are masked as keys, excluded from the pooled means, and as queries only produce rows
+    that nothing reads), so the engine drops them after the tokenizer and runs every layer on a packed
+    ``[sum_b (len_b + ns), d]`` matrix with per-sample row offsets.  ``packed=False`` keeps the
+    reference's padded ``[B, T, d]`` layout (used for several sequence domains and as a cross-check).
     """
 
     def __init__(self, state_dict: dict[str, torch.Tensor], spec: OneTransSpec, *, device: torch.device | str = "cuda",
-                 dtype: torch.dtype = torch.bfloat16, attention_kernel: int = 0) -> None:
+                 dtype: torch.dtype = torch.bfloat16, attention_kernel: int = 0, ffn: str = "bf16",
+                 packed: bool = True) -> None:
         if not ops.cuda_available():
             raise RuntimeError("OneTransInference needs the cuda backend (libtb200 + an sm_100 device)")
         self.spec = spec
         self.device = torch.device(device)
         self.dtype = dtype
         self.attention_kernel = attention_kernel
+        if ffn not in ("bf16", "fp8"):
+            raise ValueError(f"unknown ffn mode {ffn}")
+        if ffn == "fp8" and (dtype != torch.bfloat16 or spec.d_model % 256 or (spec.d_model * spec.hidden_mult) % 256):
+            raise RuntimeError("ffn='fp8' needs bf16 activations, d_model % 256 == 0 and hidden % 256 == 0")
+        self.ffn_mode = ffn
+        self.packed = bool(packed)
         self.d = spec.d_model
         heads = max(1, spec.num_heads)
         if self.d % heads:  # choose_num_heads (modeling/sequence.py:70-78)
@@ -265,6 +283,10 @@ class OneTransInference:
         for layer in range(self.n_blocks):
             p = f"blocks.{layer}"
             blk = {"p": p}
+            if self.ffn_mode == "fp8":
+                blk["ffn_fp8"] = ops.Fp8FfnWeights(
+                    self.w[p + ".ffn.shared.net.0.weight"], self.w[p + ".ffn.shared.net.3.weight"], gated=False,
+                    b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"])
             if ns > 0:
                 def stack(fmt: str, kind: str) -> torch.Tensor:
                     return torch.stack([self._p(fmt.format(i=i) + "." + kind) for i in range(ns)])
@@ -373,6 +395,13 @@ class OneTransInference:
         return tokens.gather(1, idx[:, :, None].expand(-1, -1, tokens.shape[-1]))
 
     # ------------------------------------------------------------------ blocks
+    def _shared_ffn_residual(self, blk: dict, x: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens + FFN(x) for every row (`FeedForward`, experiments/onetrans/model.py:33-44)."""
+        if self.ffn_mode == "fp8":
+            return ops.ffn_fp8(x, blk["ffn_fp8"], residual=tokens)
+        p = blk["p"]
+        return tokens + self._linear(F.silu(self._linear(x, p + ".ffn.shared.net.0")), p + ".ffn.shared.net.3")
+
     def _block(self, blk: dict, tokens: torch.Tensor, mask: dict, seq_count: int) -> torch.Tensor:
         """`OneTransBlock.forward` (experiments/onetrans/model.py:97-107)."""
         p = blk["p"]
@@ -386,26 +415,61 @@ class OneTransInference:
                 blk["ns_qkv_b"][:ns_here], x_ns, blk["ns_qkv_w"][:ns_here]
             ).transpose(0, 1)
         q, k, v = (qkv[:, :, i * d : (i + 1) * d].unflatten(-1, (self.heads, self.head_dim)) for i in range(3))
-        if q.dtype == torch.float32:
-            q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        if q.dtype == torch.float32:  # score-parity mode: 16-bit tensor-core inputs with the most mantissa bits
+            q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
         attn = ops.varlen_attention(q, k, v, causal=True, padded_query_self=True, layout="blhd",
                                     kernel=self.attention_kernel, **mask)
         attn = attn.view(batch, total, d).to(self.dtype)
         tokens = tokens + self._linear(attn, p + ".attention.out")
 
         x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
-        out = self._linear(F.silu(self._linear(x, p + ".ffn.shared.net.0")), p + ".ffn.shared.net.3")
-        if ns_here > 0:
+        out = self._shared_ffn_residual(blk, x, tokens.contiguous())
+        if ns_here > 0:  # the NS tokens own their FFNs (model.py:89-93): overwrite their rows
             x_ns = x[:, seq_count : seq_count + ns_here].transpose(0, 1)
             h = F.silu(torch.baddbmm(blk["ns_b1"][:ns_here], x_ns, blk["ns_w1"][:ns_here]))
-            out[:, seq_count : seq_count + ns_here] = torch.baddbmm(blk["ns_b2"][:ns_here], h, blk["ns_w2"][:ns_here]).transpose(0, 1)
-        return tokens + out
+            y_ns = torch.baddbmm(blk["ns_b2"][:ns_here], h, blk["ns_w2"][:ns_here]).transpose(0, 1)
+            out[:, seq_count : seq_count + ns_here] = tokens[:, seq_count : seq_count + ns_here] + y_ns
+        return out
 
     # ------------------------------------------------------------------ forward
+    def _ns_tokens(self, inputs, stat_vectors: list[torch.Tensor]) -> torch.Tensor:
+        """All non-sequence tokens [B, ns, d] (experiments/onetrans/model.py:240-252)."""
+        spec = self.spec
+        parts = [self._ns_tokenizer("user_tokenizer", self.user_bank, self.user_tokens, spec.user_ns_groups,
+                                    inputs.user.int_values, inputs.user.int_missing_mask)]
+        tok = self._dense_token("user_dense", spec.user_dense_dim, inputs.user.dense_values, inputs.user.dense_missing_mask)
+        if tok is not None:
+            parts.append(tok)
+        parts.append(self._ns_tokenizer("item_tokenizer", self.item_bank, self.item_tokens, spec.item_ns_groups,
+                                        inputs.item.int_values, inputs.item.int_missing_mask))
+        tok = self._dense_token("item_dense", spec.item_dense_dim, inputs.item.dense_values, inputs.item.dense_missing_mask)
+        if tok is not None:
+            parts.append(tok)
+        if stat_vectors:
+            parts.append(torch.stack(stat_vectors, dim=1).mean(dim=1, keepdim=True).to(self.dtype))
+        return torch.cat(parts, dim=1)
+
+    def _stats_vector(self, stats: torch.Tensor) -> torch.Tensor:
+        # raw counts (up to the sequence length) do not survive bf16: this small projector stays fp32
+        h = F.silu(F.linear(stats, self.w["sequence_stats_projector.0.weight"].float(),
+                            self.w["sequence_stats_projector.0.bias"].float()))
+        return ops.layer_norm(h, self.w["sequence_stats_projector.2.weight"].float(),
+                              self.w["sequence_stats_projector.2.bias"].float(), 1e-5)
+
+    def _classify(self, seq_summary: torch.Tensor, ns_summary: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        embeddings = torch.cat([seq_summary, ns_summary], dim=-1)
+        h = F.silu(F.linear(embeddings, self.w["classifier.0.weight"].float(), self.w["classifier.0.bias"].float()))
+        logits = F.linear(h, self.w["classifier.3.weight"].float(), self.w["classifier.3.bias"].float())
+        return logits, embeddings
+
     @torch.inference_mode()
     def predict(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
         """(logits [B, action_num], pooled embeddings [B, 2 d]) in fp32 — `PCVROneTrans.predict`."""
-        spec = self.spec
+        if self.packed and len(self.domains) == 1:
+            return self._predict_packed(inputs)
+        return self._predict_padded(inputs)
+
+    def _predict_padded(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
         dev = self.device
         batch = inputs.user.int_values.shape[0]
         request_ts = inputs.request_timestamp
@@ -416,12 +480,8 @@ class OneTransInference:
         for di, domain in enumerate(self.domains):
             seq = inputs.sequences[domain]
             sort = _SequenceSort(seq.values, seq.lengths)
-            stats = sequence_stats(seq.values, seq.lengths, seq.timestamps, request_ts, self._edges, sort)
-            # raw counts (up to the sequence length) do not survive bf16: this small projector stays fp32
-            h = F.silu(F.linear(stats, self.w["sequence_stats_projector.0.weight"].float(),
-                                self.w["sequence_stats_projector.0.bias"].float()))
-            stat_vectors.append(ops.layer_norm(h, self.w["sequence_stats_projector.2.weight"].float(),
-                                               self.w["sequence_stats_projector.2.bias"].float(), 1e-5))
+            stat_vectors.append(self._stats_vector(
+                sequence_stats(seq.values, seq.lengths, seq.timestamps, request_ts, self._edges, sort)))
             values, lengths, ts = deduplicate_sequence_events(seq.values, seq.lengths, seq.timestamps, sort)
             seq_len = lengths.clamp(min=0, max=values.shape[2])
             tokens = self._sequence_tokens(domain, values, ts, request_ts)
@@ -436,21 +496,7 @@ class OneTransInference:
                 valid_parts.append(torch.ones(batch, 1, dtype=torch.bool, device=dev))
         seq_tokens = torch.cat(pieces, dim=1) if pieces else torch.zeros(batch, 0, self.d, dtype=self.dtype, device=dev)
         seq_count = seq_tokens.shape[1]
-
-        # ---- non-sequence tokens (:240-252)
-        parts = [self._ns_tokenizer("user_tokenizer", self.user_bank, self.user_tokens, spec.user_ns_groups,
-                                    inputs.user.int_values, inputs.user.int_missing_mask)]
-        tok = self._dense_token("user_dense", spec.user_dense_dim, inputs.user.dense_values, inputs.user.dense_missing_mask)
-        if tok is not None:
-            parts.append(tok)
-        parts.append(self._ns_tokenizer("item_tokenizer", self.item_bank, self.item_tokens, spec.item_ns_groups,
-                                        inputs.item.int_values, inputs.item.int_missing_mask))
-        tok = self._dense_token("item_dense", spec.item_dense_dim, inputs.item.dense_values, inputs.item.dense_missing_mask)
-        if tok is not None:
-            parts.append(tok)
-        if stat_vectors:
-            parts.append(torch.stack(stat_vectors, dim=1).mean(dim=1, keepdim=True).to(self.dtype))
-        ns_tokens = torch.cat(parts, dim=1)
+        ns_tokens = self._ns_tokens(inputs, stat_vectors)
         tokens = torch.cat([seq_tokens, ns_tokens], dim=1)
 
         # ---- mask description: one valid prefix (single domain) or a per-key validity map
@@ -490,10 +536,125 @@ class OneTransInference:
             seq_summary = torch.zeros(batch, self.d, device=dev)
         ns_part = tokens[:, seq_count:]
         ns_summary = ns_part.mean(dim=1) if ns_part.shape[1] > 0 else torch.zeros(batch, self.d, device=dev)
-        embeddings = torch.cat([seq_summary, ns_summary], dim=-1)
-        h = F.silu(F.linear(embeddings, self.w["classifier.0.weight"].float(), self.w["classifier.0.bias"].float()))
-        logits = F.linear(h, self.w["classifier.3.weight"].float(), self.w["classifier.3.bias"].float())
-        return logits, embeddings
+        return self._classify(seq_summary, ns_summary)
+
+    def _predict_packed(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
+        """Same forward on valid tokens only (one sequence domain).
+
+        Sample b owns ``n[b] + ns`` consecutive rows: its valid sequence tokens in order, then its NS
+        tokens.  After block i the reference keeps the last ``S[i+1]`` padded positions; in packed form
+        that drops the first ``min(n[b], S[i] - S[i+1])`` sequence rows of every sample.  All row counts
+        follow from the per-sample lengths and the static pyramid schedule, so one device-to-host read
+        of a few integers sizes every buffer of the forward."""
+        dev = self.device
+        domain = self.domains[0]
+        batch = inputs.user.int_values.shape[0]
+        ns = self.num_ns
+        seq = inputs.sequences[domain]
+        request_ts = inputs.request_timestamp
+        sort = _SequenceSort(seq.values, seq.lengths)
+        stat_vectors = [self._stats_vector(sequence_stats(seq.values, seq.lengths, seq.timestamps, request_ts, self._edges, sort))]
+        values, lengths, ts = deduplicate_sequence_events(seq.values, seq.lengths, seq.timestamps, sort)
+        max_len = values.shape[2]
+        raw_len = lengths.clamp(min=0, max=max_len).to(torch.long)
+        width = min(max_len, self.seq_keep)            # padded sequence width S[0] after the tail crop
+        start = (raw_len - width).clamp_min(0)         # first kept position of every row
+        n0 = raw_len.clamp_max(width)                  # valid sequence tokens per sample at layer 0
+
+        # static schedule of padded widths and the valid counts they imply
+        widths = [width]
+        for layer in range(self.n_blocks):
+            widths.append(pyramid_keep_count(widths[-1], layer, self.n_blocks, ns))
+        counts = [(n0 - (width - w)).clamp(min=0) for w in widths]            # [layers + 1] x [B]
+        rows = [c + ns for c in counts]
+        meta = torch.stack([torch.stack([r.sum(), r.max()]) for r in rows]).tolist()  # the one host read
+        totals = [int(m[0]) for m in meta]
+        max_rows = [int(m[1]) for m in meta]
+        arange_b = torch.arange(batch, device=dev)
+
+        def offsets(r: torch.Tensor) -> torch.Tensor:
+            cu = torch.zeros(batch + 1, dtype=torch.long, device=dev)
+            cu[1:] = torch.cumsum(r, dim=0)
+            return cu
+
+        cu = [offsets(r) for r in rows]
+
+        # ---- sequence tokenizer on the valid events only (modeling/tokenizers.py:156-190)
+        n_seq = totals[0] - batch * ns
+        sample_of = torch.repeat_interleave(arange_b, n0, output_size=n_seq)
+        seq_cu = offsets(n0)
+        j_idx = torch.arange(n_seq, device=dev) - seq_cu[sample_of]              # position after the tail crop
+        src_pos = start[sample_of] + j_idx                                        # position in the padded input
+        prefix = f"sequence_tokenizers.{domain}"
+        entries = self.seq_tables[domain]
+        n_feat = values.shape[1]
+        emb = self.spec.emb_dim
+        live = [f for f in range(n_feat) if f < len(entries) and entries[f][1] is not None]
+        if live:
+            token_input = (torch.empty if len(live) == n_feat else torch.zeros)(
+                (n_seq, n_feat * emb), dtype=self.dtype, device=dev)
+            for f in live:
+                kind, table = entries[f]
+                ids = values[sample_of, f, src_pos]
+                if kind == "compressed":
+                    ids = hash_compress_ids(ids.clamp_min(0), table.shape[0] - 1)
+                ops.gather_rows(table, ids, out=token_input, col0=f * emb)
+        else:
+            token_input = torch.zeros(n_seq, max(1, n_feat * emb), dtype=self.dtype, device=dev)
+        seq_tok = self._layer_norm(F.silu(self._linear(token_input, prefix + ".project.0")), prefix + ".project.2")
+        if prefix + ".time_embedding.weight" in self.w:
+            buckets = sequence_time_buckets(ts, request_ts, self._edges)[sample_of, src_pos]
+            seq_tok = seq_tok + ops.gather_rows(self._p(prefix + ".time_embedding.weight"), buckets)
+        seq_tok = seq_tok + self._positions(width)[j_idx]
+
+        # ---- interleave with the NS tokens: [seq rows of b | ns rows of b]
+        ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
+        ns_off = torch.arange(ns, device=dev)[None, :]
+        tokens = torch.empty(totals[0], self.d, dtype=self.dtype, device=dev)
+        tokens.index_copy_(0, cu[0][sample_of] + j_idx, seq_tok)
+        ns_rows = (cu[0][:-1] + counts[0])[:, None] + ns_off                       # [B, ns]
+        tokens.index_copy_(0, ns_rows.reshape(-1), ns_tokens.reshape(batch * ns, self.d))
+
+        d, heads, hd = self.d, self.heads, self.head_dim
+        for layer, blk in enumerate(self.blocks):
+            p = blk["p"]
+            cu32 = cu[layer].to(torch.int32)
+            x = ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
+            qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
+            flat_ns = ns_rows.reshape(-1)
+            x_ns = x[flat_ns].view(batch, ns, d).transpose(0, 1)                   # [ns, B, d]
+            qkv.index_copy_(0, flat_ns, torch.baddbmm(blk["ns_qkv_b"], x_ns, blk["ns_qkv_w"]).transpose(0, 1).reshape(batch * ns, 3 * d))
+            q, k, v = (qkv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(3))
+            if q.dtype == torch.float32:
+                q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+            attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
+                                        kernel=self.attention_kernel)
+            tokens = tokens + self._linear(attn.view(-1, d).to(self.dtype), p + ".attention.out")
+            x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
+            out = self._shared_ffn_residual(blk, x, tokens)
+            x_ns = x[flat_ns].view(batch, ns, d).transpose(0, 1)
+            h = F.silu(torch.baddbmm(blk["ns_b1"], x_ns, blk["ns_w1"]))
+            y_ns = torch.baddbmm(blk["ns_b2"], h, blk["ns_w2"]).transpose(0, 1).reshape(batch * ns, d)
+            out.index_copy_(0, flat_ns, tokens[flat_ns] + y_ns)
+            tokens = out
+            if widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
+                new_rows = rows[layer + 1]
+                owner = torch.repeat_interleave(arange_b, new_rows, output_size=totals[layer + 1])
+                r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]
+                src = cu[layer][owner] + (counts[layer] - counts[layer + 1])[owner] + r
+                tokens = tokens.index_select(0, src)
+                ns_rows = (cu[layer + 1][:-1] + counts[layer + 1])[:, None] + ns_off
+
+        last = len(widths) - 1
+        tokens = ops.rms_norm(tokens, self._p("final_norm.weight"), 1e-6).float()
+        n_last = counts[last]
+        total_seq = totals[last] - batch * ns
+        owner = torch.repeat_interleave(arange_b, n_last, output_size=total_seq)
+        seq_rows = cu[last][owner] + (torch.arange(total_seq, device=dev) - offsets(n_last)[owner])
+        seq_sum = torch.zeros(batch, d, device=dev).index_add_(0, owner, tokens[seq_rows])
+        seq_summary = seq_sum / n_last.clamp_min(1).to(torch.float32)[:, None]
+        ns_summary = tokens[ns_rows.reshape(-1)].view(batch, ns, d).mean(dim=1)
+        return self._classify(seq_summary, ns_summary)
 
     @torch.inference_mode()
     def scores(self, inputs, micro_batch: int | None = None) -> torch.Tensor:

@@ -355,10 +355,13 @@ def sequence_gather(tables: list[torch.Tensor | None], sequence: torch.Tensor) -
     return out
 
 
-def gather_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-    """``table[clamp(ids)]`` for an id tensor of any shape (bit-exact ``nn.Embedding`` lookup)."""
+def gather_rows(table: torch.Tensor, ids: torch.Tensor, *, out: torch.Tensor | None = None, col0: int = 0) -> torch.Tensor:
+    """``table[clamp(ids)]`` for an id tensor of any shape (bit-exact ``nn.Embedding`` lookup).
+
+    With ``out`` (a contiguous [ids.numel(), width] matrix) the rows are written into its columns
+    ``[col0, col0 + dim)`` instead of a new tensor — the packed-batch form of ``sequence_gather``."""
     _require_backend("gather_rows", "cuda")
-    _require_cuda_tensors("cuda gather_rows", table, ids)
+    _require_cuda_tensors("cuda gather_rows", table, ids, out)
     if ids.dtype not in _ID_CODES:
         raise RuntimeError(f"cuda gather_rows requires int32 or int64 values, got {ids.dtype}")
     if table.ndim != 2:
@@ -367,15 +370,24 @@ def gather_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         raise RuntimeError(f"cuda gather_rows does not support dtype {table.dtype}")
     weight = table.contiguous()
     flat = ids.contiguous().view(-1)
-    out = torch.empty((flat.shape[0], weight.shape[1]), dtype=weight.dtype, device=weight.device)
     n = flat.shape[0]
-    with torch.cuda.device(weight.device):
+    dim = weight.shape[1]
+    if out is None:
+        target = torch.empty((n, dim), dtype=weight.dtype, device=weight.device)
+        width, col0 = dim, 0
+    else:
+        if out.ndim != 2 or out.shape[0] != n or not out.is_contiguous() or out.dtype != weight.dtype:
+            raise ValueError("gather_rows out must be a contiguous [ids.numel(), width] matrix of the table's dtype")
+        if col0 < 0 or col0 + dim > out.shape[1]:
+            raise ValueError("gather_rows column range does not fit in out")
+        target, width = out, out.shape[1]
+    with torch.cuda.device(weight.device), _timed("gather_rows", ids=flat, dim=dim, esize=weight.element_size()):
         code = _lib.load().tb200_gather_rows(
-            _ptr(weight), weight.shape[0], weight.shape[1], _ptr(flat), _ID_CODES[flat.dtype], n, max(n, 1), 0,
-            _ptr(out), weight.shape[1], 0, _DTYPE_CODES[weight.dtype], _stream_ptr(),
+            _ptr(weight), weight.shape[0], dim, _ptr(flat), _ID_CODES[flat.dtype], n, max(n, 1), 0,
+            _ptr(target), width, col0, _DTYPE_CODES[weight.dtype], _stream_ptr(),
         )
     _lib.check(code, "cuda gather_rows")
-    return out.view(*ids.shape, weight.shape[1])
+    return target if out is not None else target.view(*ids.shape, dim)
 
 
 # --------------------------------------------------------------------------------------------

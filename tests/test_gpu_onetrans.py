@@ -40,13 +40,14 @@ def _to_model_input(ns) -> ModelInput:
                       ns.request_timestamp)
 
 
+@pytest.mark.parametrize("packed", [True, False])
 @pytest.mark.parametrize("name", ["onetrans_a", "onetrans_b"])
-def test_matches_reference_golden(name):
+def test_matches_reference_golden(name, packed):
+    """onetrans_a has one sequence domain (packed valid-token layout by default), onetrans_b two
+    domains, time buckets, hashed tables and a tail crop (padded layout with a key-validity map)."""
     sd, spec_dict, inputs, logits, embeddings = load_onetrans_fixture(name)
     spec = _spec_from_dict(spec_dict)
-    if spec.d_model // spec.num_heads not in (32, 64, 128):
-        pytest.skip("fixture head_dim has no CUDA attention kernel (reference fixture uses head_dim 8/16)")
-    model = OneTransInference(sd, spec, dtype=torch.float32)
+    model = OneTransInference(sd, spec, dtype=torch.float32, packed=packed)
     got_logits, got_emb = model.predict(_to_model_input(inputs).to("cuda"))
     assert np.abs(torch.sigmoid(got_logits).cpu().numpy() - torch.sigmoid(logits).numpy()).max() <= 1e-3
     torch.testing.assert_close(got_emb.cpu(), embeddings, atol=2e-2, rtol=2e-2)
@@ -60,8 +61,9 @@ def _mini_spec() -> OneTransSpec:
     )
 
 
+@pytest.mark.parametrize("packed", [True, False])
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-3), (torch.bfloat16, 5e-3)])
-def test_matches_oracle_on_synthetic_batch(dtype, tol):
+def test_matches_oracle_on_synthetic_batch(dtype, tol, packed):
     """512 samples of the baseline shape in miniature.  Labels are drawn from the oracle's own logits
     (standardised, temperature 2) so that the AUC is well away from 0.5; the AUC of the CUDA scores must
     agree to 4 decimals (|difference| < 5e-5; comparing rounded strings would fail spuriously whenever
@@ -70,7 +72,7 @@ def test_matches_oracle_on_synthetic_batch(dtype, tol):
     sd = random_state_dict(spec, seed=0)
     batch = synthetic_batch(spec, 512, seq_len=96, min_len=4, seed=1)
     want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
-    model = OneTransInference(sd, spec, dtype=dtype)
+    model = OneTransInference(sd, spec, dtype=dtype, packed=packed)
     got = model.scores(batch.to("cuda")).cpu().numpy()
     want = oracle_model.sigmoid_scores(want_logits).reshape(-1)
     assert np.abs(got - want).max() <= tol
@@ -94,3 +96,28 @@ def test_scores_are_batch_independent():
     full = model.scores(batch)
     halves = torch.cat([model.scores(batch.slice(0, 32)), model.scores(batch.slice(32, 64))])
     assert (full - halves).abs().max().item() <= 2e-3
+
+
+def _wide_spec() -> OneTransSpec:
+    """Small tables, serving-size backbone (d 512, 8 heads of 64, hidden 2048): the shapes the FP8 FFN
+    and the head_dim-64 attention kernels are built for."""
+    return OneTransSpec(
+        user_int_specs=[(500, i, 1) for i in range(6)], item_int_specs=[(500, i, 1) for i in range(3)],
+        user_dense_dim=16, item_dense_dim=0, seq_vocab_sizes={"seq_a": [3000]}, d_model=512, emb_dim=128,
+        num_blocks=3, num_heads=8, hidden_mult=4, seq_top_k=200, user_ns_tokens=5, item_ns_tokens=2,
+    )
+
+
+@pytest.mark.parametrize("ffn,tol", [("bf16", 5e-3), ("fp8", 1e-2)])
+def test_serving_shape_against_oracle(ffn, tol):
+    """d_model 512 with a tail crop (sequence 260 > seq_top_k 200), packed layout, bf16 and FP8 FFN."""
+    spec = _wide_spec()
+    sd = random_state_dict(spec, seed=5)
+    batch = synthetic_batch(spec, 48, seq_len=260, min_len=0, seed=6)
+    want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
+    want = oracle_model.sigmoid_scores(want_logits).reshape(-1)
+    model = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn=ffn)
+    got = model.scores(batch.to("cuda"), micro_batch=20).cpu().numpy()
+    assert np.abs(got - want).max() <= tol
+    padded = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn=ffn, packed=False).scores(batch.to("cuda")).cpu().numpy()
+    assert np.abs(got - padded).max() <= tol
