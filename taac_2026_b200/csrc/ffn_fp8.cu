@@ -9,10 +9,13 @@
 // promote it into fp32 register accumulators with the block's scale while the tensor cores already
 // work on the next K block (two TMEM accumulator buffers of 256 columns).
 //
-// Roles in a CTA of 320 threads (persistent, one CTA per SM, static round-robin over output tiles):
-//   warp 0      TMA producer: 4-stage ring of {A 128 x 128 B, B 256 x 128 B} tiles
-//   warp 1      MMA issuer (one elected lane), owner of the TMEM allocation
-//   warps 2..9  promotion + epilogue: each thread owns one output row and 128 of the 256 columns
+// Roles in a CTA of 576 threads (persistent, one CTA per SM, static round-robin over output tiles):
+//   warp 0       TMA producer: 4-stage ring of {A 128 x 128 B, B 256 x 128 B} tiles
+//   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
+//   warps 2..17  promotion + epilogue: each thread owns one output row and 64 of the 256 columns
+//                (four warps per TMEM lane quarter, so that four warps per scheduler hide each
+//                other's tcgen05.ld and MUFU latencies; the per-element instruction budget at K = 512
+//                is only about eight issue slots, hence packed fp32x2 math and a tanh-based SiLU)
 // Every wait on an mbarrier is bounded; a wait that gives up raises the status word and all roles
 // drain out through the same final barrier, where the TMEM allocation is released.
 #include <cuda_fp8.h>
@@ -30,8 +33,8 @@ constexpr int kBM = 128;          // output rows per tile
 constexpr int kBN = 256;          // output columns per tile
 constexpr int kBK = 128;          // K bytes (= e4m3 elements) per stage: one 128-byte swizzle atom
 constexpr int kStages = 4;
-constexpr int kThreads = 320;
-constexpr int kEpiThreads = 256;
+constexpr int kThreads = 576;
+constexpr int kEpiThreads = 512;
 constexpr uint32_t kABytes = kBM * kBK;  // 16 KB
 constexpr uint32_t kBBytes = kBN * kBK;  // 32 KB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -57,7 +60,14 @@ struct GemmArgs {
     int32_t out_ld;      // row pitch of `out` in elements
 };
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+// silu(x) = x * sigmoid(x) = h * tanh(h) + h with h = x / 2: one MUFU and two FMA-pipe instructions.
+// tanh.approx has about 11 bits of accuracy, far below the 3-bit mantissa of the e4m3 result.
+__device__ __forceinline__ float silu(float x) {
+    const float h = 0.5f * x;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+    return fmaf(h, t, h);
+}
 
 // 64 fp32 -> 64 e4m3 bytes (as 16 words) with q = x * inv_scale, round-to-nearest, saturating
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
@@ -76,7 +86,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     __shared__ uint64_t tmem_full[2];
     __shared__ uint64_t tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ float amax_xchg[2][kBM];
+    __shared__ float amax_xchg[4][kBM];
     __shared__ int s_abort;
 
     // stage tiles need 1024-byte alignment for the 128-byte swizzle pattern
@@ -176,14 +186,14 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
     } else {
         // ---------------------------------------------------------------- promotion + epilogue
-        const int et = threadIdx.x - 64;          // 0..255
-        const int half = et >> 7;                 // which 128-column half of the tile this thread serves
+        const int et = threadIdx.x - 64;          // 0..511
+        const int cq = et >> 7;                   // which 64-column quarter of the tile this thread serves
         const int quarter = warp & 3;             // TMEM lanes [32 * quarter, +32) are visible to this warp
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        // this thread's two 64-column ranges inside the 256-column accumulator
-        const int col_a = MODE == kSwiGLU ? half * 64 : half * 128;
-        const int col_b = MODE == kSwiGLU ? 128 + half * 64 : half * 128 + 64;
+        // this thread's two 32-column ranges inside the 256-column accumulator
+        const int col_a = MODE == kSwiGLU ? cq * 32 : cq * 64;
+        const int col_b = MODE == kSwiGLU ? 128 + cq * 32 : cq * 64 + 32;
         const int kb_scales = g.K / kBK;
         uint32_t acc_it = 0;
         bool ok = true;
@@ -197,127 +207,126 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             const float* sb_a = g.sb + static_cast<int64_t>((n0 + col_a) / 128) * kb_scales;
             const float* sb_b = g.sb + static_cast<int64_t>((n0 + col_b) / 128) * kb_scales;
 
-            float acc[128];
+            // accumulators start from the bias: acc[0..31] <- columns col_a.., acc[32..63] <- col_b..
+            float2 acc[32];
+            if (g.bias != nullptr) {
+                const float4* ba = reinterpret_cast<const float4*>(g.bias + n0 + col_a);
+                const float4* bb = reinterpret_cast<const float4*>(g.bias + n0 + col_b);
 #pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+                for (int i = 0; i < 8; ++i) {
+                    const float4 va = ba[i];
+                    const float4 vb = bb[i];
+                    acc[2 * i] = make_float2(va.x, va.y);
+                    acc[2 * i + 1] = make_float2(va.z, va.w);
+                    acc[16 + 2 * i] = make_float2(vb.x, vb.y);
+                    acc[16 + 2 * i + 1] = make_float2(vb.z, vb.w);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.f, 0.f);
+            }
 
             for (int kb = 0; kb < k_blocks; ++kb, ++acc_it) {
                 const uint32_t buf = acc_it & 1;
                 const uint32_t aph = (acc_it >> 1) & 1;
                 const float sa = row_ok ? sa_row[kb] : 0.f;
-                const float scale_a = sa * sb_a[kb];
-                const float scale_b = sa * sb_b[kb];
-                // all 256 epilogue threads wait for the same phase, so they pass or give up together
+                const float s_a = sa * sb_a[kb];
+                const float s_b = sa * sb_b[kb];
+                const float2 scale_a = make_float2(s_a, s_a);
+                const float2 scale_b = make_float2(s_b, s_b);
+                // all epilogue threads wait for the same phase, so they pass or give up together
                 if (!mbar_wait(&tmem_full[buf], aph)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
                 const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
-                uint32_t r0[32], r1[32];
-                tmem_ld_x32(t0 + col_a, r0);
-                tmem_ld_x32(t0 + col_a + 32, r1);
+                uint32_t r[32];
+                tmem_ld_x32(t0 + col_a, r);
                 tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    acc[i] = fmaf(__uint_as_float(r0[i]), scale_a, acc[i]);
-                    acc[32 + i] = fmaf(__uint_as_float(r1[i]), scale_a, acc[32 + i]);
-                }
-                tmem_ld_x32(t0 + col_b, r0);
-                tmem_ld_x32(t0 + col_b + 32, r1);
+                for (int i = 0; i < 16; ++i)
+                    acc[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), scale_a, acc[i]);
+                tmem_ld_x32(t0 + col_b, r);
                 tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale_b, acc[64 + i]);
-                    acc[96 + i] = fmaf(__uint_as_float(r1[i]), scale_b, acc[96 + i]);
-                }
+                for (int i = 0; i < 16; ++i)
+                    acc[16 + i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), scale_b, acc[16 + i]);
                 tc_fence_before_sync();
                 mbar_arrive(&tmem_empty[buf]);
             }
             if (!ok) break;
 
             // ------------------------------------------------------------ tile epilogue
-            if (MODE == kSwiGLU) {
-                // acc[0..63] = gate, acc[64..127] = up of hidden columns h0 + half * 64 + (0..63)
-                const int h0 = (n0 / kBN) * 128;
+            if (MODE == kSwiGLU || MODE == kSiLU) {
+                // kSwiGLU: acc[0..15] = gate, acc[16..31] = value of hidden columns h0 + cq * 32 + (0..31);
+                //          the 128-column quantisation block of the row is shared by the four column quarters.
+                // kSiLU:   64 hidden columns n0 + cq * 64 + (0..63); the block is shared by two quarters.
+                constexpr int NV = MODE == kSwiGLU ? 16 : 32;  // float2 values this thread produces
                 float amax = 0.f;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    float gate = acc[i];
-                    float up = acc[64 + i];
-                    if (g.bias != nullptr) {
-                        gate += g.bias[n0 + col_a + i];
-                        up += g.bias[n0 + col_b + i];
+                for (int i = 0; i < NV; ++i) {
+                    float2 h;
+                    if (MODE == kSwiGLU) {
+                        h.x = silu(acc[i].x) * acc[16 + i].x;
+                        h.y = silu(acc[i].y) * acc[16 + i].y;
+                    } else {
+                        h.x = silu(acc[i].x);
+                        h.y = silu(acc[i].y);
                     }
-                    const float h = silu(gate) * up;
                     acc[i] = h;
-                    amax = fmaxf(amax, fabsf(h));
+                    amax = fmaxf(amax, fmaxf(fabsf(h.x), fabsf(h.y)));
                 }
-                amax_xchg[half][row_in_tile] = amax;
+                amax_xchg[cq][row_in_tile] = amax;
                 asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-                amax = fmaxf(amax, amax_xchg[half ^ 1][row_in_tile]);
+                if (MODE == kSwiGLU) {
+                    amax = fmaxf(fmaxf(amax_xchg[0][row_in_tile], amax_xchg[1][row_in_tile]),
+                                 fmaxf(amax_xchg[2][row_in_tile], amax_xchg[3][row_in_tile]));
+                } else {
+                    amax = fmaxf(amax, amax_xchg[cq ^ 1][row_in_tile]);
+                }
                 const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
-                const float inv = 1.0f / scale;
+                const float inv1 = 1.0f / scale;
+                const float2 inv = make_float2(inv1, inv1);
                 if (row_ok) {
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + h0 + half * 64);
+                    const int64_t col0 = MODE == kSwiGLU ? (n0 / kBN) * 128 + cq * 32 : n0 + cq * 64;
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + col0);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint4 w;
-                        w.x = pack_e4m3x4(acc[16 * c + 0] * inv, acc[16 * c + 1] * inv, acc[16 * c + 2] * inv, acc[16 * c + 3] * inv);
-                        w.y = pack_e4m3x4(acc[16 * c + 4] * inv, acc[16 * c + 5] * inv, acc[16 * c + 6] * inv, acc[16 * c + 7] * inv);
-                        w.z = pack_e4m3x4(acc[16 * c + 8] * inv, acc[16 * c + 9] * inv, acc[16 * c + 10] * inv, acc[16 * c + 11] * inv);
-                        w.w = pack_e4m3x4(acc[16 * c + 12] * inv, acc[16 * c + 13] * inv, acc[16 * c + 14] * inv, acc[16 * c + 15] * inv);
-                        dst[c] = w;
+                    for (int c = 0; c < NV / 8; ++c) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 lo = __fmul2_rn(acc[8 * c + 2 * e], inv);
+                            const float2 hi = __fmul2_rn(acc[8 * c + 2 * e + 1], inv);
+                            w[e] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3)) |
+                                   (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3)) << 16);
+                        }
+                        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    if (half == 0) g.out_scale[row * (g.N / 256) + n0 / kBN] = scale;
+                    if (MODE == kSwiGLU) {
+                        if (cq == 0) g.out_scale[row * (g.N / 256) + n0 / kBN] = scale;
+                    } else if ((cq & 1) == 0) {
+                        g.out_scale[row * (g.N / 128) + (n0 + cq * 64) / 128] = scale;
+                    }
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // amax_xchg is reused by the next tile
-            } else if (MODE == kSiLU) {
-                const int c0 = n0 + half * 128;
-                float amax = 0.f;
-#pragma unroll
-                for (int i = 0; i < 128; ++i) {
-                    float v = acc[i];
-                    if (g.bias != nullptr) v += g.bias[c0 + i];
-                    v = silu(v);
-                    acc[i] = v;
-                    amax = fmaxf(amax, fabsf(v));
-                }
-                const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
-                const float inv = 1.0f / scale;
-                if (row_ok) {
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + c0);
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        uint4 w;
-                        w.x = pack_e4m3x4(acc[16 * c + 0] * inv, acc[16 * c + 1] * inv, acc[16 * c + 2] * inv, acc[16 * c + 3] * inv);
-                        w.y = pack_e4m3x4(acc[16 * c + 4] * inv, acc[16 * c + 5] * inv, acc[16 * c + 6] * inv, acc[16 * c + 7] * inv);
-                        w.z = pack_e4m3x4(acc[16 * c + 8] * inv, acc[16 * c + 9] * inv, acc[16 * c + 10] * inv, acc[16 * c + 11] * inv);
-                        w.w = pack_e4m3x4(acc[16 * c + 12] * inv, acc[16 * c + 13] * inv, acc[16 * c + 14] * inv, acc[16 * c + 15] * inv);
-                        dst[c] = w;
-                    }
-                    g.out_scale[row * (g.N / 128) + c0 / 128] = scale;
-                }
             } else {
-                const int c0 = n0 + half * 128;
+                const int c0 = n0 + cq * 64;
                 if (row_ok) {
                     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + row * g.out_ld + c0;
                     const __nv_bfloat16* res = g.residual != nullptr ? g.residual + row * g.out_ld + c0 : nullptr;
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        float v[8];
+                    for (int c = 0; c < 8; ++c) {
+                        float2 v[4];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            v[e] = acc[8 * c + e];
-                            if (g.bias != nullptr) v[e] += g.bias[c0 + 8 * c + e];
-                        }
+                        for (int e = 0; e < 4; ++e) v[e] = acc[4 * c + e];
                         if (res != nullptr) {
-                            float r[8];
-                            Vec16<__nv_bfloat16>::unpack(reinterpret_cast<const uint4*>(res)[c], r);
+                            float2 rr[4];
+                            Vec16<__nv_bfloat16>::unpack2(reinterpret_cast<const uint4*>(res)[c], rr);
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) v[e] += r[e];
+                            for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
                         }
-                        reinterpret_cast<uint4*>(dst)[c] = Vec16<__nv_bfloat16>::pack(v);
+                        reinterpret_cast<uint4*>(dst)[c] = Vec16<__nv_bfloat16>::pack2(v);
                     }
                 }
             }
