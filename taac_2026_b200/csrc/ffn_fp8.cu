@@ -76,34 +76,76 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
     return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
 }
 
-template <int MODE>
+// Work distribution: a CTA keeps ONE column tile (256 weight rows) for its whole life and walks down
+// the row tiles, so the weight tile, its scales and the bias are fetched once per CTA.  With
+// n_tiles <= gridDim.x, CTA c owns column tile c % n_tiles and row tiles j, j + G, ... (j = c / n_tiles,
+// G = gridDim.x / n_tiles); the n_tiles CTAs that share j read the same activation rows at about the
+// same time, so those rows come from HBM once.  If K <= 512 the weight tile stays resident in shared
+// memory (B_RES) and only the activation tiles stream through the ring.
+struct Schedule {
+    int n_first, n_step, j, G;
+    bool active;
+};
+__device__ __forceinline__ Schedule make_schedule(int n_tiles) {
+    Schedule sc;
+    const int c = blockIdx.x;
+    const int grid = gridDim.x;
+    if (n_tiles <= grid) {
+        sc.G = grid / n_tiles;
+        sc.n_first = c % n_tiles;
+        sc.j = c / n_tiles;
+        sc.n_step = 0x40000000;  // a single column tile per CTA
+        sc.active = sc.j < sc.G;
+    } else {
+        sc.G = 1;
+        sc.j = 0;
+        sc.n_first = c;
+        sc.n_step = grid;
+        sc.active = true;
+    }
+    return sc;
+}
+
+constexpr int kStagesRes = 5;     // activation stages when the weight tile is resident
+constexpr int kMaxStages = 5;
+constexpr int kMaxKBlocks = 64;   // K <= 8192
+
+template <int MODE, bool B_RES>
 __global__ void __launch_bounds__(kThreads, 1)
 ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[kStages];
-    __shared__ uint64_t empty_bar[kStages];
+    __shared__ uint64_t full_bar[kMaxStages];
+    __shared__ uint64_t empty_bar[kMaxStages];
+    __shared__ uint64_t b_full;
     __shared__ uint64_t tmem_full[2];
     __shared__ uint64_t tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ float amax_xchg[4][kBM];
+    __shared__ __align__(16) float bias_s[kBN];
+    __shared__ float sb_s[2][kMaxKBlocks];
+    __shared__ float amax_xchg[2][4][kBM];
     __shared__ int s_abort;
 
-    // stage tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     const int64_t m_tiles = (g.M + kBM - 1) / kBM;
     const int n_tiles = g.N / kBN;
-    const int64_t total_tiles = m_tiles * n_tiles;
     const int k_blocks = g.K / kBK;
+    constexpr int STAGES = B_RES ? kStagesRes : kStages;
+    constexpr uint32_t STAGE_BYTES = B_RES ? kABytes : kStageBytes;
+    uint8_t* b_res = smem;                                              // [k_blocks][kBBytes] when B_RES
+    uint8_t* ring = B_RES ? smem + static_cast<size_t>(k_blocks) * kBBytes : smem;
+    const Schedule sc = make_schedule(n_tiles);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
+        mbar_init(&b_full, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], kEpiThreads);
@@ -122,25 +164,36 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
-        if (lane == 0) {
+        if (lane == 0 && sc.active) {
             tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
             uint32_t it = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = static_cast<int>(tile / n_tiles) * kBM;
-                const int n0 = static_cast<int>(tile % n_tiles) * kBN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
-                        ok = false;
-                        break;
+            for (int n = sc.n_first; n < n_tiles && ok; n += sc.n_step) {
+                const int n0 = n * kBN;
+                if (B_RES) {
+                    if (it > 0) {  // the previous column tile's MMAs must have finished reading b_res
+                        const uint32_t last = it - 1;
+                        if (!mbar_wait(&empty_bar[last % STAGES], (last / STAGES) & 1)) { ok = false; break; }
                     }
-                    uint8_t* a_dst = smem + s * kStageBytes;
-                    mbar_expect_tx(&full_bar[s], kStageBytes);
-                    tma_load_2d(a_dst, &tmap_a, kb * kBK, m0, &full_bar[s]);
-                    tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, n0, &full_bar[s]);
+                    mbar_expect_tx(&b_full, static_cast<uint32_t>(k_blocks) * kBBytes);
+                    for (int kb = 0; kb < k_blocks; ++kb)
+                        tma_load_2d(b_res + static_cast<size_t>(kb) * kBBytes, &tmap_b, kb * kBK, n0, &b_full);
+                }
+                for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G) {
+                    const int m0 = static_cast<int>(m) * kBM;
+                    for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                        const uint32_t s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* a_dst = ring + static_cast<size_t>(s) * STAGE_BYTES;
+                        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                        tma_load_2d(a_dst, &tmap_a, kb * kBK, m0, &full_bar[s]);
+                        if (!B_RES) tma_load_2d(a_dst + kABytes, &tmap_b, kb * kBK, n0, &full_bar[s]);
+                    }
                 }
             }
             if (!ok) {
@@ -150,33 +203,39 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && sc.active) {
             const uint32_t idesc = umma_idesc(0, 0, 0, 0, kBM, kBN);  // e4m3 x e4m3 -> f32, both K-major
-            uint32_t it = 0, acc_it = 0;
+            uint32_t it = 0, acc_it = 0, b_phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < k_blocks; ++kb, ++it, ++acc_it) {
-                    const uint32_t buf = acc_it & 1;
-                    const uint32_t aph = (acc_it >> 1) & 1;
-                    const uint32_t s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!mbar_wait(&tmem_empty[buf], aph ^ 1) || !mbar_wait(&full_bar[s], ph) ||
-                        *reinterpret_cast<volatile int*>(&s_abort)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
-                    const uint32_t b_addr = a_addr + kABytes;
-                    const uint32_t d_tmem = tmem_base + buf * kBN;
+            for (int n = sc.n_first; n < n_tiles && ok; n += sc.n_step) {
+                if (B_RES) {
+                    if (!mbar_wait(&b_full, b_phase)) { ok = false; break; }
+                    b_phase ^= 1;
+                }
+                for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G) {
+                    for (int kb = 0; kb < k_blocks; ++kb, ++it, ++acc_it) {
+                        const uint32_t buf = acc_it & 1;
+                        const uint32_t aph = (acc_it >> 1) & 1;
+                        const uint32_t s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!mbar_wait(&tmem_empty[buf], aph ^ 1) || !mbar_wait(&full_bar[s], ph) ||
+                            *reinterpret_cast<volatile int*>(&s_abort)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t a_addr = smem_u32(ring + static_cast<size_t>(s) * STAGE_BYTES);
+                        const uint32_t b_addr = B_RES ? smem_u32(b_res + static_cast<size_t>(kb) * kBBytes) : a_addr + kABytes;
+                        const uint32_t d_tmem = tmem_base + buf * kBN;
 #pragma unroll
-                    for (int k = 0; k < kBK / 32; ++k) {
-                        const uint64_t da = umma_desc_sw128(a_addr + k * 32, 1024, 16);
-                        const uint64_t db = umma_desc_sw128(b_addr + k * 32, 1024, 16);
-                        mma_f8_ss(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+                        for (int k = 0; k < kBK / 32; ++k) {
+                            const uint64_t da = umma_desc_sw128(a_addr + k * 32, 1024, 16);
+                            const uint64_t db = umma_desc_sw128(b_addr + k * 32, 1024, 16);
+                            mma_f8_ss(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+                        }
+                        tc_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
+                        tc_commit(&tmem_full[buf]);   // the partial product of this K block is complete
                     }
-                    tc_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
-                    tc_commit(&tmem_full[buf]);   // the partial product of this K block is complete
                 }
             }
             if (!ok) {
@@ -194,139 +253,167 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // this thread's two 32-column ranges inside the 256-column accumulator
         const int col_a = MODE == kSwiGLU ? cq * 32 : cq * 64;
         const int col_b = MODE == kSwiGLU ? 128 + cq * 32 : cq * 64 + 32;
-        const int kb_scales = g.K / kBK;
+        const int nb_a = col_a >> 7;              // which of the tile's two 128-row weight blocks
+        const int nb_b = col_b >> 7;
         uint32_t acc_it = 0;
+        uint32_t tile_count = 0;
         bool ok = true;
 
-        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int64_t m0 = (tile / n_tiles) * kBM;
-            const int n0 = static_cast<int>(tile % n_tiles) * kBN;
-            const int64_t row = m0 + row_in_tile;
-            const bool row_ok = row < g.M;
-            const float* sa_row = g.sa + (row_ok ? row : 0) * kb_scales;
-            const float* sb_a = g.sb + static_cast<int64_t>((n0 + col_a) / 128) * kb_scales;
-            const float* sb_b = g.sb + static_cast<int64_t>((n0 + col_b) / 128) * kb_scales;
-
-            // accumulators start from the bias: acc[0..31] <- columns col_a.., acc[32..63] <- col_b..
-            float2 acc[32];
-            if (g.bias != nullptr) {
-                const float4* ba = reinterpret_cast<const float4*>(g.bias + n0 + col_a);
-                const float4* bb = reinterpret_cast<const float4*>(g.bias + n0 + col_b);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float4 va = ba[i];
-                    const float4 vb = bb[i];
-                    acc[2 * i] = make_float2(va.x, va.y);
-                    acc[2 * i + 1] = make_float2(va.z, va.w);
-                    acc[16 + 2 * i] = make_float2(vb.x, vb.y);
-                    acc[16 + 2 * i + 1] = make_float2(vb.z, vb.w);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.f, 0.f);
+        for (int n = sc.n_first; n < n_tiles && ok && sc.active; n += sc.n_step) {
+            const int n0 = n * kBN;
+            // per-column-tile constants -> shared memory
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            if (et < kBN) bias_s[et] = g.bias != nullptr ? g.bias[n0 + et] : 0.f;
+            for (int i = et; i < 2 * k_blocks; i += kEpiThreads) {
+                const int blk = i / k_blocks;
+                const int kb = i - blk * k_blocks;
+                sb_s[blk][kb] = g.sb[static_cast<int64_t>(n0 / 128 + blk) * k_blocks + kb];
             }
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
 
-            for (int kb = 0; kb < k_blocks; ++kb, ++acc_it) {
-                const uint32_t buf = acc_it & 1;
-                const uint32_t aph = (acc_it >> 1) & 1;
-                const float sa = row_ok ? sa_row[kb] : 0.f;
-                const float s_a = sa * sb_a[kb];
-                const float s_b = sa * sb_b[kb];
-                const float2 scale_a = make_float2(s_a, s_a);
-                const float2 scale_b = make_float2(s_b, s_b);
-                // all epilogue threads wait for the same phase, so they pass or give up together
-                if (!mbar_wait(&tmem_full[buf], aph)) {
-                    ok = false;
-                    break;
+            // activation scales are fetched two K blocks ahead of their use; the cursor walks the same
+            // (row tile, K block) sequence as the main loop
+            int64_t pf_m = sc.j;
+            int pf_kb = 0;
+            auto next_sa = [&]() -> float {
+                float v = 0.f;
+                if (pf_m < m_tiles) {
+                    const int64_t r = pf_m * kBM + row_in_tile;
+                    if (r < g.M) v = g.sa[r * k_blocks + pf_kb];
+                    if (++pf_kb == k_blocks) {
+                        pf_kb = 0;
+                        pf_m += sc.G;
+                    }
                 }
-                tc_fence_after_sync();
-                const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
-                uint32_t r[32];
-                tmem_ld_x32(t0 + col_a, r);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    acc[i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), scale_a, acc[i]);
-                tmem_ld_x32(t0 + col_b, r);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    acc[16 + i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), scale_b, acc[16 + i]);
-                tc_fence_before_sync();
-                mbar_arrive(&tmem_empty[buf]);
-            }
-            if (!ok) break;
+                return v;
+            };
+            float sa_q0 = next_sa();
+            float sa_q1 = next_sa();
 
-            // ------------------------------------------------------------ tile epilogue
-            if (MODE == kSwiGLU || MODE == kSiLU) {
-                // kSwiGLU: acc[0..15] = gate, acc[16..31] = value of hidden columns h0 + cq * 32 + (0..31);
-                //          the 128-column quantisation block of the row is shared by the four column quarters.
-                // kSiLU:   64 hidden columns n0 + cq * 64 + (0..63); the block is shared by two quarters.
-                constexpr int NV = MODE == kSwiGLU ? 16 : 32;  // float2 values this thread produces
-                float amax = 0.f;
+            for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G, ++tile_count) {
+                const int64_t row = m * kBM + row_in_tile;
+                const bool row_ok = row < g.M;
+
+                // accumulators start from the bias: acc[0..15] <- columns col_a.., acc[16..31] <- col_b..
+                float2 acc[32];
+                {
+                    const float4* ba = reinterpret_cast<const float4*>(bias_s + col_a);
+                    const float4* bb = reinterpret_cast<const float4*>(bias_s + col_b);
 #pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    float2 h;
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 va = ba[i];
+                        const float4 vb = bb[i];
+                        acc[2 * i] = make_float2(va.x, va.y);
+                        acc[2 * i + 1] = make_float2(va.z, va.w);
+                        acc[16 + 2 * i] = make_float2(vb.x, vb.y);
+                        acc[16 + 2 * i + 1] = make_float2(vb.z, vb.w);
+                    }
+                }
+
+                for (int kb = 0; kb < k_blocks; ++kb, ++acc_it) {
+                    const uint32_t buf = acc_it & 1;
+                    const uint32_t aph = (acc_it >> 1) & 1;
+                    const float sa = sa_q0;
+                    sa_q0 = sa_q1;
+                    sa_q1 = next_sa();
+                    const float s_a = sa * sb_s[nb_a][kb];
+                    const float s_b = sa * sb_s[nb_b][kb];
+                    const float2 scale_a = make_float2(s_a, s_a);
+                    const float2 scale_b = make_float2(s_b, s_b);
+                    // all epilogue threads wait for the same phase, so they pass or give up together
+                    if (!mbar_wait(&tmem_full[buf], aph)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
+                    // 16 columns at a time: the accumulators already take 64 registers of a 96-register budget
+                    uint32_t r[16];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld_x16(t0 + (c < 2 ? col_a + 16 * c : col_b + 16 * (c - 2)), r);
+                        tc_wait_ld();
+                        const float2 sc2 = c < 2 ? scale_a : scale_b;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            acc[8 * c + i] = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, acc[8 * c + i]);
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive(&tmem_empty[buf]);
+                }
+                if (!ok) break;
+
+                // -------------------------------------------------------- tile epilogue
+                if (MODE == kSwiGLU || MODE == kSiLU) {
+                    // kSwiGLU: acc[0..15] = gate, acc[16..31] = value of hidden columns h0 + cq * 32 + (0..31);
+                    //          the 128-column quantisation block of the row is shared by the four column quarters.
+                    // kSiLU:   64 hidden columns n0 + cq * 64 + (0..63); the block is shared by two quarters.
+                    constexpr int NV = MODE == kSwiGLU ? 16 : 32;  // float2 values this thread produces
+                    float amax = 0.f;
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) {
+                        float2 h;
+                        if (MODE == kSwiGLU) {
+                            h.x = silu(acc[i].x) * acc[16 + i].x;
+                            h.y = silu(acc[i].y) * acc[16 + i].y;
+                        } else {
+                            h.x = silu(acc[i].x);
+                            h.y = silu(acc[i].y);
+                        }
+                        acc[i] = h;
+                        amax = fmaxf(amax, fmaxf(fabsf(h.x), fabsf(h.y)));
+                    }
+                    float (*xchg)[kBM] = amax_xchg[tile_count & 1];  // alternate buffers: one barrier per tile
+                    xchg[cq][row_in_tile] = amax;
+                    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
                     if (MODE == kSwiGLU) {
-                        h.x = silu(acc[i].x) * acc[16 + i].x;
-                        h.y = silu(acc[i].y) * acc[16 + i].y;
+                        amax = fmaxf(fmaxf(xchg[0][row_in_tile], xchg[1][row_in_tile]),
+                                     fmaxf(xchg[2][row_in_tile], xchg[3][row_in_tile]));
                     } else {
-                        h.x = silu(acc[i].x);
-                        h.y = silu(acc[i].y);
+                        amax = fmaxf(amax, xchg[cq ^ 1][row_in_tile]);
                     }
-                    acc[i] = h;
-                    amax = fmaxf(amax, fmaxf(fabsf(h.x), fabsf(h.y)));
-                }
-                amax_xchg[cq][row_in_tile] = amax;
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-                if (MODE == kSwiGLU) {
-                    amax = fmaxf(fmaxf(amax_xchg[0][row_in_tile], amax_xchg[1][row_in_tile]),
-                                 fmaxf(amax_xchg[2][row_in_tile], amax_xchg[3][row_in_tile]));
+                    const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+                    const float inv1 = 1.0f / scale;
+                    const float2 inv = make_float2(inv1, inv1);
+                    if (row_ok) {
+                        const int64_t col0 = MODE == kSwiGLU ? (n0 / kBN) * 128 + cq * 32 : n0 + cq * 64;
+                        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + col0);
+#pragma unroll
+                        for (int c = 0; c < NV / 8; ++c) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 lo = __fmul2_rn(acc[8 * c + 2 * e], inv);
+                                const float2 hi = __fmul2_rn(acc[8 * c + 2 * e + 1], inv);
+                                w[e] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3)) |
+                                       (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3)) << 16);
+                            }
+                            dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                        if (MODE == kSwiGLU) {
+                            if (cq == 0) g.out_scale[row * (g.N / 256) + n0 / kBN] = scale;
+                        } else if ((cq & 1) == 0) {
+                            g.out_scale[row * (g.N / 128) + (n0 + cq * 64) / 128] = scale;
+                        }
+                    }
                 } else {
-                    amax = fmaxf(amax, amax_xchg[cq ^ 1][row_in_tile]);
-                }
-                const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
-                const float inv1 = 1.0f / scale;
-                const float2 inv = make_float2(inv1, inv1);
-                if (row_ok) {
-                    const int64_t col0 = MODE == kSwiGLU ? (n0 / kBN) * 128 + cq * 32 : n0 + cq * 64;
-                    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + col0);
+                    const int c0 = n0 + cq * 64;
+                    if (row_ok) {
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + row * g.out_ld + c0;
+                        const __nv_bfloat16* res = g.residual != nullptr ? g.residual + row * g.out_ld + c0 : nullptr;
 #pragma unroll
-                    for (int c = 0; c < NV / 8; ++c) {
-                        uint32_t w[4];
+                        for (int c = 0; c < 8; ++c) {
+                            float2 v[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 lo = __fmul2_rn(acc[8 * c + 2 * e], inv);
-                            const float2 hi = __fmul2_rn(acc[8 * c + 2 * e + 1], inv);
-                            w[e] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3)) |
-                                   (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3)) << 16);
+                            for (int e = 0; e < 4; ++e) v[e] = acc[4 * c + e];
+                            if (res != nullptr) {
+                                float2 rr[4];
+                                Vec16<__nv_bfloat16>::unpack2(reinterpret_cast<const uint4*>(res)[c], rr);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
+                            }
+                            reinterpret_cast<uint4*>(dst)[c] = Vec16<__nv_bfloat16>::pack2(v);
                         }
-                        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    if (MODE == kSwiGLU) {
-                        if (cq == 0) g.out_scale[row * (g.N / 256) + n0 / kBN] = scale;
-                    } else if ((cq & 1) == 0) {
-                        g.out_scale[row * (g.N / 128) + (n0 + cq * 64) / 128] = scale;
-                    }
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // amax_xchg is reused by the next tile
-            } else {
-                const int c0 = n0 + cq * 64;
-                if (row_ok) {
-                    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + row * g.out_ld + c0;
-                    const __nv_bfloat16* res = g.residual != nullptr ? g.residual + row * g.out_ld + c0 : nullptr;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        float2 v[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) v[e] = acc[4 * c + e];
-                        if (res != nullptr) {
-                            float2 rr[4];
-                            Vec16<__nv_bfloat16>::unpack2(reinterpret_cast<const uint4*>(res)[c], rr);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
-                        }
-                        reinterpret_cast<uint4*>(dst)[c] = Vec16<__nv_bfloat16>::pack2(v);
                     }
                 }
             }
@@ -413,21 +500,35 @@ bool make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t k_bytes, uint6
     return r == CUDA_SUCCESS;
 }
 
-template <int MODE>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t stream) {
+template <int MODE, bool B_RES>
+int launch_gemm_impl(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t stream) {
     const DeviceInfo& dev = device_info();
-    const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
+    const size_t tiles_bytes = B_RES ? static_cast<size_t>(g.K / kBK) * kBBytes + static_cast<size_t>(kStagesRes) * kABytes
+                                     : static_cast<size_t>(kStages) * kStageBytes;
+    const size_t smem = tiles_bytes + 1024;
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
-        cudaFuncSetAttribute(ffn_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaFuncSetAttribute(ffn_gemm_kernel<MODE, B_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(static_cast<size_t>(B_RES ? 4 * kBBytes + kStagesRes * kABytes : kStages * kStageBytes) + 1024));
         attr_set[dev.index] = true;
     }
-    const int64_t tiles = ((g.M + kBM - 1) / kBM) * (g.N / kBN);
+    const int64_t m_tiles = (g.M + kBM - 1) / kBM;
+    const int n_tiles = g.N / kBN;
     int64_t grid = dev.sm_count;
-    if (grid > tiles) grid = tiles;
-    ffn_gemm_kernel<MODE><<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(ta, tb, g);
+    if (n_tiles <= grid) {  // no more row walkers per column tile than there are row tiles
+        int64_t walkers = grid / n_tiles;
+        if (walkers > m_tiles) walkers = m_tiles;
+        grid = walkers * n_tiles;
+    }
+    ffn_gemm_kernel<MODE, B_RES><<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(ta, tb, g);
     count_launch();
     return launch_status();
+}
+
+template <int MODE>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t stream) {
+    if (g.K <= 4 * kBK) return launch_gemm_impl<MODE, true>(ta, tb, g, stream);
+    return launch_gemm_impl<MODE, false>(ta, tb, g, stream);
 }
 
 }  // namespace
@@ -454,7 +555,7 @@ extern "C" int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const vo
                               const float* bias, const void* residual, void* out, float* out_scales, int64_t M,
                               int32_t N, int32_t K, int32_t mode, int32_t* status_word, void* stream) {
     using namespace tb200;
-    if (M < 0 || N < 256 || N % 256 != 0 || K < 128 || K % 128 != 0) return TB200_ERR_SHAPE;
+    if (M < 0 || N < 256 || N % 256 != 0 || K < 128 || K % 128 != 0 || K > 8192) return TB200_ERR_SHAPE;
     if (mode < 0 || mode > 2) return TB200_ERR_UNSUPPORTED;
     if (M == 0) return TB200_OK;
     if (a_fp8 == nullptr || a_scales == nullptr || b_fp8 == nullptr || b_scales == nullptr || out == nullptr)
