@@ -32,6 +32,7 @@ extern "C" {
 #define TB200_ERR_UNSUPPORTED (-5) /* valid request that this build has no kernel for */
 #define TB200_ERR_DEVICE (-6)      /* current device is not compute capability 10.x */
 #define TB200_ERR_DRIVER (-7)      /* a driver entry point (tensor-map encode) is unavailable or failed */
+#define TB200_ERR_SCRATCH (-8)     /* the request does not fit the fixed scratch of a no-allocation entry point */
 
 /* ---- element / index type codes ------------------------------------------------------- */
 #define TB200_F32 0
@@ -158,6 +159,39 @@ int tb200_quant_act_1x128(const void* x_bf16, void* x_fp8, float* scales, int64_
 int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const void* b_fp8, const float* b_scales,
                    const float* bias, const void* residual, void* out, float* out_scales, int64_t M, int32_t N,
                    int32_t K, int32_t mode, int32_t* status_word, void* stream);
+
+/* ---- whole FFN without any allocation --------------------------------------------------------
+ * No counterpart in the reference (which has neither an FP8 path nor a C interface).
+ *
+ * y = [residual +] W_down . act(W_up . x + b_up) + b_down for bf16 x [M, d_in], i.e. the three calls
+ * tb200_quant_act_1x128 -> tb200_fp8_gemm(mode 0 if gated else 1) -> tb200_fp8_gemm(mode 2) in one
+ * entry point that needs no workspace from the caller.  It exists for callers that cannot allocate
+ * device memory at the point where they run the layer: code inside a serving loop whose memory was
+ * handed out once at start-up and is fully committed, a plugin called from a host framework that
+ * owns the allocator, or a latency-critical path where a cudaMalloc (which synchronises the device)
+ * is not acceptable.  Such a caller still passes x, the prepared weights and y; the quantised input,
+ * the e4m3 hidden activation and their scales live in a fixed array inside the library.
+ *
+ * Limits and rules:
+ *  - the array is tb200_ffn_fp8_static_scratch_bytes() = 64 MiB per GPU, held from library load to
+ *    process exit; a call needs about M * (d_in + hidden) * 1.04 bytes (d_in 512, hidden 2048:
+ *    M <= 25 000 rows).  Larger requests return TB200_ERR_SCRATCH and launch nothing — split the rows;
+ *  - the first call on each device looks the array's address up (cudaGetSymbolAddress) and sets kernel
+ *    attributes; make that call once per device before capturing a stream or timing anything;
+ *  - the entry point calls no cudaMalloc / cudaFree and no allocating library routine;
+ *  - every call on a device uses the same array: two calls that overlap on the GPU (different streams,
+ *    or graphs replayed concurrently) race on it.  Calls on one stream are ordered and safe.  Nothing
+ *    in the array needs clearing between calls: each call overwrites all bytes it later reads.
+ * w_up_fp8 / w_up_scales / b_up and w_down_* are exactly what the two tb200_fp8_gemm calls take
+ * (for gated != 0 the [gate | value] row interleave of mode 0); b_up, b_down and residual may be NULL.
+ * d_in % 128 == 0, hidden % 256 == 0, d_out % 256 == 0. */
+int tb200_ffn_fp8_fwd_static(const void* x_bf16, const void* w_up_fp8, const float* w_up_scales, const float* b_up,
+                             const void* w_down_fp8, const float* w_down_scales, const float* b_down,
+                             const void* residual, void* y_bf16, int64_t M, int32_t d_in, int32_t hidden,
+                             int32_t d_out, int32_t gated, void* stream);
+
+/* Size in bytes of the fixed array behind tb200_ffn_fp8_fwd_static. */
+int64_t tb200_ffn_fp8_static_scratch_bytes(void);
 
 #ifdef __cplusplus
 }

@@ -40,6 +40,10 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     ),
     "tb200_quant_act_1x128": (_INT, [_P, _P, _P, _I64, _I32, _P]),
     "tb200_fp8_gemm": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _P]),
+    "tb200_ffn_fp8_fwd_static": (
+        _INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _P],
+    ),
+    "tb200_ffn_fp8_static_scratch_bytes": (_I64, []),
     "tb200_gather_rows": (_INT, [_P, _I64, _I32, _P, _INT, _I64, _I64, _I64, _P, _I64, _I32, _INT, _P]),
 }
 
@@ -82,7 +86,7 @@ def check(code: int, what: str) -> None:
     if code == 0:
         return
     message = f"{what}: {strerror(code)} (status {code})"
-    if code in (-3,):
+    if code in (-3, -8):
         raise ValueError(message)
     raise RuntimeError(message)
 

@@ -52,6 +52,8 @@ extern "C" const char* tb200_strerror(int code) {
         case TB200_ERR_UNSUPPORTED: return "tb200: no kernel for this configuration";
         case TB200_ERR_DEVICE: return "tb200: current device is not compute capability 10.x (sm_100)";
         case TB200_ERR_DRIVER: return "tb200: tensor-map driver entry point unavailable or failed";
+        case TB200_ERR_SCRATCH:
+            return "tb200: request exceeds the 64 MiB fixed scratch of the no-allocation entry point; split the rows";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

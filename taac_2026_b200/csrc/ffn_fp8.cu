@@ -21,6 +21,8 @@
 #include <cuda_fp8.h>
 #include <cudaTypedefs.h>
 
+#include <mutex>
+
 #include "tb200_common.cuh"
 #include "tb200_ptx.cuh"
 
@@ -531,6 +533,36 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g,
     return launch_gemm_impl<MODE, false>(ta, tb, g, stream);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Fixed scratch for callers that must not allocate
+// ------------------------------------------------------------------------------------------------
+// The whole FFN (quantise -> GEMM 1 -> GEMM 2) needs the quantised input, the e4m3 hidden activation
+// and their scale vectors between its three kernels.  tb200_ffn_fp8_fwd_static keeps them in this
+// array, which lives in the library's device image: every GPU that loads the library holds these
+// bytes until the process exits, and every call on that GPU shares them.
+constexpr size_t kStaticScratchBytes = size_t(64) << 20;
+static __device__ __align__(256) uint8_t g_ffn_scratch[kStaticScratchBytes];
+
+// In host code `g_ffn_scratch` is only a handle for the runtime, not a device address; the address
+// a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_base(uint8_t** base) {
+    static std::mutex lock;
+    static uint8_t* cached[64] = {};
+    const DeviceInfo& dev = device_info();
+    if (!dev.valid) return TB200_ERR_DEVICE;
+    std::lock_guard<std::mutex> guard(lock);
+    if (cached[dev.index] == nullptr) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_ffn_scratch);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        cached[dev.index] = static_cast<uint8_t*>(ptr);
+    }
+    *base = cached[dev.index];
+    return TB200_OK;
+}
+
+inline size_t round256(size_t v) { return (v + 255) & ~size_t(255); }
+
 }  // namespace
 }  // namespace tb200
 
@@ -586,4 +618,42 @@ extern "C" int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const vo
     if (mode == kSwiGLU) return launch_gemm<kSwiGLU>(ta, tb, g, s);
     if (mode == kSiLU) return launch_gemm<kSiLU>(ta, tb, g, s);
     return launch_gemm<kLinear>(ta, tb, g, s);
+}
+
+extern "C" int64_t tb200_ffn_fp8_static_scratch_bytes(void) { return static_cast<int64_t>(tb200::kStaticScratchBytes); }
+
+extern "C" int tb200_ffn_fp8_fwd_static(const void* x_bf16, const void* w_up_fp8, const float* w_up_scales,
+                                        const float* b_up, const void* w_down_fp8, const float* w_down_scales,
+                                        const float* b_down, const void* residual, void* y_bf16, int64_t M,
+                                        int32_t d_in, int32_t hidden, int32_t d_out, int32_t gated, void* stream) {
+    using namespace tb200;
+    if (M < 0 || d_in < 128 || d_in % 128 != 0 || hidden < 256 || hidden % 256 != 0 || d_out < 256 || d_out % 256 != 0)
+        return TB200_ERR_SHAPE;
+    if (M == 0) return TB200_OK;
+    if (x_bf16 == nullptr || w_up_fp8 == nullptr || w_up_scales == nullptr || w_down_fp8 == nullptr ||
+        w_down_scales == nullptr || y_bf16 == nullptr)
+        return TB200_ERR_NULL;
+    // carve the fixed array: [x e4m3 | x scales | hidden e4m3 | hidden scales], each part 256-byte aligned
+    const size_t um = static_cast<size_t>(M);
+    const size_t xq_bytes = round256(um * d_in);
+    const size_t sx_bytes = round256(um * (d_in / 128) * sizeof(float));
+    const size_t h_bytes = round256(um * hidden);
+    const size_t sh_bytes = round256(um * (hidden / 128) * sizeof(float));
+    if (xq_bytes + sx_bytes + h_bytes + sh_bytes > kStaticScratchBytes) return TB200_ERR_SCRATCH;
+    uint8_t* base = nullptr;
+    const int rc = static_scratch_base(&base);
+    if (rc != TB200_OK) return rc;
+    uint8_t* xq = base;
+    float* sx = reinterpret_cast<float*>(base + xq_bytes);
+    uint8_t* h = base + xq_bytes + sx_bytes;
+    float* sh = reinterpret_cast<float*>(base + xq_bytes + sx_bytes + h_bytes);
+    // Nothing in the array has to start at zero: the three kernels below overwrite every byte they later
+    // read (rows [0, M) of each part), so what an earlier call left behind is never seen.
+    int code = tb200_quant_act_1x128(x_bf16, xq, sx, M, d_in, stream);
+    if (code != TB200_OK) return code;
+    code = tb200_fp8_gemm(xq, sx, w_up_fp8, w_up_scales, b_up, nullptr, h, sh, M, gated ? 2 * hidden : hidden, d_in,
+                          gated ? 0 : 1, nullptr, stream);
+    if (code != TB200_OK) return code;
+    return tb200_fp8_gemm(h, sh, w_down_fp8, w_down_scales, b_down, residual, y_bf16, nullptr, M, d_out, hidden, 2,
+                          nullptr, stream);
 }

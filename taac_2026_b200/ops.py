@@ -803,10 +803,54 @@ def ffn_fp8(x: torch.Tensor, weights: Fp8FfnWeights, *, residual: torch.Tensor |
     return y.view(*shape[:-1], weights.w_down.shape[0])
 
 
+
+def ffn_fp8_static_capacity() -> int:
+    """Bytes of the fixed in-library scratch array used by ``ffn_fp8_static`` (per GPU)."""
+    return int(_lib.load().tb200_ffn_fp8_static_scratch_bytes())
+
+
+def ffn_fp8_static(x: torch.Tensor, weights: Fp8FfnWeights, out: torch.Tensor, *,
+                   residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``ffn_fp8`` for callers that must not allocate device memory while the layer runs.
+
+    The caller owns every tensor: ``x`` (bf16 ``[M, d_in]``), the prepared weights, ``out`` (bf16
+    ``[M, d_out]``, written in place and returned) and the optional ``residual``.  The buffers that
+    ``ffn_fp8`` would get from the torch allocator (quantised input, e4m3 hidden activation, scales)
+    sit in a fixed 64 MiB array inside the library instead, so this call touches neither the torch
+    caching allocator nor cudaMalloc — which is what a serving loop with a fully committed memory
+    plan, or an extension hosted by a runtime that owns the allocator, needs.  Consequences:
+    a request that does not fit (about ``M * (d_in + hidden) * 1.04`` bytes) raises ``ValueError``;
+    all calls on one GPU share the array, so calls that may overlap on the device (different
+    streams) must be serialised by the caller; and the first call on each device does a one-time
+    address lookup, so issue one warm-up call before capturing a stream or timing."""
+    _require_backend("ffn_fp8_static", "cuda")
+    _require_cuda_tensors("cuda ffn_fp8_static", x, out, residual, weights.w_up)
+    if x.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.ndim != 2 or out.ndim != 2:
+        raise RuntimeError("cuda ffn_fp8_static needs 2-D bf16 x and out")
+    if not x.is_contiguous() or not out.is_contiguous():
+        raise ValueError("ffn_fp8_static needs contiguous x and out")
+    d_out = weights.w_down.shape[0]
+    if out.shape[0] != x.shape[0] or out.shape[1] != d_out or x.shape[1] != weights.w_up.shape[1]:
+        raise ValueError("ffn_fp8_static: shapes of x, out and the weights do not agree")
+    if residual is not None and (residual.dtype != torch.bfloat16 or tuple(residual.shape) != tuple(out.shape)
+                                 or not residual.is_contiguous()):
+        raise ValueError("ffn_fp8_static residual must be a contiguous bf16 [M, d_out] tensor")
+    with torch.cuda.device(x.device):
+        code = _lib.load().tb200_ffn_fp8_fwd_static(
+            _ptr(x), _ptr(weights.w_up), _ptr(weights.s_up), _ptr(weights.b_up), _ptr(weights.w_down),
+            _ptr(weights.s_down), _ptr(weights.b_down), _ptr(residual), _ptr(out), x.shape[0], x.shape[1],
+            weights.hidden, d_out, int(weights.gated), _stream_ptr(),
+        )
+    _lib.check(code, "cuda ffn_fp8_static")
+    return out
+
+
 __all__ = [
     "AttentionMaskPlan",
     "Fp8FfnWeights",
     "ffn_fp8",
+    "ffn_fp8_static",
+    "ffn_fp8_static_capacity",
     "fp8_gemm",
     "quantize_activation_1x128",
     "quantize_weight_128x128",

@@ -40,7 +40,7 @@ def test_status_text_and_version():
     lib = _lib.load()
     assert lib.tb200_abi_version() >= 1
     assert _lib.strerror(0) == "ok"
-    for code in range(-7, 0):
+    for code in range(-8, 0):
         assert _lib.strerror(code).startswith("tb200:")
     with pytest.raises(ValueError):
         _lib.check(-3, "x")
