@@ -129,11 +129,15 @@ int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t dim, const 
  * key_valid: device uint8[B, Lk] or NULL; when given it replaces the (seq_len, ns_start) rule by
  * "key k is valid iff key_valid[b, k] != 0" for arbitrary padding patterns (several sequence domains
  * with separators, experiments/onetrans/model.py:287-315); padded queries are the invalid positions.
- * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.  kernel: 0 = automatic choice. */
+ * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.
+ * kernel: 0 = automatic, 1 = mma.sync kernel (every supported shape), 2 = tcgen05/TMEM kernel (D = 64, bf16,
+ * no key_valid map; TB200_ERR_UNSUPPORTED otherwise).  total_rows: row count of the packed matrices when
+ * cu_rows is given (bounds the TMA tensor maps), ignored otherwise.  status_word: optional device int32 that
+ * the tcgen05 kernel sets to 1 if one of its bounded waits gave up. */
 int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
                    int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len, const int32_t* cu_rows,
                    const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self, float scale, int dtype,
-                   int32_t kernel, void* stream);
+                   int32_t kernel, int64_t total_rows, int32_t* status_word, void* stream);
 
 /* ---- (d) FP8 e4m3 block-scaled FFN ---------------------------------------------------------
  * The reference has no FP8 path: its FFNs are bf16/fp32 torch modules — the SiLU-gated

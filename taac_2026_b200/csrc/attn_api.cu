@@ -4,12 +4,15 @@
 
 namespace tb200 {
 int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cudaStream_t stream);
+bool attn_tc05_supported(const AttnArgs& a, int head_dim, int dtype);
+int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t* status, cudaStream_t stream);
 }  // namespace tb200
 
 extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
                               int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len,
                               const int32_t* cu_rows, const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self,
-                              float scale, int dtype, int32_t kernel, void* stream) {
+                              float scale, int dtype, int32_t kernel, int64_t total_rows, int32_t* status_word,
+                              void* stream) {
     using namespace tb200;
     if (B < 0 || H < 1 || Lq < 0 || Lk < 0 || D < 1) return TB200_ERR_SHAPE;
     if (B == 0 || Lq == 0) return TB200_OK;
@@ -36,6 +39,13 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     a.causal = causal != 0;
     a.padded_query_self = padded_query_self != 0;
     a.scale_log2 = scale * 1.4426950408889634f;
-    (void)kernel;
-    return attn_mma_forward(a, D, dtype, Lq, static_cast<cudaStream_t>(stream));
+    if (cu_rows != nullptr && total_rows < 0) return TB200_ERR_SHAPE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // kernel: 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel
+    const bool tc_ok = attn_tc05_supported(a, D, dtype) && (cu_rows == nullptr || total_rows > 0);
+    if (kernel == 2 && !tc_ok) return TB200_ERR_UNSUPPORTED;
+    if (kernel < 0 || kernel > 2) return TB200_ERR_UNSUPPORTED;
+    // the tcgen05 kernel works on 128-row halves; short samples are cheaper on the 64-row mma.sync tiles
+    if (kernel == 2 || (kernel == 0 && tc_ok && Lq >= 128)) return attn_tc05_forward(a, Lq, total_rows, status_word, s);
+    return attn_mma_forward(a, D, dtype, Lq, s);
 }

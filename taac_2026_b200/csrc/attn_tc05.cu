@@ -1,0 +1,463 @@
+// Varlen masked attention forward on the 5th-generation tensor cores (sm_100a): head_dim 64, bf16.
+//
+// One CTA serves 256 query rows of one (sample, head) as two independent 128-row halves that share
+// the K/V stream.  Roles (320 threads):
+//   warp 0       TMA producer: Q halves once, then a 2-stage ring of K tiles and one of V tiles
+//                (128 keys x 128 bytes each, 128-byte swizzle, no multicast)
+//   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
+//   warps 2..9   softmax: warps 2-5 own half 0, warps 6-9 half 1; one thread per query row
+// Per KV tile and half:  S = Q K^T   (tcgen05.mma kind::f16, M 128 x N 128 x K 64, fp32 in TMEM)
+//                        softmax thread reads its S row from TMEM (two passes of 4 x 32 columns:
+//                        row max, then exp2), writes P as bf16 into swizzled shared memory
+//                        O_tile = P V   (M 128 x N 64 x K 128, V is the MN-major B operand)
+//                        the thread folds O_tile into its fp32 register accumulator with the
+//                        online-softmax correction while the tensor cores work on the other half.
+// Key tiles without a visible key are skipped; masks come as lengths, never as a matrix.
+// Every mbarrier wait is bounded; a wait that gives up raises the status word and all roles drain
+// through the final barrier, where TMEM is released.
+#include <cudaTypedefs.h>
+
+#include "attn_common.cuh"
+#include "tb200_common.cuh"
+#include "tb200_ptx.cuh"
+
+namespace tb200 {
+void count_launch();
+
+namespace {
+
+constexpr int kD = 64;            // head dim
+constexpr int kHalf = 128;        // query rows per half == TMEM lanes
+constexpr int kBM = 2 * kHalf;    // query rows per CTA
+constexpr int kBN = 128;          // keys per tile
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 128;  // per half
+constexpr uint32_t kTileBytes = kBN * kD * 2;       // 16 KB: one Q half, K tile or V tile
+constexpr uint32_t kPBytes = kHalf * kBN * 2;       // 32 KB: P of one half (two 64-key swizzle atoms)
+constexpr uint32_t kTmemCols = 512;
+// TMEM columns: S of half h at h * 128, O_tile of half h at 256 + h * 64
+constexpr uint32_t kTmemS = 0;
+constexpr uint32_t kTmemO = 256;
+
+struct Tc05Args {
+    AttnArgs a;
+    int32_t* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Per-CTA description of which key tiles each half works on; every role derives the same sequence.
+struct Plan {
+    int lq, lk, valid_len, ns_start, m0;
+    bool causal, self_rows, packed;
+    int64_t row_base;     // packed: first row of the sample
+    int n_tiles;          // key tiles that any half may need
+    int kv_end[2];        // keys [0, kv_end[h]) can be visible to half h
+    bool half_on[2];      // half has rows to compute
+    __device__ __forceinline__ bool live(int j) const {
+        const int n0 = j * kBN;
+        return n0 < valid_len || n0 + kBN > ns_start;
+    }
+    __device__ __forceinline__ bool active(int j, int h) const { return half_on[h] && live(j) && j * kBN < kv_end[h]; }
+};
+
+__device__ __forceinline__ Plan make_plan(const AttnArgs& a, int b, int m0) {
+    Plan p;
+    p.packed = a.cu_rows != nullptr;
+    p.lq = a.Lq;
+    p.lk = a.Lk;
+    p.row_base = 0;
+    if (p.packed) {
+        p.row_base = a.cu_rows[b];
+        p.lq = p.lk = a.cu_rows[b + 1] - static_cast<int32_t>(p.row_base);
+    }
+    p.m0 = m0;
+    p.valid_len = (a.seq_len != nullptr && !p.packed) ? min(max(a.seq_len[b], 0), p.lk) : p.lk;
+    p.ns_start = p.packed ? p.lk : min(a.ns_start, p.lk);
+    p.causal = a.causal != 0;
+    p.self_rows = a.padded_query_self != 0;
+    int n_max = 0;
+    for (int h = 0; h < 2; ++h) {
+        const int r0 = m0 + h * kHalf;
+        const int r1 = min(r0 + kHalf, p.lq);
+        // a half wholly inside the padded query range only copies value rows
+        const bool all_padded = p.self_rows && r0 >= p.valid_len && r1 <= p.ns_start;
+        p.half_on[h] = r0 < p.lq && !all_padded;
+        p.kv_end[h] = p.causal ? min(p.lk, r1) : p.lk;
+        if (p.half_on[h]) n_max = max(n_max, (p.kv_end[h] + kBN - 1) / kBN);
+    }
+    p.n_tiles = n_max;
+    return p;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const Tc05Args args) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t q_full;
+    __shared__ uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int s_abort;
+
+    const AttnArgs& a = args.a;
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;                              // 2 halves x 16 KB
+    uint8_t* sK = sQ + 2 * kTileBytes;               // 2 stages x 16 KB
+    uint8_t* sV = sK + 2 * kTileBytes;               // 2 stages x 16 KB
+    uint8_t* sP = sV + 2 * kTileBytes;               // 2 halves x 32 KB
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.z;
+    const int h_idx = blockIdx.y;
+    const int m0 = blockIdx.x * kBM;
+    const Plan plan = make_plan(a, b, m0);
+    if (m0 >= plan.lq) return;  // uniform for the CTA: nothing allocated yet
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_free[i], kSoftmaxThreads);
+            mbar_init(&p_full[i], kSoftmaxThreads);
+            mbar_init(&o_full[i], 1);
+            mbar_init(&o_free[i], kSoftmaxThreads);
+        }
+        s_abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    // TMA coordinates: (d, row, head, batch); packed batches address rows of the whole matrix
+    const int row0 = plan.packed ? static_cast<int>(plan.row_base) : 0;
+    const int bz = plan.packed ? 0 : b;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_k);
+            tma_prefetch_desc(&tmap_v);
+            const uint32_t q_bytes = (plan.half_on[0] ? kTileBytes : 0) + (plan.half_on[1] ? kTileBytes : 0);
+            if (q_bytes > 0) {
+                mbar_expect_tx(&q_full, q_bytes);
+                for (int h = 0; h < 2; ++h)
+                    if (plan.half_on[h])
+                        tma_load_4d(sQ + h * kTileBytes, &tmap_q, 0, row0 + m0 + h * kHalf, h_idx, bz, &q_full);
+            }
+            uint32_t kc = 0;
+            bool ok = true;
+            for (int j = 0; j < plan.n_tiles && ok; ++j) {
+                if (!plan.active(j, 0) && !plan.active(j, 1)) continue;
+                const uint32_t s = kc & 1;
+                const uint32_t ph = (kc >> 1) & 1;
+                if (!mbar_wait(&k_empty[s], ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&k_full[s], kTileBytes);
+                tma_load_4d(sK + s * kTileBytes, &tmap_k, 0, row0 + j * kBN, h_idx, bz, &k_full[s]);
+                if (!mbar_wait(&v_empty[s], ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&v_full[s], kTileBytes);
+                tma_load_4d(sV + s * kTileBytes, &tmap_v, 0, row0 + j * kBN, h_idx, bz, &v_full[s]);
+                ++kc;
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (args.status != nullptr) atomicExch(args.status, 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(1, 1, 0, 0, kHalf, kBN);  // bf16 x bf16, Q and K both K-major
+            const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, kHalf, kD);   // P K-major, V MN-major (head dim contiguous)
+            uint32_t kc = 0;
+            uint32_t hc[2] = {0, 0};  // tiles issued so far per half
+            bool ok = plan.n_tiles == 0 || mbar_wait(&q_full, 0);
+            for (int j = 0; j < plan.n_tiles && ok; ++j) {
+                const bool act0 = plan.active(j, 0), act1 = plan.active(j, 1);
+                if (!act0 && !act1) continue;
+                const uint32_t s = kc & 1;
+                const uint32_t ph = (kc >> 1) & 1;
+                if (!mbar_wait(&k_full[s], ph)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    if (!(h == 0 ? act0 : act1)) continue;
+                    if (!mbar_wait(&s_free[h], (hc[h] & 1) ^ 1)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t q_addr = smem_u32(sQ + h * kTileBytes);
+#pragma unroll
+                    for (int k = 0; k < kD / 16; ++k) {
+                        mma_f16_ss(tmem_base + kTmemS + h * kBN, umma_desc_sw128(q_addr + k * 32, 1024, 16),
+                                   umma_desc_sw128(k_addr + k * 32, 1024, 16), idesc_s, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&s_full[h]);
+                }
+                if (!ok) break;
+                tc_commit(&k_empty[s]);  // K tile free once the S products above have read it
+                if (!mbar_wait(&v_full[s], ph)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t v_addr = smem_u32(sV + s * kTileBytes);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    if (!(h == 0 ? act0 : act1)) continue;
+                    if (!mbar_wait(&p_full[h], hc[h] & 1) || !mbar_wait(&o_free[h], (hc[h] & 1) ^ 1)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t p_addr = smem_u32(sP + h * kPBytes);
+#pragma unroll
+                    for (int k = 0; k < kBN / 16; ++k) {
+                        // A: P, K-major, two 64-key atoms of 16 KB; B: V, MN-major, 16 key rows = 2 KB per step
+                        const uint32_t pa = p_addr + (k >> 2) * (kHalf * 128) + (k & 3) * 32;
+                        mma_f16_ss(tmem_base + kTmemO + h * kD, umma_desc_sw128(pa, 1024, 16),
+                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(&o_full[h]);
+                    ++hc[h];
+                }
+                if (!ok) break;
+                tc_commit(&v_empty[s]);
+                ++kc;
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (args.status != nullptr) atomicExch(args.status, 1);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + output
+        const int h = (warp - 2) >> 2;                 // half served by this warp
+        const int quarter = warp & 3;                  // TMEM lanes [32 * quarter, +32)
+        const int r_local = quarter * 32 + lane;       // row inside the half
+        const int row = m0 + h * kHalf + r_local;      // query index inside the sample
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t t_s = tmem_base + kTmemS + h * kBN + lane_addr;
+        const uint32_t t_o = tmem_base + kTmemO + h * kD + lane_addr;
+        uint8_t* p_row = sP + h * kPBytes + r_local * 128;
+        const int sw = r_local & 7;
+
+        float o_acc[kD];
+#pragma unroll
+        for (int i = 0; i < kD; ++i) o_acc[i] = 0.f;
+        float m_run = -INFINITY;
+        float l_run = 0.f;
+        uint32_t hc = 0;
+        bool ok = true;
+        bool pending = false;  // an O_tile of this half is in flight
+
+        for (int j = 0; j < plan.n_tiles && ok; ++j) {
+            if (!plan.active(j, h)) continue;
+            const int n0 = j * kBN;
+            if (!mbar_wait(&s_full[h], hc & 1)) { ok = false; break; }
+            tc_fence_after_sync();
+            const bool full = (n0 + kBN <= plan.valid_len || n0 >= plan.ns_start) && n0 + kBN <= plan.lk &&
+                              (!plan.causal || n0 + kBN - 1 <= m0 + h * kHalf);
+            // pass 1: row max of the visible scores
+            float mx = m_run;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_x32(t_s + c * 32, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float sv = __uint_as_float(r[i]);
+                    if (!full && !attn_visible(row, n0 + c * 32 + i, plan.valid_len, plan.ns_start, plan.lk, plan.causal))
+                        sv = -INFINITY;
+                    mx = fmaxf(mx, sv);
+                }
+            }
+            const float m_use = mx == -INFINITY ? 0.f : mx;
+            const float corr = ex2((m_run - m_use) * a.scale_log2);  // 0 on the first tile (m_run = -inf)
+            const float ms = m_use * a.scale_log2;
+            m_run = mx;
+
+            // fold the previous tile's P V into the accumulator before P is overwritten
+            if (pending) {
+                if (!mbar_wait(&o_full[h], (hc - 1) & 1)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_x32(t_o + c * 32, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&o_free[h]);
+            }
+#pragma unroll
+            for (int i = 0; i < kD; ++i) o_acc[i] *= corr;
+
+            // pass 2: probabilities -> bf16 P in shared memory (K-major, 128-byte swizzle)
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_x32(t_s + c * 32, r);
+                tc_wait_ld();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float s0 = __uint_as_float(r[2 * i]);
+                    float s1 = __uint_as_float(r[2 * i + 1]);
+                    if (!full) {
+                        const int col = n0 + c * 32 + 2 * i;
+                        if (!attn_visible(row, col, plan.valid_len, plan.ns_start, plan.lk, plan.causal)) s0 = -INFINITY;
+                        if (!attn_visible(row, col + 1, plan.valid_len, plan.ns_start, plan.lk, plan.causal)) s1 = -INFINITY;
+                    }
+                    const float p0 = ex2(fmaf(s0, a.scale_log2, -ms));
+                    const float p1 = ex2(fmaf(s1, a.scale_log2, -ms));
+                    sum += p0 + p1;
+                    __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&pb);
+                }
+                // 32 keys = 4 chunks of 16 bytes; key chunk index inside the 64-key atom: (c & 1) * 4 + q
+                uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int chunk = ((c & 1) * 4 + q) ^ sw;
+                    *reinterpret_cast<uint4*>(atom + chunk * 16) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            l_run = l_run * corr + sum;
+            tc_fence_before_sync();
+            mbar_arrive(&s_free[h]);     // S of this half may be overwritten
+            fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
+            mbar_arrive(&p_full[h]);
+            pending = true;
+            ++hc;
+        }
+
+        if (ok && pending) {
+            if (!mbar_wait(&o_full[h], (hc - 1) & 1)) {
+                ok = false;
+            } else {
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_x32(t_o + c * 32, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&o_free[h]);
+            }
+        }
+        if (!ok) {
+            s_abort = 1;
+            if (args.status != nullptr) atomicExch(args.status, 1);
+        } else if (row < plan.lq) {
+            const int64_t o_off = (plan.packed ? plan.row_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) +
+                                  static_cast<int64_t>(h_idx) * a.o_sh + static_cast<int64_t>(row) * a.o_sl;
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.o) + o_off);
+            const bool padded_q = plan.self_rows && row >= plan.valid_len && row < plan.ns_start;
+            if (padded_q) {
+                const int64_t v_off = (plan.packed ? plan.row_base * a.v_sl : static_cast<int64_t>(b) * a.v_sb) +
+                                      static_cast<int64_t>(h_idx) * a.v_sh + static_cast<int64_t>(row) * a.v_sl;
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.v) + v_off);
+#pragma unroll
+                for (int c = 0; c < kD / 8; ++c) dst[c] = src[c];
+            } else {
+                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+#pragma unroll
+                for (int c = 0; c < kD / 8; ++c) {
+                    float v8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v8[e] = o_acc[8 * c + e] * inv;
+                    dst[c] = Vec16<__nv_bfloat16>::pack(v8);
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return fn;
+}
+
+// bf16 tensor addressed as (d, row, head, batch) with element strides (1, sl, sh, sb); tiles of 128 rows x 64
+bool make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t heads, int64_t batch, int64_t sl, int64_t sh,
+               int64_t sb) {
+    PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads),
+                                static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(sl) * 2, static_cast<cuuint64_t>(sh) * 2,
+                                   static_cast<cuuint64_t>(sb > 0 ? sb : sl * rows) * 2};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(kD), static_cast<cuuint32_t>(kBN), 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool attn_tc05_supported(const AttnArgs& a, int head_dim, int dtype) {
+    return head_dim == kD && dtype == TB200_BF16 && a.key_valid == nullptr;
+}
+
+// total_rows: rows of the packed matrices (cu_rows given), ignored otherwise
+int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t* status, cudaStream_t stream) {
+    const bool packed = a.cu_rows != nullptr;
+    CUtensorMap tq, tk, tv;
+    const int64_t q_rows = packed ? total_rows : a.Lq;
+    const int64_t k_rows = packed ? total_rows : a.Lk;
+    const int64_t nb = packed ? 1 : a.B;
+    if (!make_tmap(&tq, a.q, q_rows, a.H, nb, a.q_sl, a.q_sh, packed ? 0 : a.q_sb) ||
+        !make_tmap(&tk, a.k, k_rows, a.H, nb, a.k_sl, a.k_sh, packed ? 0 : a.k_sb) ||
+        !make_tmap(&tv, a.v, k_rows, a.H, nb, a.v_sl, a.v_sh, packed ? 0 : a.v_sb))
+        return TB200_ERR_DRIVER;
+    const DeviceInfo& dev = device_info();
+    const size_t smem = 6 * kTileBytes + 2 * kPBytes + 1024;
+    static bool attr_set[64] = {};
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(attn_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        attr_set[dev.index] = true;
+    }
+    Tc05Args args{a, status};
+    dim3 grid((max_lq + kBM - 1) / kBM, a.H, a.B);
+    attn_tc05_kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, args);
+    count_launch();
+    return launch_status();
+}
+
+}  // namespace tb200

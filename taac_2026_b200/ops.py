@@ -562,8 +562,13 @@ def varlen_attention(
     max_rows: int | None = None,
     key_valid: torch.Tensor | None = None,
     kernel: int = 0,
+    check: bool = False,
 ) -> torch.Tensor:
     """Masked attention forward with the mask given by lengths (never materialised).
+
+    ``kernel``: 0 picks automatically (the tcgen05/TMEM kernel for head_dim 64 bf16 with at least 128
+    rows, the mma.sync kernel otherwise), 1 / 2 force one of them.  ``check=True`` reads the tcgen05
+    kernel's status word back (one sync) and raises if a bounded wait inside it gave up.
 
     ``key_valid`` (bool / uint8 [B, Lk]) replaces ``seq_len`` / ``ns_start`` for padding patterns that
     are not `valid prefix | padding | valid suffix`.
@@ -617,15 +622,18 @@ def varlen_attention(
     if scale is None:
         scale = 1.0 / math.sqrt(dim)
     stride_arr = (ctypes.c_int64 * 12)(*strides)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
     with torch.cuda.device(q.device), _timed("attention", seq_len=lens, cu_rows=cu, key_valid=kv, batch=batch, heads=heads,
                                              lq=lq, lk=lk, dim=dim, ns_start=lk if ns_start is None else int(ns_start),
                                              causal=bool(causal), self_rows=bool(padded_query_self)):
         code = _lib.load().tb200_attn_fwd(
             _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu), _ptr(kv),
             lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)), float(scale),
-            _DTYPE_CODES[q.dtype], int(kernel), _stream_ptr(),
+            _DTYPE_CODES[q.dtype], int(kernel), int(q.shape[0]) if cu is not None else 0, _ptr(status), _stream_ptr(),
         )
     _lib.check(code, "cuda varlen_attention")
+    if status is not None and int(status.item()) != 0:
+        raise RuntimeError("cuda varlen_attention: a bounded wait inside the kernel gave up; the output is incomplete")
     return out
 
 

@@ -17,7 +17,14 @@ from oracle import reference_ops as R
 from taac_2026_b200 import ops
 
 pytestmark = pytest.mark.gpu
-KERNELS = [0]
+KERNELS = [1, 2]  # 1 = mma.sync kernel (all shapes), 2 = tcgen05/TMEM kernel (head_dim 64, bf16)
+
+
+def _kw(kernel, D=64, dtype=torch.bfloat16):
+    if kernel == 2 and (D != 64 or dtype != torch.bfloat16):
+        pytest.skip("the tcgen05 kernel serves head_dim 64 bf16")
+    return {"kernel": kernel, "check": kernel == 2}
+
 
 
 @pytest.fixture(autouse=True)
@@ -56,7 +63,7 @@ def test_key_padding_noncausal(kernel, dtype, D, L):
     B, H = 3, 2
     q, k, v = _qkv(B, H, L, D, dtype, seed=L * 7 + D)
     lens = torch.tensor([L, max(1, L // 3), max(1, L - 1)])
-    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), kernel=kernel)
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), **_kw(kernel, D, dtype))
     _check(got, q, k, v, R.structured_attention_mask(lens, L, L, False, False))
 
 
@@ -71,7 +78,7 @@ def test_causal_valid_with_ns_suffix(kernel, D, L, ns):
     q, k, v = _qkv(B, H, L, D, torch.bfloat16, seed=L + ns)
     lens = torch.tensor([S, 0, min(S, 1), S // 2, max(S - 1, 0)])
     got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), ns_start=S, causal=True,
-                               padded_query_self=True, kernel=kernel)
+                               padded_query_self=True, **_kw(kernel, D))
     mask = R.structured_attention_mask(lens, L, S, True, True)
     pos = torch.arange(L)[None]
     self_rows = (pos >= lens[:, None]) & (pos < S)
@@ -82,11 +89,11 @@ def test_causal_valid_with_ns_suffix(kernel, D, L, ns):
 def test_cross_lengths_and_plain_causal(kernel):
     q, k, v = _qkv(2, 4, 70, 64, torch.bfloat16, seed=3, lk=150)
     lens = torch.tensor([150, 61])
-    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), kernel=kernel)
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), **_kw(kernel))
     mask = (torch.arange(150)[None, None, :] < lens[:, None, None]).expand(2, 70, 150)
     _check(got, q, k, v, mask)
     q, k, v = _qkv(2, 4, 190, 64, torch.bfloat16, seed=4)
-    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), causal=True, kernel=kernel)
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), causal=True, **_kw(kernel))
     _check(got, q, k, v, R.structured_attention_mask(torch.tensor([190, 190]), 190, 190, True, False))
 
 
@@ -94,7 +101,7 @@ def test_cross_lengths_and_plain_causal(kernel):
 def test_rows_without_visible_key_are_zero(kernel):
     q, k, v = _qkv(2, 2, 50, 64, torch.bfloat16, seed=5)
     lens = torch.tensor([0, 20])
-    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), kernel=kernel).cpu()
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), **_kw(kernel)).cpu()
     assert torch.equal(got[0], torch.zeros_like(got[0]))
     _check(got[1:], q[1:], k[1:], v[1:], R.structured_attention_mask(lens[1:], 50, 50, False, False))
 
@@ -108,7 +115,7 @@ def test_blhd_views_of_fused_qkv_and_packed_batch(kernel):
     lens = torch.tensor([150, 3, 77, 128])
     dev = qkv.cuda()
     got = ops.varlen_attention(dev[:, :, 0], dev[:, :, 1], dev[:, :, 2], seq_len=lens.cuda(), causal=True,
-                               padded_query_self=True, layout="blhd", kernel=kernel)
+                               padded_query_self=True, layout="blhd", **_kw(kernel))
     assert got.shape == (B, L, H, D)
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
     mask = R.structured_attention_mask(lens, L, L, True, True)
@@ -119,15 +126,17 @@ def test_blhd_views_of_fused_qkv_and_packed_batch(kernel):
     cu[1:] = torch.cumsum(lens, 0)
     packed = torch.cat([qkv[b, : lens[b]] for b in range(B)], dim=0).cuda()  # [rows, 3, H, D]
     got_p = ops.varlen_attention(packed[:, 0], packed[:, 1], packed[:, 2], causal=True, cu_rows=cu.cuda(),
-                                 max_rows=int(lens.max()), kernel=kernel).cpu()
+                                 max_rows=int(lens.max()), **_kw(kernel)).cpu()
     for b in range(B):
         lo, hi = int(cu[b]), int(cu[b + 1])
         ref = got[b, : hi - lo].cpu()
-        assert (got_p[lo:hi].float() - ref.float()).abs().max().item() <= 1e-6
+        assert (got_p[lo:hi].float() - ref.float()).abs().max().item() <= (1e-6 if kernel == 1 else 4e-3)
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_reference_signature_and_golden(kernel, ops_golden):
+    if kernel == 2:
+        pytest.skip("the reference's golden cases have head_dim 16 (padded to 32): mma.sync kernel only")
     """`flash_attention(q, k, v, backend="cuda", attn_mask=...)` on the reference's golden cases; fp32
     callers are served in bf16 and get fp32 back."""
     q, k, v = (torch.from_numpy(ops_golden[f"attn_{n}"].copy()) for n in "qkv")
@@ -162,7 +171,7 @@ def test_full_size_properties(kernel, causal):
     k = (torch.randn(B, H, L, D, generator=g) / 8).bfloat16()
     v = (torch.randn(B, H, L, D, generator=g) / 8).bfloat16()
     lens = torch.randint(32, 1025, (B,), generator=g)
-    kw = dict(seq_len=lens.cuda(), causal=causal, padded_query_self=causal, kernel=kernel)
+    kw = dict(seq_len=lens.cuda(), causal=causal, padded_query_self=causal, **_kw(kernel))
     qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
     got = ops.varlen_attention(qd, kd, vd, **kw)
     ones = ops.varlen_attention(qd, kd, torch.ones_like(vd), **kw).float()
