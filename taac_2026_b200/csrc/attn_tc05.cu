@@ -17,6 +17,8 @@
 // through the final barrier, where TMEM is released.
 #include <cudaTypedefs.h>
 
+#include <type_traits>
+
 #include "attn_common.cuh"
 #include "tb200_common.cuh"
 #include "tb200_ptx.cuh"
@@ -249,45 +251,57 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint8_t* p_row = sP + h * kPBytes + r_local * 128;
         const int sw = r_local & 7;
 
-        float o_acc[kD];
+        float2 o_acc[kD / 2];
 #pragma unroll
-        for (int i = 0; i < kD; ++i) o_acc[i] = 0.f;
+        for (int i = 0; i < kD / 2; ++i) o_acc[i] = make_float2(0.f, 0.f);
         float m_run = -INFINITY;
         float l_run = 0.f;
         uint32_t hc = 0;
         bool ok = true;
         bool pending = false;  // an O_tile of this half is in flight
 
-        for (int j = 0; j < plan.n_tiles && ok; ++j) {
-            if (!plan.active(j, h)) continue;
-            const int n0 = j * kBN;
-            if (!mbar_wait(&s_full[h], hc & 1)) { ok = false; break; }
+        // Visibility of key column c for this thread's row, as two half-open ranges:
+        //   [0, lim_lo) and [ns_lo, lim_hi)  with lim_hi = min(lk, causal ? row + 1 : lk)
+        const int lim_hi = plan.causal ? min(plan.lk, row + 1) : plan.lk;
+        const int lim_lo = min(plan.valid_len, lim_hi);
+        const int ns_lo = plan.ns_start;
+        const float sl2 = a.scale_log2;
+
+        // One KV tile of this half.  FULL tiles (every key visible to every row) carry no mask code.
+        auto tile = [&](const int n0, auto full_tag) -> bool {
+            constexpr bool FULL = decltype(full_tag)::value;
+            if (!mbar_wait(&s_full[h], hc & 1)) return false;
             tc_fence_after_sync();
-            const bool full = (n0 + kBN <= plan.valid_len || n0 >= plan.ns_start) && n0 + kBN <= plan.lk &&
-                              (!plan.causal || n0 + kBN - 1 <= m0 + h * kHalf);
             // pass 1: row max of the visible scores
-            float mx = m_run;
+            float mx0 = m_run, mx1 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(t_s + c * 32, r);
+            for (int c = 0; c < 8; ++c) {
+                uint32_t r[16];
+                tmem_ld_x16(t_s + c * 16, r);
                 tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float sv = __uint_as_float(r[i]);
-                    if (!full && !attn_visible(row, n0 + c * 32 + i, plan.valid_len, plan.ns_start, plan.lk, plan.causal))
-                        sv = -INFINITY;
-                    mx = fmaxf(mx, sv);
+                for (int i = 0; i < 16; i += 2) {
+                    float s0 = __uint_as_float(r[i]);
+                    float s1 = __uint_as_float(r[i + 1]);
+                    if (!FULL) {
+                        const int col = n0 + c * 16 + i;
+                        if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) s0 = -INFINITY;
+                        if (!(col + 1 < lim_lo || (col + 1 >= ns_lo && col + 1 < lim_hi))) s1 = -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, s0);
+                    mx1 = fmaxf(mx1, s1);
                 }
             }
+            const float mx = fmaxf(mx0, mx1);
             const float m_use = mx == -INFINITY ? 0.f : mx;
-            const float corr = ex2((m_run - m_use) * a.scale_log2);  // 0 on the first tile (m_run = -inf)
-            const float ms = m_use * a.scale_log2;
+            const float corr = ex2((m_run - m_use) * sl2);  // 0 on the first tile (m_run = -inf)
+            const float ms = m_use * sl2;
             m_run = mx;
 
             // fold the previous tile's P V into the accumulator before P is overwritten
+            const float2 corr2 = make_float2(corr, corr);
             if (pending) {
-                if (!mbar_wait(&o_full[h], (hc - 1) & 1)) { ok = false; break; }
+                if (!mbar_wait(&o_full[h], (hc - 1) & 1)) return false;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -295,53 +309,64 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     tmem_ld_x32(t_o + c * 32, r);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 pv = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                        o_acc[c * 16 + i] = __fmul2_rn(__fadd2_rn(o_acc[c * 16 + i], pv), corr2);
+                    }
                 }
                 tc_fence_before_sync();
                 mbar_arrive(&o_free[h]);
             }
-#pragma unroll
-            for (int i = 0; i < kD; ++i) o_acc[i] *= corr;
 
             // pass 2: probabilities -> bf16 P in shared memory (K-major, 128-byte swizzle)
-            float sum = 0.f;
+            float2 sum2 = make_float2(0.f, 0.f);
+            const float2 sl22 = make_float2(sl2, sl2);
+            const float2 nms2 = make_float2(-ms, -ms);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_x32(t_s + c * 32, r);
+            for (int c = 0; c < 8; ++c) {
+                uint32_t r[16];
+                tmem_ld_x16(t_s + c * 16, r);
                 tc_wait_ld();
-                uint32_t packed[16];
+                uint32_t packed[8];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float s0 = __uint_as_float(r[2 * i]);
-                    float s1 = __uint_as_float(r[2 * i + 1]);
-                    if (!full) {
-                        const int col = n0 + c * 32 + 2 * i;
-                        if (!attn_visible(row, col, plan.valid_len, plan.ns_start, plan.lk, plan.causal)) s0 = -INFINITY;
-                        if (!attn_visible(row, col + 1, plan.valid_len, plan.ns_start, plan.lk, plan.causal)) s1 = -INFINITY;
+                for (int i = 0; i < 8; ++i) {
+                    float2 sv = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    if (!FULL) {
+                        const int col = n0 + c * 16 + 2 * i;
+                        if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) sv.x = -INFINITY;
+                        if (!(col + 1 < lim_lo || (col + 1 >= ns_lo && col + 1 < lim_hi))) sv.y = -INFINITY;
                     }
-                    const float p0 = ex2(fmaf(s0, a.scale_log2, -ms));
-                    const float p1 = ex2(fmaf(s1, a.scale_log2, -ms));
-                    sum += p0 + p1;
-                    __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                    const float2 e = __ffma2_rn(sv, sl22, nms2);
+                    const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                    sum2 = __fadd2_rn(sum2, p);
+                    __nv_bfloat162 pb = __float22bfloat162_rn(p);
                     packed[i] = *reinterpret_cast<uint32_t*>(&pb);
                 }
-                // 32 keys = 4 chunks of 16 bytes; key chunk index inside the 64-key atom: (c & 1) * 4 + q
-                uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
+                // 16 keys = 2 chunks of 16 bytes; key chunk index inside the 64-key atom: (c & 3) * 2 + q
+                uint8_t* atom = p_row + (c >> 2) * (kHalf * 128);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int chunk = ((c & 1) * 4 + q) ^ sw;
+                for (int q = 0; q < 2; ++q) {
+                    const int chunk = ((c & 3) * 2 + q) ^ sw;
                     *reinterpret_cast<uint4*>(atom + chunk * 16) =
                         make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
             }
-            l_run = l_run * corr + sum;
+            l_run = l_run * corr + (sum2.x + sum2.y);
             tc_fence_before_sync();
             mbar_arrive(&s_free[h]);     // S of this half may be overwritten
             fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
             mbar_arrive(&p_full[h]);
             pending = true;
             ++hc;
+            return true;
+        };
+
+        for (int j = 0; j < plan.n_tiles && ok; ++j) {
+            if (!plan.active(j, h)) continue;
+            const int n0 = j * kBN;
+            const bool full = (n0 + kBN <= plan.valid_len || n0 >= plan.ns_start) && n0 + kBN <= plan.lk &&
+                              (!plan.causal || n0 + kBN - 1 <= m0 + h * kHalf);
+            ok = full ? tile(n0, std::true_type{}) : tile(n0, std::false_type{});
         }
 
         if (ok && pending) {
@@ -355,7 +380,8 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     tmem_ld_x32(t_o + c * 32, r);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+                    for (int i = 0; i < 16; ++i)
+                        o_acc[c * 16 + i] = __fadd2_rn(o_acc[c * 16 + i], make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
                 }
                 tc_fence_before_sync();
                 mbar_arrive(&o_free[h]);
@@ -376,13 +402,14 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
                 for (int c = 0; c < kD / 8; ++c) dst[c] = src[c];
             } else {
-                const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+                const float inv1 = l_run > 0.f ? 1.0f / l_run : 0.f;
+                const float2 inv = make_float2(inv1, inv1);
 #pragma unroll
                 for (int c = 0; c < kD / 8; ++c) {
-                    float v8[8];
+                    float2 v4[4];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v8[e] = o_acc[8 * c + e] * inv;
-                    dst[c] = Vec16<__nv_bfloat16>::pack(v8);
+                    for (int e = 0; e < 4; ++e) v4[e] = __fmul2_rn(o_acc[4 * c + e], inv);
+                    dst[c] = Vec16<__nv_bfloat16>::pack2(v4);
                 }
             }
         }

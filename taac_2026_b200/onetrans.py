@@ -579,12 +579,17 @@ class OneTransInference:
 
         cu = [offsets(r) for r in rows]
 
-        # ---- sequence tokenizer on the valid events only (modeling/tokenizers.py:156-190)
-        n_seq = totals[0] - batch * ns
+        # ---- sequence tokenizer on the valid events only (modeling/tokenizers.py:156-190).  It works
+        # directly in the packed layout of layer 0: the rows reserved for the NS tokens carry id 0 (the
+        # zero padding row) through the projection and are overwritten afterwards, which costs ns / (n + ns)
+        # extra rows but saves a full scatter of the token matrix.
+        total0 = totals[0]
+        n_seq = total0 - batch * ns
         sample_of = torch.repeat_interleave(arange_b, n0, output_size=n_seq)
         seq_cu = offsets(n0)
         j_idx = torch.arange(n_seq, device=dev) - seq_cu[sample_of]              # position after the tail crop
         src_pos = start[sample_of] + j_idx                                        # position in the padded input
+        dest = cu[0][sample_of] + j_idx                                           # row in the packed matrix
         prefix = f"sequence_tokenizers.{domain}"
         entries = self.seq_tables[domain]
         n_feat = values.shape[1]
@@ -592,26 +597,27 @@ class OneTransInference:
         live = [f for f in range(n_feat) if f < len(entries) and entries[f][1] is not None]
         if live:
             token_input = (torch.empty if len(live) == n_feat else torch.zeros)(
-                (n_seq, n_feat * emb), dtype=self.dtype, device=dev)
+                (total0, n_feat * emb), dtype=self.dtype, device=dev)
             for f in live:
                 kind, table = entries[f]
                 ids = values[sample_of, f, src_pos]
                 if kind == "compressed":
                     ids = hash_compress_ids(ids.clamp_min(0), table.shape[0] - 1)
-                ops.gather_rows(table, ids, out=token_input, col0=f * emb)
+                ids_full = torch.zeros(total0, dtype=ids.dtype, device=dev).index_copy_(0, dest, ids)
+                ops.gather_rows(table, ids_full, out=token_input, col0=f * emb)
         else:
-            token_input = torch.zeros(n_seq, max(1, n_feat * emb), dtype=self.dtype, device=dev)
-        seq_tok = self._layer_norm(F.silu(self._linear(token_input, prefix + ".project.0")), prefix + ".project.2")
+            token_input = torch.zeros(total0, max(1, n_feat * emb), dtype=self.dtype, device=dev)
+        tokens = self._layer_norm(F.silu(self._linear(token_input, prefix + ".project.0")), prefix + ".project.2")
+        pos_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, j_idx)
         if prefix + ".time_embedding.weight" in self.w:
             buckets = sequence_time_buckets(ts, request_ts, self._edges)[sample_of, src_pos]
-            seq_tok = seq_tok + ops.gather_rows(self._p(prefix + ".time_embedding.weight"), buckets)
-        seq_tok = seq_tok + self._positions(width)[j_idx]
+            buckets_full = torch.zeros(total0, dtype=buckets.dtype, device=dev).index_copy_(0, dest, buckets)
+            tokens = tokens + ops.gather_rows(self._p(prefix + ".time_embedding.weight"), buckets_full)
+        tokens = tokens + ops.gather_rows(self._positions(width), pos_full)
 
-        # ---- interleave with the NS tokens: [seq rows of b | ns rows of b]
+        # ---- the NS tokens take the rows left for them: [seq rows of b | ns rows of b]
         ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
         ns_off = torch.arange(ns, device=dev)[None, :]
-        tokens = torch.empty(totals[0], self.d, dtype=self.dtype, device=dev)
-        tokens.index_copy_(0, cu[0][sample_of] + j_idx, seq_tok)
         ns_rows = (cu[0][:-1] + counts[0])[:, None] + ns_off                       # [B, ns]
         tokens.index_copy_(0, ns_rows.reshape(-1), ns_tokens.reshape(batch * ns, self.d))
 
@@ -621,9 +627,9 @@ class OneTransInference:
             cu32 = cu[layer].to(torch.int32)
             x = ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
             qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
-            flat_ns = ns_rows.reshape(-1)
-            x_ns = x[flat_ns].view(batch, ns, d).transpose(0, 1)                   # [ns, B, d]
-            qkv.index_copy_(0, flat_ns, torch.baddbmm(blk["ns_qkv_b"], x_ns, blk["ns_qkv_w"]).transpose(0, 1).reshape(batch * ns, 3 * d))
+            flat_ns = ns_rows.t().reshape(-1)                                      # token-major: [ns, B] row ids
+            x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)                  # [ns, B, d], contiguous
+            qkv.index_copy_(0, flat_ns, torch.baddbmm(blk["ns_qkv_b"], x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d))
             q, k, v = (qkv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(3))
             if q.dtype == torch.float32:
                 q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
@@ -632,10 +638,10 @@ class OneTransInference:
             tokens = tokens + self._linear(attn.view(-1, d).to(self.dtype), p + ".attention.out")
             x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
             out = self._shared_ffn_residual(blk, x, tokens)
-            x_ns = x[flat_ns].view(batch, ns, d).transpose(0, 1)
+            x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)
             h = F.silu(torch.baddbmm(blk["ns_b1"], x_ns, blk["ns_w1"]))
-            y_ns = torch.baddbmm(blk["ns_b2"], h, blk["ns_w2"]).transpose(0, 1).reshape(batch * ns, d)
-            out.index_copy_(0, flat_ns, tokens[flat_ns] + y_ns)
+            y_ns = torch.baddbmm(blk["ns_b2"], h, blk["ns_w2"]).view(ns * batch, d)
+            out.index_copy_(0, flat_ns, ops.gather_rows(tokens, flat_ns) + y_ns)
             tokens = out
             if widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
                 new_rows = rows[layer + 1]
