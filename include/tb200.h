@@ -164,6 +164,21 @@ int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const void* b_fp8, 
                    const float* bias, const void* residual, void* out, float* out_scales, int64_t M, int32_t N,
                    int32_t K, int32_t mode, int32_t* status_word, void* stream);
 
+/* ---- integer sequence preprocessing ---------------------------------------------------------
+ * Per sample of one sequence domain: which events survive duplicate removal, and the six sequence
+ * statistics.  Replaces `deduplicate_sequence_events`
+ * (src/taac2026/infrastructure/modeling/sequence.py:141-198) and `compute_sequence_stats`
+ * (src/taac2026/infrastructure/modeling/time_features.py:49-105), bit for bit.
+ * values [batch, n_feat, max_len], lengths [batch], timestamps [batch, max_len], request_ts [batch], all int64.
+ * out_len [batch] int64: length after duplicate removal (the input length for untouched samples);
+ * out_src [batch, max_len] int32: source position of every output slot (identity for untouched samples,
+ *   -1 for the zero-filled tail of changed samples) — new_values[b, f, j] = values[b, f, out_src[b, j]];
+ * out_stats [batch, 6] fp32: [length, active, distinct, 1 - distinct / active, positive share, last gap bucket].
+ * The statistics always describe the INPUT (before removal).  max_len <= 8192. */
+int tb200_sequence_prepare(const int64_t* values, const int64_t* lengths, const int64_t* timestamps,
+                           const int64_t* request_ts, int64_t batch, int32_t n_feat, int32_t max_len,
+                           int64_t* out_len, int32_t* out_src, float* out_stats, void* stream);
+
 /* ---- whole FFN without any allocation --------------------------------------------------------
  * No counterpart in the reference (which has neither an FP8 path nor a C interface).
  *

@@ -1,0 +1,194 @@
+// Integer preprocessing of a behaviour-sequence domain, one CTA per sample:
+//   * duplicate-event removal (keep the LAST occurrence of every distinct active event, in order), and
+//   * the six sequence statistics,
+// which the reference computes with F stable argsorts plus gather / scatter passes over [B, L] int64
+// tensors.  Here every sample is handled in shared memory: the active events are inserted into an
+// open-addressing hash table keyed by the full feature tuple (exact comparison against the slot's
+// representative event, so hash collisions cannot merge different events), each slot remembers the
+// largest position that hit it, and an event survives iff it is that position.  A block-wide scan
+// then compacts the survivors.  All arithmetic is integer; the statistics are converted to fp32 the
+// same way the reference converts them.
+#include "tb200_common.cuh"
+
+namespace tb200 {
+void count_launch();
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kEdges = 63;
+
+__constant__ int64_t c_edges[kEdges] = {
+    5, 10, 15, 20, 25, 30, 35, 40, 45, 50, 55, 60, 120, 180, 240, 300, 360, 420, 480, 540, 600, 900, 1200, 1500, 1800,
+    2100, 2400, 2700, 3000, 3300, 3600, 5400, 7200, 9000, 10800, 12600, 14400, 16200, 18000, 19800, 21600, 32400,
+    43200, 54000, 64800, 75600, 86400, 172800, 259200, 345600, 432000, 518400, 604800, 1123200, 1641600, 2160000,
+    2592000, 4320000, 6048000, 7776000, 11664000, 15552000, 31536000};
+
+// number of edges strictly below gap (torch.searchsorted, side = "left"), clamped as the reference does
+__device__ __forceinline__ int gap_bucket(int64_t ts, int64_t request) {
+    if (ts == 0) return 0;
+    int64_t gap = request - ts;
+    if (gap < 0) gap = 0;
+    int lo = 0, hi = kEdges;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (c_edges[mid] < gap) lo = mid + 1;
+        else hi = mid;
+    }
+    return (lo > kEdges - 1 ? kEdges - 1 : lo) + 1;
+}
+
+__device__ __forceinline__ uint32_t mix(uint64_t x) {
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdULL;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ULL;
+    x ^= x >> 33;
+    return static_cast<uint32_t>(x);
+}
+
+__global__ void __launch_bounds__(kThreads)
+seqprep_kernel(const int64_t* __restrict__ values, const int64_t* __restrict__ lengths,
+               const int64_t* __restrict__ timestamps, const int64_t* __restrict__ request_ts, int n_feat, int max_len,
+               int table_size, int64_t* __restrict__ out_len, int32_t* __restrict__ out_src,
+               float* __restrict__ out_stats) {
+    extern __shared__ int32_t smem_i[];
+    int32_t* rep = smem_i;                    // [table_size] representative position of the slot, -1 = empty
+    int32_t* last = rep + table_size;         // [table_size] largest position that hit the slot
+    int32_t* slot_of = last + table_size;     // [max_len] slot of every active position, -1 = inactive
+    int32_t* scan = slot_of + max_len;        // [kThreads] block scan scratch
+    __shared__ int s_active, s_positive, s_kept;
+
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int64_t* row = values + static_cast<int64_t>(b) * n_feat * max_len;
+    int64_t raw = lengths[b];
+    raw = raw < 0 ? 0 : (raw > max_len ? max_len : raw);
+    const int raw_len = static_cast<int>(raw);
+
+    for (int i = tid; i < table_size; i += kThreads) {
+        rep[i] = -1;
+        last[i] = -1;
+    }
+    if (tid == 0) {
+        s_active = 0;
+        s_positive = 0;
+        s_kept = 0;
+    }
+    __syncthreads();
+
+    // ---- insert the active events
+    int n_active = 0, n_positive = 0;
+    for (int p = tid; p < max_len; p += kThreads) {
+        bool any_pos = false;
+        uint64_t h = 0x9e3779b97f4a7c15ULL;
+        for (int f = 0; f < n_feat; ++f) {
+            const int64_t v = row[static_cast<int64_t>(f) * max_len + p];
+            if (v > 0) {
+                any_pos = true;
+                ++n_positive;
+            }
+            h = (h ^ static_cast<uint64_t>(v)) * 0x100000001b3ULL + (h >> 29);
+        }
+        int my_slot = -1;
+        if (any_pos && p < raw_len) {
+            ++n_active;
+            uint32_t s = mix(h) & (table_size - 1);
+            for (int probe = 0; probe < table_size; ++probe) {
+                const int cur = atomicCAS(&rep[s], -1, p);
+                bool same = cur == -1 || cur == p;
+                if (!same) {
+                    same = true;
+                    for (int f = 0; f < n_feat; ++f)
+                        if (row[static_cast<int64_t>(f) * max_len + cur] != row[static_cast<int64_t>(f) * max_len + p]) {
+                            same = false;
+                            break;
+                        }
+                }
+                if (same) {
+                    atomicMax(&last[s], p);
+                    my_slot = static_cast<int>(s);
+                    break;
+                }
+                s = (s + 1) & (table_size - 1);
+            }
+        }
+        slot_of[p] = my_slot;
+    }
+    atomicAdd(&s_active, n_active);
+    atomicAdd(&s_positive, n_positive);
+    __syncthreads();
+
+    // ---- survivors, compacted in original order (chunks of kThreads positions, running offset)
+    int32_t* src_row = out_src + static_cast<int64_t>(b) * max_len;
+    int base = 0;
+    for (int p0 = 0; p0 < max_len; p0 += kThreads) {
+        const int p = p0 + tid;
+        const bool keep = p < max_len && slot_of[p] >= 0 && last[slot_of[p]] == p;
+        scan[tid] = keep ? 1 : 0;
+        __syncthreads();
+        for (int off = 1; off < kThreads; off <<= 1) {  // Hillis-Steele inclusive scan
+            const int add = tid >= off ? scan[tid - off] : 0;
+            __syncthreads();
+            scan[tid] += add;
+            __syncthreads();
+        }
+        if (keep) src_row[base + scan[tid] - 1] = p;
+        base += scan[kThreads - 1];
+        __syncthreads();
+    }
+    if (tid == 0) s_kept = base;
+    __syncthreads();
+    const int kept = s_kept;
+    const bool changed = kept != raw_len && raw_len > 1;
+    if (!changed) {  // untouched rows keep every position, active or not
+        for (int p = tid; p < max_len; p += kThreads) src_row[p] = p;
+    } else {
+        for (int p = kept + tid; p < max_len; p += kThreads) src_row[p] = -1;  // zero-filled tail
+    }
+    if (tid == 0) {
+        out_len[b] = changed ? static_cast<int64_t>(kept) : lengths[b];
+        float* st = out_stats + static_cast<int64_t>(b) * 6;
+        const int active = s_active;
+        const bool has = active > 0;
+        const float active_f = static_cast<float>(active);
+        const float kept_f = static_cast<float>(kept);
+        const int64_t denom = static_cast<int64_t>(raw_len) * n_feat > 1 ? static_cast<int64_t>(raw_len) * n_feat : 1;
+        st[0] = has ? static_cast<float>(raw_len) : 0.f;
+        st[1] = has ? active_f : 0.f;
+        st[2] = has ? kept_f : 0.f;
+        st[3] = has ? 1.0f - __fdiv_rn(kept_f, fmaxf(active_f, 1.0f)) : 0.f;
+        st[4] = has ? __fdiv_rn(static_cast<float>(s_positive), static_cast<float>(denom)) : 0.f;
+        const int last_index = raw_len > 0 ? raw_len - 1 : 0;
+        st[5] = (has && raw_len > 0) ? static_cast<float>(gap_bucket(timestamps[static_cast<int64_t>(b) * max_len + last_index], request_ts[b])) : 0.f;
+    }
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_sequence_prepare(const int64_t* values, const int64_t* lengths, const int64_t* timestamps,
+                                      const int64_t* request_ts, int64_t batch, int32_t n_feat, int32_t max_len,
+                                      int64_t* out_len, int32_t* out_src, float* out_stats, void* stream) {
+    using namespace tb200;
+    if (batch < 0 || n_feat < 1 || max_len < 1 || max_len > 8192) return TB200_ERR_SHAPE;
+    if (batch == 0) return TB200_OK;
+    if (values == nullptr || lengths == nullptr || timestamps == nullptr || request_ts == nullptr || out_len == nullptr ||
+        out_src == nullptr || out_stats == nullptr)
+        return TB200_ERR_NULL;
+    if (batch > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    int table = 64;
+    while (table < 2 * max_len) table <<= 1;
+    const size_t smem = (static_cast<size_t>(2) * table + max_len + kThreads) * sizeof(int32_t);
+    static bool attr_set[64] = {};
+    const DeviceInfo& dev = device_info();
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(seqprep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set[dev.index] = true;
+    }
+    seqprep_kernel<<<static_cast<unsigned>(batch), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        values, lengths, timestamps, request_ts, n_feat, max_len, table, out_len, out_src, out_stats);
+    count_launch();
+    return launch_status();
+}

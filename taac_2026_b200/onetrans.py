@@ -479,10 +479,12 @@ class OneTransInference:
         single_len = None
         for di, domain in enumerate(self.domains):
             seq = inputs.sequences[domain]
-            sort = _SequenceSort(seq.values, seq.lengths)
-            stat_vectors.append(self._stats_vector(
-                sequence_stats(seq.values, seq.lengths, seq.timestamps, request_ts, self._edges, sort)))
-            values, lengths, ts = deduplicate_sequence_events(seq.values, seq.lengths, seq.timestamps, sort)
+            lengths, src_map, stats = ops.sequence_prepare(seq.values, seq.lengths, seq.timestamps, request_ts)
+            stat_vectors.append(self._stats_vector(stats))
+            keep_pos = src_map.clamp_min(0).long()
+            gone = src_map < 0
+            values = seq.values.gather(2, keep_pos[:, None, :].expand(-1, seq.values.shape[1], -1)).masked_fill(gone[:, None, :], 0)
+            ts = seq.timestamps.gather(1, keep_pos).masked_fill(gone, 0)
             seq_len = lengths.clamp(min=0, max=values.shape[2])
             tokens = self._sequence_tokens(domain, values, ts, request_ts)
             tokens = self._tail_crop(tokens, seq_len)
@@ -552,9 +554,11 @@ class OneTransInference:
         ns = self.num_ns
         seq = inputs.sequences[domain]
         request_ts = inputs.request_timestamp
-        sort = _SequenceSort(seq.values, seq.lengths)
-        stat_vectors = [self._stats_vector(sequence_stats(seq.values, seq.lengths, seq.timestamps, request_ts, self._edges, sort))]
-        values, lengths, ts = deduplicate_sequence_events(seq.values, seq.lengths, seq.timestamps, sort)
+        # duplicate removal + statistics: one kernel; `src` maps output slots to input positions, so the
+        # compacted [B, F, L] / [B, L] tensors of the reference are never materialised
+        lengths, src_map, stats = ops.sequence_prepare(seq.values, seq.lengths, seq.timestamps, request_ts)
+        stat_vectors = [self._stats_vector(stats)]
+        values, ts = seq.values, seq.timestamps
         max_len = values.shape[2]
         raw_len = lengths.clamp(min=0, max=max_len).to(torch.long)
         width = min(max_len, self.seq_keep)            # padded sequence width S[0] after the tail crop
@@ -588,7 +592,7 @@ class OneTransInference:
         sample_of = torch.repeat_interleave(arange_b, n0, output_size=n_seq)
         seq_cu = offsets(n0)
         j_idx = torch.arange(n_seq, device=dev) - seq_cu[sample_of]              # position after the tail crop
-        src_pos = start[sample_of] + j_idx                                        # position in the padded input
+        src_pos = src_map[sample_of, start[sample_of] + j_idx].long()             # position in the raw input
         dest = cu[0][sample_of] + j_idx                                           # row in the packed matrix
         prefix = f"sequence_tokenizers.{domain}"
         entries = self.seq_tables[domain]
@@ -610,7 +614,7 @@ class OneTransInference:
         tokens = self._layer_norm(F.silu(self._linear(token_input, prefix + ".project.0")), prefix + ".project.2")
         pos_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, j_idx)
         if prefix + ".time_embedding.weight" in self.w:
-            buckets = sequence_time_buckets(ts, request_ts, self._edges)[sample_of, src_pos]
+            buckets = sequence_time_buckets(ts[sample_of, src_pos][:, None], request_ts[sample_of], self._edges)[:, 0]
             buckets_full = torch.zeros(total0, dtype=buckets.dtype, device=dev).index_copy_(0, dest, buckets)
             tokens = tokens + ops.gather_rows(self._p(prefix + ".time_embedding.weight"), buckets_full)
         tokens = tokens + ops.gather_rows(self._positions(width), pos_full)

@@ -853,6 +853,35 @@ def ffn_fp8_static(x: torch.Tensor, weights: Fp8FfnWeights, out: torch.Tensor, *
     return out
 
 
+
+def sequence_prepare(values: torch.Tensor, lengths: torch.Tensor, timestamps: torch.Tensor,
+                     request_ts: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Duplicate-event removal and sequence statistics of one domain in a single kernel.
+
+    ``values`` [B, F, L], ``lengths`` [B], ``timestamps`` [B, L], ``request_ts`` [B] (int64) ->
+    ``(new_lengths [B] int64, src [B, L] int32, stats [B, 6] fp32)`` where ``src[b, j]`` is the input
+    position that lands in output slot ``j`` (-1 = zero fill).  Integer-exact counterpart of
+    `deduplicate_sequence_events` (modeling/sequence.py:141-198) + `compute_sequence_stats`
+    (modeling/time_features.py:49-105)."""
+    _require_backend("sequence_prepare", "cuda")
+    _require_cuda_tensors("cuda sequence_prepare", values, lengths, timestamps, request_ts)
+    if values.ndim != 3 or timestamps.ndim != 2 or lengths.ndim != 1 or request_ts.ndim != 1:
+        raise ValueError("sequence_prepare expects values [B, F, L], lengths [B], timestamps [B, L], request_ts [B]")
+    batch, n_feat, max_len = values.shape
+    if n_feat < 1 or max_len < 1 or max_len > 8192:
+        raise ValueError("sequence_prepare needs at least one feature and 1 <= L <= 8192")
+    values, lengths = values.to(torch.int64).contiguous(), lengths.to(torch.int64).contiguous()
+    timestamps, request_ts = timestamps.to(torch.int64).contiguous(), request_ts.to(torch.int64).contiguous()
+    new_len = torch.empty(batch, dtype=torch.int64, device=values.device)
+    src = torch.empty(batch, max_len, dtype=torch.int32, device=values.device)
+    stats = torch.empty(batch, 6, dtype=torch.float32, device=values.device)
+    with torch.cuda.device(values.device), _timed("sequence_prepare", batch=batch, n_feat=n_feat, max_len=max_len):
+        code = _lib.load().tb200_sequence_prepare(_ptr(values), _ptr(lengths), _ptr(timestamps), _ptr(request_ts), batch,
+                                                  n_feat, max_len, _ptr(new_len), _ptr(src), _ptr(stats), _stream_ptr())
+    _lib.check(code, "cuda sequence_prepare")
+    return new_len, src, stats
+
+
 __all__ = [
     "AttentionMaskPlan",
     "Fp8FfnWeights",
@@ -879,4 +908,5 @@ __all__ = [
     "resolved_rms_norm_backend",
     "rms_norm",
     "sequence_gather",
+    "sequence_prepare",
 ]
