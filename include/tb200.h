@@ -109,6 +109,18 @@ int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t dim, const 
                       int64_t seq_len, int64_t ids_batch_stride, void* out, int64_t out_stride, int32_t out_col0,
                       int dtype, void* stream);
 
+/* dst[ids[i], dst_col0 : dst_col0 + dim] = src[i, :] (+ bias[i / rows_per_group, :]) (+ residual[ids[i], :dim])
+ * for i in [0, n): the row scatter behind the per-token overrides of OneTrans's non-sequence tokens
+ * (`q[:, position, :] = q_proj(token)` and `output[:, position, :] = ffn(...)`,
+ * experiments/onetrans/model.py:60-67, :89-93), with the projection bias and the residual stream folded
+ * in.  ids: device int64[n], distinct rows of dst; src [n, dim] dense; bias [n / rows_per_group, dim] or
+ * NULL; residual rows of residual_stride elements or NULL (may alias dst only if dst_col0 == 0 and the
+ * strides agree, since every row is read before it is written by the same thread).  dim, dst_col0 and
+ * the strides times sizeof(dtype) must be multiples of 16. */
+int tb200_scatter_rows(void* dst, int64_t dst_rows, int64_t dst_stride, int32_t dst_col0, const int64_t* ids,
+                       const void* src, int64_t n, int32_t dim, const void* bias, int64_t rows_per_group,
+                       const void* residual, int64_t residual_stride, int dtype, void* stream);
+
 /* ---- (c) varlen masked attention forward ----------------------------------------------------
  * o[b, h, q, :] = softmax_k(scale * <q[b, h, q, :], k[b, h, k, :]> over visible k) . v[b, h, k, :]
  * with fp32 softmax statistics and accumulation.  Key k is visible to query q of sample b iff

@@ -182,6 +182,48 @@ bag_mean_kernel(BagArgs a, const void* __restrict__ ids, T* __restrict__ out) {
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// scatter_rows: dst[ids[i], :] = src[i, :] (+ bias[i / rows_per_group, :]) (+ residual[ids[i], :])
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+scatter_rows_kernel(uint4* __restrict__ dst, int64_t dst_stride_chunks, int dst_col0_chunks,
+                    const int64_t* __restrict__ ids, const uint4* __restrict__ src, int chunks, int64_t n,
+                    const uint4* __restrict__ bias, int64_t rows_per_group, const uint4* __restrict__ residual,
+                    int64_t res_stride_chunks, int lanes_per_row) {
+    constexpr int N = Vec16<T>::N;
+    const int G = lanes_per_row;
+    const int group = threadIdx.x / G;
+    const int lane_g = threadIdx.x % G;
+    const int n_groups = kThreads / G;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * n_groups + group; i < n; i += static_cast<int64_t>(gridDim.x) * n_groups) {
+        const int64_t row = ids[i];
+        const uint4* brow = bias != nullptr ? bias + (i / rows_per_group) * chunks : nullptr;
+        for (int c = lane_g; c < chunks; c += G) {
+            uint4 v = ld_nc_v4(src + i * chunks + c);
+            if (brow != nullptr || residual != nullptr) {
+                float f[N];
+                Vec16<T>::unpack(v, f);
+                if (brow != nullptr) {
+                    float b[N];
+                    Vec16<T>::unpack(brow[c], b);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) f[e] += b[e];
+                }
+                if (residual != nullptr) {
+                    float r[N];
+                    Vec16<T>::unpack(residual[row * res_stride_chunks + c], r);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) f[e] += r[e];
+                }
+                v = Vec16<T>::pack(f);
+            }
+            dst[row * dst_stride_chunks + dst_col0_chunks + c] = v;
+        }
+    }
+}
+
+
 int lanes_for(int chunks) {
     int g = 1;
     while (g < 32 && g < chunks) g <<= 1;
@@ -297,6 +339,45 @@ extern "C" int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t 
         gather_rows_kernel<int32_t><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(
             static_cast<const uint4*>(table), vocab_rows, chunks, ids, n, seq_len, ids_batch_stride,
             static_cast<uint4*>(out), out_stride * es / 16, out_col0 * es / 16, G);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int tb200_scatter_rows(void* dst, int64_t dst_rows, int64_t dst_stride, int32_t dst_col0, const int64_t* ids,
+                                  const void* src, int64_t n, int32_t dim, const void* bias, int64_t rows_per_group,
+                                  const void* residual, int64_t residual_stride, int dtype, void* stream) {
+    using namespace tb200;
+    if (n < 0 || dim < 1 || dst_rows < 0 || dst_stride < dim || dst_col0 < 0 || dst_col0 + dim > dst_stride) return TB200_ERR_SHAPE;
+    if (bias != nullptr && rows_per_group < 1) return TB200_ERR_SHAPE;
+    if (residual != nullptr && residual_stride < dim) return TB200_ERR_SHAPE;
+    if (n == 0) return TB200_OK;
+    const int es = dtype_size(dtype);
+    if (es == 0) return TB200_ERR_DTYPE;
+    if (dst == nullptr || ids == nullptr || src == nullptr) return TB200_ERR_NULL;
+    if ((static_cast<int64_t>(dim) * es) % 16 != 0 || (dst_stride * es) % 16 != 0 || (static_cast<int64_t>(dst_col0) * es) % 16 != 0 ||
+        (residual != nullptr && (residual_stride * es) % 16 != 0) || !aligned16(dst) || !aligned16(src) ||
+        (bias != nullptr && !aligned16(bias)) || (residual != nullptr && !aligned16(residual)))
+        return TB200_ERR_ALIGN;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    const int chunks = dim * es / 16;
+    const int G = lanes_for(chunks);
+    const int n_groups = kThreads / G;
+    int64_t grid = (n + n_groups - 1) / n_groups;
+    const int64_t cap = static_cast<int64_t>(device_info().sm_count) * 16;
+    if (grid > cap) grid = cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TB200_SCATTER(T)                                                                                              \
+    scatter_rows_kernel<T><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(                                          \
+        static_cast<uint4*>(dst), dst_stride * es / 16, dst_col0 * es / 16, ids, static_cast<const uint4*>(src), chunks, \
+        n, static_cast<const uint4*>(bias), rows_per_group < 1 ? 1 : rows_per_group, static_cast<const uint4*>(residual), \
+        residual_stride * es / 16, G)
+    switch (dtype) {
+        case TB200_F32: TB200_SCATTER(float); break;
+        case TB200_F16: TB200_SCATTER(__half); break;
+        case TB200_BF16: TB200_SCATTER(__nv_bfloat16); break;
+        default: return TB200_ERR_DTYPE;
+    }
+#undef TB200_SCATTER
     count_launch();
     return launch_status();
 }

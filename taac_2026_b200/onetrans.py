@@ -623,7 +623,7 @@ class OneTransInference:
         ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
         ns_off = torch.arange(ns, device=dev)[None, :]
         ns_rows = (cu[0][:-1] + counts[0])[:, None] + ns_off                       # [B, ns]
-        tokens.index_copy_(0, ns_rows.reshape(-1), ns_tokens.reshape(batch * ns, self.d))
+        ops.scatter_rows(tokens, ns_rows.reshape(-1), ns_tokens.reshape(batch * ns, self.d).contiguous())
 
         d, heads, hd = self.d, self.heads, self.head_dim
         for layer, blk in enumerate(self.blocks):
@@ -633,7 +633,7 @@ class OneTransInference:
             qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
             flat_ns = ns_rows.t().reshape(-1)                                      # token-major: [ns, B] row ids
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)                  # [ns, B, d], contiguous
-            qkv.index_copy_(0, flat_ns, torch.baddbmm(blk["ns_qkv_b"], x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d))
+            ops.scatter_rows(qkv, flat_ns, torch.bmm(x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d), bias=blk["ns_qkv_b"])
             q, k, v = (qkv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(3))
             if q.dtype == torch.float32:
                 q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
@@ -643,9 +643,9 @@ class OneTransInference:
             x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
             out = self._shared_ffn_residual(blk, x, tokens)
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)
-            h = F.silu(torch.baddbmm(blk["ns_b1"], x_ns, blk["ns_w1"]))
-            y_ns = torch.baddbmm(blk["ns_b2"], h, blk["ns_w2"]).view(ns * batch, d)
-            out.index_copy_(0, flat_ns, ops.gather_rows(tokens, flat_ns) + y_ns)
+            h = F.silu(torch.bmm(x_ns, blk["ns_w1"]).add_(blk["ns_b1"]))
+            y_ns = torch.bmm(h, blk["ns_w2"]).view(ns * batch, d)
+            ops.scatter_rows(out, flat_ns, y_ns, bias=blk["ns_b2"], residual=tokens)   # tokens + b2 + FFN_ns(x)
             tokens = out
             if widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
                 new_rows = rows[layer + 1]

@@ -882,6 +882,41 @@ def sequence_prepare(values: torch.Tensor, lengths: torch.Tensor, timestamps: to
     return new_len, src, stats
 
 
+
+def scatter_rows(dst: torch.Tensor, ids: torch.Tensor, src: torch.Tensor, *, col0: int = 0,
+                 bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``dst[ids[i], col0 : col0 + dim] = src[i] (+ bias[i // rows_per_group]) (+ residual[ids[i]])`` in place.
+
+    ``dst`` [rows, width] and ``src`` [n, dim] are contiguous matrices of one dtype, ``ids`` int64 [n] with
+    distinct entries.  ``bias`` [groups, dim] is applied to consecutive blocks of ``n // groups`` source rows
+    (the token-major order of the NS projections); ``residual`` is a [rows, dim] matrix indexed like ``dst``."""
+    _require_backend("scatter_rows", "cuda")
+    _require_cuda_tensors("cuda scatter_rows", dst, ids, src, bias, residual)
+    if dst.ndim != 2 or src.ndim != 2 or not dst.is_contiguous() or not src.is_contiguous() or dst.dtype != src.dtype:
+        raise ValueError("scatter_rows needs contiguous 2-D dst and src of one dtype")
+    if ids.dtype != torch.int64 or ids.numel() != src.shape[0]:
+        raise ValueError("scatter_rows ids must be int64 with one entry per source row")
+    if not cuda_supported_floating_dtype(dst.dtype):
+        raise RuntimeError(f"cuda scatter_rows does not support dtype {dst.dtype}")
+    n, dim = src.shape
+    per_group = 1
+    if bias is not None:
+        bias = bias.to(dst.dtype).reshape(-1, dim).contiguous()
+        if bias.shape[0] < 1 or n % bias.shape[0]:
+            raise ValueError("scatter_rows bias groups must divide the number of source rows")
+        per_group = max(n // bias.shape[0], 1)
+    if residual is not None and (residual.ndim != 2 or residual.shape[1] < dim or not residual.is_contiguous() or residual.dtype != dst.dtype):
+        raise ValueError("scatter_rows residual must be a contiguous matrix of dst's dtype with at least dim columns")
+    ids = ids.contiguous()
+    with torch.cuda.device(dst.device), _timed("scatter_rows", rows=n, dim=dim, esize=dst.element_size()):
+        code = _lib.load().tb200_scatter_rows(
+            _ptr(dst), dst.shape[0], dst.shape[1], int(col0), _ptr(ids), _ptr(src), n, dim, _ptr(bias), per_group,
+            _ptr(residual), 0 if residual is None else residual.shape[1], _DTYPE_CODES[dst.dtype], _stream_ptr(),
+        )
+    _lib.check(code, "cuda scatter_rows")
+    return dst
+
+
 __all__ = [
     "AttentionMaskPlan",
     "Fp8FfnWeights",
@@ -907,6 +942,7 @@ __all__ = [
     "resolved_layer_norm_backend",
     "resolved_rms_norm_backend",
     "rms_norm",
+    "scatter_rows",
     "sequence_gather",
     "sequence_prepare",
 ]

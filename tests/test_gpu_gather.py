@@ -99,3 +99,23 @@ def test_large_gather_checksum():
     valid = (bag != 0).unsqueeze(-1)
     want = (table[bag].float() * valid).sum(dim=1) / valid.sum(dim=1).clamp_min(1)
     assert (got - want.to(torch.bfloat16).float()).abs().max().item() <= 2e-2  # summation order differs from torch's
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_scatter_rows_with_bias_and_residual(dtype):
+    g = torch.Generator().manual_seed(21)
+    rows, width, dim, groups, per = 500, 96, 32, 3, 40
+    dst = torch.randn(rows, width, generator=g).to(dtype)
+    src = torch.randn(groups * per, dim, generator=g).to(dtype)
+    bias = torch.randn(groups, dim, generator=g).to(dtype)
+    res = torch.randn(rows, dim, generator=g).to(dtype)
+    ids = torch.randperm(rows, generator=g)[: groups * per]
+    want = dst.clone()
+    want[ids, 64:96] = src
+    got = ops.scatter_rows(dst.clone().cuda(), ids.cuda(), src.cuda(), col0=64).cpu()
+    assert torch.equal(got, want)  # a plain scatter is a copy
+    want = dst.clone()
+    want[ids, :dim] = (src.float() + bias.float().repeat_interleave(per, dim=0) + res[ids].float()).to(dtype)
+    got = ops.scatter_rows(dst.clone().cuda(), ids.cuda(), src.cuda(), bias=bias.cuda(), residual=res.cuda()).cpu()
+    assert torch.equal(got, want)  # one fp32 sum, one rounding
+    assert ops.scatter_rows(dst.clone().cuda(), ids[:0].cuda(), src[:0].cuda()).shape == dst.shape
