@@ -7,11 +7,14 @@
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
 //   warps 2..9   softmax: warps 2-5 own half 0, warps 6-9 half 1; one thread per query row
 // Per KV tile and half:  S = Q K^T   (tcgen05.mma kind::f16, M 128 x N 128 x K 64, fp32 in TMEM)
-//                        softmax thread reads its S row from TMEM (two passes of 4 x 32 columns:
-//                        row max, then exp2), writes P as bf16 into swizzled shared memory
-//                        O_tile = P V   (M 128 x N 64 x K 128, V is the MN-major B operand)
-//                        the thread folds O_tile into its fp32 register accumulator with the
-//                        online-softmax correction while the tensor cores work on the other half.
+//                        the softmax thread pulls its whole S row into registers (4 x tcgen05.ld of
+//                        32 columns, one wait), frees S at once, takes the row max, writes
+//                        P = exp2(...) as bf16 into swizzled shared memory
+//                        O += P V    (M 128 x N 64 x K 128, V is the MN-major B operand), accumulated
+//                        in TMEM across the key tiles.  The running max is only advanced when it grows
+//                        by more than 2^8 (the exponent stays within fp32 / bf16 range, the final
+//                        division by the row sum makes the result exact); when it does, the threads
+//                        rescale their O rows in TMEM (tcgen05.ld / tcgen05.st) before P is released.
 // Key tiles without a visible key are skipped; masks come as lengths, never as a matrix.
 // Every mbarrier wait is bounded; a wait that gives up raises the status word and all roles drain
 // through the final barrier, where TMEM is released.
@@ -102,7 +105,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_full;
     __shared__ uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-    __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
+    __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int s_abort;
 
@@ -132,7 +135,6 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(&s_free[i], kSoftmaxThreads);
             mbar_init(&p_full[i], kSoftmaxThreads);
             mbar_init(&o_full[i], 1);
-            mbar_init(&o_free[i], kSoftmaxThreads);
         }
         s_abort = 0;
         fence_mbar_init();
@@ -217,7 +219,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 const uint32_t v_addr = smem_u32(sV + s * kTileBytes);
                 for (int h = 0; h < 2 && ok; ++h) {
                     if (!(h == 0 ? act0 : act1)) continue;
-                    if (!mbar_wait(&p_full[h], hc[h] & 1) || !mbar_wait(&o_free[h], (hc[h] & 1) ^ 1)) { ok = false; break; }
+                    if (!mbar_wait(&p_full[h], hc[h] & 1)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t p_addr = smem_u32(sP + h * kPBytes);
 #pragma unroll
@@ -225,7 +227,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         // A: P, K-major, two 64-key atoms of 16 KB; B: V, MN-major, 16 key rows = 2 KB per step
                         const uint32_t pa = p_addr + (k >> 2) * (kHalf * 128) + (k & 3) * 32;
                         mma_f16_ss(tmem_base + kTmemO + h * kD, umma_desc_sw128(pa, 1024, 16),
-                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, k > 0 ? 1u : 0u);
+                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || hc[h] > 0) ? 1u : 0u);
                     }
                     tc_commit(&o_full[h]);
                     ++hc[h];
@@ -251,14 +253,10 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint8_t* p_row = sP + h * kPBytes + r_local * 128;
         const int sw = r_local & 7;
 
-        float2 o_acc[kD / 2];
-#pragma unroll
-        for (int i = 0; i < kD / 2; ++i) o_acc[i] = make_float2(0.f, 0.f);
-        float m_run = -INFINITY;
+        float m_ref = -INFINITY;   // reference max of the exponent (lags the true max by at most 2^8)
         float l_run = 0.f;
         uint32_t hc = 0;
         bool ok = true;
-        bool pending = false;  // an O_tile of this half is in flight
 
         // Visibility of key column c for this thread's row, as two half-open ranges:
         //   [0, lim_lo) and [ns_lo, lim_hi)  with lim_hi = min(lk, causal ? row + 1 : lk)
@@ -272,91 +270,93 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             constexpr bool FULL = decltype(full_tag)::value;
             if (!mbar_wait(&s_full[h], hc & 1)) return false;
             tc_fence_after_sync();
-            // pass 1: row max of the visible scores
-            float mx0 = m_run, mx1 = -INFINITY;
+            uint32_t sr[4][32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t r[16];
-                tmem_ld_x16(t_s + c * 16, r);
-                tc_wait_ld();
+            for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, sr[c]);
+            tc_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(&s_free[h]);     // the row is in registers: S of this half may be overwritten
+
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    float s0 = __uint_as_float(r[i]);
-                    float s1 = __uint_as_float(r[i + 1]);
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
                     if (!FULL) {
-                        const int col = n0 + c * 16 + i;
-                        if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) s0 = -INFINITY;
-                        if (!(col + 1 < lim_lo || (col + 1 >= ns_lo && col + 1 < lim_hi))) s1 = -INFINITY;
+                        const int col = n0 + c * 32 + i;
+                        if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) sr[c][i] = 0xff800000u;          // -inf
+                        if (!(col + 1 < lim_lo || (col + 1 >= ns_lo && col + 1 < lim_hi))) sr[c][i + 1] = 0xff800000u;
                     }
-                    mx0 = fmaxf(mx0, s0);
-                    mx1 = fmaxf(mx1, s1);
+                    mx0 = fmaxf(mx0, __uint_as_float(sr[c][i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(sr[c][i + 1]));
                 }
             }
             const float mx = fmaxf(mx0, mx1);
-            const float m_use = mx == -INFINITY ? 0.f : mx;
-            const float corr = ex2((m_run - m_use) * sl2);  // 0 on the first tile (m_run = -inf)
-            const float ms = m_use * sl2;
-            m_run = mx;
-
-            // fold the previous tile's P V into the accumulator before P is overwritten
-            const float2 corr2 = make_float2(corr, corr);
-            if (pending) {
-                if (!mbar_wait(&o_full[h], (hc - 1) & 1)) return false;
-                tc_fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_x32(t_o + c * 32, r);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float2 pv = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                        o_acc[c * 16 + i] = __fmul2_rn(__fadd2_rn(o_acc[c * 16 + i], pv), corr2);
-                    }
-                }
-                tc_fence_before_sync();
-                mbar_arrive(&o_free[h]);
+            // advance the reference max only for a large jump (or on the first visible key of the row)
+            float corr = 1.0f;
+            bool grow = false;
+            if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sl2 > 8.0f)) {
+                corr = m_ref == -INFINITY ? 0.f : ex2((m_ref - mx) * sl2);
+                m_ref = mx;
+                grow = true;
             }
+            const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * sl2;
 
-            // pass 2: probabilities -> bf16 P in shared memory (K-major, 128-byte swizzle)
+            // probabilities, packed to bf16 in place (sr[c][0..15] hold the 32 values of chunk c)
             float2 sum2 = make_float2(0.f, 0.f);
             const float2 sl22 = make_float2(sl2, sl2);
             const float2 nms2 = make_float2(-ms, -ms);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t r[16];
-                tmem_ld_x16(t_s + c * 16, r);
-                tc_wait_ld();
-                uint32_t packed[8];
+            for (int c = 0; c < 4; ++c) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float2 sv = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    if (!FULL) {
-                        const int col = n0 + c * 16 + 2 * i;
-                        if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) sv.x = -INFINITY;
-                        if (!(col + 1 < lim_lo || (col + 1 >= ns_lo && col + 1 < lim_hi))) sv.y = -INFINITY;
-                    }
+                for (int i = 0; i < 16; ++i) {
+                    const float2 sv = make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
                     const float2 e = __ffma2_rn(sv, sl22, nms2);
                     const float2 p = make_float2(ex2(e.x), ex2(e.y));
                     sum2 = __fadd2_rn(sum2, p);
                     __nv_bfloat162 pb = __float22bfloat162_rn(p);
-                    packed[i] = *reinterpret_cast<uint32_t*>(&pb);
-                }
-                // 16 keys = 2 chunks of 16 bytes; key chunk index inside the 64-key atom: (c & 3) * 2 + q
-                uint8_t* atom = p_row + (c >> 2) * (kHalf * 128);
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int chunk = ((c & 3) * 2 + q) ^ sw;
-                    *reinterpret_cast<uint4*>(atom + chunk * 16) =
-                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    sr[c][i] = *reinterpret_cast<uint32_t*>(&pb);
                 }
             }
             l_run = l_run * corr + (sum2.x + sum2.y);
-            tc_fence_before_sync();
-            mbar_arrive(&s_free[h]);     // S of this half may be overwritten
+
+            // the previous P V of this half must be done before P is overwritten or O is rescaled
+            if (hc > 0) {
+                if (!mbar_wait(&o_full[h], (hc - 1) & 1)) return false;
+                tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, grow)) {  // tcgen05.ld / st are warp-wide: rescale with corr = 1 where unchanged
+                    const float2 corr2 = make_float2(corr, corr);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_x32(t_o + c * 32, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), corr2);
+                            r[2 * i] = __float_as_uint(v.x);
+                            r[2 * i + 1] = __float_as_uint(v.y);
+                        }
+                        tmem_st_x32(t_o + c * 32, r);
+                    }
+                    tc_wait_st();
+                    tc_fence_before_sync();
+                }
+            }
+
+            // P -> shared memory (K-major, 128-byte swizzle): chunk c covers keys [32 c, 32 c + 32) = 4 x 16 bytes
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int chunk = ((c & 1) * 4 + q) ^ sw;
+                    *reinterpret_cast<uint4*>(atom + chunk * 16) =
+                        make_uint4(sr[c][4 * q], sr[c][4 * q + 1], sr[c][4 * q + 2], sr[c][4 * q + 3]);
+                }
+            }
             fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
             mbar_arrive(&p_full[h]);
-            pending = true;
             ++hc;
             return true;
         };
@@ -369,7 +369,10 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             ok = full ? tile(n0, std::true_type{}) : tile(n0, std::false_type{});
         }
 
-        if (ok && pending) {
+        float2 o_acc[kD / 2];
+#pragma unroll
+        for (int i = 0; i < kD / 2; ++i) o_acc[i] = make_float2(0.f, 0.f);
+        if (ok && hc > 0) {
             if (!mbar_wait(&o_full[h], (hc - 1) & 1)) {
                 ok = false;
             } else {
@@ -381,10 +384,9 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     tc_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        o_acc[c * 16 + i] = __fadd2_rn(o_acc[c * 16 + i], make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+                        o_acc[c * 16 + i] = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
                 }
                 tc_fence_before_sync();
-                mbar_arrive(&o_free[h]);
             }
         }
         if (!ok) {
