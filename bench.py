@@ -344,7 +344,8 @@ def run_e2e(args) -> None:
 
     sd = random_state_dict(spec, seed=0, device=dev, dtype=torch.bfloat16)
     ffn_mode = args.ffn if spec.d_model % 256 == 0 else "bf16"
-    model = OneTransInference(sd, spec, device=dev, dtype=torch.bfloat16, ffn=ffn_mode, packed=not args.padded)
+    model = OneTransInference(sd, spec, device=dev, dtype=torch.bfloat16, ffn=ffn_mode, packed=not args.padded,
+                              attention_kernel=args.kernel)
     host_batch = synthetic_batch(spec, batch_size, seq_len=wl["seq_len"], min_len=wl["min_len"], seed=rank,
                                  field_exponent=wl["field_exp"], seq_exponent=wl["seq_exp"]).pin_memory()
     dev_batch = host_batch.to(dev)

@@ -1,11 +1,12 @@
 // Varlen masked attention forward on the 5th-generation tensor cores (sm_100a): head_dim 64, bf16.
 //
-// One CTA serves 256 query rows of one (sample, head) as two independent 128-row halves that share
-// the K/V stream.  Roles (320 threads):
-//   warp 0       TMA producer: Q halves once, then a 2-stage ring of K tiles and one of V tiles
+// One CTA serves kHalves x 128 query rows of one (sample, head); with one block per CTA two CTAs fit
+// an SM (256 TMEM columns and 97 KB of shared memory each) and one runs its softmax while the other
+// owns the tensor cores.  Roles (64 + 128 x kHalves threads):
+//   warp 0       TMA producer: Q once, then a 2-stage ring of K tiles and a single V tile buffer
 //                (128 keys x 128 bytes each, 128-byte swizzle, no multicast)
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
-//   warps 2..9   softmax: warps 2-5 own half 0, warps 6-9 half 1; one thread per query row
+//   warps 2..    softmax: four warps per 128-row block; one thread per query row
 // Per KV tile and half:  S = Q K^T   (tcgen05.mma kind::f16, M 128 x N 128 x K 64, fp32 in TMEM)
 //                        the softmax thread pulls its whole S row into registers (4 x tcgen05.ld of
 //                        32 columns, one wait), frees S at once, takes the row max, writes
@@ -33,16 +34,17 @@ namespace {
 
 constexpr int kD = 64;            // head dim
 constexpr int kHalf = 128;        // query rows per half == TMEM lanes
-constexpr int kBM = 2 * kHalf;    // query rows per CTA
+constexpr int kHalves = 1;        // 128-row query blocks per CTA (two CTAs share an SM and overlap each other)
+constexpr int kBM = kHalves * kHalf;  // query rows per CTA
 constexpr int kBN = 128;          // keys per tile
-constexpr int kThreads = 320;
+constexpr int kThreads = 64 + kHalves * 128;
 constexpr int kSoftmaxThreads = 128;  // per half
 constexpr uint32_t kTileBytes = kBN * kD * 2;       // 16 KB: one Q half, K tile or V tile
 constexpr uint32_t kPBytes = kHalf * kBN * 2;       // 32 KB: P of one half (two 64-key swizzle atoms)
-constexpr uint32_t kTmemCols = 512;
-// TMEM columns: S of half h at h * 128, O_tile of half h at 256 + h * 64
+constexpr uint32_t kTmemCols = kHalves == 1 ? 256 : 512;
+// TMEM columns: S of half h at h * 128, O of half h behind the S blocks at h * 64
 constexpr uint32_t kTmemS = 0;
-constexpr uint32_t kTmemO = 256;
+constexpr uint32_t kTmemO = kHalves * 128;
 
 struct Tc05Args {
     AttnArgs a;
@@ -86,7 +88,9 @@ __device__ __forceinline__ Plan make_plan(const AttnArgs& a, int b, int m0) {
     p.causal = a.causal != 0;
     p.self_rows = a.padded_query_self != 0;
     int n_max = 0;
-    for (int h = 0; h < 2; ++h) {
+    p.half_on[1] = false;
+    p.kv_end[1] = 0;
+    for (int h = 0; h < kHalves; ++h) {
         const int r0 = m0 + h * kHalf;
         const int r1 = min(r0 + kHalf, p.lq);
         // a half wholly inside the padded query range only copies value rows
@@ -99,7 +103,7 @@ __device__ __forceinline__ Plan make_plan(const AttnArgs& a, int b, int m0) {
     return p;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kHalves == 1 ? 2 : 1)
 attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const Tc05Args args) {
     extern __shared__ uint8_t smem_raw[];
@@ -111,10 +115,10 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
     const AttnArgs& a = args.a;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;                              // 2 halves x 16 KB
-    uint8_t* sK = sQ + 2 * kTileBytes;               // 2 stages x 16 KB
-    uint8_t* sV = sK + 2 * kTileBytes;               // 2 stages x 16 KB
-    uint8_t* sP = sV + 2 * kTileBytes;               // 2 halves x 32 KB
+    uint8_t* sQ = smem;                              // kHalves x 16 KB
+    uint8_t* sK = sQ + kHalves * kTileBytes;         // 2 stages x 16 KB
+    uint8_t* sV = sK + 2 * kTileBytes;               // 1 stage x 16 KB (V is only needed once P is ready)
+    uint8_t* sP = sV + kTileBytes;                   // kHalves x 32 KB
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -161,7 +165,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const uint32_t q_bytes = (plan.half_on[0] ? kTileBytes : 0) + (plan.half_on[1] ? kTileBytes : 0);
             if (q_bytes > 0) {
                 mbar_expect_tx(&q_full, q_bytes);
-                for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < kHalves; ++h)
                     if (plan.half_on[h])
                         tma_load_4d(sQ + h * kTileBytes, &tmap_q, 0, row0 + m0 + h * kHalf, h_idx, bz, &q_full);
             }
@@ -174,9 +178,9 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (!mbar_wait(&k_empty[s], ph ^ 1)) { ok = false; break; }
                 mbar_expect_tx(&k_full[s], kTileBytes);
                 tma_load_4d(sK + s * kTileBytes, &tmap_k, 0, row0 + j * kBN, h_idx, bz, &k_full[s]);
-                if (!mbar_wait(&v_empty[s], ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&v_full[s], kTileBytes);
-                tma_load_4d(sV + s * kTileBytes, &tmap_v, 0, row0 + j * kBN, h_idx, bz, &v_full[s]);
+                if (!mbar_wait(&v_empty[0], (kc & 1) ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&v_full[0], kTileBytes);
+                tma_load_4d(sV, &tmap_v, 0, row0 + j * kBN, h_idx, bz, &v_full[0]);
                 ++kc;
             }
             if (!ok) {
@@ -200,7 +204,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (!mbar_wait(&k_full[s], ph)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
-                for (int h = 0; h < 2 && ok; ++h) {
+                for (int h = 0; h < kHalves && ok; ++h) {
                     if (!(h == 0 ? act0 : act1)) continue;
                     if (!mbar_wait(&s_free[h], (hc[h] & 1) ^ 1)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -214,10 +218,10 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 if (!ok) break;
                 tc_commit(&k_empty[s]);  // K tile free once the S products above have read it
-                if (!mbar_wait(&v_full[s], ph)) { ok = false; break; }
+                if (!mbar_wait(&v_full[0], kc & 1)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(sV + s * kTileBytes);
-                for (int h = 0; h < 2 && ok; ++h) {
+                const uint32_t v_addr = smem_u32(sV);
+                for (int h = 0; h < kHalves && ok; ++h) {
                     if (!(h == 0 ? act0 : act1)) continue;
                     if (!mbar_wait(&p_full[h], hc[h] & 1)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -233,7 +237,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     ++hc[h];
                 }
                 if (!ok) break;
-                tc_commit(&v_empty[s]);
+                tc_commit(&v_empty[0]);
                 ++kc;
             }
             if (!ok) {
@@ -476,7 +480,7 @@ int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t
         !make_tmap(&tv, a.v, k_rows, a.H, nb, a.v_sl, a.v_sh, packed ? 0 : a.v_sb))
         return TB200_ERR_DRIVER;
     const DeviceInfo& dev = device_info();
-    const size_t smem = 6 * kTileBytes + 2 * kPBytes + 1024;
+    const size_t smem = (kHalves + 3) * kTileBytes + kHalves * kPBytes + 1024;
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
         cudaFuncSetAttribute(attn_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
