@@ -1,12 +1,13 @@
 // Varlen masked attention forward on the 5th-generation tensor cores (sm_100a): head_dim 64, bf16.
 //
-// One CTA serves kHalves x 128 query rows of one (sample, head); with one block per CTA two CTAs fit
-// an SM (256 TMEM columns and 97 KB of shared memory each) and one runs its softmax while the other
-// owns the tensor cores.  Roles (64 + 128 x kHalves threads):
+// Persistent CTAs walk the work items (128 query rows of one sample and head); two CTAs fit an SM
+// (256 TMEM columns and 97 KB of shared memory each), so one runs its softmax while the other owns the
+// tensor cores, and the TMA producer of a CTA already fetches the next item's Q / K / V while the
+// current item is being finished.  Roles (192 threads):
 //   warp 0       TMA producer: Q once, then a 2-stage ring of K tiles and a single V tile buffer
 //                (128 keys x 128 bytes each, 128-byte swizzle, no multicast)
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
-//   warps 2..    softmax: four warps per 128-row block; one thread per query row
+//   warps 2..5   softmax: one thread per query row
 // Per KV tile and half:  S = Q K^T   (tcgen05.mma kind::f16, M 128 x N 128 x K 64, fp32 in TMEM)
 //                        the softmax thread pulls its whole S row into registers (4 x tcgen05.ld of
 //                        32 columns, one wait), frees S at once, takes the row max, writes
@@ -103,44 +104,64 @@ __device__ __forceinline__ Plan make_plan(const AttnArgs& a, int b, int m0) {
     return p;
 }
 
-__global__ void __launch_bounds__(kThreads, kHalves == 1 ? 2 : 1)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// Work items: (query block of 128 rows, head, sample), walked in the same order by every role of a
+// persistent CTA (item w = blockIdx.x + i * gridDim.x).  Later query blocks come first: under a causal
+// mask they own the most key tiles, so the long items start early and the short ones fill the tail.
+struct Work {
+    int n_qb, heads, batch;
+    int64_t total;
+    __device__ __forceinline__ void decode(int64_t w, int& qb, int& h, int& b) const {
+        const int64_t per_qb = static_cast<int64_t>(heads) * batch;
+        qb = n_qb - 1 - static_cast<int>(w / per_qb);
+        const int rem = static_cast<int>(w % per_qb);
+        h = rem % heads;
+        b = rem / heads;
+    }
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
 attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const Tc05Args args) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_full;
-    __shared__ uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-    __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2];
+    __shared__ uint64_t q_full, q_empty;
+    __shared__ uint64_t k_full[2], k_empty[2], v_full, v_empty;
+    __shared__ uint64_t s_full, s_free, p_full, o_full;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int s_abort;
 
     const AttnArgs& a = args.a;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;                              // kHalves x 16 KB
-    uint8_t* sK = sQ + kHalves * kTileBytes;         // 2 stages x 16 KB
-    uint8_t* sV = sK + 2 * kTileBytes;               // 1 stage x 16 KB (V is only needed once P is ready)
-    uint8_t* sP = sV + kTileBytes;                   // kHalves x 32 KB
+    uint8_t* sQ = smem;                              // 16 KB
+    uint8_t* sK = sQ + kTileBytes;                   // 2 stages x 16 KB
+    uint8_t* sV = sK + 2 * kTileBytes;               // 16 KB (V is only needed once P is ready)
+    uint8_t* sP = sV + kTileBytes;                   // 32 KB
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int b = blockIdx.z;
-    const int h_idx = blockIdx.y;
-    const int m0 = blockIdx.x * kBM;
-    const Plan plan = make_plan(a, b, m0);
-    if (m0 >= plan.lq) return;  // uniform for the CTA: nothing allocated yet
+    Work work;
+    work.n_qb = (a.Lq + kBM - 1) / kBM;
+    work.heads = a.H;
+    work.batch = a.B;
+    work.total = static_cast<int64_t>(work.n_qb) * a.H * a.B;
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
+        mbar_init(&q_empty, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
-            mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1);
-            mbar_init(&s_free[i], kSoftmaxThreads);
-            mbar_init(&p_full[i], kSoftmaxThreads);
-            mbar_init(&o_full[i], 1);
         }
-        s_abort = 0;
+        mbar_init(&v_full, 1);
+        mbar_init(&v_empty, 1);
+        mbar_init(&s_full, 1);
+        mbar_init(&s_free, kSoftmaxThreads);
+        mbar_init(&p_full, kSoftmaxThreads);
+        mbar_init(&o_full, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -152,39 +173,39 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
-    // TMA coordinates: (d, row, head, batch); packed batches address rows of the whole matrix
-    const int row0 = plan.packed ? static_cast<int>(plan.row_base) : 0;
-    const int bz = plan.packed ? 0 : b;
-
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             tma_prefetch_desc(&tmap_q);
             tma_prefetch_desc(&tmap_k);
             tma_prefetch_desc(&tmap_v);
-            const uint32_t q_bytes = (plan.half_on[0] ? kTileBytes : 0) + (plan.half_on[1] ? kTileBytes : 0);
-            if (q_bytes > 0) {
-                mbar_expect_tx(&q_full, q_bytes);
-                for (int h = 0; h < kHalves; ++h)
-                    if (plan.half_on[h])
-                        tma_load_4d(sQ + h * kTileBytes, &tmap_q, 0, row0 + m0 + h * kHalf, h_idx, bz, &q_full);
-            }
-            uint32_t kc = 0;
+            uint32_t qc = 0, kc = 0;
             bool ok = true;
-            for (int j = 0; j < plan.n_tiles && ok; ++j) {
-                if (!plan.active(j, 0) && !plan.active(j, 1)) continue;
-                const uint32_t s = kc & 1;
-                const uint32_t ph = (kc >> 1) & 1;
-                if (!mbar_wait(&k_empty[s], ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&k_full[s], kTileBytes);
-                tma_load_4d(sK + s * kTileBytes, &tmap_k, 0, row0 + j * kBN, h_idx, bz, &k_full[s]);
-                if (!mbar_wait(&v_empty[0], (kc & 1) ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&v_full[0], kTileBytes);
-                tma_load_4d(sV, &tmap_v, 0, row0 + j * kBN, h_idx, bz, &v_full[0]);
-                ++kc;
+            for (int64_t w = blockIdx.x; w < work.total && ok; w += gridDim.x) {
+                int qb, h_idx, b;
+                work.decode(w, qb, h_idx, b);
+                const Plan plan = make_plan(a, b, qb * kBM);
+                if (!plan.half_on[0] || plan.n_tiles == 0) continue;
+                // TMA coordinates: (d, row, head, batch); packed batches address rows of the whole matrix
+                const int row0 = plan.packed ? static_cast<int>(plan.row_base) : 0;
+                const int bz = plan.packed ? 0 : b;
+                if (!mbar_wait(&q_empty, (qc & 1) ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&q_full, kTileBytes);
+                tma_load_4d(sQ, &tmap_q, 0, row0 + plan.m0, h_idx, bz, &q_full);
+                ++qc;
+                for (int j = 0; j < plan.n_tiles && ok; ++j) {
+                    if (!plan.active(j, 0)) continue;
+                    const uint32_t s = kc & 1;
+                    if (!mbar_wait(&k_empty[s], ((kc >> 1) & 1) ^ 1)) { ok = false; break; }
+                    mbar_expect_tx(&k_full[s], kTileBytes);
+                    tma_load_4d(sK + s * kTileBytes, &tmap_k, 0, row0 + j * kBN, h_idx, bz, &k_full[s]);
+                    if (!mbar_wait(&v_empty, (kc & 1) ^ 1)) { ok = false; break; }
+                    mbar_expect_tx(&v_full, kTileBytes);
+                    tma_load_4d(sV, &tmap_v, 0, row0 + j * kBN, h_idx, bz, &v_full);
+                    ++kc;
+                }
             }
             if (!ok) {
-                s_abort = 1;
                 if (args.status != nullptr) atomicExch(args.status, 1);
             }
         }
@@ -193,193 +214,199 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(1, 1, 0, 0, kHalf, kBN);  // bf16 x bf16, Q and K both K-major
             const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, kHalf, kD);   // P K-major, V MN-major (head dim contiguous)
-            uint32_t kc = 0;
-            uint32_t hc[2] = {0, 0};  // tiles issued so far per half
-            bool ok = plan.n_tiles == 0 || mbar_wait(&q_full, 0);
-            for (int j = 0; j < plan.n_tiles && ok; ++j) {
-                const bool act0 = plan.active(j, 0), act1 = plan.active(j, 1);
-                if (!act0 && !act1) continue;
-                const uint32_t s = kc & 1;
-                const uint32_t ph = (kc >> 1) & 1;
-                if (!mbar_wait(&k_full[s], ph)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
-                for (int h = 0; h < kHalves && ok; ++h) {
-                    if (!(h == 0 ? act0 : act1)) continue;
-                    if (!mbar_wait(&s_free[h], (hc[h] & 1) ^ 1)) { ok = false; break; }
+            const uint32_t q_addr = smem_u32(sQ);
+            const uint32_t p_addr = smem_u32(sP);
+            const uint32_t v_addr = smem_u32(sV);
+            uint32_t qc = 0, kc = 0;
+            bool ok = true;
+            for (int64_t w = blockIdx.x; w < work.total && ok; w += gridDim.x) {
+                int qb, h_idx, b;
+                work.decode(w, qb, h_idx, b);
+                const Plan plan = make_plan(a, b, qb * kBM);
+                if (!plan.half_on[0] || plan.n_tiles == 0) continue;
+                if (!mbar_wait(&q_full, qc & 1)) { ok = false; break; }
+                ++qc;
+                int last = -1;
+                for (int j = plan.n_tiles - 1; j >= 0; --j)
+                    if (plan.active(j, 0)) { last = j; break; }
+                bool first = true;
+                for (int j = 0; j < plan.n_tiles && ok; ++j) {
+                    if (!plan.active(j, 0)) continue;
+                    const uint32_t s = kc & 1;
+                    if (!mbar_wait(&k_full[s], (kc >> 1) & 1) || !mbar_wait(&s_free, (kc & 1) ^ 1)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t q_addr = smem_u32(sQ + h * kTileBytes);
+                    const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
 #pragma unroll
                     for (int k = 0; k < kD / 16; ++k) {
-                        mma_f16_ss(tmem_base + kTmemS + h * kBN, umma_desc_sw128(q_addr + k * 32, 1024, 16),
+                        mma_f16_ss(tmem_base + kTmemS, umma_desc_sw128(q_addr + k * 32, 1024, 16),
                                    umma_desc_sw128(k_addr + k * 32, 1024, 16), idesc_s, k > 0 ? 1u : 0u);
                     }
-                    tc_commit(&s_full[h]);
-                }
-                if (!ok) break;
-                tc_commit(&k_empty[s]);  // K tile free once the S products above have read it
-                if (!mbar_wait(&v_full[0], kc & 1)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(sV);
-                for (int h = 0; h < kHalves && ok; ++h) {
-                    if (!(h == 0 ? act0 : act1)) continue;
-                    if (!mbar_wait(&p_full[h], hc[h] & 1)) { ok = false; break; }
+                    tc_commit(&s_full);
+                    tc_commit(&k_empty[s]);            // K tile free once the S product has read it
+                    if (j == last) tc_commit(&q_empty); // and so is Q after the item's last S product
+                    if (!mbar_wait(&v_full, kc & 1) || !mbar_wait(&p_full, kc & 1)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t p_addr = smem_u32(sP + h * kPBytes);
 #pragma unroll
                     for (int k = 0; k < kBN / 16; ++k) {
                         // A: P, K-major, two 64-key atoms of 16 KB; B: V, MN-major, 16 key rows = 2 KB per step
                         const uint32_t pa = p_addr + (k >> 2) * (kHalf * 128) + (k & 3) * 32;
-                        mma_f16_ss(tmem_base + kTmemO + h * kD, umma_desc_sw128(pa, 1024, 16),
-                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || hc[h] > 0) ? 1u : 0u);
+                        mma_f16_ss(tmem_base + kTmemO, umma_desc_sw128(pa, 1024, 16),
+                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || !first) ? 1u : 0u);
                     }
-                    tc_commit(&o_full[h]);
-                    ++hc[h];
+                    tc_commit(&o_full);
+                    tc_commit(&v_empty);
+                    first = false;
+                    ++kc;
                 }
-                if (!ok) break;
-                tc_commit(&v_empty[0]);
-                ++kc;
             }
             if (!ok) {
-                s_abort = 1;
                 if (args.status != nullptr) atomicExch(args.status, 1);
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax + output
-        const int h = (warp - 2) >> 2;                 // half served by this warp
         const int quarter = warp & 3;                  // TMEM lanes [32 * quarter, +32)
-        const int r_local = quarter * 32 + lane;       // row inside the half
-        const int row = m0 + h * kHalf + r_local;      // query index inside the sample
+        const int r_local = quarter * 32 + lane;       // row inside the block
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t t_s = tmem_base + kTmemS + h * kBN + lane_addr;
-        const uint32_t t_o = tmem_base + kTmemO + h * kD + lane_addr;
-        uint8_t* p_row = sP + h * kPBytes + r_local * 128;
+        const uint32_t t_s = tmem_base + kTmemS + lane_addr;
+        const uint32_t t_o = tmem_base + kTmemO + lane_addr;
+        uint8_t* p_row = sP + r_local * 128;
         const int sw = r_local & 7;
-
-        float m_ref = -INFINITY;   // reference max of the exponent (lags the true max by at most 2^8)
-        float l_run = 0.f;
-        uint32_t hc = 0;
+        const float sl2 = a.scale_log2;
+        uint32_t kc = 0;
         bool ok = true;
 
-        // Visibility of key column c for this thread's row, as two half-open ranges:
-        //   [0, lim_lo) and [ns_lo, lim_hi)  with lim_hi = min(lk, causal ? row + 1 : lk)
-        const int lim_hi = plan.causal ? min(plan.lk, row + 1) : plan.lk;
-        const int lim_lo = min(plan.valid_len, lim_hi);
-        const int ns_lo = plan.ns_start;
-        const float sl2 = a.scale_log2;
+        for (int64_t w = blockIdx.x; w < work.total && ok; w += gridDim.x) {
+            int qb, h_idx, b;
+            work.decode(w, qb, h_idx, b);
+            const int m0 = qb * kBM;
+            const Plan plan = make_plan(a, b, m0);
+            if (m0 >= plan.lq) continue;
+            const int row = m0 + r_local;              // query index inside the sample
+            // Visibility of key column c for this thread's row, as two half-open ranges:
+            //   [0, lim_lo) and [ns_lo, lim_hi)  with lim_hi = min(lk, causal ? row + 1 : lk)
+            const int lim_hi = plan.causal ? min(plan.lk, row + 1) : plan.lk;
+            const int lim_lo = min(plan.valid_len, lim_hi);
+            const int ns_lo = plan.ns_start;
+            float m_ref = -INFINITY;   // reference max of the exponent (lags the true max by at most 2^8)
+            float l_run = 0.f;
+            int tiles_done = 0;
 
-        // One KV tile of this half.  FULL tiles (every key visible to every row) carry no mask code.
-        auto tile = [&](const int n0, auto full_tag) -> bool {
-            constexpr bool FULL = decltype(full_tag)::value;
-            if (!mbar_wait(&s_full[h], hc & 1)) return false;
-            tc_fence_after_sync();
-            uint32_t sr[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, sr[c]);
-            tc_wait_ld();
-            tc_fence_before_sync();
-            mbar_arrive(&s_free[h]);     // the row is in registers: S of this half may be overwritten
-
-            float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    if (!FULL) {
-                        const int col = n0 + c * 32 + i;
-                        if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) sr[c][i] = 0xff800000u;          // -inf
-                        if (!(col + 1 < lim_lo || (col + 1 >= ns_lo && col + 1 < lim_hi))) sr[c][i + 1] = 0xff800000u;
-                    }
-                    mx0 = fmaxf(mx0, __uint_as_float(sr[c][i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(sr[c][i + 1]));
-                }
-            }
-            const float mx = fmaxf(mx0, mx1);
-            // advance the reference max only for a large jump (or on the first visible key of the row)
-            float corr = 1.0f;
-            bool grow = false;
-            if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sl2 > 8.0f)) {
-                corr = m_ref == -INFINITY ? 0.f : ex2((m_ref - mx) * sl2);
-                m_ref = mx;
-                grow = true;
-            }
-            const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * sl2;
-
-            // probabilities, packed to bf16 in place (sr[c][0..15] hold the 32 values of chunk c)
-            float2 sum2 = make_float2(0.f, 0.f);
-            const float2 sl22 = make_float2(sl2, sl2);
-            const float2 nms2 = make_float2(-ms, -ms);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float2 sv = make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
-                    const float2 e = __ffma2_rn(sv, sl22, nms2);
-                    const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                    sum2 = __fadd2_rn(sum2, p);
-                    __nv_bfloat162 pb = __float22bfloat162_rn(p);
-                    sr[c][i] = *reinterpret_cast<uint32_t*>(&pb);
-                }
-            }
-            l_run = l_run * corr + (sum2.x + sum2.y);
-
-            // the previous P V of this half must be done before P is overwritten or O is rescaled
-            if (hc > 0) {
-                if (!mbar_wait(&o_full[h], (hc - 1) & 1)) return false;
+            // One KV tile.  FULL tiles (every key visible to every row) carry no mask code.
+            auto tile = [&](const int n0, auto full_tag) -> bool {
+                constexpr bool FULL = decltype(full_tag)::value;
+                if (!mbar_wait(&s_full, kc & 1)) return false;
                 tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, grow)) {  // tcgen05.ld / st are warp-wide: rescale with corr = 1 where unchanged
-                    const float2 corr2 = make_float2(corr, corr);
+                uint32_t sr[4][32];
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t r[32];
-                        tmem_ld_x32(t_o + c * 32, r);
-                        tc_wait_ld();
+                for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, sr[c]);
+                tc_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(&s_free);     // the row is in registers: S may be overwritten
+
+                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), corr2);
-                            r[2 * i] = __float_as_uint(v.x);
-                            r[2 * i + 1] = __float_as_uint(v.y);
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        if (!FULL) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int col = n0 + c * 32 + i + e;
+                                if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) sr[c][i + e] = 0xff800000u;  // -inf
+                            }
                         }
-                        tmem_st_x32(t_o + c * 32, r);
+                        mx0 = max3(mx0, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+                        mx1 = max3(mx1, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
                     }
-                    tc_wait_st();
-                    tc_fence_before_sync();
+                }
+                const float mx = fmaxf(mx0, mx1);
+                // advance the reference max only for a large jump (or on the first visible key of the row)
+                float corr = 1.0f;
+                bool grow = false;
+                if (mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sl2 > 8.0f)) {
+                    corr = m_ref == -INFINITY ? 0.f : ex2((m_ref - mx) * sl2);
+                    m_ref = mx;
+                    grow = true;
+                }
+                const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * sl2;
+
+                // probabilities, packed to bf16 in place (sr[c][0..15] then hold the 32 values of chunk c)
+                float2 sum2 = make_float2(0.f, 0.f);
+                const float2 sl22 = make_float2(sl2, sl2);
+                const float2 nms2 = make_float2(-ms, -ms);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 sv = make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
+                        const float2 e = __ffma2_rn(sv, sl22, nms2);
+                        const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                        sum2 = __fadd2_rn(sum2, p);
+                        __nv_bfloat162 pb = __float22bfloat162_rn(p);
+                        sr[c][i] = *reinterpret_cast<uint32_t*>(&pb);
+                    }
+                }
+                l_run = l_run * corr + (sum2.x + sum2.y);
+
+                // the previous P V of this item must be done before P is overwritten or O is rescaled
+                if (tiles_done > 0) {
+                    if (!mbar_wait(&o_full, (kc - 1) & 1)) return false;
+                    tc_fence_after_sync();
+                    if (__any_sync(0xffffffffu, grow)) {  // tcgen05.ld / st are warp-wide: corr = 1 where unchanged
+                        const float2 corr2 = make_float2(corr, corr);
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            uint32_t r[32];
+                            tmem_ld_x32(t_o + c * 32, r);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), corr2);
+                                r[2 * i] = __float_as_uint(v.x);
+                                r[2 * i + 1] = __float_as_uint(v.y);
+                            }
+                            tmem_st_x32(t_o + c * 32, r);
+                        }
+                        tc_wait_st();
+                        tc_fence_before_sync();
+                    }
+                }
+
+                // P -> shared memory (K-major, 128-byte swizzle): chunk c covers keys [32 c, 32 c + 32) = 4 x 16 bytes
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int chunk = ((c & 1) * 4 + q) ^ sw;
+                        *reinterpret_cast<uint4*>(atom + chunk * 16) =
+                            make_uint4(sr[c][4 * q], sr[c][4 * q + 1], sr[c][4 * q + 2], sr[c][4 * q + 3]);
+                    }
+                }
+                fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
+                mbar_arrive(&p_full);
+                ++kc;
+                ++tiles_done;
+                return true;
+            };
+
+            if (plan.half_on[0]) {
+                for (int j = 0; j < plan.n_tiles && ok; ++j) {
+                    if (!plan.active(j, 0)) continue;
+                    const int n0 = j * kBN;
+                    const bool full = (n0 + kBN <= plan.valid_len || n0 >= plan.ns_start) && n0 + kBN <= plan.lk &&
+                                      (!plan.causal || n0 + kBN - 1 <= m0);
+                    ok = full ? tile(n0, std::true_type{}) : tile(n0, std::false_type{});
                 }
             }
+            if (!ok) break;
 
-            // P -> shared memory (K-major, 128-byte swizzle): chunk c covers keys [32 c, 32 c + 32) = 4 x 16 bytes
+            float2 o_acc[kD / 2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int chunk = ((c & 1) * 4 + q) ^ sw;
-                    *reinterpret_cast<uint4*>(atom + chunk * 16) =
-                        make_uint4(sr[c][4 * q], sr[c][4 * q + 1], sr[c][4 * q + 2], sr[c][4 * q + 3]);
-                }
-            }
-            fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
-            mbar_arrive(&p_full[h]);
-            ++hc;
-            return true;
-        };
-
-        for (int j = 0; j < plan.n_tiles && ok; ++j) {
-            if (!plan.active(j, h)) continue;
-            const int n0 = j * kBN;
-            const bool full = (n0 + kBN <= plan.valid_len || n0 >= plan.ns_start) && n0 + kBN <= plan.lk &&
-                              (!plan.causal || n0 + kBN - 1 <= m0 + h * kHalf);
-            ok = full ? tile(n0, std::true_type{}) : tile(n0, std::false_type{});
-        }
-
-        float2 o_acc[kD / 2];
-#pragma unroll
-        for (int i = 0; i < kD / 2; ++i) o_acc[i] = make_float2(0.f, 0.f);
-        if (ok && hc > 0) {
-            if (!mbar_wait(&o_full[h], (hc - 1) & 1)) {
-                ok = false;
-            } else {
+            for (int i = 0; i < kD / 2; ++i) o_acc[i] = make_float2(0.f, 0.f);
+            if (tiles_done > 0) {
+                if (!mbar_wait(&o_full, (kc - 1) & 1)) { ok = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -392,32 +419,32 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 tc_fence_before_sync();
             }
-        }
-        if (!ok) {
-            s_abort = 1;
-            if (args.status != nullptr) atomicExch(args.status, 1);
-        } else if (row < plan.lq) {
-            const int64_t o_off = (plan.packed ? plan.row_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) +
-                                  static_cast<int64_t>(h_idx) * a.o_sh + static_cast<int64_t>(row) * a.o_sl;
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.o) + o_off);
-            const bool padded_q = plan.self_rows && row >= plan.valid_len && row < plan.ns_start;
-            if (padded_q) {
-                const int64_t v_off = (plan.packed ? plan.row_base * a.v_sl : static_cast<int64_t>(b) * a.v_sb) +
-                                      static_cast<int64_t>(h_idx) * a.v_sh + static_cast<int64_t>(row) * a.v_sl;
-                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.v) + v_off);
+            if (row < plan.lq) {
+                const int64_t o_off = (plan.packed ? plan.row_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) +
+                                      static_cast<int64_t>(h_idx) * a.o_sh + static_cast<int64_t>(row) * a.o_sl;
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.o) + o_off);
+                const bool padded_q = plan.self_rows && row >= plan.valid_len && row < plan.ns_start;
+                if (padded_q) {
+                    const int64_t v_off = (plan.packed ? plan.row_base * a.v_sl : static_cast<int64_t>(b) * a.v_sb) +
+                                          static_cast<int64_t>(h_idx) * a.v_sh + static_cast<int64_t>(row) * a.v_sl;
+                    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.v) + v_off);
 #pragma unroll
-                for (int c = 0; c < kD / 8; ++c) dst[c] = src[c];
-            } else {
-                const float inv1 = l_run > 0.f ? 1.0f / l_run : 0.f;
-                const float2 inv = make_float2(inv1, inv1);
+                    for (int c = 0; c < kD / 8; ++c) dst[c] = src[c];
+                } else {
+                    const float inv1 = l_run > 0.f ? 1.0f / l_run : 0.f;
+                    const float2 inv = make_float2(inv1, inv1);
 #pragma unroll
-                for (int c = 0; c < kD / 8; ++c) {
-                    float2 v4[4];
+                    for (int c = 0; c < kD / 8; ++c) {
+                        float2 v4[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) v4[e] = __fmul2_rn(o_acc[4 * c + e], inv);
-                    dst[c] = Vec16<__nv_bfloat16>::pack2(v4);
+                        for (int e = 0; e < 4; ++e) v4[e] = __fmul2_rn(o_acc[4 * c + e], inv);
+                        dst[c] = Vec16<__nv_bfloat16>::pack2(v4);
+                    }
                 }
             }
+        }
+        if (!ok) {
+            if (args.status != nullptr) atomicExch(args.status, 1);
         }
     }
 
@@ -480,15 +507,18 @@ int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t
         !make_tmap(&tv, a.v, k_rows, a.H, nb, a.v_sl, a.v_sh, packed ? 0 : a.v_sb))
         return TB200_ERR_DRIVER;
     const DeviceInfo& dev = device_info();
-    const size_t smem = (kHalves + 3) * kTileBytes + kHalves * kPBytes + 1024;
+    const size_t smem = 4 * kTileBytes + kPBytes + 1024;
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
         cudaFuncSetAttribute(attn_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         attr_set[dev.index] = true;
     }
     Tc05Args args{a, status};
-    dim3 grid((max_lq + kBM - 1) / kBM, a.H, a.B);
-    attn_tc05_kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, args);
+    (void)max_lq;
+    const int64_t items = static_cast<int64_t>((a.Lq + kBM - 1) / kBM) * a.H * a.B;
+    int64_t grid = static_cast<int64_t>(dev.sm_count) * 2;  // persistent: two CTAs per SM
+    if (grid > items) grid = items;
+    attn_tc05_kernel<<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(tq, tk, tv, args);
     count_launch();
     return launch_status();
 }
