@@ -4,7 +4,7 @@
 // (256 TMEM columns and 97 KB of shared memory each), so one runs its softmax while the other owns the
 // tensor cores, and the TMA producer of a CTA already fetches the next item's Q / K / V while the
 // current item is being finished.  Roles (192 threads):
-//   warp 0       TMA producer: Q once, then a 2-stage ring of K tiles and a single V tile buffer
+//   warp 0       TMA producer: Q per item, K and V tiles alternating through one ring of three slots
 //                (128 keys x 128 bytes each, 128-byte swizzle, no multicast)
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
 //   warps 2..5   softmax: one thread per query row
@@ -130,16 +130,16 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                  const __grid_constant__ CUtensorMap tmap_v, const Tc05Args args) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_full, q_empty;
-    __shared__ uint64_t k_full[2], k_empty[2], v_full, v_empty;
+    __shared__ uint64_t kv_full[3], kv_empty[3];  // one ring of three tile slots: K_0, V_0, K_1, V_1, ...
     __shared__ uint64_t s_full, s_free, p_full, o_full;
     __shared__ uint32_t tmem_base_slot;
 
     const AttnArgs& a = args.a;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                              // 16 KB
-    uint8_t* sK = sQ + kTileBytes;                   // 2 stages x 16 KB
-    uint8_t* sV = sK + 2 * kTileBytes;               // 16 KB (V is only needed once P is ready)
-    uint8_t* sP = sV + kTileBytes;                   // 32 KB
+    uint8_t* sKV = sQ + kTileBytes;                  // 3 slots x 16 KB: K and V tiles alternate through one ring,
+                                                     // so K_{j+1} and V_{j+1} are both in flight during tile j
+    uint8_t* sP = sKV + 3 * kTileBytes;              // 32 KB
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -152,12 +152,10 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
         mbar_init(&q_empty, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_empty[i], 1);
         }
-        mbar_init(&v_full, 1);
-        mbar_init(&v_empty, 1);
         mbar_init(&s_full, 1);
         mbar_init(&s_free, kSoftmaxThreads);
         mbar_init(&p_full, kSoftmaxThreads);
@@ -195,13 +193,14 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 ++qc;
                 for (int j = 0; j < plan.n_tiles && ok; ++j) {
                     if (!plan.active(j, 0)) continue;
-                    const uint32_t s = kc & 1;
-                    if (!mbar_wait(&k_empty[s], ((kc >> 1) & 1) ^ 1)) { ok = false; break; }
-                    mbar_expect_tx(&k_full[s], kTileBytes);
-                    tma_load_4d(sK + s * kTileBytes, &tmap_k, 0, row0 + j * kBN, h_idx, bz, &k_full[s]);
-                    if (!mbar_wait(&v_empty, (kc & 1) ^ 1)) { ok = false; break; }
-                    mbar_expect_tx(&v_full, kTileBytes);
-                    tma_load_4d(sV, &tmap_v, 0, row0 + j * kBN, h_idx, bz, &v_full);
+                    for (int which = 0; which < 2; ++which) {  // K tile, then V tile
+                        const uint32_t t = 2 * kc + which;
+                        const uint32_t slot = t % 3;
+                        if (!mbar_wait(&kv_empty[slot], ((t / 3) & 1) ^ 1)) { ok = false; break; }
+                        mbar_expect_tx(&kv_full[slot], kTileBytes);
+                        tma_load_4d(sKV + slot * kTileBytes, which == 0 ? &tmap_k : &tmap_v, 0, row0 + j * kBN, h_idx, bz,
+                                    &kv_full[slot]);
+                    }
                     ++kc;
                 }
             }
@@ -216,7 +215,6 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, kHalf, kD);   // P K-major, V MN-major (head dim contiguous)
             const uint32_t q_addr = smem_u32(sQ);
             const uint32_t p_addr = smem_u32(sP);
-            const uint32_t v_addr = smem_u32(sV);
             uint32_t qc = 0, kc = 0;
             bool ok = true;
             for (int64_t w = blockIdx.x; w < work.total && ok; w += gridDim.x) {
@@ -226,36 +224,47 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (!plan.half_on[0] || plan.n_tiles == 0) continue;
                 if (!mbar_wait(&q_full, qc & 1)) { ok = false; break; }
                 ++qc;
-                int last = -1;
-                for (int j = plan.n_tiles - 1; j >= 0; --j)
-                    if (plan.active(j, 0)) { last = j; break; }
-                bool first = true;
-                for (int j = 0; j < plan.n_tiles && ok; ++j) {
-                    if (!plan.active(j, 0)) continue;
-                    const uint32_t s = kc & 1;
-                    if (!mbar_wait(&k_full[s], (kc >> 1) & 1) || !mbar_wait(&s_free, (kc & 1) ^ 1)) { ok = false; break; }
+                // S of tile j + 1 is issued before P V of tile j: the softmax of j runs from registers, so the
+                // tensor cores fill the S buffer again while it computes
+                auto issue_s = [&](uint32_t tile_index, bool last_of_item) -> bool {
+                    const uint32_t t = 2 * tile_index;
+                    const uint32_t slot = t % 3;
+                    if (!mbar_wait(&kv_full[slot], (t / 3) & 1) || !mbar_wait(&s_free, (tile_index & 1) ^ 1)) return false;
                     tc_fence_after_sync();
-                    const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
+                    const uint32_t k_addr = smem_u32(sKV + slot * kTileBytes);
 #pragma unroll
                     for (int k = 0; k < kD / 16; ++k) {
                         mma_f16_ss(tmem_base + kTmemS, umma_desc_sw128(q_addr + k * 32, 1024, 16),
                                    umma_desc_sw128(k_addr + k * 32, 1024, 16), idesc_s, k > 0 ? 1u : 0u);
                     }
                     tc_commit(&s_full);
-                    tc_commit(&k_empty[s]);            // K tile free once the S product has read it
-                    if (j == last) tc_commit(&q_empty); // and so is Q after the item's last S product
-                    if (!mbar_wait(&v_full, kc & 1) || !mbar_wait(&p_full, kc & 1)) { ok = false; break; }
+                    tc_commit(&kv_empty[slot]);             // K tile free once the S product has read it
+                    if (last_of_item) tc_commit(&q_empty);   // and so is Q after the item's last S product
+                    return true;
+                };
+                int n_active = 0;
+                for (int j = 0; j < plan.n_tiles; ++j) n_active += plan.active(j, 0) ? 1 : 0;
+                if (n_active == 0) {          // nothing visible: hand Q back to the producer directly
+                    mbar_arrive(&q_empty);
+                    continue;
+                }
+                if (!issue_s(kc, n_active == 1)) { ok = false; break; }
+                for (int i = 0; i < n_active && ok; ++i) {
+                    if (i + 1 < n_active && !issue_s(kc + 1, i + 2 == n_active)) { ok = false; break; }
+                    const uint32_t t = 2 * kc + 1;
+                    const uint32_t slot = t % 3;
+                    if (!mbar_wait(&kv_full[slot], (t / 3) & 1) || !mbar_wait(&p_full, kc & 1)) { ok = false; break; }
                     tc_fence_after_sync();
+                    const uint32_t v_addr = smem_u32(sKV + slot * kTileBytes);
 #pragma unroll
                     for (int k = 0; k < kBN / 16; ++k) {
                         // A: P, K-major, two 64-key atoms of 16 KB; B: V, MN-major, 16 key rows = 2 KB per step
                         const uint32_t pa = p_addr + (k >> 2) * (kHalf * 128) + (k & 3) * 32;
                         mma_f16_ss(tmem_base + kTmemO, umma_desc_sw128(pa, 1024, 16),
-                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || !first) ? 1u : 0u);
+                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || i > 0) ? 1u : 0u);
                     }
                     tc_commit(&o_full);
-                    tc_commit(&v_empty);
-                    first = false;
+                    tc_commit(&kv_empty[slot]);
                     ++kc;
                 }
             }
@@ -292,32 +301,36 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             float l_run = 0.f;
             int tiles_done = 0;
 
-            // One KV tile.  FULL tiles (every key visible to every row) carry no mask code.
+            // One KV tile.  FULL tiles (every key visible to every row) carry no mask code.  The tile is read from
+            // TMEM twice (row max, then probabilities) in rolled loops over 32-column chunks: the instruction
+            // footprint stays small enough for the instruction caches, which a fully unrolled 128-column body
+            // held in registers did not.
             auto tile = [&](const int n0, auto full_tag) -> bool {
                 constexpr bool FULL = decltype(full_tag)::value;
                 if (!mbar_wait(&s_full, kc & 1)) return false;
                 tc_fence_after_sync();
-                uint32_t sr[4][32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, sr[c]);
-                tc_wait_ld();
-                tc_fence_before_sync();
-                mbar_arrive(&s_free);     // the row is in registers: S may be overwritten
+                // visibility of the 32 columns from `base` on as a bit mask
+                auto chunk_mask = [&](const int base) -> uint32_t {
+                    auto low = [](int k) -> uint32_t { return k <= 0 ? 0u : (k >= 32 ? 0xffffffffu : ((1u << k) - 1u)); };
+                    return low(lim_lo - base) | (low(lim_hi - base) & ~low(ns_lo - base));
+                };
 
                 float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
+#pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_x32(t_s + c * 32, r);
+                    tc_wait_ld();
+                    if (!FULL) {
+                        const uint32_t vis = chunk_mask(n0 + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (!((vis >> i) & 1u)) r[i] = 0xff800000u;  // -inf
+                    }
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        if (!FULL) {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int col = n0 + c * 32 + i + e;
-                                if (!(col < lim_lo || (col >= ns_lo && col < lim_hi))) sr[c][i + e] = 0xff800000u;  // -inf
-                            }
-                        }
-                        mx0 = max3(mx0, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-                        mx1 = max3(mx1, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+                        mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                        mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
                     }
                 }
                 const float mx = fmaxf(mx0, mx1);
@@ -331,31 +344,13 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 const float ms = (m_ref == -INFINITY ? 0.f : m_ref) * sl2;
 
-                // probabilities, packed to bf16 in place (sr[c][0..15] then hold the 32 values of chunk c)
-                float2 sum2 = make_float2(0.f, 0.f);
-                const float2 sl22 = make_float2(sl2, sl2);
-                const float2 nms2 = make_float2(-ms, -ms);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float2 sv = make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
-                        const float2 e = __ffma2_rn(sv, sl22, nms2);
-                        const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                        sum2 = __fadd2_rn(sum2, p);
-                        __nv_bfloat162 pb = __float22bfloat162_rn(p);
-                        sr[c][i] = *reinterpret_cast<uint32_t*>(&pb);
-                    }
-                }
-                l_run = l_run * corr + (sum2.x + sum2.y);
-
                 // the previous P V of this item must be done before P is overwritten or O is rescaled
                 if (tiles_done > 0) {
                     if (!mbar_wait(&o_full, (kc - 1) & 1)) return false;
                     tc_fence_after_sync();
                     if (__any_sync(0xffffffffu, grow)) {  // tcgen05.ld / st are warp-wide: corr = 1 where unchanged
                         const float2 corr2 = make_float2(corr, corr);
-#pragma unroll
+#pragma unroll 1
                         for (int c = 0; c < 2; ++c) {
                             uint32_t r[32];
                             tmem_ld_x32(t_o + c * 32, r);
@@ -373,17 +368,44 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     }
                 }
 
-                // P -> shared memory (K-major, 128-byte swizzle): chunk c covers keys [32 c, 32 c + 32) = 4 x 16 bytes
-#pragma unroll
+                // probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle): chunk c covers keys
+                // [32 c, 32 c + 32) = 4 x 16 bytes of the 64-key atom c / 2
+                float2 sum2 = make_float2(0.f, 0.f);
+                const float2 sl22 = make_float2(sl2, sl2);
+                const float2 nms2 = make_float2(-ms, -ms);
+#pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_x32(t_s + c * 32, r);
+                    tc_wait_ld();
+                    if (c == 3) {              // the whole row has been read: S may be overwritten
+                        tc_fence_before_sync();
+                        mbar_arrive(&s_free);
+                    }
+                    if (!FULL) {
+                        const uint32_t vis = chunk_mask(n0 + c * 32);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (!((vis >> i) & 1u)) r[i] = 0xff800000u;
+                    }
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 sv = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                        const float2 e = __ffma2_rn(sv, sl22, nms2);
+                        const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                        sum2 = __fadd2_rn(sum2, p);
+                        __nv_bfloat162 pb = __float22bfloat162_rn(p);
+                        pk[i] = *reinterpret_cast<uint32_t*>(&pb);
+                    }
                     uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int chunk = ((c & 1) * 4 + q) ^ sw;
-                        *reinterpret_cast<uint4*>(atom + chunk * 16) =
-                            make_uint4(sr[c][4 * q], sr[c][4 * q + 1], sr[c][4 * q + 2], sr[c][4 * q + 3]);
+                        *reinterpret_cast<uint4*>(atom + chunk * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
                     }
                 }
+                l_run = l_run * corr + (sum2.x + sum2.y);
                 fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
                 mbar_arrive(&p_full);
                 ++kc;
