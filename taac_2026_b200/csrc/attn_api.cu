@@ -45,10 +45,10 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     const bool tc_ok = attn_tc05_supported(a, D, dtype) && (cu_rows == nullptr || total_rows > 0);
     if (kernel == 2 && !tc_ok) return TB200_ERR_UNSUPPORTED;
     if (kernel < 0 || kernel > 2) return TB200_ERR_UNSUPPORTED;
-    // Automatic choice: the tcgen05 kernel wins on long non-causal rows (its 256-row CTAs amortise the
-    // per-tile softmax round trip through TMEM); causal or short samples are still faster on the 64-row
-    // mma.sync tiles, several CTAs per SM.
-    if (kernel == 2 || (kernel == 0 && tc_ok && !a.causal && cu_rows == nullptr && Lq >= 512))
+    // Automatic choice: the tcgen05 kernel wherever it applies (bf16, head_dim 64, no key_valid map); measured
+    // on full-length rows it leads the mma.sync kernel from 128 keys up, causal or not.  Samples shorter than
+    // one 128-row block leave most of its tile idle, so those stay on the 64-row mma.sync tiles.
+    if (kernel == 2 || (kernel == 0 && tc_ok && Lq >= 128))
         return attn_tc05_forward(a, Lq, total_rows, status_word, s);
     return attn_mma_forward(a, D, dtype, Lq, s);
 }

@@ -41,11 +41,13 @@ constexpr int kBN = 128;          // keys per tile
 constexpr int kThreads = 64 + kHalves * 128;
 constexpr int kSoftmaxThreads = 128;  // per half
 constexpr uint32_t kTileBytes = kBN * kD * 2;       // 16 KB: one Q half, K tile or V tile
-constexpr uint32_t kPBytes = kHalf * kBN * 2;       // 32 KB: P of one half (two 64-key swizzle atoms)
+constexpr uint32_t kSlots = 5;                      // K / V tile ring
 constexpr uint32_t kTmemCols = kHalves == 1 ? 256 : 512;
 // TMEM columns: S of half h at h * 128, O of half h behind the S blocks at h * 64
 constexpr uint32_t kTmemS = 0;
 constexpr uint32_t kTmemO = kHalves * 128;
+// P (bf16 probabilities, two per 32-bit column) is the TMEM A operand of the P V product
+constexpr uint32_t kTmemP = kTmemO + kHalves * 64;
 
 struct Tc05Args {
     AttnArgs a;
@@ -130,16 +132,15 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                  const __grid_constant__ CUtensorMap tmap_v, const Tc05Args args) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_full, q_empty;
-    __shared__ uint64_t kv_full[3], kv_empty[3];  // one ring of three tile slots: K_0, V_0, K_1, V_1, ...
-    __shared__ uint64_t s_full, s_free, p_full, o_full;
+    __shared__ uint64_t kv_full[kSlots], kv_empty[kSlots];  // one ring of tile slots: K_0, V_0, K_1, V_1, ...
+    __shared__ uint64_t s_full, s_free, p_full[2], o_full;   // p_full[i]: P of keys [64 i, 64 i + 64) of the tile is in TMEM
     __shared__ uint32_t tmem_base_slot;
 
     const AttnArgs& a = args.a;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                              // 16 KB
-    uint8_t* sKV = sQ + kTileBytes;                  // 3 slots x 16 KB: K and V tiles alternate through one ring,
-                                                     // so K_{j+1} and V_{j+1} are both in flight during tile j
-    uint8_t* sP = sKV + 3 * kTileBytes;              // 32 KB
+    uint8_t* sKV = sQ + kTileBytes;                  // kSlots x 16 KB: K and V tiles alternate through one ring,
+                                                     // so the tiles of the next two steps are in flight during tile j
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -152,13 +153,14 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
         mbar_init(&q_empty, 1);
-        for (int i = 0; i < 3; ++i) {
+        for (int i = 0; i < static_cast<int>(kSlots); ++i) {
             mbar_init(&kv_full[i], 1);
             mbar_init(&kv_empty[i], 1);
         }
         mbar_init(&s_full, 1);
         mbar_init(&s_free, kSoftmaxThreads);
-        mbar_init(&p_full, kSoftmaxThreads);
+        mbar_init(&p_full[0], kSoftmaxThreads);
+        mbar_init(&p_full[1], kSoftmaxThreads);
         mbar_init(&o_full, 1);
         fence_mbar_init();
     }
@@ -195,8 +197,8 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     if (!plan.active(j, 0)) continue;
                     for (int which = 0; which < 2; ++which) {  // K tile, then V tile
                         const uint32_t t = 2 * kc + which;
-                        const uint32_t slot = t % 3;
-                        if (!mbar_wait(&kv_empty[slot], ((t / 3) & 1) ^ 1)) { ok = false; break; }
+                        const uint32_t slot = t % kSlots;
+                        if (!mbar_wait(&kv_empty[slot], ((t / kSlots) & 1) ^ 1)) { ok = false; break; }
                         mbar_expect_tx(&kv_full[slot], kTileBytes);
                         tma_load_4d(sKV + slot * kTileBytes, which == 0 ? &tmap_k : &tmap_v, 0, row0 + j * kBN, h_idx, bz,
                                     &kv_full[slot]);
@@ -214,7 +216,6 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const uint32_t idesc_s = umma_idesc(1, 1, 0, 0, kHalf, kBN);  // bf16 x bf16, Q and K both K-major
             const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, kHalf, kD);   // P K-major, V MN-major (head dim contiguous)
             const uint32_t q_addr = smem_u32(sQ);
-            const uint32_t p_addr = smem_u32(sP);
             uint32_t qc = 0, kc = 0;
             bool ok = true;
             for (int64_t w = blockIdx.x; w < work.total && ok; w += gridDim.x) {
@@ -228,8 +229,8 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 // tensor cores fill the S buffer again while it computes
                 auto issue_s = [&](uint32_t tile_index, bool last_of_item) -> bool {
                     const uint32_t t = 2 * tile_index;
-                    const uint32_t slot = t % 3;
-                    if (!mbar_wait(&kv_full[slot], (t / 3) & 1) || !mbar_wait(&s_free, (tile_index & 1) ^ 1)) return false;
+                    const uint32_t slot = t % kSlots;
+                    if (!mbar_wait(&kv_full[slot], (t / kSlots) & 1) || !mbar_wait(&s_free, (tile_index & 1) ^ 1)) return false;
                     tc_fence_after_sync();
                     const uint32_t k_addr = smem_u32(sKV + slot * kTileBytes);
 #pragma unroll
@@ -248,21 +249,29 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     mbar_arrive(&q_empty);
                     continue;
                 }
+                // Per tile the issuer follows the order in which the softmax warps release things: first half of P
+                // -> P V over keys [0, 64); S buffer free -> S of the next tile; second half of P -> rest of P V.
+                // The first half of P V and the next S product run while the softmax still works on the tile.
                 if (!issue_s(kc, n_active == 1)) { ok = false; break; }
                 for (int i = 0; i < n_active && ok; ++i) {
-                    if (i + 1 < n_active && !issue_s(kc + 1, i + 2 == n_active)) { ok = false; break; }
                     const uint32_t t = 2 * kc + 1;
-                    const uint32_t slot = t % 3;
-                    if (!mbar_wait(&kv_full[slot], (t / 3) & 1) || !mbar_wait(&p_full, kc & 1)) { ok = false; break; }
-                    tc_fence_after_sync();
+                    const uint32_t slot = t % kSlots;
                     const uint32_t v_addr = smem_u32(sKV + slot * kTileBytes);
+                    if (!mbar_wait(&kv_full[slot], (t / kSlots) & 1)) { ok = false; break; }
+#pragma unroll 1
+                    for (int half = 0; half < 2; ++half) {
+                        if (half == 1 && i + 1 < n_active && !issue_s(kc + 1, i + 2 == n_active)) { ok = false; break; }
+                        if (!mbar_wait(&p_full[half], kc & 1)) { ok = false; break; }
+                        tc_fence_after_sync();
 #pragma unroll
-                    for (int k = 0; k < kBN / 16; ++k) {
-                        // A: P, K-major, two 64-key atoms of 16 KB; B: V, MN-major, 16 key rows = 2 KB per step
-                        const uint32_t pa = p_addr + (k >> 2) * (kHalf * 128) + (k & 3) * 32;
-                        mma_f16_ss(tmem_base + kTmemO, umma_desc_sw128(pa, 1024, 16),
-                                   umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || i > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < kBN / 32; ++kk) {
+                            const int k = half * (kBN / 32) + kk;
+                            // A: P from TMEM, 16 keys = 8 columns per step; B: V, MN-major, 16 key rows = 2 KB per step
+                            mma_f16_ts(tmem_base + kTmemO, tmem_base + kTmemP + k * 8,
+                                       umma_desc_sw128(v_addr + k * 2048, 1024, 1024), idesc_o, (k > 0 || i > 0) ? 1u : 0u);
+                        }
                     }
+                    if (!ok) break;
                     tc_commit(&o_full);
                     tc_commit(&kv_empty[slot]);
                     ++kc;
@@ -279,8 +288,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t t_s = tmem_base + kTmemS + lane_addr;
         const uint32_t t_o = tmem_base + kTmemO + lane_addr;
-        uint8_t* p_row = sP + r_local * 128;
-        const int sw = r_local & 7;
+        const uint32_t t_p = tmem_base + kTmemP + lane_addr;
         const float sl2 = a.scale_log2;
         uint32_t kc = 0;
         bool ok = true;
@@ -315,22 +323,27 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     return low(lim_lo - base) | (low(lim_hi - base) & ~low(ns_lo - base));
                 };
 
+                // pass 1, row max: the four chunk loads are issued together, so one TMEM latency is exposed
                 float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_x32(t_s + c * 32, r);
-                    tc_wait_ld();
-                    if (!FULL) {
-                        const uint32_t vis = chunk_mask(n0 + c * 32);
+                {
+                    uint32_t sr[4][32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (!((vis >> i) & 1u)) r[i] = 0xff800000u;  // -inf
-                    }
+                    for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, sr[c]);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                        mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    for (int c = 0; c < 4; ++c) tc_wait_ld(sr[c]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        if (!FULL) {
+                            const uint32_t vis = chunk_mask(n0 + c * 32);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (!((vis >> i) & 1u)) sr[c][i] = 0xff800000u;  // -inf
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            mx0 = max3(mx0, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+                            mx1 = max3(mx1, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+                        }
                     }
                 }
                 const float mx = fmaxf(mx0, mx1);
@@ -373,15 +386,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 float2 sum2 = make_float2(0.f, 0.f);
                 const float2 sl22 = make_float2(sl2, sl2);
                 const float2 nms2 = make_float2(-ms, -ms);
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_x32(t_s + c * 32, r);
-                    tc_wait_ld();
-                    if (c == 3) {              // the whole row has been read: S may be overwritten
-                        tc_fence_before_sync();
-                        mbar_arrive(&s_free);
-                    }
+                auto emit = [&](const int c, uint32_t (&r)[32]) {
                     if (!FULL) {
                         const uint32_t vis = chunk_mask(n0 + c * 32);
 #pragma unroll
@@ -398,16 +403,32 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         __nv_bfloat162 pb = __float22bfloat162_rn(p);
                         pk[i] = *reinterpret_cast<uint32_t*>(&pb);
                     }
-                    uint8_t* atom = p_row + (c >> 1) * (kHalf * 128);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int chunk = ((c & 1) * 4 + q) ^ sw;
-                        *reinterpret_cast<uint4*>(atom + chunk * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                    tmem_st_x16(t_p + c * 16, pk);
+                };
+                // pass 2: the load of chunk c + 1 is in flight while chunk c is turned into probabilities
+                {
+                    uint32_t ra[32], rb[32];
+                    tmem_ld_x32(t_s, ra);
+                    tc_wait_ld(ra);
+#pragma unroll 1
+                    for (int c = 0; c < 4; c += 2) {
+                        tmem_ld_x32(t_s + (c + 1) * 32, rb);
+                        emit(c, ra);
+                        tc_wait_ld(rb);
+                        if (c == 0) {
+                            tmem_ld_x32(t_s + 2 * 32, ra);
+                        } else {               // the whole row has been read: S may be overwritten
+                            tc_fence_before_sync();
+                            mbar_arrive(&s_free);
+                        }
+                        emit(c + 1, rb);
+                        tc_wait_st();          // this half of P is in TMEM before the issuer is told
+                        tc_fence_before_sync();
+                        mbar_arrive(&p_full[c >> 1]);
+                        if (c == 0) tc_wait_ld(ra);
                     }
                 }
                 l_run = l_run * corr + (sum2.x + sum2.y);
-                fence_proxy_async_smem();    // P (generic-proxy writes) -> visible to the tensor cores
-                mbar_arrive(&p_full);
                 ++kc;
                 ++tiles_done;
                 return true;
@@ -529,7 +550,7 @@ int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t
         !make_tmap(&tv, a.v, k_rows, a.H, nb, a.v_sl, a.v_sh, packed ? 0 : a.v_sb))
         return TB200_ERR_DRIVER;
     const DeviceInfo& dev = device_info();
-    const size_t smem = 4 * kTileBytes + kPBytes + 1024;
+    const size_t smem = (1 + kSlots) * kTileBytes + 1024;
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
         cudaFuncSetAttribute(attn_tc05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -207,7 +207,12 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0 && sc.active) {
             const uint32_t idesc = umma_idesc(0, 0, 0, 0, kBM, kBN);  // e4m3 x e4m3 -> f32, both K-major
-            uint32_t it = 0, acc_it = 0, b_phase = 0;
+            // This one thread sets the pace of the tensor pipe, so its loop carries no division and builds each
+            // descriptor with one add: the start-address field counts 16-byte units, a 32-byte K step adds 2.
+            const uint64_t desc0 = umma_desc_sw128(0, 1024, 16);
+            const uint32_t ring_lo = (smem_u32(ring) & 0x3FFFFu) >> 4;
+            const uint32_t bres_lo = B_RES ? (smem_u32(b_res) & 0x3FFFFu) >> 4 : 0u;
+            uint32_t s = 0, ph = 0, buf = 0, aph = 0, b_phase = 0;
             bool ok = true;
             for (int n = sc.n_first; n < n_tiles && ok; n += sc.n_step) {
                 if (B_RES) {
@@ -215,28 +220,27 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     b_phase ^= 1;
                 }
                 for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G) {
-                    for (int kb = 0; kb < k_blocks; ++kb, ++it, ++acc_it) {
-                        const uint32_t buf = acc_it & 1;
-                        const uint32_t aph = (acc_it >> 1) & 1;
-                        const uint32_t s = it % STAGES;
-                        const uint32_t ph = (it / STAGES) & 1;
-                        if (!mbar_wait(&tmem_empty[buf], aph ^ 1) || !mbar_wait(&full_bar[s], ph) ||
-                            *reinterpret_cast<volatile int*>(&s_abort)) {
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait(&tmem_empty[buf], aph ^ 1) || !mbar_wait(&full_bar[s], ph)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t a_addr = smem_u32(ring + static_cast<size_t>(s) * STAGE_BYTES);
-                        const uint32_t b_addr = B_RES ? smem_u32(b_res + static_cast<size_t>(kb) * kBBytes) : a_addr + kABytes;
+                        const uint32_t a_lo = ring_lo + s * (STAGE_BYTES >> 4);
+                        const uint32_t b_lo = B_RES ? bres_lo + static_cast<uint32_t>(kb) * (kBBytes >> 4) : a_lo + (kABytes >> 4);
+                        const uint64_t da = desc0 + a_lo;
+                        const uint64_t db = desc0 + b_lo;
                         const uint32_t d_tmem = tmem_base + buf * kBN;
 #pragma unroll
-                        for (int k = 0; k < kBK / 32; ++k) {
-                            const uint64_t da = umma_desc_sw128(a_addr + k * 32, 1024, 16);
-                            const uint64_t db = umma_desc_sw128(b_addr + k * 32, 1024, 16);
-                            mma_f8_ss(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
-                        }
+                        for (int k = 0; k < kBK / 32; ++k) mma_f8_ss(d_tmem, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
                         tc_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
                         tc_commit(&tmem_full[buf]);   // the partial product of this K block is complete
+                        if (++s == STAGES) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                        aph ^= buf;                   // the accumulator phase flips after buffer 1
+                        buf ^= 1;
                     }
                 }
             }
