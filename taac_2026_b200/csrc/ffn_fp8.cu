@@ -10,12 +10,16 @@
 // work on the next K block (two TMEM accumulator buffers of 256 columns).
 //
 // Roles in a CTA of 576 threads (persistent, one CTA per SM, static round-robin over output tiles):
-//   warp 0       TMA producer: 4-stage ring of {A 128 x 128 B, B 256 x 128 B} tiles
+//   warp 0       TMA producer: ring of {A 128 x 128 B, B 256 x 128 B} tiles (3 to 4 stages)
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
 //   warps 2..17  promotion + epilogue: each thread owns one output row and 64 of the 256 columns
 //                (four warps per TMEM lane quarter, so that four warps per scheduler hide each
 //                other's tcgen05.ld and MUFU latencies; the per-element instruction budget at K = 512
 //                is only about eight issue slots, hence packed fp32x2 math and a tanh-based SiLU)
+// The output tile leaves through shared memory: every epilogue thread writes its 16-byte pieces into a
+// 128-byte-swizzled staging tile and one thread hands the tile to TMA, so global memory sees full rows of
+// the tile instead of one 32-byte sector per lane; the residual tile of the linear mode arrives the same
+// way, fetched by TMA while the K loop runs.
 // Every wait on an mbarrier is bounded; a wait that gives up raises the status word and all roles
 // drain out through the same final barrier, where the TMEM allocation is released.
 #include <cuda_fp8.h>
@@ -34,7 +38,6 @@ namespace {
 constexpr int kBM = 128;          // output rows per tile
 constexpr int kBN = 256;          // output columns per tile
 constexpr int kBK = 128;          // K bytes (= e4m3 elements) per stage: one 128-byte swizzle atom
-constexpr int kStages = 4;
 constexpr int kThreads = 576;
 constexpr int kEpiThreads = 512;
 constexpr uint32_t kABytes = kBM * kBK;  // 16 KB
@@ -63,7 +66,9 @@ struct GemmArgs {
 };
 
 // silu(x) = x * sigmoid(x) = h * tanh(h) + h with h = x / 2: one MUFU and two FMA-pipe instructions.
-// tanh.approx has about 11 bits of accuracy, far below the 3-bit mantissa of the e4m3 result.
+// tanh.approx has about 11 bits of accuracy, far below the 3-bit mantissa of the e4m3 result.  (The packed
+// tanh.approx.f16x2 halves the MUFU count but was measured no faster here, and its absolute error near -1
+// shows in the hidden activation of strongly negative inputs.)
 __device__ __forceinline__ float silu(float x) {
     const float h = 0.5f * x;
     float t;
@@ -108,18 +113,32 @@ __device__ __forceinline__ Schedule make_schedule(int n_tiles) {
     return sc;
 }
 
-constexpr int kStagesRes = 5;     // activation stages when the weight tile is resident
 constexpr int kMaxStages = 5;
+constexpr uint32_t kOutBoxBytes = kBM * 128;   // one staging box: 128 rows x 128 bytes, 128-byte swizzle
+
+// Shared-memory plan per instantiation.  Static shared memory takes about 6 KB, so tiles + staging stay
+// at or below 208 KB.  B_RES keeps up to four 32 KB weight K blocks resident.
+template <int MODE, bool B_RES>
+struct Plan {
+    static constexpr int kOutBoxes = MODE == kSwiGLU ? 1 : (MODE == kSiLU ? 2 : 4);
+    static constexpr uint32_t kOutBytes = kOutBoxes * kOutBoxBytes;
+    static constexpr int kStagesN = B_RES ? (MODE == kSwiGLU ? 4 : 3) : (MODE == kSwiGLU ? 4 : 3);
+    static constexpr uint32_t kStageBytesN = B_RES ? kABytes : kStageBytes;
+    static constexpr size_t tiles_bytes(int k_blocks) {
+        return (B_RES ? static_cast<size_t>(k_blocks) * kBBytes : 0) + static_cast<size_t>(kStagesN) * kStageBytesN + kOutBytes;
+    }
+};
 constexpr int kMaxKBlocks = 64;   // K <= 8192
 
 template <int MODE, bool B_RES>
 __global__ void __launch_bounds__(kThreads, 1)
 ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const GemmArgs g) {
+                const __grid_constant__ CUtensorMap tmap_o, const __grid_constant__ CUtensorMap tmap_r, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kMaxStages];
     __shared__ uint64_t empty_bar[kMaxStages];
     __shared__ uint64_t b_full;
+    __shared__ uint64_t res_full;   // residual tile of the linear mode has landed in the staging tile
     __shared__ uint64_t tmem_full[2];
     __shared__ uint64_t tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -136,10 +155,12 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     const int64_t m_tiles = (g.M + kBM - 1) / kBM;
     const int n_tiles = g.N / kBN;
     const int k_blocks = g.K / kBK;
-    constexpr int STAGES = B_RES ? kStagesRes : kStages;
-    constexpr uint32_t STAGE_BYTES = B_RES ? kABytes : kStageBytes;
+    using P = Plan<MODE, B_RES>;
+    constexpr int STAGES = P::kStagesN;
+    constexpr uint32_t STAGE_BYTES = P::kStageBytesN;
     uint8_t* b_res = smem;                                              // [k_blocks][kBBytes] when B_RES
     uint8_t* ring = B_RES ? smem + static_cast<size_t>(k_blocks) * kBBytes : smem;
+    uint8_t* out_s = ring + static_cast<size_t>(STAGES) * STAGE_BYTES;    // staging tile: kOutBoxes boxes of 16 KB
     const Schedule sc = make_schedule(n_tiles);
 
     if (threadIdx.x == 0) {
@@ -148,6 +169,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&b_full, 1);
+        mbar_init(&res_full, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], kEpiThreads);
@@ -299,6 +321,16 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G, ++tile_count) {
                 const int64_t row = m * kBM + row_in_tile;
                 const bool row_ok = row < g.M;
+                const int m0 = static_cast<int>(m) * kBM;
+                if (MODE == kLinear && g.residual != nullptr && et == 0) {
+                    // the staging tile is free once the previous tile's store has read it; the residual tile
+                    // then lands in it while the K loop runs
+                    bulk_wait_read<0>();
+                    mbar_expect_tx(&res_full, P::kOutBytes);
+#pragma unroll
+                    for (int b = 0; b < P::kOutBoxes; ++b)
+                        tma_load_2d(out_s + b * kOutBoxBytes, &tmap_r, 2 * n0 + b * 128, m0, &res_full);
+                }
 
                 // accumulators start from the bias: acc[0..15] <- columns col_a.., acc[16..31] <- col_b..
                 float2 acc[32];
@@ -350,6 +382,8 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 if (!ok) break;
 
                 // -------------------------------------------------------- tile epilogue
+                // Staging address of this thread's 16-byte piece j of its row (128-byte swizzle: piece ^ row % 8)
+                const int swz = row_in_tile & 7;
                 if (MODE == kSwiGLU || MODE == kSiLU) {
                     // kSwiGLU: acc[0..15] = gate, acc[16..31] = value of hidden columns h0 + cq * 32 + (0..31);
                     //          the 128-column quantisation block of the row is shared by the four column quarters.
@@ -359,18 +393,14 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < NV; ++i) {
                         float2 h;
-                        if (MODE == kSwiGLU) {
-                            h.x = silu(acc[i].x) * acc[16 + i].x;
-                            h.y = silu(acc[i].y) * acc[16 + i].y;
-                        } else {
-                            h.x = silu(acc[i].x);
-                            h.y = silu(acc[i].y);
-                        }
+                        h = make_float2(silu(acc[i].x), silu(acc[i].y));
+                        if (MODE == kSwiGLU) h = __fmul2_rn(h, acc[16 + i]);
                         acc[i] = h;
                         amax = fmaxf(amax, fmaxf(fabsf(h.x), fabsf(h.y)));
                     }
-                    float (*xchg)[kBM] = amax_xchg[tile_count & 1];  // alternate buffers: one barrier per tile
+                    float (*xchg)[kBM] = amax_xchg[tile_count & 1];  // alternate buffers: no third barrier per tile
                     xchg[cq][row_in_tile] = amax;
+                    if (et == 0) bulk_wait_read<0>();       // the previous tile's store has read the staging tile
                     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
                     if (MODE == kSwiGLU) {
                         amax = fmaxf(fmaxf(xchg[0][row_in_tile], xchg[1][row_in_tile]),
@@ -381,21 +411,22 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
                     const float inv1 = 1.0f / scale;
                     const float2 inv = make_float2(inv1, inv1);
-                    if (row_ok) {
-                        const int64_t col0 = MODE == kSwiGLU ? (n0 / kBN) * 128 + cq * 32 : n0 + cq * 64;
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + row * g.out_ld + col0);
+                    // kSwiGLU: one box, pieces cq * 2 + {0, 1}; kSiLU: box cq / 2, pieces (cq % 2) * 4 + {0..3}
+                    uint8_t* box_row = out_s + (MODE == kSiLU ? (cq >> 1) * kOutBoxBytes : 0) + row_in_tile * 128;
+                    const int piece0 = MODE == kSwiGLU ? cq * 2 : (cq & 1) * 4;
 #pragma unroll
-                        for (int c = 0; c < NV / 8; ++c) {
-                            uint32_t w[4];
+                    for (int c = 0; c < NV / 8; ++c) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 lo = __fmul2_rn(acc[8 * c + 2 * e], inv);
-                                const float2 hi = __fmul2_rn(acc[8 * c + 2 * e + 1], inv);
-                                w[e] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3)) |
-                                       (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3)) << 16);
-                            }
-                            dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 lo = __fmul2_rn(acc[8 * c + 2 * e], inv);
+                            const float2 hi = __fmul2_rn(acc[8 * c + 2 * e + 1], inv);
+                            w[e] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3)) |
+                                   (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3)) << 16);
                         }
+                        *reinterpret_cast<uint4*>(box_row + (((piece0 + c) ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    if (row_ok) {
                         if (MODE == kSwiGLU) {
                             if (cq == 0) g.out_scale[row * (g.N / 256) + n0 / kBN] = scale;
                         } else if ((cq & 1) == 0) {
@@ -403,27 +434,42 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                         }
                     }
                 } else {
-                    const int c0 = n0 + cq * 64;
-                    if (row_ok) {
-                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(g.out) + row * g.out_ld + c0;
-                        const __nv_bfloat16* res = g.residual != nullptr ? g.residual + row * g.out_ld + c0 : nullptr;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            float2 v[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) v[e] = acc[4 * c + e];
-                            if (res != nullptr) {
-                                float2 rr[4];
-                                Vec16<__nv_bfloat16>::unpack2(reinterpret_cast<const uint4*>(res)[c], rr);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
-                            }
-                            reinterpret_cast<uint4*>(dst)[c] = Vec16<__nv_bfloat16>::pack2(v);
-                        }
+                    // 64 bf16 columns = one 128-byte box row per thread: box cq, pieces 0..7
+                    uint8_t* box_row = out_s + cq * kOutBoxBytes + row_in_tile * 128;
+                    const bool has_res = g.residual != nullptr;
+                    if (et == 0) bulk_wait_read<0>();
+                    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+                    if (has_res && !mbar_wait(&res_full, tile_count & 1)) {
+                        ok = false;
+                        break;
                     }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint4* slot = reinterpret_cast<uint4*>(box_row + ((c ^ swz) << 4));
+                        float2 v[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = acc[4 * c + e];
+                        if (has_res) {
+                            float2 rr[4];
+                            Vec16<__nv_bfloat16>::unpack2(*slot, rr);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
+                        }
+                        *slot = Vec16<__nv_bfloat16>::pack2(v);
+                    }
+                }
+                // staging tile complete -> one thread hands it to TMA (rows past M are clipped by the tensor map)
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+                if (et == 0) {
+                    const int x0 = MODE == kSwiGLU ? (n0 / kBN) * 128 : (MODE == kSiLU ? n0 : 2 * n0);
+#pragma unroll
+                    for (int b = 0; b < P::kOutBoxes; ++b) tma_store_2d(&tmap_o, out_s + b * kOutBoxBytes, x0 + b * 128, m0);
+                    bulk_commit();
                 }
             }
         }
+        if (et == 0) bulk_wait<0>();   // the last store must have left shared memory before the CTA ends
         if (!ok) {
             s_abort = 1;
             if (g.status != nullptr) atomicExch(g.status, 1);
@@ -507,15 +553,15 @@ bool make_tmap_bytes(CUtensorMap* map, const void* base, uint64_t k_bytes, uint6
 }
 
 template <int MODE, bool B_RES>
-int launch_gemm_impl(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t stream) {
+int launch_gemm_impl(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
+                     const GemmArgs& g, cudaStream_t stream) {
+    using P = Plan<MODE, B_RES>;
     const DeviceInfo& dev = device_info();
-    const size_t tiles_bytes = B_RES ? static_cast<size_t>(g.K / kBK) * kBBytes + static_cast<size_t>(kStagesRes) * kABytes
-                                     : static_cast<size_t>(kStages) * kStageBytes;
-    const size_t smem = tiles_bytes + 1024;
+    const size_t smem = P::tiles_bytes(g.K / kBK) + 1024;
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
         cudaFuncSetAttribute(ffn_gemm_kernel<MODE, B_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(static_cast<size_t>(B_RES ? 4 * kBBytes + kStagesRes * kABytes : kStages * kStageBytes) + 1024));
+                             static_cast<int>(P::tiles_bytes(4) + 1024));
         attr_set[dev.index] = true;
     }
     const int64_t m_tiles = (g.M + kBM - 1) / kBM;
@@ -526,15 +572,18 @@ int launch_gemm_impl(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArg
         if (walkers > m_tiles) walkers = m_tiles;
         grid = walkers * n_tiles;
     }
-    ffn_gemm_kernel<MODE, B_RES><<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(ta, tb, g);
+    ffn_gemm_kernel<MODE, B_RES><<<static_cast<unsigned>(grid), kThreads, smem, stream>>>(ta, tb, to, tr, g);
     count_launch();
     return launch_status();
 }
 
 template <int MODE>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, cudaStream_t stream) {
-    if (g.K <= 4 * kBK) return launch_gemm_impl<MODE, true>(ta, tb, g, stream);
-    return launch_gemm_impl<MODE, false>(ta, tb, g, stream);
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tr,
+                const GemmArgs& g, cudaStream_t stream) {
+    // the resident weight tile pays off for the short K of the up projection; the linear mode needs the room
+    // for its 64 KB staging tile instead
+    if (MODE != kLinear && g.K <= 4 * kBK) return launch_gemm_impl<MODE, true>(ta, tb, to, tr, g, stream);
+    return launch_gemm_impl<MODE, false>(ta, tb, to, tr, g, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -606,6 +655,12 @@ extern "C" int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const vo
     if (!make_tmap_bytes(&ta, a_fp8, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), kBM) ||
         !make_tmap_bytes(&tb, b_fp8, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), kBN))
         return TB200_ERR_DRIVER;
+    // output (and residual) as byte matrices in boxes of 128 rows x 128 bytes
+    const uint64_t out_row_bytes = mode == kSwiGLU ? static_cast<uint64_t>(N) / 2 : (mode == kSiLU ? static_cast<uint64_t>(N) : 2ull * N);
+    CUtensorMap to, tr;
+    if (!make_tmap_bytes(&to, out, out_row_bytes, static_cast<uint64_t>(M), out_row_bytes, kBM)) return TB200_ERR_DRIVER;
+    if (!make_tmap_bytes(&tr, residual != nullptr ? residual : out, out_row_bytes, static_cast<uint64_t>(M), out_row_bytes, kBM))
+        return TB200_ERR_DRIVER;
     GemmArgs g{};
     g.sa = a_scales;
     g.sb = b_scales;
@@ -619,9 +674,9 @@ extern "C" int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const vo
     g.K = K;
     g.out_ld = mode == kSwiGLU ? N / 2 : N;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (mode == kSwiGLU) return launch_gemm<kSwiGLU>(ta, tb, g, s);
-    if (mode == kSiLU) return launch_gemm<kSiLU>(ta, tb, g, s);
-    return launch_gemm<kLinear>(ta, tb, g, s);
+    if (mode == kSwiGLU) return launch_gemm<kSwiGLU>(ta, tb, to, tr, g, s);
+    if (mode == kSiLU) return launch_gemm<kSiLU>(ta, tb, to, tr, g, s);
+    return launch_gemm<kLinear>(ta, tb, to, tr, g, s);
 }
 
 extern "C" int64_t tb200_ffn_fp8_static_scratch_bytes(void) { return static_cast<int64_t>(tb200::kStaticScratchBytes); }
