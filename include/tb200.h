@@ -73,6 +73,19 @@ int tb200_rmsnorm_fwd(const void* x, const void* gamma, void* y, int64_t rows, i
 int tb200_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int32_t cols,
                         float eps, int dtype, void* stream);
 
+/* y = rmsnorm(x + in_bias) * gamma, the bias added in fp32 before the statistics.  In OneTrans's block
+ * (`tokens = tokens + attention(...)`, then `ffn_norm(tokens)`, experiments/onetrans/model.py:106-107) the
+ * output projection's bias reaches the norm this way, so the residual addition can stay inside the
+ * projection GEMM and no separate pass adds the bias.  in_bias: [cols] of `dtype`. */
+int tb200_rmsnorm_bias_fwd(const void* x, const void* in_bias, const void* gamma, void* y, int64_t rows, int32_t cols,
+                           float eps, int dtype, void* stream);
+
+/* y = layernorm(silu(x)) with the SiLU result rounded to `dtype` first: the tail of the tokenizers'
+ * `nn.Sequential(nn.Linear, nn.SiLU(), nn.LayerNorm)` projections
+ * (src/taac2026/infrastructure/modeling/tokenizers.py:94, :144) without the intermediate tensor. */
+int tb200_layernorm_silu_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int32_t cols,
+                             float eps, int dtype, void* stream);
+
 /* ---- (a) sparse-field embedding gather / pool ---------------------------------------------
  * out[b, :] = mean over hot h of table[ids[b, h], :] for ids in (0, vocab_rows); ids equal to 0
  * (padding) or outside the table are skipped; an empty bag gives zeros.  fp32 sum in hot order,
@@ -120,6 +133,22 @@ int tb200_gather_rows(const void* table, int64_t vocab_rows, int32_t dim, const 
 int tb200_scatter_rows(void* dst, int64_t dst_rows, int64_t dst_stride, int32_t dst_col0, const int64_t* ids,
                        const void* src, int64_t n, int32_t dim, const void* bias, int64_t rows_per_group,
                        const void* residual, int64_t residual_stride, int dtype, void* stream);
+
+/* x[i, :] = x[i, :] + table_a[ids_a[i], :], then (table_b != NULL) + table_b[ids_b[i], :], in place; ids are
+ * clamped into their table and every sum is rounded to `dtype` like a tensor addition of its own.  The
+ * sequence tokenizer's `tokens = tokens + self.time_embedding(time_values)`
+ * (src/taac2026/infrastructure/modeling/tokenizers.py:188-189) and the sinusoidal position rows added by
+ * the experiment model, without materialising the gathered rows.  x: [n, dim]; ids: device int64[n];
+ * dim * sizeof(dtype) a multiple of 16. */
+int tb200_add_gathered_rows(void* x, int64_t n, int32_t dim, const void* table_a, int64_t rows_a, const int64_t* ids_a,
+                            const void* table_b, int64_t rows_b, const int64_t* ids_b, int dtype, void* stream);
+
+/* x[r, :] = silu(x[r, :] + bias[r / rows_per_group, :]) in place, the sum rounded to `dtype` before the
+ * activation: first half of OneTrans's per-token `FeedForward` (`nn.Linear` bias + `nn.SiLU()`,
+ * experiments/onetrans/model.py:36-41) when the linear parts of all tokens run as one batched product.
+ * x: [rows, cols]; bias: [rows / rows_per_group, cols]; cols * sizeof(dtype) a multiple of 16. */
+int tb200_bias_silu_rows(void* x, int64_t rows, int32_t cols, const void* bias, int64_t rows_per_group, int dtype,
+                         void* stream);
 
 /* ---- (c) varlen masked attention forward ----------------------------------------------------
  * o[b, h, q, :] = softmax_k(scale * <q[b, h, q, :], k[b, h, k, :]> over visible k) . v[b, h, k, :]

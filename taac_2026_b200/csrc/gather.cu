@@ -224,6 +224,74 @@ scatter_rows_kernel(uint4* __restrict__ dst, int64_t dst_stride_chunks, int dst_
 }
 
 
+// ---------------------------------------------------------------------------------------
+// add_gathered_rows: x[i, :] = x[i, :] + table_a[ids_a[i], :]  (then + table_b[ids_b[i], :]), in place.
+// Each sum is rounded to T before the next one, like two separate tensor additions.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_gathered_rows_kernel(uint4* __restrict__ x, int64_t n, int chunks, const uint4* __restrict__ table_a, int64_t rows_a,
+                         const int64_t* __restrict__ ids_a, const uint4* __restrict__ table_b, int64_t rows_b,
+                         const int64_t* __restrict__ ids_b, int lanes_per_row) {
+    constexpr int N = Vec16<T>::N;
+    const int G = lanes_per_row;
+    const int group = threadIdx.x / G;
+    const int lane_g = threadIdx.x % G;
+    const int n_groups = kThreads / G;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * n_groups + group; i < n; i += static_cast<int64_t>(gridDim.x) * n_groups) {
+        int64_t ia = ids_a[i];
+        ia = ia < 0 ? 0 : (ia > rows_a - 1 ? rows_a - 1 : ia);
+        int64_t ib = 0;
+        if (table_b != nullptr) {
+            ib = ids_b[i];
+            ib = ib < 0 ? 0 : (ib > rows_b - 1 ? rows_b - 1 : ib);
+        }
+        for (int c = lane_g; c < chunks; c += G) {
+            float f[N], a[N];
+            Vec16<T>::unpack(x[i * chunks + c], f);
+            Vec16<T>::unpack(ld_nc_v4(table_a + ia * chunks + c), a);
+#pragma unroll
+            for (int e = 0; e < N; ++e) f[e] += a[e];
+            uint4 v = Vec16<T>::pack(f);
+            if (table_b != nullptr) {
+                Vec16<T>::unpack(v, f);   // the first sum as T stores it
+                Vec16<T>::unpack(ld_nc_v4(table_b + ib * chunks + c), a);
+#pragma unroll
+                for (int e = 0; e < N; ++e) f[e] += a[e];
+                v = Vec16<T>::pack(f);
+            }
+            x[i * chunks + c] = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// bias_silu_rows: x[r, :] = silu(x[r, :] + bias[r / rows_per_group, :]), in place; the sum is rounded to T
+// before the activation, like an addition followed by a separate SiLU.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+bias_silu_rows_kernel(uint4* __restrict__ x, int64_t rows, int chunks, const uint4* __restrict__ bias,
+                      int64_t rows_per_group) {
+    constexpr int N = Vec16<T>::N;
+    const int64_t total = rows * chunks;
+    for (int64_t j = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; j < total;
+         j += static_cast<int64_t>(gridDim.x) * kThreads) {
+        const int64_t r = j / chunks;
+        const int c = static_cast<int>(j - r * chunks);
+        float f[N], b[N];
+        Vec16<T>::unpack(x[j], f);
+        Vec16<T>::unpack(bias[(r / rows_per_group) * chunks + c], b);
+#pragma unroll
+        for (int e = 0; e < N; ++e) f[e] += b[e];
+        Vec16<T>::unpack(Vec16<T>::pack(f), f);
+#pragma unroll
+        for (int e = 0; e < N; ++e) f[e] = f[e] / (1.0f + __expf(-f[e]));
+        x[j] = Vec16<T>::pack(f);
+    }
+}
+
+
 int lanes_for(int chunks) {
     int g = 1;
     while (g < 32 && g < chunks) g <<= 1;
@@ -378,6 +446,70 @@ extern "C" int tb200_scatter_rows(void* dst, int64_t dst_rows, int64_t dst_strid
         default: return TB200_ERR_DTYPE;
     }
 #undef TB200_SCATTER
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int tb200_add_gathered_rows(void* x, int64_t n, int32_t dim, const void* table_a, int64_t rows_a,
+                                       const int64_t* ids_a, const void* table_b, int64_t rows_b, const int64_t* ids_b,
+                                       int dtype, void* stream) {
+    using namespace tb200;
+    if (n < 0 || dim < 1 || rows_a < 1 || (table_b != nullptr && rows_b < 1)) return TB200_ERR_SHAPE;
+    if (n == 0) return TB200_OK;
+    const int es = dtype_size(dtype);
+    if (es == 0) return TB200_ERR_DTYPE;
+    if (x == nullptr || table_a == nullptr || ids_a == nullptr || (table_b != nullptr && ids_b == nullptr)) return TB200_ERR_NULL;
+    if ((static_cast<int64_t>(dim) * es) % 16 != 0 || !aligned16(x) || !aligned16(table_a) ||
+        (table_b != nullptr && !aligned16(table_b)))
+        return TB200_ERR_ALIGN;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    const int chunks = dim * es / 16;
+    const int G = lanes_for(chunks);
+    const int n_groups = kThreads / G;
+    int64_t grid = (n + n_groups - 1) / n_groups;
+    const int64_t cap = static_cast<int64_t>(device_info().sm_count) * 16;
+    if (grid > cap) grid = cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TB200_ADDG(T)                                                                                                 \
+    add_gathered_rows_kernel<T><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(                                     \
+        static_cast<uint4*>(x), n, chunks, static_cast<const uint4*>(table_a), rows_a, ids_a,                         \
+        static_cast<const uint4*>(table_b), rows_b, ids_b, G)
+    switch (dtype) {
+        case TB200_F32: TB200_ADDG(float); break;
+        case TB200_F16: TB200_ADDG(__half); break;
+        case TB200_BF16: TB200_ADDG(__nv_bfloat16); break;
+        default: return TB200_ERR_DTYPE;
+    }
+#undef TB200_ADDG
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int tb200_bias_silu_rows(void* x, int64_t rows, int32_t cols, const void* bias, int64_t rows_per_group,
+                                    int dtype, void* stream) {
+    using namespace tb200;
+    if (rows < 0 || cols < 1 || rows_per_group < 1) return TB200_ERR_SHAPE;
+    if (rows == 0) return TB200_OK;
+    const int es = dtype_size(dtype);
+    if (es == 0) return TB200_ERR_DTYPE;
+    if (x == nullptr || bias == nullptr) return TB200_ERR_NULL;
+    if ((static_cast<int64_t>(cols) * es) % 16 != 0 || !aligned16(x) || !aligned16(bias)) return TB200_ERR_ALIGN;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    const int chunks = cols * es / 16;
+    int64_t grid = (rows * chunks + kThreads - 1) / kThreads;
+    const int64_t cap = static_cast<int64_t>(device_info().sm_count) * 16;
+    if (grid > cap) grid = cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TB200_BSILU(T)                                                                                        \
+    bias_silu_rows_kernel<T><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(static_cast<uint4*>(x), rows, chunks, \
+                                                                              static_cast<const uint4*>(bias), rows_per_group)
+    switch (dtype) {
+        case TB200_F32: TB200_BSILU(float); break;
+        case TB200_F16: TB200_BSILU(__half); break;
+        case TB200_BF16: TB200_BSILU(__nv_bfloat16); break;
+        default: return TB200_ERR_DTYPE;
+    }
+#undef TB200_BSILU
     count_launch();
     return launch_status();
 }

@@ -25,7 +25,26 @@ constexpr int kStages = 4;
 // (a few rows, about 2 KB) with its own mbarriers: lane 0 issues the bulk loads and stores,
 // the warp normalises RU rows per lane group at a time (independent shuffle chains), and no
 // CTA-wide barrier is ever taken after start-up.  gamma / beta sit in shared memory.
-template <typename T, bool LAYER, int CPL, int RU>
+//
+// PRE selects an operation fused in front of the statistics:
+//   kPreNone  y = norm(x)
+//   kPreBias  y = rmsnorm(x + bias)            (RMS only; the bias vector arrives through `beta`)
+//   kPreSilu  y = layernorm(silu(x)), the SiLU result rounded to T like the tensor a separate SiLU
+//             kernel would have written
+enum Pre : int { kPreNone = 0, kPreBias = 1, kPreSilu = 2 };
+
+__device__ __forceinline__ float silu_f(float x) {
+    const float h = 0.5f * x;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+    return fmaf(h, t, h);
+}
+template <typename T>
+__device__ __forceinline__ float round_to(float v) {
+    return to_float<T>(from_float<T>(v));
+}
+
+template <typename T, bool LAYER, int CPL, int RU, int PRE>
 __global__ void __launch_bounds__(kMaxThreads, 3)
 norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                 int64_t rows, int cols, float eps, int lanes_per_row, int* __restrict__ status) {
@@ -77,7 +96,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
         Vec16<T>::unpack2(reinterpret_cast<const uint4*>(gamma)[c], f);
 #pragma unroll
         for (int e = 0; e < N / 2; ++e) gamma_s[((e >> 1) * chunks + c) * 2 + (e & 1)] = f[e];
-        if (LAYER) {
+        if (LAYER || PRE == kPreBias) {
             Vec16<T>::unpack2(reinterpret_cast<const uint4*>(beta)[c], f);
 #pragma unroll
             for (int e = 0; e < N / 2; ++e) beta_s[((e >> 1) * chunks + c) * 2 + (e & 1)] = f[e];
@@ -116,6 +135,19 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                 const int c = lane_g + j * G;
                 if (valid[u] && c < chunks) {
                     Vec16<T>::unpack2(rowp[c], v[u][j]);
+                    if (PRE == kPreBias) {
+#pragma unroll
+                        for (int e = 0; e < N / 2; e += 2) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(&beta_s[((e >> 1) * chunks + c) * 2]);
+                            v[u][j][e] = __fadd2_rn(v[u][j][e], make_float2(b4.x, b4.y));
+                            v[u][j][e + 1] = __fadd2_rn(v[u][j][e + 1], make_float2(b4.z, b4.w));
+                        }
+                    }
+                    if (PRE == kPreSilu) {
+#pragma unroll
+                        for (int e = 0; e < N / 2; ++e)
+                            v[u][j][e] = make_float2(round_to<T>(silu_f(v[u][j][e].x)), round_to<T>(silu_f(v[u][j][e].y)));
+                    }
                 } else {
 #pragma unroll
                     for (int e = 0; e < N / 2; ++e) v[u][j][e] = make_float2(0.f, 0.f);
@@ -213,7 +245,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 }
 
 // Warp per row, scalar accesses, any cols / alignment.
-template <typename T, bool LAYER>
+template <typename T, bool LAYER, int PRE>
 __global__ void __launch_bounds__(kMaxThreads)
 norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                     T* __restrict__ y, int64_t rows, int cols, float eps) {
@@ -221,25 +253,31 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kMaxThreads + threadIdx.x) >> 5;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * kMaxThreads) >> 5;
     const float inv_cols = 1.0f / static_cast<float>(cols);
+    auto load = [&](const T* xr, int c) -> float {
+        float v = to_float<T>(xr[c]);
+        if (PRE == kPreBias) v += to_float<T>(beta[c]);
+        if (PRE == kPreSilu) v = round_to<T>(silu_f(v));
+        return v;
+    };
     for (int64_t r = warp; r < rows; r += n_warps) {
         const T* xr = x + r * cols;
         T* yr = y + r * cols;
         float mean = 0.f;
         if (LAYER) {
             float sum = 0.f;
-            for (int c = lane; c < cols; c += 32) sum += to_float<T>(xr[c]);
+            for (int c = lane; c < cols; c += 32) sum += load(xr, c);
             for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             mean = sum * inv_cols;
         }
         float sq = 0.f;
         for (int c = lane; c < cols; c += 32) {
-            const float d = to_float<T>(xr[c]) - mean;
+            const float d = load(xr, c) - mean;
             sq = fmaf(d, d, sq);
         }
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
         const float inv = rsqrtf(sq * inv_cols + eps);
         for (int c = lane; c < cols; c += 32) {
-            const float v = to_float<T>(xr[c]);
+            const float v = load(xr, c);
             float o;
             if (LAYER) o = fmaf((v - mean) * inv, to_float<T>(gamma[c]), to_float<T>(beta[c]));
             else o = (v * inv) * to_float<T>(gamma[c]);
@@ -248,7 +286,7 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     }
 }
 
-template <typename T, bool LAYER, int CPL, int RU>
+template <typename T, bool LAYER, int CPL, int RU, int PRE>
 int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
                int lanes_per_row, cudaStream_t stream) {
     const int N = Vec16<T>::N;
@@ -260,7 +298,7 @@ int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int6
     const DeviceInfo& dev = device_info();
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
-        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024);
         attr_set[dev.index] = true;
     }
@@ -271,54 +309,54 @@ int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int6
     const int64_t useful = (rows + static_cast<int64_t>(tile_rows) * kWarps - 1) / (static_cast<int64_t>(tile_rows) * kWarps);
     if (grid > useful) grid = useful;
     if (grid < 1) grid = 1;
-    norm_tma_kernel<T, LAYER, CPL, RU><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
+    norm_tma_kernel<T, LAYER, CPL, RU, PRE><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
         cols, eps, lanes_per_row, nullptr);
     count_launch();
     return launch_status();
 }
 
-template <typename T, bool LAYER>
+template <typename T, bool LAYER, int PRE>
 int norm_dispatch(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
                   cudaStream_t stream) {
     const int N = Vec16<T>::N;
     const bool vec_ok = (cols % N == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) &&
-                        (!LAYER || aligned16(beta)) && (cols / N) <= 256;
+                        ((!LAYER && PRE != kPreBias) || aligned16(beta)) && (cols / N) <= 256;
     if (vec_ok) {
         const int chunks = cols / N;
         int G = 1;
         while (G < 32 && G < chunks) G <<= 1;  // lanes per row: power of two, <= 32
         const int cpl = (chunks + G - 1) / G;
         // RU rows per lane group and tile, so that a lane holds about 4 chunks whatever the row width
-        if (cpl <= 1) return launch_tma<T, LAYER, 1, 4>(x, gamma, beta, y, rows, cols, eps, G, stream);
-        if (cpl <= 2) return launch_tma<T, LAYER, 2, 2>(x, gamma, beta, y, rows, cols, eps, G, stream);
-        if (cpl <= 4) return launch_tma<T, LAYER, 4, 1>(x, gamma, beta, y, rows, cols, eps, G, stream);
-        return launch_tma<T, LAYER, 8, 1>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        if (cpl <= 1) return launch_tma<T, LAYER, 1, 4, PRE>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        if (cpl <= 2) return launch_tma<T, LAYER, 2, 2, PRE>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        if (cpl <= 4) return launch_tma<T, LAYER, 4, 1, PRE>(x, gamma, beta, y, rows, cols, eps, G, stream);
+        return launch_tma<T, LAYER, 8, 1, PRE>(x, gamma, beta, y, rows, cols, eps, G, stream);
     }
     const DeviceInfo& dev = device_info();
     int64_t blocks = (rows + (kMaxThreads / 32) - 1) / (kMaxThreads / 32);
     const int64_t cap = static_cast<int64_t>(dev.sm_count) * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    norm_rowwarp_kernel<T, LAYER><<<static_cast<unsigned>(blocks), kMaxThreads, 0, stream>>>(
+    norm_rowwarp_kernel<T, LAYER, PRE><<<static_cast<unsigned>(blocks), kMaxThreads, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
         cols, eps);
     count_launch();
     return launch_status();
 }
 
-template <bool LAYER>
+template <bool LAYER, int PRE>
 int norm_entry(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int32_t cols, float eps,
                int dtype, void* stream) {
     if (rows < 0 || cols < 1) return TB200_ERR_SHAPE;
     if (rows == 0) return TB200_OK;
-    if (x == nullptr || gamma == nullptr || y == nullptr || (LAYER && beta == nullptr)) return TB200_ERR_NULL;
+    if (x == nullptr || gamma == nullptr || y == nullptr || ((LAYER || PRE == kPreBias) && beta == nullptr)) return TB200_ERR_NULL;
     if (!device_info().valid) return TB200_ERR_DEVICE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (dtype) {
-        case TB200_F32: return norm_dispatch<float, LAYER>(x, gamma, beta, y, rows, cols, eps, s);
-        case TB200_F16: return norm_dispatch<__half, LAYER>(x, gamma, beta, y, rows, cols, eps, s);
-        case TB200_BF16: return norm_dispatch<__nv_bfloat16, LAYER>(x, gamma, beta, y, rows, cols, eps, s);
+        case TB200_F32: return norm_dispatch<float, LAYER, PRE>(x, gamma, beta, y, rows, cols, eps, s);
+        case TB200_F16: return norm_dispatch<__half, LAYER, PRE>(x, gamma, beta, y, rows, cols, eps, s);
+        case TB200_BF16: return norm_dispatch<__nv_bfloat16, LAYER, PRE>(x, gamma, beta, y, rows, cols, eps, s);
         default: return TB200_ERR_DTYPE;
     }
 }
@@ -328,10 +366,20 @@ int norm_entry(const void* x, const void* gamma, const void* beta, void* y, int6
 
 extern "C" int tb200_rmsnorm_fwd(const void* x, const void* gamma, void* y, int64_t rows, int32_t cols, float eps,
                                  int dtype, void* stream) {
-    return tb200::norm_entry<false>(x, gamma, nullptr, y, rows, cols, eps, dtype, stream);
+    return tb200::norm_entry<false, tb200::kPreNone>(x, gamma, nullptr, y, rows, cols, eps, dtype, stream);
 }
 
 extern "C" int tb200_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows,
                                    int32_t cols, float eps, int dtype, void* stream) {
-    return tb200::norm_entry<true>(x, gamma, beta, y, rows, cols, eps, dtype, stream);
+    return tb200::norm_entry<true, tb200::kPreNone>(x, gamma, beta, y, rows, cols, eps, dtype, stream);
+}
+
+extern "C" int tb200_rmsnorm_bias_fwd(const void* x, const void* in_bias, const void* gamma, void* y, int64_t rows,
+                                      int32_t cols, float eps, int dtype, void* stream) {
+    return tb200::norm_entry<false, tb200::kPreBias>(x, gamma, in_bias, y, rows, cols, eps, dtype, stream);
+}
+
+extern "C" int tb200_layernorm_silu_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows,
+                                        int32_t cols, float eps, int dtype, void* stream) {
+    return tb200::norm_entry<true, tb200::kPreSilu>(x, gamma, beta, y, rows, cols, eps, dtype, stream);
 }

@@ -22,6 +22,7 @@ GPU; there is no CPU path.
 
 from __future__ import annotations
 
+import copy
 import math
 from dataclasses import dataclass
 
@@ -287,6 +288,13 @@ class OneTransInference:
                 blk["ffn_fp8"] = ops.Fp8FfnWeights(
                     self.w[p + ".ffn.shared.net.0.weight"], self.w[p + ".ffn.shared.net.3.weight"], gated=False,
                     b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"])
+                # The packed path leaves the attention output bias out of the residual stream it hands to the
+                # FFN (the norm in between adds it on the fly), so the FFN's own output bias carries it.
+                folded = copy.copy(blk["ffn_fp8"])
+                folded.b_down = (folded.b_down + self.w[p + ".attention.out.bias"].float()).contiguous()
+                blk["ffn_fp8_folded"] = folded
+            blk["out_w_t"] = self._p(p + ".attention.out.weight").t()
+            blk["out_b"] = self._p(p + ".attention.out.bias")
             if ns > 0:
                 def stack(fmt: str, kind: str) -> torch.Tensor:
                     return torch.stack([self._p(fmt.format(i=i) + "." + kind) for i in range(ns)])
@@ -299,6 +307,7 @@ class OneTransInference:
                 blk["ns_b1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "bias").unsqueeze(1)
                 blk["ns_w2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "weight").transpose(1, 2).contiguous()
                 blk["ns_b2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "bias").unsqueeze(1)
+                blk["ns_b2_folded"] = (blk["ns_b2"].float() + blk["out_b"].float()).to(blk["ns_b2"].dtype)
             self.blocks.append(blk)
 
     # ------------------------------------------------------------------ pieces
@@ -611,13 +620,18 @@ class OneTransInference:
                 ops.gather_rows(table, ids_full, out=token_input, col0=f * emb)
         else:
             token_input = torch.zeros(total0, max(1, n_feat * emb), dtype=self.dtype, device=dev)
-        tokens = self._layer_norm(F.silu(self._linear(token_input, prefix + ".project.0")), prefix + ".project.2")
+        # Linear -> SiLU -> LayerNorm with the activation inside the norm kernel, then the time-bucket and
+        # position rows added in place by one pass over the token matrix
+        tokens = ops.layer_norm(self._linear(token_input, prefix + ".project.0"), self._p(prefix + ".project.2.weight"),
+                                self._p(prefix + ".project.2.bias"), 1e-5, pre_silu=True)
         pos_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, j_idx)
+        pos_table = self._positions(width).to(self.dtype).contiguous()
         if prefix + ".time_embedding.weight" in self.w:
             buckets = sequence_time_buckets(ts[sample_of, src_pos][:, None], request_ts[sample_of], self._edges)[:, 0]
-            buckets_full = torch.zeros(total0, dtype=buckets.dtype, device=dev).index_copy_(0, dest, buckets)
-            tokens = tokens + ops.gather_rows(self._p(prefix + ".time_embedding.weight"), buckets_full)
-        tokens = tokens + ops.gather_rows(self._positions(width), pos_full)
+            buckets_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, buckets.long())
+            ops.add_gathered_rows(tokens, self._p(prefix + ".time_embedding.weight"), buckets_full, pos_table, pos_full)
+        else:
+            ops.add_gathered_rows(tokens, pos_table, pos_full)
 
         # ---- the NS tokens take the rows left for them: [seq rows of b | ns rows of b]
         ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
@@ -639,13 +653,23 @@ class OneTransInference:
                 q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
             attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
                                         kernel=self.attention_kernel)
-            tokens = tokens + self._linear(attn.view(-1, d).to(self.dtype), p + ".attention.out")
-            x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
-            out = self._shared_ffn_residual(blk, x, tokens)
+            attn2d = attn.view(-1, d).to(self.dtype)
+            if self.ffn_mode == "fp8":
+                # tokens + attention out-projection with the residual inside the GEMM (beta = 1); its bias is
+                # added by the norm on the fly and rides on the FFN output biases into the next residual
+                tokens = torch.addmm(tokens, attn2d, blk["out_w_t"])
+                x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
+                out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens)
+                ns_b2 = blk["ns_b2_folded"]
+            else:
+                tokens = tokens + F.linear(attn2d, blk["out_w_t"].t(), blk["out_b"])
+                x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
+                out = self._shared_ffn_residual(blk, x, tokens)
+                ns_b2 = blk["ns_b2"]
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)
-            h = F.silu(torch.bmm(x_ns, blk["ns_w1"]).add_(blk["ns_b1"]))
+            h = ops.bias_silu_rows(torch.bmm(x_ns, blk["ns_w1"]), blk["ns_b1"])
             y_ns = torch.bmm(h, blk["ns_w2"]).view(ns * batch, d)
-            ops.scatter_rows(out, flat_ns, y_ns, bias=blk["ns_b2"], residual=tokens)   # tokens + b2 + FFN_ns(x)
+            ops.scatter_rows(out, flat_ns, y_ns, bias=ns_b2, residual=tokens)   # tokens + b2 + FFN_ns(x)
             tokens = out
             if widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
                 new_rows = rows[layer + 1]

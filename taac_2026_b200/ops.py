@@ -136,19 +136,31 @@ def rms_norm(
     *,
     backend: str = "cuda",
     block_rows: int | None = None,
+    in_bias: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``x * rsqrt(mean(x^2, -1) + eps) * weight`` with fp32 accumulation, one fused kernel.
 
     ``block_rows`` is accepted for signature compatibility; the kernel sizes its own tiles.
+    ``in_bias`` (an extension, [cols]) is added to every row in fp32 before the statistics:
+    ``rms_norm(x + in_bias)`` without the pass that would form the sum.
     """
     matrix, normalized_weight, original_shape = _normalize_rms_norm_inputs(x, weight)
     resolved_rms_norm_backend(matrix, backend, eps=eps, block_rows=block_rows)
     out = torch.empty_like(matrix)
+    if in_bias is not None and tuple(in_bias.shape) != (matrix.shape[1],):
+        raise ValueError("rms_norm in_bias must be a vector of the normalised width")
     with torch.cuda.device(matrix.device), _timed("rms_norm", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
-        code = _lib.load().tb200_rmsnorm_fwd(
-            _ptr(matrix), _ptr(normalized_weight), _ptr(out), matrix.shape[0], matrix.shape[1], float(eps),
-            _DTYPE_CODES[matrix.dtype], _stream_ptr(),
-        )
+        if in_bias is None:
+            code = _lib.load().tb200_rmsnorm_fwd(
+                _ptr(matrix), _ptr(normalized_weight), _ptr(out), matrix.shape[0], matrix.shape[1], float(eps),
+                _DTYPE_CODES[matrix.dtype], _stream_ptr(),
+            )
+        else:
+            vec = in_bias.to(device=matrix.device, dtype=matrix.dtype).contiguous()
+            code = _lib.load().tb200_rmsnorm_bias_fwd(
+                _ptr(matrix), _ptr(vec), _ptr(normalized_weight), _ptr(out), matrix.shape[0], matrix.shape[1],
+                float(eps), _DTYPE_CODES[matrix.dtype], _stream_ptr(),
+            )
     _lib.check(code, "cuda rms_norm")
     return out.reshape(original_shape)
 
@@ -192,13 +204,18 @@ def layer_norm(
     *,
     backend: str = "cuda",
     block_rows: int | None = None,
+    pre_silu: bool = False,
 ) -> torch.Tensor:
-    """``(x - mean) * rsqrt(var + eps) * weight + bias`` over the last dimension (fp32 statistics)."""
+    """``(x - mean) * rsqrt(var + eps) * weight + bias`` over the last dimension (fp32 statistics).
+
+    ``pre_silu=True`` (an extension) normalises ``silu(x)`` instead, the SiLU result rounded to the tensor's
+    dtype as a separate activation would leave it: the ``Linear -> SiLU -> LayerNorm`` tail in one pass."""
     matrix, normalized_weight, normalized_bias, original_shape = _normalize_layer_norm_inputs(x, weight, bias)
     resolved_layer_norm_backend(matrix, backend, eps=eps, block_rows=block_rows)
     out = torch.empty_like(matrix)
     with torch.cuda.device(matrix.device), _timed("layer_norm", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
-        code = _lib.load().tb200_layernorm_fwd(
+        fn = _lib.load().tb200_layernorm_silu_fwd if pre_silu else _lib.load().tb200_layernorm_fwd
+        code = fn(
             _ptr(matrix), _ptr(normalized_weight), _ptr(normalized_bias), _ptr(out), matrix.shape[0],
             matrix.shape[1], float(eps), _DTYPE_CODES[matrix.dtype], _stream_ptr(),
         )
@@ -917,7 +934,60 @@ def scatter_rows(dst: torch.Tensor, ids: torch.Tensor, src: torch.Tensor, *, col
     return dst
 
 
+def add_gathered_rows(x: torch.Tensor, table_a: torch.Tensor, ids_a: torch.Tensor,
+                      table_b: torch.Tensor | None = None, ids_b: torch.Tensor | None = None) -> torch.Tensor:
+    """``x[i] += table_a[ids_a[i]]`` and then ``x[i] += table_b[ids_b[i]]``, in place and in one pass.
+
+    ``x`` [n, dim] and the tables are contiguous matrices of one dtype, the ids int64 [n] (clamped into
+    their table).  Each sum is rounded to the dtype before the next, so the result equals
+    ``x + table_a[ids_a] + table_b[ids_b]`` evaluated left to right as tensor additions."""
+    _require_backend("add_gathered_rows", "cuda")
+    _require_cuda_tensors("cuda add_gathered_rows", x, table_a, ids_a, table_b, ids_b)
+    if x.ndim != 2 or not x.is_contiguous() or not cuda_supported_floating_dtype(x.dtype):
+        raise ValueError("add_gathered_rows needs a contiguous 2-D floating-point matrix")
+    n, dim = x.shape
+    if (table_b is None) != (ids_b is None):
+        raise ValueError("add_gathered_rows: table_b and ids_b come together")
+    for table, ids in ((table_a, ids_a), (table_b, ids_b)):
+        if table is None:
+            continue
+        if table.ndim != 2 or table.shape[1] != dim or table.dtype != x.dtype or not table.is_contiguous():
+            raise ValueError("add_gathered_rows tables must be contiguous [rows, dim] matrices of x's dtype")
+        if ids.dtype != torch.int64 or ids.numel() != n or not ids.is_contiguous():
+            raise ValueError("add_gathered_rows ids must be contiguous int64 with one entry per row of x")
+    with torch.cuda.device(x.device), _timed("add_gathered_rows", rows=n, dim=dim, esize=x.element_size(),
+                                            tables=1 if table_b is None else 2):
+        code = _lib.load().tb200_add_gathered_rows(
+            _ptr(x), n, dim, _ptr(table_a), table_a.shape[0], _ptr(ids_a), _ptr(table_b),
+            0 if table_b is None else table_b.shape[0], _ptr(ids_b), _DTYPE_CODES[x.dtype], _stream_ptr(),
+        )
+    _lib.check(code, "cuda add_gathered_rows")
+    return x
+
+
+def bias_silu_rows(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``x = silu(x + bias[group])`` in place for a contiguous ``x`` [groups, rows_per_group, cols] (or
+    [rows, cols] with ``bias`` [cols]); the sum is rounded to the dtype before the activation."""
+    _require_backend("bias_silu_rows", "cuda")
+    _require_cuda_tensors("cuda bias_silu_rows", x, bias)
+    if not x.is_contiguous() or x.ndim < 2 or not cuda_supported_floating_dtype(x.dtype):
+        raise ValueError("bias_silu_rows needs a contiguous floating-point tensor with at least 2 dimensions")
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    bias2 = bias.to(x.dtype).reshape(-1, cols).contiguous()
+    groups = bias2.shape[0]
+    if groups < 1 or rows % groups:
+        raise ValueError("bias_silu_rows: the bias groups must divide the rows")
+    with torch.cuda.device(x.device), _timed("bias_silu_rows", rows=rows, cols=cols, esize=x.element_size()):
+        code = _lib.load().tb200_bias_silu_rows(_ptr(x), rows, cols, _ptr(bias2), max(rows // groups, 1),
+                                                _DTYPE_CODES[x.dtype], _stream_ptr())
+    _lib.check(code, "cuda bias_silu_rows")
+    return x
+
+
 __all__ = [
+    "add_gathered_rows",
+    "bias_silu_rows",
     "AttentionMaskPlan",
     "Fp8FfnWeights",
     "ffn_fp8",

@@ -119,3 +119,39 @@ def test_scatter_rows_with_bias_and_residual(dtype):
     got = ops.scatter_rows(dst.clone().cuda(), ids.cuda(), src.cuda(), bias=bias.cuda(), residual=res.cuda()).cpu()
     assert torch.equal(got, want)  # one fp32 sum, one rounding
     assert ops.scatter_rows(dst.clone().cuda(), ids[:0].cuda(), src[:0].cuda()).shape == dst.shape
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("two", [False, True])
+def test_add_gathered_rows_bit_exact(dtype, two):
+    """In-place x += A[ia] (+= B[ib]) equals the tensor additions evaluated left to right, bit for bit."""
+    g = torch.Generator().manual_seed(5)
+    n, dim = 1237, 512
+    x = torch.randn(n, dim, generator=g).to(dtype)
+    a = torch.randn(65, dim, generator=g).to(dtype)
+    b = torch.randn(1040, dim, generator=g).to(dtype)
+    ia = torch.randint(-2, 70, (n,), generator=g)      # out-of-range ids clamp into the table
+    ib = torch.randint(0, 1040, (n,), generator=g)
+    want = x + a[ia.clamp(0, 64)]
+    if two:
+        want = want + b[ib]
+    xd = x.cuda()
+    out = ops.add_gathered_rows(xd, a.cuda(), ia.cuda(), *( (b.cuda(), ib.cuda()) if two else () ))
+    assert out.data_ptr() == xd.data_ptr()
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bias_silu_rows(dtype):
+    """x = silu(x + bias[group]) in place against the two torch operations it replaces."""
+    g = torch.Generator().manual_seed(6)
+    groups, per, cols = 5, 77, 256
+    x = (2.0 * torch.randn(groups, per, cols, generator=g)).to(dtype)
+    bias = torch.randn(groups, 1, cols, generator=g).to(dtype)
+    want = torch.nn.functional.silu((x + bias).float()).to(dtype)
+    got = ops.bias_silu_rows(x.cuda(), bias.cuda()).cpu()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() <= tol
+    if dtype == torch.bfloat16:   # one rounding step apart at most, identical almost everywhere
+        assert (got != want).float().mean().item() < 0.02

@@ -105,3 +105,24 @@ def test_full_size_sweep_properties(cols):
     assert (got.float() - R.rms_norm_fp32(x[idx], w, 1e-6).float()).abs().max().item() <= 2e-2
     got = ops.layer_norm(xd, w.cuda(), b.cuda(), 1e-6)[idx.cuda()].cpu()
     assert (got.float() - R.layer_norm_fp32(x[idx], w, b, 1e-6).float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols", [7, 128, 384, 512, 1024, 4096])
+def test_rms_norm_with_input_bias(dtype, cols):
+    """rms_norm(x, in_bias=b) == rms_norm of the fp32 sum x + b (the bias never rounds on its own)."""
+    x, w, b = _inputs(257, cols, dtype, seed=cols + 1)
+    got = ops.rms_norm(x.cuda(), w.cuda(), 1e-6, in_bias=b.cuda()).cpu()
+    want = R.rms_norm_fp32(x.float() + b.float(), w.float(), 1e-6)
+    assert (got.float() - want.float()).abs().max().item() <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols", [7, 128, 384, 512, 1024, 4096])
+def test_layer_norm_of_silu(dtype, cols):
+    """layer_norm(x, pre_silu=True) == layer_norm(silu(x)) with the activation rounded to the dtype."""
+    x, w, b = _inputs(257, cols, dtype, seed=cols + 2)
+    got = ops.layer_norm(x.cuda(), w.cuda(), b.cuda(), 1e-5, pre_silu=True).cpu()
+    act = torch.nn.functional.silu(x.float()).to(dtype)
+    want = R.layer_norm_fp32(act, w, b, 1e-5)
+    assert (got.float() - want.float()).abs().max().item() <= TOL[dtype]
