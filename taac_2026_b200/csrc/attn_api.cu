@@ -6,6 +6,8 @@ namespace tb200 {
 int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cudaStream_t stream);
 bool attn_tc05_supported(const AttnArgs& a, int head_dim, int dtype);
 int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t* status, cudaStream_t stream);
+bool attn_small_supported(const AttnArgs& a, int head_dim, int max_lq, int max_lk);
+int attn_small_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 }  // namespace tb200
 
 extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
@@ -41,10 +43,14 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     a.scale_log2 = scale * 1.4426950408889634f;
     if (cu_rows != nullptr && total_rows < 0) return TB200_ERR_SHAPE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // kernel: 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel
+    // kernel: 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel, 3 = one-warp-per-(sample, head) kernel
     const bool tc_ok = attn_tc05_supported(a, D, dtype) && (cu_rows == nullptr || total_rows > 0);
     if (kernel == 2 && !tc_ok) return TB200_ERR_UNSUPPORTED;
-    if (kernel < 0 || kernel > 2) return TB200_ERR_UNSUPPORTED;
+    if (kernel < 0 || kernel > 3) return TB200_ERR_UNSUPPORTED;
+    const bool small_ok = attn_small_supported(a, D, Lq, Lk);
+    if (kernel == 3 && !small_ok) return TB200_ERR_UNSUPPORTED;
+    // samples of at most 32 rows (the non-sequence tokens alone, late in the pyramid): no tensor-core tile pays
+    if (kernel == 3 || (kernel == 0 && small_ok)) return attn_small_forward(a, dtype, s);
     // Automatic choice: the tcgen05 kernel wherever it applies (bf16, head_dim 64, no key_valid map); measured
     // on full-length rows it leads the mma.sync kernel from 128 keys up, causal or not.  Samples shorter than
     // one 128-row block leave most of its tile idle, so those stay on the 64-row mma.sync tiles.

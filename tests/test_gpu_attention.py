@@ -183,3 +183,39 @@ def test_full_size_properties(kernel, causal):
         mask = R.structured_attention_mask(lens[b : b + 1], L, L, causal, causal)
         self_rows = (torch.arange(L)[None] >= lens[b : b + 1, None]) if causal else None
         _check(got[b : b + 1, :2], q[b : b + 1, :2], k[b : b + 1, :2], v[b : b + 1, :2], mask, self_rows)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("L", [1, 9, 17, 32])
+def test_small_sample_kernel(dtype, L):
+    """Kernel 3 (one warp per sample and head, at most 32 rows): every mask form of the other kernels."""
+    B, H, D = 37, 3, 64
+    q, k, v = _qkv(B, H, L, D, dtype, seed=40 + L)
+    g = torch.Generator().manual_seed(L)
+    lens = torch.randint(0, L + 1, (B,), generator=g)
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    # key padding, non-causal
+    got = ops.varlen_attention(dq, dk, dv, seq_len=lens.cuda(), kernel=3)
+    _check(got, q, k, v, R.structured_attention_mask(lens, L, L, False, False))
+    # causal with a non-sequence suffix and padded queries returning their value rows
+    ns = min(3, L)
+    lens_ns = torch.minimum(lens, torch.tensor(L - ns))
+    got = ops.varlen_attention(dq, dk, dv, seq_len=lens_ns.cuda(), ns_start=L - ns, causal=True, padded_query_self=True,
+                               kernel=3)
+    mask = R.structured_attention_mask(lens_ns, L, L - ns, True, True)
+    pos = torch.arange(L)[None]
+    self_rows = (pos >= lens_ns[:, None]) & (pos < L - ns)
+    _check(got, q, k, v, mask, self_rows)
+    # packed rows, causal: must agree with the mma.sync kernel on the same data
+    lens_p = lens.clamp_min(1)
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens_p, 0)
+    rows = int(cu[-1])
+    qkv = (torch.randn(rows, 3, H, D, generator=g) * 0.5).to(dtype).cuda()
+    kw = dict(causal=True, cu_rows=cu.cuda(), max_rows=int(lens_p.max()))
+    small = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], kernel=3, **kw).float()
+    ref = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], kernel=1, **kw).float()
+    assert (small - ref).abs().max().item() <= 1e-2
+    # automatic choice takes this kernel for such samples and gives the same bits
+    auto = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], kernel=0, **kw).float()
+    assert torch.equal(auto, small)
