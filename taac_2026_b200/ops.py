@@ -564,6 +564,19 @@ def _strided_ok(t: torch.Tensor) -> bool:
     return t.stride(-1) == 1 and all(s % 8 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
 
 
+def _attention_record_name(kernel: int, dtype: torch.dtype, dim: int, lq: int, lk: int, has_key_valid: bool) -> str:
+    """Name of the timing record: which of the three kernels ``tb200_attn_fwd`` picks (same rule as its
+    automatic choice), so that a benchmark can attribute time to each of them."""
+    if kernel == 0:
+        if dim == 64 and not has_key_valid and lq <= 32 and lk <= 32:
+            kernel = 3
+        elif dim == 64 and dtype == torch.bfloat16 and not has_key_valid and lq >= 128:
+            kernel = 2
+        else:
+            kernel = 1
+    return {1: "attention_mma", 2: "attention_tc05", 3: "attention_small"}.get(int(kernel), "attention")
+
+
 def varlen_attention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -640,7 +653,8 @@ def varlen_attention(
         scale = 1.0 / math.sqrt(dim)
     stride_arr = (ctypes.c_int64 * 12)(*strides)
     status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
-    with torch.cuda.device(q.device), _timed("attention", seq_len=lens, cu_rows=cu, key_valid=kv, batch=batch, heads=heads,
+    with torch.cuda.device(q.device), _timed(_attention_record_name(kernel, q.dtype, dim, lq, lk, kv is not None),
+                                             seq_len=lens, cu_rows=cu, key_valid=kv, batch=batch, heads=heads,
                                              lq=lq, lk=lk, dim=dim, ns_start=lk if ns_start is None else int(ns_start),
                                              causal=bool(causal), self_rows=bool(padded_query_self)):
         code = _lib.load().tb200_attn_fwd(
