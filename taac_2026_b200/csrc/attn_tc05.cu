@@ -328,7 +328,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 {
                     uint32_t sr[4][32];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_ld_x32(t_s + c * 32, sr[c]);
+                    for (int c = 0; c < 4; ++c) tmem_ld_2x16(t_s + c * 32, sr[c]);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tc_wait_ld(sr[c]);
 #pragma unroll
@@ -408,15 +408,15 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 // pass 2: the load of chunk c + 1 is in flight while chunk c is turned into probabilities
                 {
                     uint32_t ra[32], rb[32];
-                    tmem_ld_x32(t_s, ra);
+                    tmem_ld_2x16(t_s, ra);
                     tc_wait_ld(ra);
 #pragma unroll 1
                     for (int c = 0; c < 4; c += 2) {
-                        tmem_ld_x32(t_s + (c + 1) * 32, rb);
+                        tmem_ld_2x16(t_s + (c + 1) * 32, rb);
                         emit(c, ra);
                         tc_wait_ld(rb);
                         if (c == 0) {
-                            tmem_ld_x32(t_s + 2 * 32, ra);
+                            tmem_ld_2x16(t_s + 2 * 32, ra);
                         } else {               // the whole row has been read: S may be overwritten
                             tc_fence_before_sync();
                             mbar_arrive(&s_free);
