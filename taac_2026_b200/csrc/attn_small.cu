@@ -1,5 +1,6 @@
 // Attention forward for very short samples (at most 32 queries and 32 keys, head_dim 64): one warp per
-// (sample, head), one query row per lane.
+// (sample, head); P = 1, 2 or 4 lanes share a query row (each holds 64 / P of its dimensions), so that a
+// sample of 9 rows still keeps 18 of the 32 lanes busy.
 //
 // After the pyramid has dropped the behaviour sequence, a sample of the packed batch is only its handful of
 // non-sequence tokens; a 64 x 64 tensor-core tile per (sample, head) is then almost all padding and the launch
@@ -28,9 +29,11 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-template <typename T>
+template <typename T, int P>
 __global__ void __launch_bounds__(kWarps * 32)
 attn_small_kernel(const AttnArgs a) {
+    constexpr int CPL = kChunks / P;      // 16-byte pieces of a row per lane
+    constexpr int kRows = kMaxL / P;      // rows one warp can serve
     __shared__ uint4 kv_s[kWarps][2][kMaxL * kChunks];   // per warp: K rows, V rows
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -46,8 +49,8 @@ attn_small_kernel(const AttnArgs a) {
         row_base = a.cu_rows[b];
         lq = lk = a.cu_rows[b + 1] - static_cast<int32_t>(row_base);
     }
-    lq = min(lq, kMaxL);
-    lk = min(lk, kMaxL);
+    lq = min(lq, kRows);
+    lk = min(lk, kRows);
     const int valid_len = (a.seq_len != nullptr && !packed) ? min(max(a.seq_len[b], 0), lk) : lk;
     const int ns_start = packed ? lk : min(a.ns_start, lk);
     const bool causal = a.causal != 0;
@@ -67,40 +70,44 @@ attn_small_kernel(const AttnArgs a) {
     }
     __syncwarp();
 
-    const int r = lane;               // this lane's query
+    const int r = lane / P;           // this lane's query
+    const int part = lane % P;        // which 64 / P dimensions of the row it holds
+    const uint32_t group_mask = (P == 1 ? 1u : ((1u << P) - 1u)) << (lane & ~(P - 1));
     if (r >= lq) return;
     if (a.padded_query_self && r >= valid_len && r < ns_start) {   // padded query: its own value row
         const uint4* src = reinterpret_cast<const uint4*>(vp + static_cast<int64_t>(r) * a.v_sl);
         uint4* dst = reinterpret_cast<uint4*>(op + static_cast<int64_t>(r) * a.o_sl);
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) dst[c] = src[c];
+        for (int c = 0; c < CPL; ++c) dst[part * CPL + c] = src[part * CPL + c];
         return;
     }
 
-    float2 q[kD / 2];
+    float2 q[CPL * 4];
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
+    for (int c = 0; c < CPL; ++c) {
         float2 f[4];
-        Vec16<T>::unpack2(reinterpret_cast<const uint4*>(qp + static_cast<int64_t>(r) * a.q_sl)[c], f);
+        Vec16<T>::unpack2(reinterpret_cast<const uint4*>(qp + static_cast<int64_t>(r) * a.q_sl)[part * CPL + c], f);
 #pragma unroll
         for (int e = 0; e < 4; ++e) q[4 * c + e] = __fmul2_rn(f[e], make_float2(a.scale_log2, a.scale_log2));
     }
-    float2 acc[kD / 2];
+    float2 acc[CPL * 4];
 #pragma unroll
-    for (int i = 0; i < kD / 2; ++i) acc[i] = make_float2(0.f, 0.f);
+    for (int i = 0; i < CPL * 4; ++i) acc[i] = make_float2(0.f, 0.f);
     float m = -INFINITY, l = 0.f;
     const int k_end = causal ? min(lk, r + 1) : lk;
     for (int j = 0; j < k_end; ++j) {
-        if (!attn_visible(r, j, valid_len, ns_start, lk, causal)) continue;
+        if (!attn_visible(r, j, valid_len, ns_start, lk, causal)) continue;   // same decision in the whole group
         float2 dot = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
+        for (int c = 0; c < CPL; ++c) {
             float2 f[4];
-            Vec16<T>::unpack2(ks[j * kChunks + c], f);
+            Vec16<T>::unpack2(ks[j * kChunks + part * CPL + c], f);
 #pragma unroll
             for (int e = 0; e < 4; ++e) dot = __ffma2_rn(q[4 * c + e], f[e], dot);
         }
-        const float s = dot.x + dot.y;
+        float s = dot.x + dot.y;
+#pragma unroll
+        for (int o = 1; o < P; o <<= 1) s += __shfl_xor_sync(group_mask, s, o);
         const float m_new = fmaxf(m, s);
         const float corr = ex2(m - m_new);      // first key: exp2(-inf) = 0
         const float p = ex2(s - m_new);
@@ -109,9 +116,9 @@ attn_small_kernel(const AttnArgs a) {
         const float2 corr2 = make_float2(corr, corr);
         const float2 p2 = make_float2(p, p);
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
+        for (int c = 0; c < CPL; ++c) {
             float2 f[4];
-            Vec16<T>::unpack2(vs[j * kChunks + c], f);
+            Vec16<T>::unpack2(vs[j * kChunks + part * CPL + c], f);
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[4 * c + e] = __ffma2_rn(f[e], p2, __fmul2_rn(acc[4 * c + e], corr2));
         }
@@ -120,12 +127,21 @@ attn_small_kernel(const AttnArgs a) {
     const float2 inv = make_float2(inv1, inv1);
     uint4* dst = reinterpret_cast<uint4*>(op + static_cast<int64_t>(r) * a.o_sl);
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
+    for (int c = 0; c < CPL; ++c) {
         float2 f[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) f[e] = __fmul2_rn(acc[4 * c + e], inv);
-        dst[c] = Vec16<T>::pack2(f);
+        dst[part * CPL + c] = Vec16<T>::pack2(f);
     }
+}
+
+template <typename T>
+void launch_small(const AttnArgs& a, int64_t grid, cudaStream_t stream) {
+    const int longest = a.Lq > a.Lk ? a.Lq : a.Lk;   // upper bound of any sample's rows
+    const unsigned g = static_cast<unsigned>(grid);
+    if (longest <= kMaxL / 4) attn_small_kernel<T, 4><<<g, kWarps * 32, 0, stream>>>(a);
+    else if (longest <= kMaxL / 2) attn_small_kernel<T, 2><<<g, kWarps * 32, 0, stream>>>(a);
+    else attn_small_kernel<T, 1><<<g, kWarps * 32, 0, stream>>>(a);
 }
 
 }  // namespace
@@ -138,10 +154,8 @@ int attn_small_forward(const AttnArgs& a, int dtype, cudaStream_t stream) {
     const int64_t pairs = static_cast<int64_t>(a.B) * a.H;
     const int64_t grid = (pairs + kWarps - 1) / kWarps;
     if (grid > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
-    if (dtype == TB200_BF16)
-        attn_small_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), kWarps * 32, 0, stream>>>(a);
-    else
-        attn_small_kernel<__half><<<static_cast<unsigned>(grid), kWarps * 32, 0, stream>>>(a);
+    if (dtype == TB200_BF16) launch_small<__nv_bfloat16>(a, grid, stream);
+    else launch_small<__half>(a, grid, stream);
     count_launch();
     return launch_status();
 }

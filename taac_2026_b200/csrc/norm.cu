@@ -33,7 +33,11 @@ constexpr int kStages = 4;
 //             kernel would have written
 enum Pre : int { kPreNone = 0, kPreBias = 1, kPreSilu = 2 };
 
+// SiLU for a value that is rounded to T afterwards: the 16-bit types take the one-MUFU form
+// h * tanh(h) + h (h = x / 2, about 11 bits), fp32 the exponential form.
+template <typename T>
 __device__ __forceinline__ float silu_f(float x) {
+    if (sizeof(T) == 4) return x / (1.0f + __expf(-x));
     const float h = 0.5f * x;
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
@@ -146,7 +150,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                     if (PRE == kPreSilu) {
 #pragma unroll
                         for (int e = 0; e < N / 2; ++e)
-                            v[u][j][e] = make_float2(round_to<T>(silu_f(v[u][j][e].x)), round_to<T>(silu_f(v[u][j][e].y)));
+                            v[u][j][e] = make_float2(round_to<T>(silu_f<T>(v[u][j][e].x)), round_to<T>(silu_f<T>(v[u][j][e].y)));
                     }
                 } else {
 #pragma unroll
@@ -256,7 +260,7 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     auto load = [&](const T* xr, int c) -> float {
         float v = to_float<T>(xr[c]);
         if (PRE == kPreBias) v += to_float<T>(beta[c]);
-        if (PRE == kPreSilu) v = round_to<T>(silu_f(v));
+        if (PRE == kPreSilu) v = round_to<T>(silu_f<T>(v));
         return v;
     };
     for (int64_t r = warp; r < rows; r += n_warps) {
