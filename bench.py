@@ -82,7 +82,7 @@ def small_spec() -> OneTransSpec:
 
 
 WORKLOADS = {
-    "full": dict(spec=full_scale_spec, batch=8192, seq_len=1024, min_len=128, field_exp=1.1, seq_exp=1.1, micro=4096,
+    "full": dict(spec=full_scale_spec, batch=8192, seq_len=1024, min_len=128, field_exp=1.1, seq_exp=1.1, micro=8192,
                  name="OneTrans full scale: 8192 samples/GPU, 64 fields x 1000001 x 128 bf16, L<=1024, d512 h8 x8 layers"),
     "small": dict(spec=small_spec, batch=512, seq_len=256, min_len=16, field_exp=1.2, seq_exp=1.1, micro=512,
                   name="OneTrans baseline size: 512 samples, 32 fields x 100001 x 64, L<=256, d128 h4 x2 layers"),

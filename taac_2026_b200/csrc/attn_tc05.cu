@@ -325,6 +325,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
                 // pass 1, row max: the four chunk loads are issued together, so one TMEM latency is exposed
                 float mx0 = -INFINITY, mx1 = -INFINITY;
+                uint32_t chunk_live = 0xfu;   // bit c: some row of the warp sees a key of chunk c
                 {
                     uint32_t sr[4][32];
 #pragma unroll
@@ -335,6 +336,12 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     for (int c = 0; c < 4; ++c) {
                         if (!FULL) {
                             const uint32_t vis = chunk_mask(n0 + c * 32);
+                            // a chunk that no row of the warp can see (above the diagonal, past the keys) is
+                            // skipped in both passes
+                            if (!__any_sync(0xffffffffu, vis != 0u)) {
+                                chunk_live &= ~(1u << c);
+                                continue;
+                            }
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
                                 if (!((vis >> i) & 1u)) sr[c][i] = 0xff800000u;  // -inf
@@ -388,6 +395,13 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 const float2 nms2 = make_float2(-ms, -ms);
                 auto emit = [&](const int c, uint32_t (&r)[32]) {
                     if (!FULL) {
+                        if (!((chunk_live >> c) & 1u)) {   // nothing visible to this warp: P = 0
+                            uint32_t zero[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) zero[i] = 0u;
+                            tmem_st_x16(t_p + c * 16, zero);
+                            return;
+                        }
                         const uint32_t vis = chunk_mask(n0 + c * 32);
 #pragma unroll
                         for (int i = 0; i < 32; ++i)

@@ -657,7 +657,7 @@ class OneTransInference:
             if self.ffn_mode == "fp8":
                 # tokens + attention out-projection with the residual inside the GEMM (beta = 1); its bias is
                 # added by the norm on the fly and rides on the FFN output biases into the next residual
-                tokens = torch.addmm(tokens, attn2d, blk["out_w_t"])
+                tokens = tokens.addmm_(attn2d, blk["out_w_t"])   # in place: an out-of-place addmm first copies C
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
                 out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens)
                 ns_b2 = blk["ns_b2_folded"]
