@@ -78,6 +78,16 @@ class ModelInput:
     def batch_size(self) -> int:
         return int(self.user.int_values.shape[0])
 
+    def tensors(self) -> list[torch.Tensor]:
+        """Every tensor of the record (for stream bookkeeping such as ``Tensor.record_stream``)."""
+        out = []
+        for entity in (self.user, self.item):
+            out += [entity.int_values, entity.int_missing_mask, entity.dense_values, entity.dense_missing_mask]
+        for seq in self.sequences.values():
+            out += [seq.values, seq.lengths, seq.timestamps]
+        out.append(self.request_timestamp)
+        return out
+
     def nbytes(self) -> int:
         total = 0
         for entity in (self.user, self.item):

@@ -705,6 +705,40 @@ class OneTransInference:
         return probs.reshape(-1) if probs.shape[1] == 1 else probs
 
 
+def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int | None = None):
+    """Scores for a stream of host-resident batches, one ``scores`` tensor (on the device) per batch.
+
+    The serving loop of `evaluation/workflow.py:246-293` with the host-to-device copy taken off the critical
+    path: the copy of batch i + 1 runs on a side stream while batch i is scored, so that in steady state a
+    step costs max(copy, compute) instead of their sum.  ``host_batches`` should be pinned
+    (``ModelInput.pin_memory()``) for the copies to be asynchronous."""
+    dev = model.device
+    compute = torch.cuda.current_stream(dev)
+    copier = torch.cuda.Stream(dev)
+
+    def stage(batch):
+        copier.wait_stream(compute)          # pinned source and allocator state are in a known order
+        with torch.cuda.stream(copier):
+            staged = batch.to(dev, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(copier)
+        return staged, done
+
+    it = iter(host_batches)
+    first = next(it, None)
+    if first is None:
+        return
+    pending = stage(first)
+    while pending is not None:
+        staged, done = pending
+        nxt = next(it, None)
+        compute.wait_event(done)
+        for t in staged.tensors():           # allocated on the copy stream, consumed on the compute stream
+            t.record_stream(compute)
+        pending = stage(nxt) if nxt is not None else None
+        yield model.scores(staged, micro_batch=micro_batch)
+
+
 def random_state_dict(spec: OneTransSpec, *, seed: int = 0, device: torch.device | str = "cpu",
                       dtype: torch.dtype = torch.float32) -> dict[str, torch.Tensor]:
     """Seeded random weights with the parameter names, shapes and init scales of the reference module
@@ -811,6 +845,7 @@ __all__ = [
     "hash_compress_ids",
     "pyramid_keep_count",
     "random_state_dict",
+    "score_stream",
     "sequence_stats",
     "sequence_time_buckets",
 ]

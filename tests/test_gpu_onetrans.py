@@ -121,3 +121,20 @@ def test_serving_shape_against_oracle(ffn, tol):
     assert np.abs(got - want).max() <= tol
     padded = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn=ffn, packed=False).scores(batch.to("cuda")).cpu().numpy()
     assert np.abs(got - padded).max() <= tol
+
+
+def test_score_stream_matches_resident_scores():
+    """The pipelined serving loop (copy of batch i + 1 under the kernels of batch i) returns, batch by
+    batch, exactly the scores of the plain call on device-resident inputs."""
+    from taac_2026_b200.onetrans import score_stream
+
+    spec = _mini_spec()
+    sd = random_state_dict(spec, seed=0)
+    model = OneTransInference(sd, spec, dtype=torch.bfloat16)
+    host = [synthetic_batch(spec, 64, seq_len=96, min_len=4, seed=s).pin_memory() for s in (3, 4, 5, 6)]
+    got = [s.clone() for s in score_stream(model, host, micro_batch=32)]
+    torch.cuda.synchronize()
+    assert len(got) == len(host)
+    for scores, batch in zip(got, host):
+        want = model.scores(batch.to("cuda"), micro_batch=32)
+        assert torch.equal(scores, want)
