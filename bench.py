@@ -277,7 +277,7 @@ def cpu_state_dict(sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
     return out
 
 
-def time_cpu_port(sd_cpu: dict, spec: OneTransSpec, batch_cpu, *, budget_s: float, steps: int = 1) -> dict:
+def time_cpu_port(sd_cpu: dict, spec: OneTransSpec, batch_cpu, *, limit_s: float, steps: int = 1) -> dict:
     from oracle import torch_cpu
 
     threads = os.cpu_count() or 1
@@ -288,7 +288,7 @@ def time_cpu_port(sd_cpu: dict, spec: OneTransSpec, batch_cpu, *, budget_s: floa
     torch_cpu.predict(sd_cpu, spec_dict, batch_cpu.slice(0, rows))  # warm-up and cost probe
     probe = time.perf_counter() - t0
     per_row = max(probe / rows, 1e-6)
-    sample = int(max(rows, min(batch_cpu.batch_size, budget_s / per_row)))
+    sample = int(max(rows, min(batch_cpu.batch_size, limit_s / per_row)))
     sample = min(sample, 256)
     times = []
     for _ in range(max(1, steps)):
@@ -326,7 +326,7 @@ def run_e2e(args) -> None:
         del sd
         batch_cpu = synthetic_batch(spec, min(batch_size, 512), seq_len=wl["seq_len"], min_len=wl["min_len"], seed=0,
                                     field_exponent=wl["field_exp"], seq_exponent=wl["seq_exp"])
-        res = time_cpu_port(sd_cpu, spec, batch_cpu, budget_s=20.0, steps=max(1, min(args.steps, 3)))
+        res = time_cpu_port(sd_cpu, spec, batch_cpu, limit_s=20.0, steps=max(1, min(args.steps, 3)))
         line = {
             "impl": "reference", "metric": "pcvr_infer_samples_per_s", "value": res["value"], "unit": "samples/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -445,7 +445,7 @@ def run_e2e(args) -> None:
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         sd_cpu = cpu_state_dict(sd)
-        cpu = time_cpu_port(sd_cpu, spec, host_batch.slice(0, min(batch_size, 256)), budget_s=15.0)
+        cpu = time_cpu_port(sd_cpu, spec, host_batch.slice(0, min(batch_size, 256)), limit_s=15.0)
         # same rows on the GPU: the bounded sample doubles as a full-scale score parity check
         from oracle import torch_cpu
 

@@ -14,7 +14,7 @@
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
 //   warps 2..17  promotion + epilogue: each thread owns one output row and 64 of the 256 columns
 //                (four warps per TMEM lane quarter, so that four warps per scheduler hide each
-//                other's tcgen05.ld and MUFU latencies; the per-element instruction budget at K = 512
+//                other's tcgen05.ld and MUFU latencies; the per-element instruction allowance at K = 512
 //                is only about eight issue slots, hence packed fp32x2 math and a tanh-based SiLU)
 // The output tile leaves through shared memory: every epilogue thread writes its 16-byte pieces into a
 // 128-byte-swizzled staging tile and one thread hands the tile to TMA, so global memory sees full rows of
@@ -365,7 +365,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     }
                     tc_fence_after_sync();
                     const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
-                    // 16 columns at a time: the accumulators already take 64 registers of a 96-register budget
+                    // 16 columns at a time: the accumulators already take 64 of the 96 registers a thread may use
                     uint32_t r[16];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {

@@ -17,7 +17,9 @@ import torch
 
 
 def _reference_root() -> Path | None:
-    for candidate in (os.environ.get("TAAC2026_REFERENCE"), "/root/reference"):
+    # the checkout named by TAAC2026_REFERENCE, else a sibling `reference/` directory of this repository
+    sibling = Path(__file__).resolve().parents[2] / "reference"
+    for candidate in (os.environ.get("TAAC2026_REFERENCE"), str(sibling)):
         if candidate and (Path(candidate) / "src" / "taac2026").is_dir():
             return Path(candidate)
     return None
