@@ -190,7 +190,7 @@ def launch_work(name: str, meta: dict) -> tuple[str, float]:
     """-> (bound, algorithmic bytes or flops) of one recorded launch."""
     if name.startswith("attention"):
         return "tensor", attention_flops(meta)
-    if name == "bias_silu_rows":     # in place: read + write of the matrix
+    if name == "bias_act_rows":     # in place: read + write of the matrix
         return "hbm", 2.0 * meta["rows"] * meta["cols"] * meta["esize"]
     if name == "add_gathered_rows":  # in place: read + write of the matrix, one table row per id (tables are L2-resident)
         return "hbm", (2.0 + meta["tables"]) * meta["rows"] * meta["dim"] * meta["esize"] + 8.0 * meta["tables"] * meta["rows"]

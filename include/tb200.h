@@ -143,12 +143,13 @@ int tb200_scatter_rows(void* dst, int64_t dst_rows, int64_t dst_stride, int32_t 
 int tb200_add_gathered_rows(void* x, int64_t n, int32_t dim, const void* table_a, int64_t rows_a, const int64_t* ids_a,
                             const void* table_b, int64_t rows_b, const int64_t* ids_b, int dtype, void* stream);
 
-/* x[r, :] = silu(x[r, :] + bias[r / rows_per_group, :]) in place, the sum rounded to `dtype` before the
- * activation: first half of OneTrans's per-token `FeedForward` (`nn.Linear` bias + `nn.SiLU()`,
- * experiments/onetrans/model.py:36-41) when the linear parts of all tokens run as one batched product.
- * x: [rows, cols]; bias: [rows / rows_per_group, cols]; cols * sizeof(dtype) a multiple of 16. */
-int tb200_bias_silu_rows(void* x, int64_t rows, int32_t cols, const void* bias, int64_t rows_per_group, int dtype,
-                         void* stream);
+/* x[r, :] = act(x[r, :] + bias[r / rows_per_group, :]) in place; act 0 = identity, 1 = SiLU with the sum
+ * rounded to `dtype` before the activation: the `nn.Linear` bias (+ `nn.SiLU()`) of OneTrans's per-token
+ * projections and `FeedForward` (experiments/onetrans/model.py:36-41, :60-67) when the linear parts of all
+ * tokens run as one batched product.  x: [rows, cols]; bias: [rows / rows_per_group, cols];
+ * cols * sizeof(dtype) a multiple of 16. */
+int tb200_bias_act_rows(void* x, int64_t rows, int32_t cols, const void* bias, int64_t rows_per_group, int32_t act,
+                        int dtype, void* stream);
 
 /* ---- (c) varlen masked attention forward ----------------------------------------------------
  * o[b, h, q, :] = softmax_k(scale * <q[b, h, q, :], k[b, h, k, :]> over visible k) . v[b, h, k, :]

@@ -266,13 +266,13 @@ add_gathered_rows_kernel(uint4* __restrict__ x, int64_t n, int chunks, const uin
 }
 
 // ---------------------------------------------------------------------------------------
-// bias_silu_rows: x[r, :] = silu(x[r, :] + bias[r / rows_per_group, :]), in place; the sum is rounded to T
-// before the activation, like an addition followed by a separate SiLU.
+// bias_act_rows: x[r, :] = act(x[r, :] + bias[r / rows_per_group, :]), in place, act = identity or SiLU; the
+// sum is rounded to T before the activation, like an addition followed by a separate SiLU.
 // ---------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool SILU>
 __global__ void __launch_bounds__(kThreads)
-bias_silu_rows_kernel(uint4* __restrict__ x, int64_t rows, int chunks, const uint4* __restrict__ bias,
-                      int64_t rows_per_group) {
+bias_act_rows_kernel(uint4* __restrict__ x, int64_t rows, int chunks, const uint4* __restrict__ bias,
+                     int64_t rows_per_group) {
     constexpr int N = Vec16<T>::N;
     const int64_t total = rows * chunks;
     for (int64_t j = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; j < total;
@@ -284,9 +284,11 @@ bias_silu_rows_kernel(uint4* __restrict__ x, int64_t rows, int chunks, const uin
         Vec16<T>::unpack(bias[(r / rows_per_group) * chunks + c], b);
 #pragma unroll
         for (int e = 0; e < N; ++e) f[e] += b[e];
-        Vec16<T>::unpack(Vec16<T>::pack(f), f);
+        if (SILU) {
+            Vec16<T>::unpack(Vec16<T>::pack(f), f);
 #pragma unroll
-        for (int e = 0; e < N; ++e) f[e] = f[e] / (1.0f + __expf(-f[e]));
+            for (int e = 0; e < N; ++e) f[e] = f[e] / (1.0f + __expf(-f[e]));
+        }
         x[j] = Vec16<T>::pack(f);
     }
 }
@@ -485,10 +487,11 @@ extern "C" int tb200_add_gathered_rows(void* x, int64_t n, int32_t dim, const vo
     return launch_status();
 }
 
-extern "C" int tb200_bias_silu_rows(void* x, int64_t rows, int32_t cols, const void* bias, int64_t rows_per_group,
-                                    int dtype, void* stream) {
+extern "C" int tb200_bias_act_rows(void* x, int64_t rows, int32_t cols, const void* bias, int64_t rows_per_group,
+                                   int32_t act, int dtype, void* stream) {
     using namespace tb200;
     if (rows < 0 || cols < 1 || rows_per_group < 1) return TB200_ERR_SHAPE;
+    if (act != 0 && act != 1) return TB200_ERR_UNSUPPORTED;
     if (rows == 0) return TB200_OK;
     const int es = dtype_size(dtype);
     if (es == 0) return TB200_ERR_DTYPE;
@@ -501,8 +504,12 @@ extern "C" int tb200_bias_silu_rows(void* x, int64_t rows, int32_t cols, const v
     if (grid > cap) grid = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define TB200_BSILU(T)                                                                                        \
-    bias_silu_rows_kernel<T><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(static_cast<uint4*>(x), rows, chunks, \
-                                                                              static_cast<const uint4*>(bias), rows_per_group)
+    if (act == 1)                                                                                             \
+        bias_act_rows_kernel<T, true><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(                       \
+            static_cast<uint4*>(x), rows, chunks, static_cast<const uint4*>(bias), rows_per_group);           \
+    else                                                                                                      \
+        bias_act_rows_kernel<T, false><<<static_cast<unsigned>(grid), kThreads, 0, s>>>(                      \
+            static_cast<uint4*>(x), rows, chunks, static_cast<const uint4*>(bias), rows_per_group)
     switch (dtype) {
         case TB200_F32: TB200_BSILU(float); break;
         case TB200_F16: TB200_BSILU(__half); break;

@@ -641,6 +641,11 @@ class OneTransInference:
 
         d, heads, hd = self.d, self.heads, self.head_dim
         for layer, blk in enumerate(self.blocks):
+            if ns > 0 and max_rows[layer] == ns:
+                # no sample has a sequence token left from here on: the remaining blocks only see the NS tokens
+                seq_summary = torch.zeros(batch, d, device=dev)
+                ns_summary = self._ns_only_blocks(tokens, layer, batch)
+                return self._classify(seq_summary, ns_summary)
             p = blk["p"]
             cu32 = cu[layer].to(torch.int32)
             x = ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
@@ -689,6 +694,36 @@ class OneTransInference:
         seq_summary = seq_sum / n_last.clamp_min(1).to(torch.float32)[:, None]
         ns_summary = tokens[ns_rows.reshape(-1)].view(batch, ns, d).mean(dim=1)
         return self._classify(seq_summary, ns_summary)
+
+    def _ns_only_blocks(self, tokens: torch.Tensor, first_layer: int, batch: int) -> torch.Tensor:
+        """Blocks ``first_layer`` .. end for a batch whose samples hold nothing but their NS tokens, then the final
+        norm and the NS mean -> [B, d] fp32.
+
+        With no sequence token left, every row of `OneTransBlock.forward` (experiments/onetrans/model.py:97-107)
+        takes the per-token projections and the per-token FeedForward, and every sample attends causally over
+        its ``ns`` tokens.  The block then is six batched or shared matrix products on a token-major
+        ``[ns, B, d]`` tensor with no gathers, scatters or shared-weight work that would be overwritten."""
+        ns, d, heads, hd = self.num_ns, self.d, self.heads, self.head_dim
+        tok = tokens.view(batch, ns, d).transpose(0, 1).contiguous()            # [ns, B, d]
+        flat = tok.view(ns * batch, d)
+        for blk in self.blocks[first_layer:]:
+            p = blk["p"]
+            x = ops.rms_norm(flat, self._p(p + ".attn_norm.weight"), 1e-6)
+            qkv = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_qkv_w"]), blk["ns_qkv_b"], silu=False)
+            # sample-major views of the token-major tensors: (B, L = ns, H, hd) with strides (3d, B * 3d, hd, 1)
+            q, k, v = (qkv[:, :, i * d : (i + 1) * d].unflatten(-1, (heads, hd)).permute(1, 0, 2, 3) for i in range(3))
+            if q.dtype == torch.float32:
+                q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+            attn = torch.empty(ns, batch, heads, hd, dtype=q.dtype, device=q.device)
+            ops.varlen_attention(q, k, v, causal=True, layout="blhd", kernel=self.attention_kernel,
+                                 out=attn.permute(1, 0, 2, 3))
+            flat.addmm_(attn.view(ns * batch, d).to(self.dtype), blk["out_w_t"])   # bias: added by the norm, kept in ns_b2_folded
+            x = ops.rms_norm(flat, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
+            h = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_w1"]), blk["ns_b1"], silu=True)
+            tok = ops.bias_act_rows(torch.baddbmm(tok, h, blk["ns_w2"]), blk["ns_b2_folded"], silu=False)
+            flat = tok.view(ns * batch, d)
+        final = ops.rms_norm(flat, self._p("final_norm.weight"), 1e-6).float()
+        return final.view(ns, batch, d).mean(dim=0)
 
     @torch.inference_mode()
     def scores(self, inputs, micro_batch: int | None = None) -> torch.Tensor:

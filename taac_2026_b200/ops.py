@@ -593,8 +593,12 @@ def varlen_attention(
     key_valid: torch.Tensor | None = None,
     kernel: int = 0,
     check: bool = False,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """Masked attention forward with the mask given by lengths (never materialised).
+
+    ``out`` (optional) receives the result instead of a new contiguous tensor: same shape and dtype as
+    ``q``, any strides whose rows are 16-byte aligned (e.g. a token-major buffer viewed sample-major).
 
     ``kernel``: 0 picks automatically (the tcgen05/TMEM kernel for head_dim 64 bf16 with at least 128
     rows, the mma.sync kernel otherwise), 1 / 2 force one of them.  ``check=True`` reads the tcgen05
@@ -622,6 +626,8 @@ def varlen_attention(
         if max_rows is None:
             raise ValueError("packed varlen_attention needs max_rows")
         lq = lk = int(max_rows)
+        if out is not None:
+            raise ValueError("varlen_attention: out= is for padded batches")
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         strides = []
         for t in (q, k, v, out):
@@ -638,7 +644,10 @@ def varlen_attention(
             lk = k.shape[1]
         else:
             raise ValueError(f"unknown layout {layout}")
-        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        elif out.shape != q.shape or out.dtype != q.dtype or out.device != q.device or not _strided_ok(out):
+            raise ValueError("varlen_attention out must match q in shape, dtype and device, with 16-byte aligned rows")
         strides = []
         for t in (q, k, v, out):
             strides += list(_attn_strides(t, layout))
@@ -979,28 +988,34 @@ def add_gathered_rows(x: torch.Tensor, table_a: torch.Tensor, ids_a: torch.Tenso
     return x
 
 
-def bias_silu_rows(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
-    """``x = silu(x + bias[group])`` in place for a contiguous ``x`` [groups, rows_per_group, cols] (or
-    [rows, cols] with ``bias`` [cols]); the sum is rounded to the dtype before the activation."""
-    _require_backend("bias_silu_rows", "cuda")
-    _require_cuda_tensors("cuda bias_silu_rows", x, bias)
+def bias_act_rows(x: torch.Tensor, bias: torch.Tensor, *, silu: bool) -> torch.Tensor:
+    """``x = act(x + bias[group])`` in place for a contiguous ``x`` [groups, rows_per_group, cols] (or
+    [rows, cols] with ``bias`` [cols]); ``act`` is SiLU (the sum rounded to the dtype first) or identity."""
+    _require_backend("bias_act_rows", "cuda")
+    _require_cuda_tensors("cuda bias_act_rows", x, bias)
     if not x.is_contiguous() or x.ndim < 2 or not cuda_supported_floating_dtype(x.dtype):
-        raise ValueError("bias_silu_rows needs a contiguous floating-point tensor with at least 2 dimensions")
+        raise ValueError("bias_act_rows needs a contiguous floating-point tensor with at least 2 dimensions")
     cols = x.shape[-1]
     rows = x.numel() // cols
     bias2 = bias.to(x.dtype).reshape(-1, cols).contiguous()
     groups = bias2.shape[0]
     if groups < 1 or rows % groups:
-        raise ValueError("bias_silu_rows: the bias groups must divide the rows")
-    with torch.cuda.device(x.device), _timed("bias_silu_rows", rows=rows, cols=cols, esize=x.element_size()):
-        code = _lib.load().tb200_bias_silu_rows(_ptr(x), rows, cols, _ptr(bias2), max(rows // groups, 1),
-                                                _DTYPE_CODES[x.dtype], _stream_ptr())
-    _lib.check(code, "cuda bias_silu_rows")
+        raise ValueError("bias_act_rows: the bias groups must divide the rows")
+    with torch.cuda.device(x.device), _timed("bias_act_rows", rows=rows, cols=cols, esize=x.element_size()):
+        code = _lib.load().tb200_bias_act_rows(_ptr(x), rows, cols, _ptr(bias2), max(rows // groups, 1),
+                                               1 if silu else 0, _DTYPE_CODES[x.dtype], _stream_ptr())
+    _lib.check(code, "cuda bias_act_rows")
     return x
+
+
+def bias_silu_rows(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``x = silu(x + bias[group])`` in place (see ``bias_act_rows``)."""
+    return bias_act_rows(x, bias, silu=True)
 
 
 __all__ = [
     "add_gathered_rows",
+    "bias_act_rows",
     "bias_silu_rows",
     "AttentionMaskPlan",
     "Fp8FfnWeights",

@@ -138,3 +138,31 @@ def test_score_stream_matches_resident_scores():
     for scores, batch in zip(got, host):
         want = model.scores(batch.to("cuda"), micro_batch=32)
         assert torch.equal(scores, want)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-3), (torch.bfloat16, 5e-3)])
+def test_blocks_with_only_ns_tokens_left(dtype, tol):
+    """Short behaviour sequences under a deep pyramid: from some block on no sample has a sequence token left
+    and the engine switches to its token-major NS-only blocks.  Scores must still match the oracle, which
+    runs the reference's padded algorithm."""
+    spec = OneTransSpec(
+        user_int_specs=[(1000, i, 1) for i in range(12)], item_int_specs=[(1000, i, 1) for i in range(6)],
+        user_dense_dim=16, item_dense_dim=0, seq_vocab_sizes={"seq_a": [5000]}, d_model=128, emb_dim=64,
+        num_blocks=4, num_heads=2, hidden_mult=4, seq_top_k=96, user_ns_tokens=4, item_ns_tokens=2,
+    )
+    sd = random_state_dict(spec, seed=3)
+    batch = synthetic_batch(spec, 96, seq_len=96, min_len=1, seed=7)
+    # keep every sequence short so that the pyramid's tail crop removes all of it after the first blocks
+    short = batch.sequences["seq_a"].lengths.clamp(max=6)
+    batch = ModelInput(batch.user, batch.item,
+                       {"seq_a": SequenceInput(batch.sequences["seq_a"].values, short, batch.sequences["seq_a"].timestamps)},
+                       batch.request_timestamp)
+    want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
+    model = OneTransInference(sd, spec, dtype=dtype)
+    calls = []
+    inner = model._ns_only_blocks
+    model._ns_only_blocks = lambda tokens, first_layer, b: (calls.append(first_layer), inner(tokens, first_layer, b))[1]
+    got = model.scores(batch.to("cuda")).cpu().numpy()
+    assert calls and 0 < calls[0] < spec.num_blocks, "the NS-only path was expected to take over after the first block"
+    want = oracle_model.sigmoid_scores(want_logits).reshape(-1)
+    assert np.abs(got - want).max() <= tol
