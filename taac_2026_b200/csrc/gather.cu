@@ -274,22 +274,39 @@ __global__ void __launch_bounds__(kThreads)
 bias_act_rows_kernel(uint4* __restrict__ x, int64_t rows, int chunks, const uint4* __restrict__ bias,
                      int64_t rows_per_group) {
     constexpr int N = Vec16<T>::N;
-    const int64_t total = rows * chunks;
-    for (int64_t j = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; j < total;
-         j += static_cast<int64_t>(gridDim.x) * kThreads) {
-        const int64_t r = j / chunks;
-        const int c = static_cast<int>(j - r * chunks);
-        float f[N], b[N];
-        Vec16<T>::unpack(x[j], f);
-        Vec16<T>::unpack(bias[(r / rows_per_group) * chunks + c], b);
+    constexpr int U = 4;   // 16-byte pieces in flight per thread
+    // a thread keeps one column piece c and walks down the rows, so its bias piece changes only with the group
+    const int cols_per_cta = kThreads < chunks ? kThreads : chunks;       // pieces of a row served by one CTA pass
+    const int rows_per_pass = kThreads / cols_per_cta;
+    const int c0 = threadIdx.x % cols_per_cta;
+    const int r_in = threadIdx.x / cols_per_cta;
+    if (r_in >= rows_per_pass) return;
+    for (int c = c0; c < chunks; c += cols_per_cta) {
+        for (int64_t r = static_cast<int64_t>(blockIdx.x) * rows_per_pass * U + r_in; r < rows;
+             r += static_cast<int64_t>(gridDim.x) * rows_per_pass * U) {
+            uint4 v[U];
 #pragma unroll
-        for (int e = 0; e < N; ++e) f[e] += b[e];
-        if (SILU) {
-            Vec16<T>::unpack(Vec16<T>::pack(f), f);
+            for (int u = 0; u < U; ++u) {
+                const int64_t ru = r + static_cast<int64_t>(u) * rows_per_pass;
+                if (ru < rows) v[u] = x[ru * chunks + c];
+            }
 #pragma unroll
-            for (int e = 0; e < N; ++e) f[e] = f[e] / (1.0f + __expf(-f[e]));
+            for (int u = 0; u < U; ++u) {
+                const int64_t ru = r + static_cast<int64_t>(u) * rows_per_pass;
+                if (ru >= rows) continue;
+                float f[N], b[N];
+                Vec16<T>::unpack(v[u], f);
+                Vec16<T>::unpack(bias[(ru / rows_per_group) * chunks + c], b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) f[e] += b[e];
+                if (SILU) {
+                    Vec16<T>::unpack(Vec16<T>::pack(f), f);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) f[e] = __fdividef(f[e], 1.0f + __expf(-f[e]));
+                }
+                x[ru * chunks + c] = Vec16<T>::pack(f);
+            }
         }
-        x[j] = Vec16<T>::pack(f);
     }
 }
 
@@ -499,7 +516,8 @@ extern "C" int tb200_bias_act_rows(void* x, int64_t rows, int32_t cols, const vo
     if ((static_cast<int64_t>(cols) * es) % 16 != 0 || !aligned16(x) || !aligned16(bias)) return TB200_ERR_ALIGN;
     if (!device_info().valid) return TB200_ERR_DEVICE;
     const int chunks = cols * es / 16;
-    int64_t grid = (rows * chunks + kThreads - 1) / kThreads;
+    const int rows_per_pass = chunks >= kThreads ? 1 : kThreads / chunks;
+    int64_t grid = (rows + rows_per_pass * 4 - 1) / (rows_per_pass * 4);
     const int64_t cap = static_cast<int64_t>(device_info().sm_count) * 16;
     if (grid > cap) grid = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
