@@ -155,3 +155,33 @@ def test_bias_silu_rows(dtype):
     assert diff.max().item() <= tol
     if dtype == torch.bfloat16:   # one rounding step apart at most, identical almost everywhere
         assert (got != want).float().mean().item() < 0.02
+
+
+def test_row_kernels_edge_cases():
+    """Empty inputs are no-ops; shapes the kernels cannot serve are rejected on the host with ValueError."""
+    dev = "cuda"
+    x0 = torch.empty(0, 64, dtype=torch.bfloat16, device=dev)
+    table = torch.randn(5, 64, device=dev).bfloat16()
+    ids0 = torch.empty(0, dtype=torch.int64, device=dev)
+    assert ops.add_gathered_rows(x0, table, ids0).shape == (0, 64)
+    assert ops.bias_act_rows(torch.empty(0, 64, dtype=torch.bfloat16, device=dev).view(0, 64),
+                             torch.zeros(64, device=dev), silu=True).shape == (0, 64)
+    x = torch.randn(6, 64, device=dev).bfloat16()
+    with pytest.raises(ValueError):
+        ops.add_gathered_rows(x, table, torch.zeros(5, dtype=torch.int64, device=dev))       # one id per row
+    with pytest.raises(ValueError):
+        ops.add_gathered_rows(x, table.float(), torch.zeros(6, dtype=torch.int64, device=dev))  # dtype mismatch
+    with pytest.raises(ValueError):
+        ops.add_gathered_rows(x, table, torch.zeros(6, dtype=torch.int64, device=dev), table, None)
+    with pytest.raises(ValueError):
+        ops.bias_act_rows(x, torch.zeros(4, 64, device=dev), silu=False)                       # 4 groups do not divide 6 rows
+    # a single group (plain bias vector) and one group per row
+    want = (x.float() + 1.0).bfloat16()
+    assert torch.equal(ops.bias_act_rows(x.clone(), torch.ones(64, device=dev), silu=False), want)
+    per_row = torch.arange(6, device=dev, dtype=torch.float32)[:, None].expand(6, 64).contiguous()
+    want = (x.float() + per_row).bfloat16()
+    assert torch.equal(ops.bias_act_rows(x.clone(), per_row, silu=False), want)
+    # odd widths: 24 columns = 48 bytes = three 16-byte pieces per row
+    y = torch.randn(7, 24, device=dev).bfloat16()
+    b = torch.randn(24, device=dev).bfloat16()
+    assert torch.equal(ops.bias_act_rows(y.clone(), b, silu=False), (y.float() + b.float()).bfloat16())

@@ -126,3 +126,20 @@ def test_layer_norm_of_silu(dtype, cols):
     act = torch.nn.functional.silu(x.float()).to(dtype)
     want = R.layer_norm_fp32(act, w, b, 1e-5)
     assert (got.float() - want.float()).abs().max().item() <= TOL[dtype]
+
+
+def test_fused_norm_variants_edge_cases():
+    """Empty matrices, a width that needs the scalar kernel, and the bias shape check."""
+    w = torch.ones(48, device="cuda").bfloat16()
+    b = torch.zeros(48, device="cuda").bfloat16()
+    empty = torch.empty(0, 48, device="cuda", dtype=torch.bfloat16)
+    assert ops.rms_norm(empty, w, 1e-6, in_bias=b).shape == (0, 48)
+    assert ops.layer_norm(empty, w, b, 1e-5, pre_silu=True).shape == (0, 48)
+    with pytest.raises(ValueError):
+        ops.rms_norm(torch.zeros(3, 48, device="cuda").bfloat16(), w, 1e-6, in_bias=torch.zeros(47, device="cuda"))
+    # 3-D input, width 5 (rows are not whole 16-byte pieces)
+    x = torch.randn(2, 3, 5)
+    w5, b5 = torch.rand(5) + 0.5, torch.randn(5)
+    got = ops.rms_norm(x.cuda(), w5.cuda(), 1e-6, in_bias=b5.cuda()).cpu()
+    want = R.rms_norm_fp32((x + b5).reshape(-1, 5), w5, 1e-6).reshape(2, 3, 5)
+    assert (got - want).abs().max().item() <= 2e-5
