@@ -160,6 +160,10 @@ def attention_flops(meta: dict) -> float:
     heads, dim, lk, lq = meta["heads"], meta["dim"], meta["lk"], meta["lq"]
     if meta.get("cu_rows") is not None:
         rows = (meta["cu_rows"][1:] - meta["cu_rows"][:-1]).double()
+        if meta.get("cu_rows_q") is not None:   # the last `qn` rows of every sample are the queries
+            qn = (meta["cu_rows_q"][1:] - meta["cu_rows_q"][:-1]).double()
+            pairs = (qn * (rows - qn) + qn * (qn + 1) / 2).sum().item() if meta["causal"] else (qn * rows).sum().item()
+            return 4.0 * dim * heads * pairs
         pairs = (rows * (rows + 1) / 2).sum().item() if meta["causal"] else (rows * rows).sum().item()
         return 4.0 * dim * heads * pairs
     if meta.get("key_valid") is not None:
@@ -351,6 +355,7 @@ def run_e2e(args) -> None:
     sd = random_state_dict(spec, seed=0, device=dev, dtype=torch.bfloat16)
     ffn_mode = args.ffn if spec.d_model % 256 == 0 else "bf16"
     model = OneTransInference(sd, spec, device=dev, dtype=torch.bfloat16, ffn=ffn_mode, packed=not args.padded,
+                              select_early=not args.late_select,
                               attention_kernel=args.kernel)
     host_batch = synthetic_batch(spec, batch_size, seq_len=wl["seq_len"], min_len=wl["min_len"], seed=rank,
                                  field_exponent=wl["field_exp"], seq_exponent=wl["seq_exp"]).pin_memory()
@@ -461,6 +466,7 @@ def run_e2e(args) -> None:
         "config": {
             "workload": wl["name"], "per_gpu_batch": batch_size, "global_batch": total, "micro_batch": micro,
             "ffn": ffn_mode, "layout": "padded" if args.padded else "packed valid tokens",
+            "pyramid_row_selection": "after the block" if (args.late_select or args.padded) else "after attention, before the row-wise half of the block",
             "parallelism": f"batch-sharded x{world}, scores all_gather", "weights": "seed 0, bf16",
             "l2": "activations and tables (>= 16 GB) are far larger than the 126 MB L2",
         },
@@ -677,6 +683,9 @@ def main() -> None:
                         help="run --warmup untimed and --steps plain steps of the main workload and exit (for ncu)")
     parser.add_argument("--ffn", choices=["fp8", "bf16"], default="fp8", help="shared FFN of every block")
     parser.add_argument("--padded", action="store_true", help="reference [B, T, d] layout instead of packed valid tokens")
+    parser.add_argument("--late-select", action="store_true",
+                        help="apply the pyramid's row selection after the whole block (the reference's order) instead of "
+                             "right after attention")
     parser.add_argument("--rows", type=int, default=0)
     parser.add_argument("--cols", type=int, default=0)
     parser.add_argument("--kind", default="")

@@ -40,7 +40,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "tb200_fields_bag_mean_fwd": (_INT, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _INT, _I64, _I32, _P, _INT, _P]),
     "tb200_attn_fwd": (
         _INT,
-        [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _I32, _I32, _I32, _F, _INT, _I32, _I64, _P, _P],
+        [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I32, _I32, _I32, _F, _INT, _I32, _I64, _P, _P],
     ),
     "tb200_quant_act_1x128": (_INT, [_P, _P, _P, _I64, _I32, _P]),
     "tb200_fp8_gemm": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _P]),

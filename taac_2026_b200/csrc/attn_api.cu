@@ -12,7 +12,7 @@ int attn_small_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 
 extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
                               int32_t Lk, int32_t D, const int64_t* strides, const int32_t* seq_len,
-                              const int32_t* cu_rows, const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self,
+                              const int32_t* cu_rows, const int32_t* cu_rows_q, const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self,
                               float scale, int dtype, int32_t kernel, int64_t total_rows, int32_t* status_word,
                               void* stream) {
     using namespace tb200;
@@ -22,6 +22,7 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     if (dtype != TB200_BF16 && dtype != TB200_F16) return TB200_ERR_DTYPE;
     if (D != 32 && D != 64 && D != 128) return TB200_ERR_UNSUPPORTED;
     if (padded_query_self && cu_rows == nullptr && Lq != Lk) return TB200_ERR_SHAPE;
+    if (cu_rows_q != nullptr && (cu_rows == nullptr || key_valid != nullptr)) return TB200_ERR_UNSUPPORTED;
     if (ns_start < 0) return TB200_ERR_SHAPE;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return TB200_ERR_ALIGN;
     for (int i = 0; i < 12; ++i)
@@ -35,6 +36,7 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     a.o_sb = strides[9]; a.o_sh = strides[10]; a.o_sl = strides[11];
     a.seq_len = seq_len;
     a.cu_rows = cu_rows;
+    a.cu_rows_q = cu_rows_q;
     a.key_valid = key_valid;
     a.B = B; a.H = H; a.Lq = Lq; a.Lk = Lk;
     a.ns_start = ns_start > Lk ? Lk : ns_start;
@@ -47,6 +49,10 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     const bool tc_ok = attn_tc05_supported(a, D, dtype) && (cu_rows == nullptr || total_rows > 0);
     if (kernel == 2 && !tc_ok) return TB200_ERR_UNSUPPORTED;
     if (kernel < 0 || kernel > 3) return TB200_ERR_UNSUPPORTED;
+    if (cu_rows_q != nullptr) {   // separate query rows: the mma.sync kernel
+        if (kernel > 1) return TB200_ERR_UNSUPPORTED;
+        return attn_mma_forward(a, D, dtype, Lq, s);
+    }
     const bool small_ok = attn_small_supported(a, D, Lq, Lk);
     if (kernel == 3 && !small_ok) return TB200_ERR_UNSUPPORTED;
     // samples of at most 32 rows (the non-sequence tokens alone, late in the pyramid): no tensor-core tile pays

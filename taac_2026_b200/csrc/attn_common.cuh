@@ -19,6 +19,10 @@ struct AttnArgs {
     int64_t o_sb, o_sh, o_sl;
     const int32_t* seq_len;  // [B] valid-prefix length of the key axis, or nullptr = all valid
     const int32_t* cu_rows;  // [B + 1] or nullptr
+    // [B + 1] or nullptr.  Packed batches only: q and o are packed by their own offsets (sample b has
+    // cu_rows_q[b+1] - cu_rows_q[b] queries, the LAST rows of its cu_rows[b+1] - cu_rows[b] keys), and the
+    // causal rule is aligned at the end: query j of lq sees keys <= j + (lk - lq).
+    const int32_t* cu_rows_q;
     const uint8_t* key_valid;  // [B, Lk] bytes (0 = padding) or nullptr; replaces seq_len / ns_start when given
     int32_t B, H, Lq, Lk;
     int32_t ns_start;           // keys >= ns_start are always valid (Lk = no such suffix)

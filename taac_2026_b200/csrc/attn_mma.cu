@@ -111,17 +111,25 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
     const int m0 = blockIdx.x * kBM;
 
     int lq = a.Lq, lk = a.Lk;
-    int64_t row_base = 0;
+    int64_t row_base = 0;      // first key / value row of the sample (packed)
+    int64_t q_base = 0;        // first query / output row of the sample (packed)
+    int off = 0;               // causal alignment: query r sees keys <= r + off
     if (a.cu_rows != nullptr) {
         row_base = a.cu_rows[b];
         lq = lk = a.cu_rows[b + 1] - static_cast<int32_t>(row_base);
+        q_base = row_base;
+        if (a.cu_rows_q != nullptr) {   // the queries are the last lq rows of the sample
+            q_base = a.cu_rows_q[b];
+            lq = a.cu_rows_q[b + 1] - static_cast<int32_t>(q_base);
+            off = max(lk - lq, 0);
+        }
     }
     if (m0 >= lq) return;
     const bool packed = a.cu_rows != nullptr;
-    const T* q = static_cast<const T*>(a.q) + (packed ? row_base * a.q_sl : b * a.q_sb) + h * a.q_sh;
+    const T* q = static_cast<const T*>(a.q) + (packed ? q_base * a.q_sl : b * a.q_sb) + h * a.q_sh;
     const T* k = static_cast<const T*>(a.k) + (packed ? row_base * a.k_sl : b * a.k_sb) + h * a.k_sh;
     const T* v = static_cast<const T*>(a.v) + (packed ? row_base * a.v_sl : b * a.v_sb) + h * a.v_sh;
-    T* o = static_cast<T*>(a.o) + (packed ? row_base * a.o_sl : b * a.o_sb) + h * a.o_sh;
+    T* o = static_cast<T*>(a.o) + (packed ? q_base * a.o_sl : b * a.o_sb) + h * a.o_sh;
 
     const int valid_len = (a.seq_len != nullptr && !packed) ? min(max(a.seq_len[b], 0), lk) : lk;
     const int ns_start = packed ? lk : min(a.ns_start, lk);
@@ -142,7 +150,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
 
     if (!tile_all_padded) {
         // key tiles that can hold a visible key for this query tile
-        const int kv_end = causal ? min(lk, m_end) : lk;
+        const int kv_end = causal ? min(lk, m_end + off) : lk;
         const int n_tiles = (kv_end + kBN - 1) / kBN;
         auto tile_live = [&](int n) {
             const int n0 = n * kBN;
@@ -201,7 +209,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
 
             // mask (only tiles that touch a boundary)
             const int n0 = n * kBN;
-            const bool full = (n0 + kBN <= valid_len || n0 >= ns_start) && n0 + kBN <= lk && (!causal || n0 + kBN - 1 <= m0);
+            const bool full = (n0 + kBN <= valid_len || n0 >= ns_start) && n0 + kBN <= lk && (!causal || n0 + kBN - 1 <= m0 + off);
             if (kvalid != nullptr) {  // arbitrary key-padding pattern: one byte per key
 #pragma unroll
                 for (int j = 0; j < kBN / 8; ++j)
@@ -209,7 +217,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
                     for (int e = 0; e < 4; ++e) {
                         const int r = m0 + warp * 16 + g + ((e >> 1) << 3);
                         const int c = n0 + j * 8 + 2 * t + (e & 1);
-                        const bool vis = c < lk && kvalid[c] != 0 && (!causal || c <= r);
+                        const bool vis = c < lk && kvalid[c] != 0 && (!causal || c <= r + off);
                         if (!vis) s[j][e] = -INFINITY;
                     }
             } else if (!full) {
@@ -219,7 +227,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
                     for (int e = 0; e < 4; ++e) {
                         const int r = m0 + warp * 16 + g + ((e >> 1) << 3);
                         const int c = n0 + j * 8 + 2 * t + (e & 1);
-                        if (!attn_visible(r, c, valid_len, ns_start, lk, causal)) s[j][e] = -INFINITY;
+                        if (!attn_visible(r + off, c, valid_len, ns_start, lk, causal)) s[j][e] = -INFINITY;
                     }
             }
 

@@ -187,13 +187,16 @@ class OneTransInference:
 
     def __init__(self, state_dict: dict[str, torch.Tensor], spec: OneTransSpec, *, device: torch.device | str = "cuda",
                  dtype: torch.dtype = torch.bfloat16, attention_kernel: int = 0, ffn: str = "bf16",
-                 packed: bool = True) -> None:
+                 packed: bool = True, select_early: bool = True) -> None:
         if not ops.cuda_available():
             raise RuntimeError("OneTransInference needs the cuda backend (libtb200 + an sm_100 device)")
         self.spec = spec
         self.device = torch.device(device)
         self.dtype = dtype
         self.attention_kernel = attention_kernel
+        # packed layout: apply the pyramid's row selection right after attention, before the row-wise half of the
+        # block (same rows, same values; False keeps the reference's order: whole block, then selection)
+        self.select_early = select_early
         if ffn not in ("bf16", "fp8"):
             raise ValueError(f"unknown ffn mode {ffn}")
         if ffn == "fp8" and (dtype != torch.bfloat16 or spec.d_model % 256 or (spec.d_model * spec.hidden_mult) % 256):
@@ -303,6 +306,11 @@ class OneTransInference:
                 bq, bk, bv = (stack(p + f".attention.ns_{n}." + "{i}", "bias") for n in "qkv")
                 blk["ns_qkv_w"] = torch.cat([wq, wk, wv], dim=1).transpose(1, 2).contiguous()  # [ns, d, 3d]
                 blk["ns_qkv_b"] = torch.cat([bq, bk, bv], dim=1).unsqueeze(1)  # [ns, 1, 3d]
+                d_model = self.d
+                blk["ns_q_w"] = blk["ns_qkv_w"][:, :, :d_model].contiguous()     # query / key-value halves for blocks
+                blk["ns_kv_w"] = blk["ns_qkv_w"][:, :, d_model:].contiguous()    # that project fewer queries than keys
+                blk["ns_q_b"] = blk["ns_qkv_b"][:, :, :d_model].contiguous()
+                blk["ns_kv_b"] = blk["ns_qkv_b"][:, :, d_model:].contiguous()
                 blk["ns_w1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "weight").transpose(1, 2).contiguous()
                 blk["ns_b1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "bias").unsqueeze(1)
                 blk["ns_w2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "weight").transpose(1, 2).contiguous()
@@ -649,15 +657,43 @@ class OneTransInference:
             p = blk["p"]
             cu32 = cu[layer].to(torch.int32)
             x = ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
-            qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
             flat_ns = ns_rows.t().reshape(-1)                                      # token-major: [ns, B] row ids
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)                  # [ns, B, d], contiguous
-            ops.scatter_rows(qkv, flat_ns, torch.bmm(x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d), bias=blk["ns_qkv_b"])
-            q, k, v = (qkv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(3))
-            if q.dtype == torch.float32:
-                q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
-            attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
-                                        kernel=self.attention_kernel)
+            selected = self.select_early and widths[layer + 1] < widths[layer]
+            if selected:
+                # The pyramid keeps only the last rows of every sample after this block, and a row of the block's
+                # output depends on the other rows through its keys and values alone.  So keys and values are
+                # projected for every row, but queries, the attention rows, the output projection, the residual,
+                # the norm and the FFN only for the rows that survive: the same rows, bit for bit in exact
+                # arithmetic, as "whole block, then selection", without the work whose result would be dropped.
+                new_rows = rows[layer + 1]
+                owner = torch.repeat_interleave(arange_b, new_rows, output_size=totals[layer + 1])
+                r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]
+                src = cu[layer][owner] + (counts[layer] - counts[layer + 1])[owner] + r
+                next_ns_rows = (cu[layer + 1][:-1] + counts[layer + 1])[:, None] + ns_off
+                next_flat_ns = next_ns_rows.t().reshape(-1)
+                w_qkv, b_qkv = self._p(p + ".attention.shared_qkv.weight"), self._p(p + ".attention.shared_qkv.bias")
+                kv = F.linear(x, w_qkv[d:], b_qkv[d:])                                              # [N, 2d]
+                qm = F.linear(x.index_select(0, src), w_qkv[:d], b_qkv[:d])                         # [N', d]
+                ops.scatter_rows(kv, flat_ns, torch.bmm(x_ns, blk["ns_kv_w"]).view(ns * batch, 2 * d), bias=blk["ns_kv_b"])
+                ops.scatter_rows(qm, next_flat_ns, torch.bmm(x_ns, blk["ns_q_w"]).view(ns * batch, d), bias=blk["ns_q_b"])
+                q = qm.unflatten(-1, (heads, hd))
+                k, v = (kv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(2))
+                if q.dtype == torch.float32:
+                    q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+                attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
+                                            cu_rows_q=cu[layer + 1].to(torch.int32), max_rows_q=max_rows[layer + 1],
+                                            kernel=min(self.attention_kernel, 1))
+                tokens = tokens.index_select(0, src)
+                ns_rows, flat_ns = next_ns_rows, next_flat_ns
+            else:
+                qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
+                ops.scatter_rows(qkv, flat_ns, torch.bmm(x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d), bias=blk["ns_qkv_b"])
+                q, k, v = (qkv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(3))
+                if q.dtype == torch.float32:
+                    q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+                attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
+                                            kernel=self.attention_kernel)
             attn2d = attn.view(-1, d).to(self.dtype)
             if self.ffn_mode == "fp8":
                 # tokens + attention out-projection with the residual inside the GEMM (beta = 1); its bias is
@@ -676,7 +712,7 @@ class OneTransInference:
             y_ns = torch.bmm(h, blk["ns_w2"]).view(ns * batch, d)
             ops.scatter_rows(out, flat_ns, y_ns, bias=ns_b2, residual=tokens)   # tokens + b2 + FFN_ns(x)
             tokens = out
-            if widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
+            if not selected and widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
                 new_rows = rows[layer + 1]
                 owner = torch.repeat_interleave(arange_b, new_rows, output_size=totals[layer + 1])
                 r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]

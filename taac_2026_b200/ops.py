@@ -594,8 +594,14 @@ def varlen_attention(
     kernel: int = 0,
     check: bool = False,
     out: torch.Tensor | None = None,
+    cu_rows_q: torch.Tensor | None = None,
+    max_rows_q: int | None = None,
 ) -> torch.Tensor:
     """Masked attention forward with the mask given by lengths (never materialised).
+
+    ``cu_rows_q`` / ``max_rows_q`` (packed batches): q is packed by its own offsets and holds, for every sample,
+    only the LAST rows of the sample (k and v still hold all of them, packed by ``cu_rows``); with ``causal`` the
+    rule is aligned at the end, so the result equals the last rows of the full computation.
 
     ``out`` (optional) receives the result instead of a new contiguous tensor: same shape and dtype as
     ``q``, any strides whose rows are 16-byte aligned (e.g. a token-major buffer viewed sample-major).
@@ -626,6 +632,10 @@ def varlen_attention(
         if max_rows is None:
             raise ValueError("packed varlen_attention needs max_rows")
         lq = lk = int(max_rows)
+        if cu_rows_q is not None:
+            if max_rows_q is None or cu_rows_q.shape != cu_rows.shape:
+                raise ValueError("varlen_attention: cu_rows_q needs max_rows_q and one offset per sample like cu_rows")
+            lq = int(max_rows_q)
         if out is not None:
             raise ValueError("varlen_attention: out= is for padded batches")
         out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
@@ -633,7 +643,11 @@ def varlen_attention(
         for t in (q, k, v, out):
             strides += [0, t.stride(1), t.stride(0)]
         cu = cu_rows.to(torch.int32).contiguous()
+        cu_q = None if cu_rows_q is None else cu_rows_q.to(torch.int32).contiguous()
     else:
+        if cu_rows_q is not None:
+            raise ValueError("varlen_attention: cu_rows_q needs cu_rows")
+        cu_q = None
         if q.ndim != 4:
             raise ValueError("varlen_attention expects 4D q, k, v")
         if layout == "bhld":
@@ -662,14 +676,14 @@ def varlen_attention(
         scale = 1.0 / math.sqrt(dim)
     stride_arr = (ctypes.c_int64 * 12)(*strides)
     status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
-    with torch.cuda.device(q.device), _timed(_attention_record_name(kernel, q.dtype, dim, lq, lk, kv is not None),
-                                             seq_len=lens, cu_rows=cu, key_valid=kv, batch=batch, heads=heads,
+    with torch.cuda.device(q.device), _timed(_attention_record_name(1 if cu_q is not None else kernel, q.dtype, dim, lq, lk, kv is not None),
+                                             seq_len=lens, cu_rows=cu, cu_rows_q=cu_q, key_valid=kv, batch=batch, heads=heads,
                                              lq=lq, lk=lk, dim=dim, ns_start=lk if ns_start is None else int(ns_start),
                                              causal=bool(causal), self_rows=bool(padded_query_self)):
         code = _lib.load().tb200_attn_fwd(
-            _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu), _ptr(kv),
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu), _ptr(cu_q), _ptr(kv),
             lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)), float(scale),
-            _DTYPE_CODES[q.dtype], int(kernel), int(q.shape[0]) if cu is not None else 0, _ptr(status), _stream_ptr(),
+            _DTYPE_CODES[q.dtype], int(kernel), int(k.shape[0]) if cu is not None else 0, _ptr(status), _stream_ptr(),
         )
     _lib.check(code, "cuda varlen_attention")
     if status is not None and int(status.item()) != 0:

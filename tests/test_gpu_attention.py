@@ -219,3 +219,31 @@ def test_small_sample_kernel(dtype, L):
     # automatic choice takes this kernel for such samples and gives the same bits
     auto = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], kernel=0, **kw).float()
     assert torch.equal(auto, small)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_packed_queries_are_the_last_rows_of_each_sample(causal):
+    """cu_rows_q: q holds only the last rows of every sample; the result equals those rows of the full
+    computation (the causal rule is aligned at the end of the sample)."""
+    g = torch.Generator().manual_seed(77)
+    B, H, D = 9, 4, 64
+    lens = torch.tensor([300, 1, 64, 65, 17, 200, 128, 5, 90])
+    keep = torch.tensor([40, 1, 64, 3, 0, 129, 70, 5, 1])        # 0 = no query for that sample
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    cu_q = torch.zeros(B + 1, dtype=torch.int32)
+    cu_q[1:] = torch.cumsum(keep, 0)
+    rows = int(cu[-1])
+    qkv = (torch.randn(rows, 3, H, D, generator=g) * 0.5).bfloat16().cuda()
+    full = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(),
+                                max_rows=int(lens.max()), kernel=1)
+    sel = torch.cat([torch.arange(int(cu[b + 1]) - int(keep[b]), int(cu[b + 1])) for b in range(B)]).cuda()
+    q_kept = qkv[:, 0].index_select(0, sel).contiguous()
+    got = ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()),
+                               cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()))
+    assert got.shape == q_kept.shape
+    want = full.index_select(0, sel)
+    assert (got.float() - want.float()).abs().max().item() <= 4e-3
+    with pytest.raises(RuntimeError):   # only the mma.sync kernel serves separate query rows
+        ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()),
+                             cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()), kernel=2)

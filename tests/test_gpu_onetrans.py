@@ -166,3 +166,15 @@ def test_blocks_with_only_ns_tokens_left(dtype, tol):
     assert calls and 0 < calls[0] < spec.num_blocks, "the NS-only path was expected to take over after the first block"
     want = oracle_model.sigmoid_scores(want_logits).reshape(-1)
     assert np.abs(got - want).max() <= tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-3)])
+def test_early_row_selection_changes_nothing(dtype, tol):
+    """Selecting the rows the pyramid keeps before the row-wise half of a block (default) or after the whole
+    block (the reference's order) gives the same scores."""
+    spec = _mini_spec()
+    sd = random_state_dict(spec, seed=0)
+    batch = synthetic_batch(spec, 128, seq_len=96, min_len=4, seed=9).to("cuda")
+    early = OneTransInference(sd, spec, dtype=dtype, select_early=True).scores(batch)
+    late = OneTransInference(sd, spec, dtype=dtype, select_early=False).scores(batch)
+    assert (early - late).abs().max().item() <= tol
