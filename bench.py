@@ -193,6 +193,13 @@ def attention_flops(meta: dict) -> float:
 def launch_work(name: str, meta: dict) -> tuple[str, float]:
     """-> (bound, algorithmic bytes or flops) of one recorded launch."""
     if name.startswith("attention"):
+        if meta.get("cu_rows_q") is not None:
+            # a few queries per sample against all of its keys: every K / V row is read once and used by a handful
+            # of queries (about 17 FLOP per byte on the full workload), so HBM bounds this launch, not the tensor pipe
+            row_bytes = meta["heads"] * meta["dim"] * meta.get("esize", 2)
+            k_rows = float(meta["cu_rows"][-1].item())
+            q_rows = float(meta["cu_rows_q"][-1].item())
+            return "hbm", 2.0 * row_bytes * (k_rows + q_rows)
         return "tensor", attention_flops(meta)
     if name == "bias_act_rows":     # in place: read + write of the matrix
         return "hbm", 2.0 * meta["rows"] * meta["cols"] * meta["esize"]

@@ -679,7 +679,7 @@ def varlen_attention(
     with torch.cuda.device(q.device), _timed(_attention_record_name(1 if cu_q is not None else kernel, q.dtype, dim, lq, lk, kv is not None),
                                              seq_len=lens, cu_rows=cu, cu_rows_q=cu_q, key_valid=kv, batch=batch, heads=heads,
                                              lq=lq, lk=lk, dim=dim, ns_start=lk if ns_start is None else int(ns_start),
-                                             causal=bool(causal), self_rows=bool(padded_query_self)):
+                                             causal=bool(causal), self_rows=bool(padded_query_self), esize=q.element_size()):
         code = _lib.load().tb200_attn_fwd(
             _ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, heads, lq, lk, dim, stride_arr, _ptr(lens), _ptr(cu), _ptr(cu_q), _ptr(kv),
             lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)), float(scale),
