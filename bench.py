@@ -473,7 +473,7 @@ def run_e2e(args) -> None:
         "config": {
             "workload": wl["name"], "per_gpu_batch": batch_size, "global_batch": total, "micro_batch": micro,
             "ffn": ffn_mode, "layout": "padded" if args.padded else "packed valid tokens",
-            "pyramid_row_selection": "after the block" if (args.late_select or args.padded) else "after attention, before the row-wise half of the block",
+            "pyramid_row_selection": "after the block (reference order)" if (args.late_select or args.padded) else "keys/values for all rows; queries, attention and the row-wise half of each block for the rows the pyramid keeps",
             "parallelism": f"batch-sharded x{world}, scores all_gather", "weights": "seed 0, bf16",
             "l2": "activations and tables (>= 16 GB) are far larger than the 126 MB L2",
         },
