@@ -578,6 +578,46 @@ def run_attention_sweep(args) -> None:
         }), flush=True)
 
 
+def run_kept_rows_attention(args) -> None:
+    """Packed causal attention in which only the last rows of every sample are queries (`cu_rows_q`): the shape of
+    a pyramid block evaluated for the rows it keeps.  Samples of 137..579 rows, 9 + U[0, 16] queries each, 8 heads,
+    head_dim 64, bf16.  Bound by the stream over K and V."""
+    peaks, peak_kind = load_peaks()
+    B, H, D = args.batch or 4096, 8, 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    lens = torch.randint(137, 580, (B,), generator=g, device="cuda")
+    keep = 9 + torch.randint(0, 17, (B,), generator=g, device="cuda")
+    cu = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
+    cu[1:] = torch.cumsum(lens, 0)
+    cu_q = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
+    cu_q[1:] = torch.cumsum(keep, 0)
+    rows, q_rows = int(cu[-1]), int(cu_q[-1])
+    kv = torch.randn(rows, 2, H, D, generator=g, device="cuda").div_(8).bfloat16()
+    q = torch.randn(q_rows, H, D, generator=g, device="cuda").div_(8).bfloat16()
+    fn = lambda: ops.varlen_attention(q, kv[:, 0], kv[:, 1], causal=True, cu_rows=cu, max_rows=int(lens.max()),  # noqa: E731
+                                      cu_rows_q=cu_q, max_rows_q=int(keep.max()))
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / args.steps
+    nbytes = 2.0 * H * D * 2 * (rows + q_rows)
+    gbs = nbytes / ms / 1e6
+    print(json.dumps({
+        "metric": "kept_rows_attention_GBps", "value": round(gbs, 1), "unit": "GB/s",
+        "config": {"workload": f"{B} packed samples of 137..579 rows, 9..25 queries each, H{H} D{D} bf16, causal",
+                   "k_rows": rows, "q_rows": q_rows},
+        "ms_per_launch": round(ms, 3),
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peak_kind},
+    }), flush=True)
+
+
 def run_gather_sweep(args) -> None:
     peaks, peak_kind = load_peaks()
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -701,7 +741,10 @@ def main() -> None:
     if args.workload == "norm":
         run_norm_sweep(args)
     elif args.workload == "attention":
-        run_attention_sweep(args)
+        if args.kind == "kept":
+            run_kept_rows_attention(args)
+        else:
+            run_attention_sweep(args)
     elif args.workload == "gather":
         run_gather_sweep(args)
     elif args.workload == "ffn":

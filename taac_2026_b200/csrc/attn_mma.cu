@@ -13,7 +13,8 @@ void count_launch();
 namespace {
 
 constexpr int kBM = 64;  // query rows per CTA (16 per warp)
-constexpr int kBN = 64;  // keys per tile
+constexpr int kBN = 64;
+constexpr int kKvStages = 2;  // K / V ring depth (three stages were measured: no faster)
 constexpr int kThreads = 128;
 
 template <int D>
@@ -95,11 +96,11 @@ __device__ __forceinline__ void load_tile(T* smem, const T* gmem, int64_t stride
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(kThreads, D <= 64 ? 4 : 2) attn_mma_kernel(const AttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     T* sQ = reinterpret_cast<T*>(smem_raw);
-    T* sK = sQ + kBM * D;       // 2 stages
-    T* sV = sK + 2 * kBN * D;   // 2 stages
+    T* sK = sQ + kBM * D;              // kKvStages stages
+    T* sV = sK + kKvStages * kBN * D;  // kKvStages stages
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -159,25 +160,40 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
         int first = 0;
         while (first < n_tiles && !tile_live(first)) ++first;
 
+        // K / V tiles go through a ring of kKvStages stages: kKvStages - 1 tiles are in flight while one is
+        // being used (with a handful of queries per sample the kernel is a stream over K and V)
+        auto next_live = [&](int n) {
+            ++n;
+            while (n < n_tiles && !tile_live(n)) ++n;
+            return n;
+        };
         load_tile<T, D>(sQ, q, a.q_sl, m0, lq, tid);
-        if (first < n_tiles) {
-            load_tile<T, D>(sK, k, a.k_sl, first * kBN, lk, tid);
-            load_tile<T, D>(sV, v, a.v_sl, first * kBN, lk, tid);
+        int to_load = first;               // next tile to request
+        int load_stage = 0;
+#pragma unroll
+        for (int i = 0; i < kKvStages - 1; ++i) {
+            if (to_load < n_tiles) {
+                load_tile<T, D>(sK + load_stage * kBN * D, k, a.k_sl, to_load * kBN, lk, tid);
+                load_tile<T, D>(sV + load_stage * kBN * D, v, a.v_sl, to_load * kBN, lk, tid);
+                to_load = next_live(to_load);
+                load_stage = load_stage + 1 == kKvStages ? 0 : load_stage + 1;
+            }
+            cp_async_commit();
         }
-        cp_async_commit();
 
         uint32_t qf[D / 16][4];
         bool q_loaded = false;
         int stage = 0;
         for (int n = first; n < n_tiles;) {
-            int next = n + 1;
-            while (next < n_tiles && !tile_live(next)) ++next;
-            if (next < n_tiles) {
-                load_tile<T, D>(sK + (stage ^ 1) * kBN * D, k, a.k_sl, next * kBN, lk, tid);
-                load_tile<T, D>(sV + (stage ^ 1) * kBN * D, v, a.v_sl, next * kBN, lk, tid);
+            const int next = next_live(n);
+            if (to_load < n_tiles) {       // refill the stage that was released at the end of the last iteration
+                load_tile<T, D>(sK + load_stage * kBN * D, k, a.k_sl, to_load * kBN, lk, tid);
+                load_tile<T, D>(sV + load_stage * kBN * D, v, a.v_sl, to_load * kBN, lk, tid);
+                to_load = next_live(to_load);
+                load_stage = load_stage + 1 == kKvStages ? 0 : load_stage + 1;
             }
             cp_async_commit();
-            cp_async_wait<1>();
+            cp_async_wait<kKvStages - 1>();
             __syncthreads();
 
             if (!q_loaded) {
@@ -278,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
                 }
             }
             __syncthreads();  // everyone is done with this stage before it is refilled
-            stage ^= 1;
+            stage = stage + 1 == kKvStages ? 0 : stage + 1;
             n = next;
         }
         cp_async_wait<0>();
@@ -326,11 +342,13 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(const AttnArgs a) {
 
 template <typename T, int D>
 int launch(const AttnArgs& a, int max_lq, cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(kBM + 4 * kBN) * D * sizeof(T);
+    const size_t smem = static_cast<size_t>(kBM + 2 * kKvStages * kBN) * D * sizeof(T);
     const DeviceInfo& dev = device_info();
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
         cudaFuncSetAttribute(attn_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        // the kernel is often a stream over K and V (a few queries per sample): room for as many CTAs as fit
+        cudaFuncSetAttribute(attn_mma_kernel<T, D>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         attr_set[dev.index] = true;
     }
     dim3 grid((max_lq + kBM - 1) / kBM, a.H, a.B);
