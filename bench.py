@@ -205,6 +205,8 @@ def launch_work(name: str, meta: dict) -> tuple[str, float]:
         return "hbm", 2.0 * meta["rows"] * meta["cols"] * meta["esize"]
     if name == "add_gathered_rows":  # in place: read + write of the matrix, one table row per id (tables are L2-resident)
         return "hbm", (2.0 + meta["tables"]) * meta["rows"] * meta["dim"] * meta["esize"] + 8.0 * meta["tables"] * meta["rows"]
+    if name == "token_tail":         # one read, two writes of the matrix, one table row per id (L2-resident tables)
+        return "hbm", (3.0 + meta["tables"]) * meta["rows"] * meta["cols"] * meta["esize"] + 8.0 * meta["tables"] * meta["rows"]
     if name == "scatter_rows":
         return "hbm", 3.0 * meta["rows"] * meta["dim"] * meta["esize"] + 8.0 * meta["rows"]
     if name in ("rms_norm", "layer_norm"):

@@ -86,6 +86,19 @@ int tb200_rmsnorm_bias_fwd(const void* x, const void* in_bias, const void* gamma
 int tb200_layernorm_silu_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int32_t cols,
                              float eps, int dtype, void* stream);
 
+/* tokens = layernorm(silu(x)) + table_a[ids_a] (+ table_b[ids_b]);  normed = rmsnorm(tokens) * rms_gamma
+ * in one pass over the matrix: the tail of the sequence tokenizer (`nn.SiLU(), nn.LayerNorm`, time-bucket
+ * and position rows, src/taac2026/infrastructure/modeling/tokenizers.py:144, :188-189) followed by the
+ * `attn_norm` of the first `OneTransBlock` (experiments/onetrans/model.py:106).  Every intermediate is rounded to
+ * `dtype` where the separate operations would have stored it, so `tokens` equals
+ * `tb200_layernorm_silu_fwd` + `tb200_add_gathered_rows` bit for bit and `normed` equals `tb200_rmsnorm_fwd` of
+ * it.  Needs rows of whole 16-byte pieces and 16-byte aligned bases (TB200_ERR_UNSUPPORTED otherwise); ids are
+ * device int64[rows], clamped into their table; table_b may be NULL. */
+int tb200_token_tail_fwd(const void* x, const void* ln_gamma, const void* ln_beta, const void* table_a, int64_t rows_a,
+                         const int64_t* ids_a, const void* table_b, int64_t rows_b, const int64_t* ids_b,
+                         const void* rms_gamma, void* tokens, void* normed, int64_t rows, int32_t cols, float ln_eps,
+                         float rms_eps, int dtype, void* stream);
+
 /* ---- (a) sparse-field embedding gather / pool ---------------------------------------------
  * out[b, :] = mean over hot h of table[ids[b, h], :] for ids in (0, vocab_rows); ids equal to 0
  * (padding) or outside the table are skipped; an empty bag gives zeros.  fp32 sum in hot order,

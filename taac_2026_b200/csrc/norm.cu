@@ -43,15 +43,37 @@ __device__ __forceinline__ float silu_f(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
     return fmaf(h, t, h);
 }
+__device__ __forceinline__ uint4 ld_nc_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 template <typename T>
 __device__ __forceinline__ float round_to(float v) {
     return to_float<T>(from_float<T>(v));
 }
 
-template <typename T, bool LAYER, int CPL, int RU, int PRE>
-__global__ void __launch_bounds__(kMaxThreads, 3)
+// Optional stage behind the normalisation (POST): the normalised row, rounded to T, receives one or two
+// gathered table rows (each sum rounded to T, like tensor additions), is written to y, and is then
+// RMS-normalised with a second weight vector into a second output.  This is the end of the sequence tokenizer
+// and the first norm of the first block in one pass over the token matrix:
+//   tokens = LayerNorm(SiLU(x)) + time_rows + position_rows;   normed = RMSNorm(tokens)
+struct PostArgs {
+    const void* table_a;
+    const int64_t* ids_a;
+    int64_t rows_a;
+    const void* table_b;   // may be nullptr
+    const int64_t* ids_b;
+    int64_t rows_b;
+    const void* gamma2;
+    void* normed;
+    float eps2;
+};
+
+template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST = false>
+__global__ void __launch_bounds__(kMaxThreads, POST ? 2 : 3)
 norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
-                int64_t rows, int cols, float eps, int lanes_per_row, int* __restrict__ status) {
+                int64_t rows, int cols, float eps, int lanes_per_row, int* __restrict__ status, const PostArgs post) {
     constexpr int N = Vec16<T>::N;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_bar[kWarps][kStages];
@@ -69,6 +91,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     // gamma / beta as fp32: [N / 4][chunks] float4 each, so that a warp's float4 reads are contiguous
     float2* gamma_s = reinterpret_cast<float2*>(smem + static_cast<size_t>(kWarps) * kStages * tile_bytes);
     float2* beta_s = gamma_s + static_cast<size_t>(chunks) * (N / 2);
+    float2* gamma2_s = beta_s + static_cast<size_t>(chunks) * (N / 2);   // POST only
 
     // contiguous, balanced row span of this warp
     const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kWarps;
@@ -104,6 +127,11 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             Vec16<T>::unpack2(reinterpret_cast<const uint4*>(beta)[c], f);
 #pragma unroll
             for (int e = 0; e < N / 2; ++e) beta_s[((e >> 1) * chunks + c) * 2 + (e & 1)] = f[e];
+        }
+        if (POST) {
+            Vec16<T>::unpack2(reinterpret_cast<const uint4*>(post.gamma2)[c], f);
+#pragma unroll
+            for (int e = 0; e < N / 2; ++e) gamma2_s[((e >> 1) * chunks + c) * 2 + (e & 1)] = f[e];
         }
     }
     __syncthreads();
@@ -194,10 +222,21 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             for (int u = 0; u < RU; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
         }
         float2 inv[RU];
+        int64_t id_a[RU], id_b[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
             const float i1 = rsqrtf(sq[u] * inv_cols + eps);
             inv[u] = make_float2(i1, i1);
+            id_a[u] = id_b[u] = 0;
+            if (POST && valid[u]) {
+                const int64_t row = row_begin + it * tile_rows + u * ng + group;
+                int64_t ia = post.ids_a[row];
+                id_a[u] = ia < 0 ? 0 : (ia > post.rows_a - 1 ? post.rows_a - 1 : ia);
+                if (post.table_b != nullptr) {
+                    int64_t ib = post.ids_b[row];
+                    id_b[u] = ib < 0 ? 0 : (ib > post.rows_b - 1 ? post.rows_b - 1 : ib);
+                }
+            }
         }
 #pragma unroll
         for (int j = 0; j < CPL; ++j) {
@@ -225,7 +264,70 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                             if (LAYER) o[e] = __ffma2_rn(__fmul2_rn(v[u][j][e], inv[u]), g[e], b[e]);
                             else o[e] = __fmul2_rn(__fmul2_rn(v[u][j][e], inv[u]), g[e]);
                         }
-                        tile[static_cast<size_t>(u * ng + group) * chunks + c] = Vec16<T>::pack2(o);
+                        uint4 packed = Vec16<T>::pack2(o);
+                        if (POST) {
+                            float2 t[N / 2];
+                            Vec16<T>::unpack2(packed, o);   // the normalised row as T stores it
+                            Vec16<T>::unpack2(ld_nc_u4(reinterpret_cast<const uint4*>(post.table_a) + id_a[u] * chunks + c), t);
+#pragma unroll
+                            for (int e = 0; e < N / 2; ++e) o[e] = __fadd2_rn(o[e], t[e]);
+                            packed = Vec16<T>::pack2(o);
+                            if (post.table_b != nullptr) {
+                                Vec16<T>::unpack2(packed, o);
+                                Vec16<T>::unpack2(ld_nc_u4(reinterpret_cast<const uint4*>(post.table_b) + id_b[u] * chunks + c), t);
+#pragma unroll
+                                for (int e = 0; e < N / 2; ++e) o[e] = __fadd2_rn(o[e], t[e]);
+                                packed = Vec16<T>::pack2(o);
+                            }
+                            Vec16<T>::unpack2(packed, v[u][j]);   // keep the row for the second normalisation
+                        }
+                        tile[static_cast<size_t>(u * ng + group) * chunks + c] = packed;
+                    }
+                }
+            }
+        }
+        if (POST) {
+            float sq2[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+                float2 acc = make_float2(0.f, 0.f);
+                if (valid[u]) {
+#pragma unroll
+                    for (int j = 0; j < CPL; ++j) {
+                        if (lane_g + j * G < chunks) {
+#pragma unroll
+                            for (int e = 0; e < N / 2; ++e) acc = __ffma2_rn(v[u][j][e], v[u][j][e], acc);
+                        }
+                    }
+                }
+                sq2[u] = acc.x + acc.y;
+            }
+            for (int o = G >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < RU; ++u) sq2[u] += __shfl_xor_sync(0xffffffffu, sq2[u], o);
+            }
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+                const int c = lane_g + j * G;
+                if (c < chunks) {
+                    float2 g2[N / 2];
+#pragma unroll
+                    for (int e = 0; e < N / 2; e += 2) {
+                        const float4 g4 = *reinterpret_cast<const float4*>(&gamma2_s[((e >> 1) * chunks + c) * 2]);
+                        g2[e] = make_float2(g4.x, g4.y);
+                        g2[e + 1] = make_float2(g4.z, g4.w);
+                    }
+#pragma unroll
+                    for (int u = 0; u < RU; ++u) {
+                        if (valid[u]) {
+                            const float i2 = rsqrtf(sq2[u] * inv_cols + post.eps2);
+                            const float2 inv2 = make_float2(i2, i2);
+                            float2 o[N / 2];
+#pragma unroll
+                            for (int e = 0; e < N / 2; ++e) o[e] = __fmul2_rn(__fmul2_rn(v[u][j][e], inv2), g2[e]);
+                            const int64_t row = row_begin + it * tile_rows + u * ng + group;
+                            reinterpret_cast<uint4*>(post.normed)[row * chunks + c] = Vec16<T>::pack2(o);
+                        }
                     }
                 }
             }
@@ -290,19 +392,19 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     }
 }
 
-template <typename T, bool LAYER, int CPL, int RU, int PRE>
+template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST = false>
 int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
-               int lanes_per_row, cudaStream_t stream) {
+               int lanes_per_row, cudaStream_t stream, const PostArgs post = PostArgs{}) {
     const int N = Vec16<T>::N;
     const int chunks = cols / N;
     const int row_bytes = chunks * 16;
     const int tile_rows = (32 / lanes_per_row) * RU;
     const size_t tile_bytes = static_cast<size_t>(tile_rows) * row_bytes;
-    const size_t smem = tile_bytes * kStages * kWarps + static_cast<size_t>(cols) * sizeof(float) * 2;
+    const size_t smem = tile_bytes * kStages * kWarps + static_cast<size_t>(cols) * sizeof(float) * (POST ? 3 : 2);
     const DeviceInfo& dev = device_info();
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
-        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU, PRE, POST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024);
         attr_set[dev.index] = true;
     }
@@ -313,9 +415,9 @@ int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int6
     const int64_t useful = (rows + static_cast<int64_t>(tile_rows) * kWarps - 1) / (static_cast<int64_t>(tile_rows) * kWarps);
     if (grid > useful) grid = useful;
     if (grid < 1) grid = 1;
-    norm_tma_kernel<T, LAYER, CPL, RU, PRE><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
+    norm_tma_kernel<T, LAYER, CPL, RU, PRE, POST><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
-        cols, eps, lanes_per_row, nullptr);
+        cols, eps, lanes_per_row, nullptr, post);
     count_launch();
     return launch_status();
 }
@@ -347,6 +449,25 @@ int norm_dispatch(const void* x, const void* gamma, const void* beta, void* y, i
         cols, eps);
     count_launch();
     return launch_status();
+}
+
+// LayerNorm(SiLU(x)) + gathered rows -> tokens, RMSNorm(tokens) -> normed: TMA-staged kernel only
+template <typename T>
+int token_tail_dispatch(const void* x, const void* gamma, const void* beta, void* tokens, int64_t rows, int cols,
+                        float eps, const PostArgs& post, cudaStream_t stream) {
+    const int N = Vec16<T>::N;
+    const bool vec_ok = (cols % N == 0) && aligned16(x) && aligned16(tokens) && aligned16(gamma) && aligned16(beta) &&
+                        aligned16(post.table_a) && (post.table_b == nullptr || aligned16(post.table_b)) &&
+                        aligned16(post.gamma2) && aligned16(post.normed) && (cols / N) <= 256;
+    if (!vec_ok) return TB200_ERR_UNSUPPORTED;
+    const int chunks = cols / N;
+    int G = 1;
+    while (G < 32 && G < chunks) G <<= 1;
+    const int cpl = (chunks + G - 1) / G;
+    if (cpl <= 1) return launch_tma<T, true, 1, 4, kPreSilu, true>(x, gamma, beta, tokens, rows, cols, eps, G, stream, post);
+    if (cpl <= 2) return launch_tma<T, true, 2, 2, kPreSilu, true>(x, gamma, beta, tokens, rows, cols, eps, G, stream, post);
+    if (cpl <= 4) return launch_tma<T, true, 4, 1, kPreSilu, true>(x, gamma, beta, tokens, rows, cols, eps, G, stream, post);
+    return launch_tma<T, true, 8, 1, kPreSilu, true>(x, gamma, beta, tokens, rows, cols, eps, G, stream, post);
 }
 
 template <bool LAYER, int PRE>
@@ -386,4 +507,25 @@ extern "C" int tb200_rmsnorm_bias_fwd(const void* x, const void* in_bias, const 
 extern "C" int tb200_layernorm_silu_fwd(const void* x, const void* gamma, const void* beta, void* y, int64_t rows,
                                         int32_t cols, float eps, int dtype, void* stream) {
     return tb200::norm_entry<true, tb200::kPreSilu>(x, gamma, beta, y, rows, cols, eps, dtype, stream);
+}
+
+extern "C" int tb200_token_tail_fwd(const void* x, const void* ln_gamma, const void* ln_beta, const void* table_a,
+                                    int64_t rows_a, const int64_t* ids_a, const void* table_b, int64_t rows_b,
+                                    const int64_t* ids_b, const void* rms_gamma, void* tokens, void* normed,
+                                    int64_t rows, int32_t cols, float ln_eps, float rms_eps, int dtype, void* stream) {
+    using namespace tb200;
+    if (rows < 0 || cols < 1 || rows_a < 1 || (table_b != nullptr && rows_b < 1)) return TB200_ERR_SHAPE;
+    if (rows == 0) return TB200_OK;
+    if (x == nullptr || ln_gamma == nullptr || ln_beta == nullptr || table_a == nullptr || ids_a == nullptr ||
+        (table_b != nullptr && ids_b == nullptr) || rms_gamma == nullptr || tokens == nullptr || normed == nullptr)
+        return TB200_ERR_NULL;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    PostArgs post{table_a, ids_a, rows_a, table_b, ids_b, rows_b, rms_gamma, normed, rms_eps};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case TB200_F32: return token_tail_dispatch<float>(x, ln_gamma, ln_beta, tokens, rows, cols, ln_eps, post, s);
+        case TB200_F16: return token_tail_dispatch<__half>(x, ln_gamma, ln_beta, tokens, rows, cols, ln_eps, post, s);
+        case TB200_BF16: return token_tail_dispatch<__nv_bfloat16>(x, ln_gamma, ln_beta, tokens, rows, cols, ln_eps, post, s);
+        default: return TB200_ERR_DTYPE;
+    }
 }

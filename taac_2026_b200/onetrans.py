@@ -628,24 +628,33 @@ class OneTransInference:
                 ops.gather_rows(table, ids_full, out=token_input, col0=f * emb)
         else:
             token_input = torch.zeros(total0, max(1, n_feat * emb), dtype=self.dtype, device=dev)
-        # Linear -> SiLU -> LayerNorm with the activation inside the norm kernel, then the time-bucket and
-        # position rows added in place by one pass over the token matrix
-        tokens = ops.layer_norm(self._linear(token_input, prefix + ".project.0"), self._p(prefix + ".project.2.weight"),
-                                self._p(prefix + ".project.2.bias"), 1e-5, pre_silu=True)
+        # Linear -> SiLU -> LayerNorm, the time-bucket and position rows and the first block's RMSNorm in one pass
+        # over the token matrix (`token_tail`); the NS rows are filled in afterwards
+        projected = self._linear(token_input, prefix + ".project.0")
+        ln_w, ln_b = self._p(prefix + ".project.2.weight"), self._p(prefix + ".project.2.bias")
         pos_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, j_idx)
         pos_table = self._positions(width).to(self.dtype).contiguous()
+        rows_a, rows_b = (pos_table, pos_full), (None, None)
         if prefix + ".time_embedding.weight" in self.w:
             buckets = sequence_time_buckets(ts[sample_of, src_pos][:, None], request_ts[sample_of], self._edges)[:, 0]
             buckets_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, buckets.long())
-            ops.add_gathered_rows(tokens, self._p(prefix + ".time_embedding.weight"), buckets_full, pos_table, pos_full)
+            rows_a, rows_b = (self._p(prefix + ".time_embedding.weight"), buckets_full), (pos_table, pos_full)
+        first_norm_w = self._p(self.blocks[0]["p"] + ".attn_norm.weight") if self.blocks else None
+        if first_norm_w is not None and projected.shape[1] % (16 // projected.element_size()) == 0:
+            tokens, x_first = ops.token_tail(projected, ln_w, ln_b, rows_a[0], rows_a[1], rows_b[0], rows_b[1], first_norm_w)
         else:
-            ops.add_gathered_rows(tokens, pos_table, pos_full)
+            tokens = ops.layer_norm(projected, ln_w, ln_b, 1e-5, pre_silu=True)
+            ops.add_gathered_rows(tokens, rows_a[0], rows_a[1], rows_b[0], rows_b[1])
+            x_first = None
 
         # ---- the NS tokens take the rows left for them: [seq rows of b | ns rows of b]
         ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
         ns_off = torch.arange(ns, device=dev)[None, :]
         ns_rows = (cu[0][:-1] + counts[0])[:, None] + ns_off                       # [B, ns]
-        ops.scatter_rows(tokens, ns_rows.reshape(-1), ns_tokens.reshape(batch * ns, self.d).contiguous())
+        ns_flat = ns_tokens.reshape(batch * ns, self.d).contiguous()
+        ops.scatter_rows(tokens, ns_rows.reshape(-1), ns_flat)
+        if x_first is not None:   # the fused pass normalised placeholder rows there
+            ops.scatter_rows(x_first, ns_rows.reshape(-1), ops.rms_norm(ns_flat, first_norm_w, 1e-6))
 
         d, heads, hd = self.d, self.heads, self.head_dim
         for layer, blk in enumerate(self.blocks):
@@ -656,7 +665,7 @@ class OneTransInference:
                 return self._classify(seq_summary, ns_summary)
             p = blk["p"]
             cu32 = cu[layer].to(torch.int32)
-            x = ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
+            x = x_first if (layer == 0 and x_first is not None) else ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
             flat_ns = ns_rows.t().reshape(-1)                                      # token-major: [ns, B] row ids
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)                  # [ns, B, d], contiguous
             selected = self.select_early and widths[layer + 1] < widths[layer]

@@ -1002,6 +1002,42 @@ def add_gathered_rows(x: torch.Tensor, table_a: torch.Tensor, ids_a: torch.Tenso
     return x
 
 
+def token_tail(x: torch.Tensor, ln_weight: torch.Tensor, ln_bias: torch.Tensor, table_a: torch.Tensor,
+               ids_a: torch.Tensor, table_b: torch.Tensor | None, ids_b: torch.Tensor | None,
+               rms_weight: torch.Tensor, *, ln_eps: float = 1e-5, rms_eps: float = 1e-6) -> tuple[torch.Tensor, torch.Tensor]:
+    """``tokens = layer_norm(silu(x)) + table_a[ids_a] (+ table_b[ids_b])`` and ``rms_norm(tokens)`` in one pass.
+
+    Returns ``(tokens, normed)``, both new ``[rows, cols]`` tensors of x's dtype; the values equal
+    ``layer_norm(..., pre_silu=True)`` -> ``add_gathered_rows`` -> ``rms_norm`` run one after the other."""
+    _require_backend("token_tail", "cuda")
+    _require_cuda_tensors("cuda token_tail", x, ln_weight, ln_bias, table_a, ids_a, table_b, ids_b, rms_weight)
+    if x.ndim != 2 or not x.is_contiguous() or not cuda_supported_floating_dtype(x.dtype):
+        raise ValueError("token_tail needs a contiguous 2-D floating-point matrix")
+    rows, cols = x.shape
+    if (table_b is None) != (ids_b is None):
+        raise ValueError("token_tail: table_b and ids_b come together")
+    for table, ids in ((table_a, ids_a), (table_b, ids_b)):
+        if table is None:
+            continue
+        if table.ndim != 2 or table.shape[1] != cols or table.dtype != x.dtype or not table.is_contiguous():
+            raise ValueError("token_tail tables must be contiguous [rows, cols] matrices of x's dtype")
+        if ids.dtype != torch.int64 or ids.numel() != rows or not ids.is_contiguous():
+            raise ValueError("token_tail ids must be contiguous int64 with one entry per row of x")
+    vecs = [v.to(device=x.device, dtype=x.dtype).contiguous() for v in (ln_weight, ln_bias, rms_weight)]
+    if any(tuple(v.shape) != (cols,) for v in vecs):
+        raise ValueError("token_tail weight vectors must have one entry per column")
+    tokens, normed = torch.empty_like(x), torch.empty_like(x)
+    with torch.cuda.device(x.device), _timed("token_tail", rows=rows, cols=cols, esize=x.element_size(),
+                                            tables=1 if table_b is None else 2):
+        code = _lib.load().tb200_token_tail_fwd(
+            _ptr(x), _ptr(vecs[0]), _ptr(vecs[1]), _ptr(table_a), table_a.shape[0], _ptr(ids_a), _ptr(table_b),
+            0 if table_b is None else table_b.shape[0], _ptr(ids_b), _ptr(vecs[2]), _ptr(tokens), _ptr(normed), rows, cols,
+            float(ln_eps), float(rms_eps), _DTYPE_CODES[x.dtype], _stream_ptr(),
+        )
+    _lib.check(code, "cuda token_tail")
+    return tokens, normed
+
+
 def bias_act_rows(x: torch.Tensor, bias: torch.Tensor, *, silu: bool) -> torch.Tensor:
     """``x = act(x + bias[group])`` in place for a contiguous ``x`` [groups, rows_per_group, cols] (or
     [rows, cols] with ``bias`` [cols]); ``act`` is SiLU (the sum rounded to the dtype first) or identity."""
@@ -1029,6 +1065,7 @@ def bias_silu_rows(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
 
 __all__ = [
     "add_gathered_rows",
+    "token_tail",
     "bias_act_rows",
     "bias_silu_rows",
     "AttentionMaskPlan",

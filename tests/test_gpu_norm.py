@@ -143,3 +143,37 @@ def test_fused_norm_variants_edge_cases():
     got = ops.rms_norm(x.cuda(), w5.cuda(), 1e-6, in_bias=b5.cuda()).cpu()
     want = R.rms_norm_fp32((x + b5).reshape(-1, 5), w5, 1e-6).reshape(2, 3, 5)
     assert (got - want).abs().max().item() <= 2e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("cols,two", [(128, True), (512, True), (512, False), (1024, True), (2048, False)])
+def test_token_tail_equals_the_separate_kernels(dtype, cols, two):
+    """layer_norm(silu(x)) + gathered rows -> tokens and rms_norm(tokens) from one kernel, bit for bit the
+    results of the three kernels it replaces."""
+    g = torch.Generator().manual_seed(cols)
+    rows = 1003
+    x = (1.5 * torch.randn(rows, cols, generator=g)).to(dtype).cuda()
+    w1 = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).cuda()
+    b1 = (0.1 * torch.randn(cols, generator=g)).to(dtype).cuda()
+    w2 = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).cuda()
+    ta = torch.randn(65, cols, generator=g).to(dtype).cuda()
+    tb = torch.randn(300, cols, generator=g).to(dtype).cuda()
+    ia = torch.randint(-1, 70, (rows,), generator=g).cuda()
+    ib = torch.randint(0, 300, (rows,), generator=g).cuda()
+    tokens, normed = ops.token_tail(x, w1, b1, ta, ia, tb if two else None, ib if two else None, w2)
+    want_tokens = ops.layer_norm(x, w1, b1, 1e-5, pre_silu=True)
+    ops.add_gathered_rows(want_tokens, ta, ia, *((tb, ib) if two else ()))
+    want_normed = ops.rms_norm(want_tokens, w2, 1e-6)
+    assert torch.equal(tokens, want_tokens)
+    assert torch.equal(normed, want_normed)
+
+
+def test_token_tail_rejects_rows_it_cannot_stage():
+    """Rows that are not whole 16-byte pieces (or wider than 256 pieces) have no fused kernel: the call fails
+    loudly instead of running something else."""
+    x = torch.randn(10, 20, device="cuda").bfloat16()
+    w = torch.ones(20, device="cuda").bfloat16()
+    table = torch.zeros(4, 20, device="cuda").bfloat16()
+    ids = torch.zeros(10, dtype=torch.int64, device="cuda")
+    with pytest.raises(RuntimeError):
+        ops.token_tail(x, w, w, table, ids, None, None, w)
