@@ -43,6 +43,7 @@ __device__ __forceinline__ float silu_f(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
     return fmaf(h, t, h);
 }
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ uint4 ld_nc_u4(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -151,6 +152,31 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             break;
         }
 
+        // POST: the table rows of this tile are requested into the L1 now, so that the loads behind the
+        // normalisation find them there instead of waiting for the L2 one row at a time
+        int64_t id_a[RU], id_b[RU];
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+            id_a[u] = id_b[u] = 0;
+            if (POST && u * ng + group < rows_here) {
+                const int64_t row = row_begin + it * tile_rows + u * ng + group;
+                int64_t ia = post.ids_a[row];
+                id_a[u] = ia < 0 ? 0 : (ia > post.rows_a - 1 ? post.rows_a - 1 : ia);
+                if (post.table_b != nullptr) {
+                    int64_t ib = post.ids_b[row];
+                    id_b[u] = ib < 0 ? 0 : (ib > post.rows_b - 1 ? post.rows_b - 1 : ib);
+                }
+#pragma unroll
+                for (int j = 0; j < CPL; ++j) {
+                    const int c = lane_g + j * G;
+                    if (c < chunks) {
+                        prefetch_l1(reinterpret_cast<const uint4*>(post.table_a) + id_a[u] * chunks + c);
+                        if (post.table_b != nullptr) prefetch_l1(reinterpret_cast<const uint4*>(post.table_b) + id_b[u] * chunks + c);
+                    }
+                }
+            }
+        }
+
         // packed fp32x2 arithmetic throughout: the kernel is issue-bound, not HBM-bound, otherwise
         float2 v[RU][CPL][N / 2];
         float sum[RU];
@@ -222,21 +248,10 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             for (int u = 0; u < RU; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
         }
         float2 inv[RU];
-        int64_t id_a[RU], id_b[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
             const float i1 = rsqrtf(sq[u] * inv_cols + eps);
             inv[u] = make_float2(i1, i1);
-            id_a[u] = id_b[u] = 0;
-            if (POST && valid[u]) {
-                const int64_t row = row_begin + it * tile_rows + u * ng + group;
-                int64_t ia = post.ids_a[row];
-                id_a[u] = ia < 0 ? 0 : (ia > post.rows_a - 1 ? post.rows_a - 1 : ia);
-                if (post.table_b != nullptr) {
-                    int64_t ib = post.ids_b[row];
-                    id_b[u] = ib < 0 ? 0 : (ib > post.rows_b - 1 ? post.rows_b - 1 : ib);
-                }
-            }
         }
 #pragma unroll
         for (int j = 0; j < CPL; ++j) {
