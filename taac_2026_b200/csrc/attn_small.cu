@@ -23,6 +23,11 @@ constexpr int kMaxL = 32;
 constexpr int kWarps = 4;
 constexpr int kChunks = kD / 8;   // 16-byte pieces per row
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -60,21 +65,33 @@ attn_small_kernel(const AttnArgs a) {
     const T* vp = static_cast<const T*>(a.v) + (packed ? row_base * a.v_sl : static_cast<int64_t>(b) * a.v_sb) + static_cast<int64_t>(h) * a.v_sh;
     T* op = static_cast<T*>(a.o) + (packed ? row_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) + static_cast<int64_t>(h) * a.o_sh;
 
-    // stage K and V: piece (lane % 8) of rows lane / 8, lane / 8 + 4, ...
+    // stage K and V with asynchronous 16-byte copies (piece lane % 8 of rows lane / 8, lane / 8 + 4, ...): all of
+    // them are in flight together with the load of the query row, instead of one round trip per four rows
     uint4* ks = kv_s[warp][0];
     uint4* vs = kv_s[warp][1];
     for (int r = lane >> 3; r < lk; r += 4) {
         const int c = lane & 7;
-        ks[r * kChunks + c] = reinterpret_cast<const uint4*>(kp + static_cast<int64_t>(r) * a.k_sl)[c];
-        vs[r * kChunks + c] = reinterpret_cast<const uint4*>(vp + static_cast<int64_t>(r) * a.v_sl)[c];
+        cp_async16(&ks[r * kChunks + c], reinterpret_cast<const uint4*>(kp + static_cast<int64_t>(r) * a.k_sl) + c);
+        cp_async16(&vs[r * kChunks + c], reinterpret_cast<const uint4*>(vp + static_cast<int64_t>(r) * a.v_sl) + c);
     }
-    __syncwarp();
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
     const int r = lane / P;           // this lane's query
     const int part = lane % P;        // which 64 / P dimensions of the row it holds
     const uint32_t group_mask = (P == 1 ? 1u : ((1u << P) - 1u)) << (lane & ~(P - 1));
-    if (r >= lq) return;
-    if (a.padded_query_self && r >= valid_len && r < ns_start) {   // padded query: its own value row
+    const bool active = r < lq;
+    const bool self_row = active && a.padded_query_self && r >= valid_len && r < ns_start;
+    uint4 qraw[CPL];
+    if (active && !self_row) {
+#pragma unroll
+        for (int c = 0; c < CPL; ++c)
+            qraw[c] = reinterpret_cast<const uint4*>(qp + static_cast<int64_t>(r) * a.q_sl)[part * CPL + c];
+    }
+    // every lane waits for its own copies, then the warp agrees that K and V are in shared memory
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    if (!active) return;
+    if (self_row) {   // padded query: its own value row
         const uint4* src = reinterpret_cast<const uint4*>(vp + static_cast<int64_t>(r) * a.v_sl);
         uint4* dst = reinterpret_cast<uint4*>(op + static_cast<int64_t>(r) * a.o_sl);
 #pragma unroll
@@ -86,7 +103,7 @@ attn_small_kernel(const AttnArgs a) {
 #pragma unroll
     for (int c = 0; c < CPL; ++c) {
         float2 f[4];
-        Vec16<T>::unpack2(reinterpret_cast<const uint4*>(qp + static_cast<int64_t>(r) * a.q_sl)[part * CPL + c], f);
+        Vec16<T>::unpack2(qraw[c], f);
 #pragma unroll
         for (int e = 0; e < 4; ++e) q[4 * c + e] = __fmul2_rn(f[e], make_float2(a.scale_log2, a.scale_log2));
     }
