@@ -7,6 +7,8 @@ int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cud
 bool attn_tc05_supported(const AttnArgs& a, int head_dim, int dtype);
 int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t* status, cudaStream_t stream);
 bool attn_small_supported(const AttnArgs& a, int head_dim, int max_lq, int max_lk);
+bool attn_tiny_supported(const AttnArgs& a, int head_dim, int max_lq, int max_lk);
+int attn_tiny_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 int attn_small_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 }  // namespace tb200
 
@@ -56,7 +58,11 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     const bool small_ok = attn_small_supported(a, D, Lq, Lk);
     if (kernel == 3 && !small_ok) return TB200_ERR_UNSUPPORTED;
     // samples of at most 32 rows (the non-sequence tokens alone, late in the pyramid): no tensor-core tile pays
-    if (kernel == 3 || (kernel == 0 && small_ok)) return attn_small_forward(a, dtype, s);
+    if (kernel == 3 || (kernel == 0 && small_ok)) {
+        // up to 16 rows the whole sample is one tensor-core tile per head; 17..32 rows take the scalar kernel
+        if (attn_tiny_supported(a, D, Lq, Lk)) return attn_tiny_forward(a, dtype, s);
+        return attn_small_forward(a, dtype, s);
+    }
     // Automatic choice: the tcgen05 kernel wherever it applies (bf16, head_dim 64, no key_valid map); measured
     // on full-length rows it leads the mma.sync kernel from 128 keys up, causal or not.  Samples shorter than
     // one 128-row block leave most of its tile idle, so those stay on the 64-row mma.sync tiles.

@@ -340,6 +340,146 @@ __global__ void __launch_bounds__(kThreads, D <= 64 ? 4 : 2) attn_mma_kernel(con
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Samples of at most 16 rows (head_dim 64): one warp per (sample, head), the whole problem is one
+// 16 x 16 score tile: 8 MMAs for Q K^T, a register softmax, 8 MMAs for P V.  Same masks and layouts as the
+// kernel above; Lq == Lk <= 16 (packed samples or padded batches).
+// ------------------------------------------------------------------------------------------------
+constexpr int kTinyL = 16;
+constexpr int kTinyWarps = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kTinyWarps * 32)
+attn_tiny_kernel(const AttnArgs a) {
+    constexpr int D = 64;
+    constexpr int CH = D / 8;
+    __shared__ __align__(128) T tiles[kTinyWarps][3][kTinyL * D];   // Q (later the output), K, V per warp
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int64_t pair = static_cast<int64_t>(blockIdx.x) * kTinyWarps + warp;
+    if (pair >= static_cast<int64_t>(a.B) * a.H) return;
+    const int b = static_cast<int>(pair / a.H);
+    const int h = static_cast<int>(pair - static_cast<int64_t>(b) * a.H);
+
+    const bool packed = a.cu_rows != nullptr;
+    int lq = a.Lq, lk = a.Lk;
+    int64_t row_base = 0;
+    if (packed) {
+        row_base = a.cu_rows[b];
+        lq = lk = a.cu_rows[b + 1] - static_cast<int32_t>(row_base);
+    }
+    lq = min(lq, kTinyL);
+    lk = min(lk, kTinyL);
+    if (lq <= 0) return;   // empty sample: nothing to read or write (uniform over the warp)
+    const int valid_len = (a.seq_len != nullptr && !packed) ? min(max(a.seq_len[b], 0), lk) : lk;
+    const int ns_start = packed ? lk : min(a.ns_start, lk);
+    const bool causal = a.causal != 0;
+    const T* q = static_cast<const T*>(a.q) + (packed ? row_base * a.q_sl : static_cast<int64_t>(b) * a.q_sb) + static_cast<int64_t>(h) * a.q_sh;
+    const T* k = static_cast<const T*>(a.k) + (packed ? row_base * a.k_sl : static_cast<int64_t>(b) * a.k_sb) + static_cast<int64_t>(h) * a.k_sh;
+    const T* v = static_cast<const T*>(a.v) + (packed ? row_base * a.v_sl : static_cast<int64_t>(b) * a.v_sb) + static_cast<int64_t>(h) * a.v_sh;
+    T* o = static_cast<T*>(a.o) + (packed ? row_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) + static_cast<int64_t>(h) * a.o_sh;
+
+    T* sQ = tiles[warp][0];
+    T* sK = tiles[warp][1];
+    T* sV = tiles[warp][2];
+    // 16 rows x 8 pieces per matrix: four pieces per lane and matrix, rows past the sample are zero-filled
+#pragma unroll
+    for (int i = lane; i < kTinyL * CH; i += 32) {
+        const int r = i / CH;
+        const int c = i - r * CH;
+        cp_async16(sQ + swz<D>(r, c), q + static_cast<int64_t>(r < lq ? r : 0) * a.q_sl + c * 8, r < lq);
+        cp_async16(sK + swz<D>(r, c), k + static_cast<int64_t>(r < lk ? r : 0) * a.k_sl + c * 8, r < lk);
+        cp_async16(sV + swz<D>(r, c), v + static_cast<int64_t>(r < lk ? r : 0) * a.v_sl + c * 8, r < lk);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // S = Q K^T: 16 x 16
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+    const int mi = lane >> 3;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t qf[4], kb[4];
+        ldsm_x4(qf, sQ + swz<D>(lane & 15, kk * 2 + (lane >> 4)));
+        ldsm_x4(kb, sK + swz<D>((mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
+        mma16816<T>(s[0], qf, kb[0], kb[1]);
+        mma16816<T>(s[1], qf, kb[2], kb[3]);
+    }
+    // mask, softmax of rows g and g + 8 (each row lives in the four lanes of a quad)
+    float inv_l[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+        const int r = g + 8 * hr;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = j * 8 + 2 * t + e;
+                if (!attn_visible(r, c, valid_len, ns_start, lk, causal)) s[j][2 * hr + e] = -INFINITY;
+                mx = fmaxf(mx, s[j][2 * hr + e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float ms = (mx == -INFINITY ? 0.f : mx) * a.scale_log2;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float p = exp2f(s[j][2 * hr + e] * a.scale_log2 - ms);   // exp2(-inf) = 0
+                s[j][2 * hr + e] = p;
+                sum += p;
+            }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        inv_l[hr] = sum > 0.f ? 1.0f / sum : 0.f;
+    }
+    // O = P V: the 16 x 16 probabilities are one A fragment
+    uint32_t pa[4];
+    pa[0] = pack2<T>(s[0][0], s[0][1]);
+    pa[1] = pack2<T>(s[0][2], s[0][3]);
+    pa[2] = pack2<T>(s[1][0], s[1][1]);
+    pa[3] = pack2<T>(s[1][2], s[1][3]);
+    float acc[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+#pragma unroll
+    for (int jp = 0; jp < D / 16; ++jp) {
+        uint32_t vb[4];
+        ldsm_x4_t(vb, sV + swz<D>((mi & 1) * 8 + (lane & 7), jp * 2 + (mi >> 1)));
+        mma16816<T>(acc[2 * jp], pa, vb[0], vb[1]);
+        mma16816<T>(acc[2 * jp + 1], pa, vb[2], vb[3]);
+    }
+    __syncwarp();   // every lane has read its Q fragments: the Q tile becomes the output staging tile
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        *reinterpret_cast<uint32_t*>(sQ + swz<D>(g, j) + 2 * t) = pack2<T>(acc[j][0] * inv_l[0], acc[j][1] * inv_l[0]);
+        *reinterpret_cast<uint32_t*>(sQ + swz<D>(g + 8, j) + 2 * t) = pack2<T>(acc[j][2] * inv_l[1], acc[j][3] * inv_l[1]);
+    }
+    __syncwarp();
+    const bool self_rows = a.padded_query_self != 0;
+#pragma unroll
+    for (int i = lane; i < kTinyL * CH; i += 32) {
+        const int r = i / CH;
+        const int c = i - r * CH;
+        if (r >= lq) continue;
+        const bool padded_q = self_rows && r >= valid_len && r < ns_start;
+        const uint4 val = padded_q ? *reinterpret_cast<const uint4*>(v + static_cast<int64_t>(r) * a.v_sl + c * 8)
+                                   : *reinterpret_cast<const uint4*>(sQ + swz<D>(r, c));
+        *reinterpret_cast<uint4*>(o + static_cast<int64_t>(r) * a.o_sl + c * 8) = val;
+    }
+}
+
 template <typename T, int D>
 int launch(const AttnArgs& a, int max_lq, cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(kBM + 2 * kKvStages * kBN) * D * sizeof(T);
@@ -358,6 +498,20 @@ int launch(const AttnArgs& a, int max_lq, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// Samples of at most 16 rows, head_dim 64, no key_valid map: one warp per (sample, head).
+bool attn_tiny_supported(const AttnArgs& a, int head_dim, int max_lq, int max_lk) {
+    return head_dim == 64 && a.key_valid == nullptr && a.cu_rows_q == nullptr && max_lq <= kTinyL && max_lk <= kTinyL;
+}
+int attn_tiny_forward(const AttnArgs& a, int dtype, cudaStream_t stream) {
+    const int64_t pairs = static_cast<int64_t>(a.B) * a.H;
+    const int64_t grid = (pairs + kTinyWarps - 1) / kTinyWarps;
+    if (grid > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (dtype == TB200_BF16) attn_tiny_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), kTinyWarps * 32, 0, stream>>>(a);
+    else attn_tiny_kernel<__half><<<static_cast<unsigned>(grid), kTinyWarps * 32, 0, stream>>>(a);
+    count_launch();
+    return launch_status();
+}
 
 // Entry used by the C ABI dispatcher in attn_api.cu.  max_lq bounds the query rows of any sample.
 int attn_mma_forward(const AttnArgs& a, int head_dim, int dtype, int max_lq, cudaStream_t stream) {

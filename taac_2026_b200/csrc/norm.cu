@@ -72,7 +72,7 @@ struct PostArgs {
 };
 
 template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST = false>
-__global__ void __launch_bounds__(kMaxThreads, POST ? 2 : 3)
+__global__ void __launch_bounds__(kMaxThreads, 3)
 norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                 int64_t rows, int cols, float eps, int lanes_per_row, int* __restrict__ status, const PostArgs post) {
     constexpr int N = Vec16<T>::N;
