@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, D <= 64 ? 4 : 2) attn_mma_kernel(con
 
         uint32_t qf[D / 16][4];
         bool q_loaded = false;
+        const bool warp_has_rows = m0 + warp * 16 < lq;
         int stage = 0;
         for (int n = first; n < n_tiles;) {
             const int next = next_live(n);
@@ -196,6 +197,9 @@ __global__ void __launch_bounds__(kThreads, D <= 64 ? 4 : 2) attn_mma_kernel(con
             cp_async_wait<kKvStages - 1>();
             __syncthreads();
 
+            // a warp whose 16 query rows all lie past the sample's last query (few queries against many keys) only
+            // helps with the loads and the barriers
+            if (warp_has_rows) {
             if (!q_loaded) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk)
@@ -293,6 +297,7 @@ __global__ void __launch_bounds__(kThreads, D <= 64 ? 4 : 2) attn_mma_kernel(con
                     mma16816<T>(acc_o[2 * jp + 1], pa, vb[2], vb[3]);
                 }
             }
+            }  // warp_has_rows
             __syncthreads();  // everyone is done with this stage before it is refilled
             stage = stage + 1 == kKvStages ? 0 : stage + 1;
             n = next;
