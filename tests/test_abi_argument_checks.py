@@ -1,0 +1,97 @@
+"""Argument validation of the C ABI, exercised without a GPU.
+
+Every entry point checks shapes, null pointers, dtypes and alignment before it looks at the device, so the
+rejections (and the empty-input successes) can be tested on any machine that can load ``libtb200.so``.  No
+call here reaches a kernel launch."""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+
+from taac_2026_b200 import _lib
+
+OK, ERR_NULL, ERR_DTYPE, ERR_SHAPE, ERR_ALIGN, ERR_UNSUPPORTED = 0, -1, -2, -3, -4, -5
+BF16 = 2
+P = ctypes.c_void_p
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not _lib.LIB_PATH.exists():
+        pytest.skip("libtb200.so is not built")
+    return _lib.load()
+
+
+def test_status_strings(lib):
+    assert lib.tb200_strerror(OK).decode()
+    for code in (ERR_NULL, ERR_DTYPE, ERR_SHAPE, ERR_ALIGN, ERR_UNSUPPORTED, -6, -7, -8):
+        text = lib.tb200_strerror(code).decode()
+        assert text and text != lib.tb200_strerror(OK).decode()
+
+
+def test_norm_entries(lib):
+    buf = (ctypes.c_uint8 * 256)()
+    p = ctypes.addressof(buf)
+    for fn, extra in ((lib.tb200_rmsnorm_fwd, ()), (lib.tb200_layernorm_fwd, (P(p),)), (lib.tb200_layernorm_silu_fwd, (P(p),))):
+        assert fn(P(p), P(p), *extra, P(p), -1, 8, 1e-6, BF16, None) == ERR_SHAPE      # negative rows
+        assert fn(P(p), P(p), *extra, P(p), 4, 0, 1e-6, BF16, None) == ERR_SHAPE       # no columns
+        assert fn(P(p), P(p), *extra, P(p), 0, 8, 1e-6, BF16, None) == OK              # empty matrix: nothing to do
+        assert fn(None, P(p), *extra, P(p), 4, 8, 1e-6, BF16, None) == ERR_NULL
+    assert lib.tb200_rmsnorm_bias_fwd(P(p), None, P(p), P(p), 4, 8, 1e-6, BF16, None) == ERR_NULL
+    assert lib.tb200_layernorm_fwd(P(p), P(p), None, P(p), 4, 8, 1e-6, BF16, None) == ERR_NULL
+
+
+def test_row_kernel_entries(lib):
+    buf = (ctypes.c_uint8 * 256)()
+    p = ctypes.addressof(buf)
+    assert lib.tb200_add_gathered_rows(P(p), 0, 8, P(p), 4, P(p), None, 0, None, BF16, None) == OK
+    assert lib.tb200_add_gathered_rows(P(p), 4, 8, P(p), 0, P(p), None, 0, None, BF16, None) == ERR_SHAPE   # empty table
+    assert lib.tb200_add_gathered_rows(P(p), 4, 8, None, 4, P(p), None, 0, None, BF16, None) == ERR_NULL
+    assert lib.tb200_add_gathered_rows(P(p), 4, 8, P(p), 4, P(p), None, 0, None, 9, None) == ERR_DTYPE
+    assert lib.tb200_add_gathered_rows(P(p), 4, 4, P(p), 4, P(p), None, 0, None, BF16, None) == ERR_ALIGN   # 8-byte rows
+    assert lib.tb200_bias_act_rows(P(p), 0, 8, P(p), 1, 1, BF16, None) == OK
+    assert lib.tb200_bias_act_rows(P(p), 4, 8, P(p), 0, 1, BF16, None) == ERR_SHAPE                       # group of zero rows
+    assert lib.tb200_bias_act_rows(P(p), 4, 8, P(p), 1, 7, BF16, None) == ERR_UNSUPPORTED                 # unknown activation
+    assert lib.tb200_bias_act_rows(P(p), 4, 8, None, 1, 0, BF16, None) == ERR_NULL
+
+
+def test_attention_entry(lib):
+    buf = (ctypes.c_uint8 * 256)()
+    p = ctypes.addressof(buf)
+    strides = (ctypes.c_int64 * 12)(*([64] * 12))
+
+    def call(**kw):
+        a = dict(q=P(p), k=P(p), v=P(p), o=P(p), B=2, H=2, Lq=4, Lk=4, D=64, strides=strides, seq_len=None, cu=None,
+                 cu_q=None, kv=None, ns=4, causal=0, self_rows=0, scale=0.125, dtype=BF16, kernel=0, total=0)
+        a.update(kw)
+        return lib.tb200_attn_fwd(a["q"], a["k"], a["v"], a["o"], a["B"], a["H"], a["Lq"], a["Lk"], a["D"], a["strides"],
+                                  a["seq_len"], a["cu"], a["cu_q"], a["kv"], a["ns"], a["causal"], a["self_rows"], a["scale"],
+                                  a["dtype"], a["kernel"], a["total"], None, None)
+
+    assert call(B=0) == OK and call(Lq=0) == OK                 # nothing to compute
+    assert call(B=-1) == ERR_SHAPE and call(H=0) == ERR_SHAPE
+    assert call(q=None) == ERR_NULL and call(strides=None) == ERR_NULL
+    assert call(dtype=0) == ERR_DTYPE                           # fp32 has no kernel (the host casts)
+    assert call(D=48) == ERR_UNSUPPORTED
+    assert call(self_rows=1, Lq=4, Lk=8) == ERR_SHAPE           # the self fallback needs a square problem
+    assert call(ns=-1) == ERR_SHAPE
+    assert call(cu_q=P(p)) == ERR_UNSUPPORTED                   # separate query rows need a packed batch
+    bad = (ctypes.c_int64 * 12)(*([64] * 11 + [60]))
+    assert call(strides=bad) == ERR_ALIGN                       # rows must start on 16-byte boundaries
+
+
+def test_fp8_entries(lib):
+    buf = (ctypes.c_uint8 * 256)()
+    p = ctypes.addressof(buf)
+    assert lib.tb200_quant_act_1x128(P(p), P(p), P(p), 0, 128, None) == OK
+    assert lib.tb200_quant_act_1x128(P(p), P(p), P(p), 4, 100, None) == ERR_SHAPE          # K not a multiple of 128
+    assert lib.tb200_quant_act_1x128(None, P(p), P(p), 4, 128, None) == ERR_NULL
+    gemm = lib.tb200_fp8_gemm
+    assert gemm(P(p), P(p), P(p), P(p), None, None, P(p), P(p), 0, 256, 128, 0, None, None) == OK
+    assert gemm(P(p), P(p), P(p), P(p), None, None, P(p), P(p), 4, 200, 128, 0, None, None) == ERR_SHAPE   # N % 256
+    assert gemm(P(p), P(p), P(p), P(p), None, None, P(p), P(p), 4, 256, 128, 5, None, None) == ERR_UNSUPPORTED
+    assert gemm(P(p), P(p), P(p), P(p), None, None, P(p), None, 4, 256, 128, 1, None, None) == ERR_NULL    # scales out
+    assert gemm(P(p), P(p), P(p), P(p), None, P(p), P(p), P(p), 4, 256, 128, 0, None, None) == ERR_UNSUPPORTED  # residual + swiglu
+    assert lib.tb200_ffn_fp8_static_scratch_bytes() == 64 << 20
