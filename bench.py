@@ -304,15 +304,16 @@ def time_cpu_port(sd_cpu: dict, spec: OneTransSpec, batch_cpu, *, limit_s: float
     sample = int(max(rows, min(batch_cpu.batch_size, limit_s / per_row)))
     sample = min(sample, 256)
     times = []
+    logits = None
     for _ in range(max(1, steps)):
         t0 = time.perf_counter()
-        torch_cpu.predict(sd_cpu, spec_dict, batch_cpu.slice(0, sample))
+        logits, _ = torch_cpu.predict(sd_cpu, spec_dict, batch_cpu.slice(0, sample))
         times.append(time.perf_counter() - t0)
     best = min(times)
     return {
         "value": round(sample / best, 2), "unit": "samples/s", "cores": torch.get_num_threads(), "kind": "port",
         "sample": f"first {sample} rows of the rank-0 batch, fp32 dense / stored-type tables, {len(times)} run(s), best",
-        "seconds": round(best, 3),
+        "seconds": round(best, 3), "_rows": sample, "_logits": logits,
     }
 
 
@@ -340,6 +341,7 @@ def run_e2e(args) -> None:
         batch_cpu = synthetic_batch(spec, min(batch_size, 512), seq_len=wl["seq_len"], min_len=wl["min_len"], seed=0,
                                     field_exponent=wl["field_exp"], seq_exponent=wl["seq_exp"])
         res = time_cpu_port(sd_cpu, spec, batch_cpu, limit_s=20.0, steps=max(1, min(args.steps, 3)))
+        res.pop("_rows"), res.pop("_logits")
         line = {
             "impl": "reference", "metric": "pcvr_infer_samples_per_s", "value": res["value"], "unit": "samples/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -460,13 +462,20 @@ def run_e2e(args) -> None:
     if world == 1 and not args.no_cpu_baseline:
         sd_cpu = cpu_state_dict(sd)
         cpu = time_cpu_port(sd_cpu, spec, host_batch.slice(0, min(batch_size, 256)), limit_s=15.0)
-        # same rows on the GPU: the bounded sample doubles as a full-scale score parity check
-        from oracle import torch_cpu
+        # the same rows on the GPU: the timed sample doubles as a full-scale parity check of scores and AUC
+        # (labels drawn from the CPU logits, standardised, so that the AUC is well away from 0.5)
+        from oracle import reference_ops as R
 
-        n = min(32, batch_size)
-        want, _ = torch_cpu.predict(sd_cpu, spec.as_dict(), host_batch.slice(0, n))
-        got = model.scores(dev_batch.slice(0, n)).cpu()
-        cpu["max_abs_score_diff_vs_gpu"] = round(float((torch.sigmoid(want.reshape(-1)) - got).abs().max()), 6)
+        n = cpu.pop("_rows")
+        want_logits = cpu.pop("_logits").reshape(-1).float()
+        want = torch.sigmoid(want_logits)
+        got = model.scores(dev_batch.slice(0, n)).cpu().reshape(-1)
+        z = (want_logits - want_logits.mean()) / want_logits.std().clamp_min(1e-6)
+        labels = (torch.rand(n, generator=torch.Generator().manual_seed(2)) < torch.sigmoid(2.0 * z)).numpy()
+        cpu["parity_rows"] = n
+        cpu["max_abs_score_diff_vs_gpu"] = round(float((want - got).abs().max()), 6)
+        cpu["auc_cpu"] = round(R.binary_auc(labels, want.numpy()), 6)
+        cpu["auc_gpu"] = round(R.binary_auc(labels, got.numpy()), 6)
     line = {
         "metric": "pcvr_infer_samples_per_s", "value": round(value, 2), "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_total / args.steps, 3),
