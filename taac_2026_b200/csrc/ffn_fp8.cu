@@ -334,7 +334,10 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
                 // accumulators start from the bias: acc[0..15] <- columns col_a.., acc[16..31] <- col_b..
                 float2 acc[32];
-                {
+                if (g.bias == nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.f, 0.f);
+                } else {
                     const float4* ba = reinterpret_cast<const float4*>(bias_s + col_a);
                     const float4* bb = reinterpret_cast<const float4*>(bias_s + col_b);
 #pragma unroll
