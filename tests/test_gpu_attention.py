@@ -247,3 +247,35 @@ def test_packed_queries_are_the_last_rows_of_each_sample(causal):
     with pytest.raises(RuntimeError):   # only the mma.sync kernel serves separate query rows
         ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()),
                              cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()), kernel=2)
+
+
+def test_random_shapes_against_the_oracle():
+    """Seeded sweep over ragged shapes and mask forms, every kernel that serves the shape, against the fp32 oracle."""
+    g = torch.Generator().manual_seed(2026)
+    for case in range(24):
+        B = int(torch.randint(1, 6, (1,), generator=g))
+        H = int(torch.randint(1, 4, (1,), generator=g))
+        L = int(torch.randint(1, 300, (1,), generator=g))
+        causal = bool(torch.randint(0, 2, (1,), generator=g))
+        ns = int(torch.randint(0, min(L, 12) + 1, (1,), generator=g))
+        lens = torch.randint(0, L - ns + 1, (B,), generator=g)
+        q, k, v = _qkv(B, H, L, 64, torch.bfloat16, seed=1000 + case)
+        mask = R.structured_attention_mask(lens, L, L - ns, causal, causal)
+        pos = torch.arange(L)[None]
+        self_rows = ((pos >= lens[:, None]) & (pos < L - ns)) if causal else None
+        kernels = [1, 2] + ([3] if L <= 32 else [])
+        for kernel in kernels:
+            got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), ns_start=L - ns, causal=causal,
+                                       padded_query_self=causal, kernel=kernel, check=kernel == 2)
+            try:
+                _check(got, q, k, v, mask, self_rows)
+            except AssertionError as exc:
+                raise AssertionError(f"case {case}: B{B} H{H} L{L} ns{ns} causal={causal} kernel={kernel}: {exc}") from exc
+        # packed form of the same samples (every row valid): kernels 1 and 2 against each other and the oracle
+        rows_per = (lens + ns).clamp_min(1)
+        cu = torch.zeros(B + 1, dtype=torch.int32)
+        cu[1:] = torch.cumsum(rows_per, 0)
+        qkv = (torch.randn(int(cu[-1]), 3, H, 64, generator=g) * 0.5).bfloat16().cuda()
+        outs = [ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(),
+                                     max_rows=int(rows_per.max()), kernel=kern).float() for kern in (1, 2)]
+        assert (outs[0] - outs[1]).abs().max().item() <= 1e-2, f"case {case}: packed kernels disagree"
