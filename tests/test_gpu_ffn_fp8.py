@@ -137,3 +137,28 @@ def test_full_size_block_against_bf16_torch_on_device():
     slab = ((got - ref).view(64, -1).norm(dim=1) / ref.view(64, -1).norm(dim=1)).max().item()
     assert slab <= 7e-2
     assert (got - ref).abs().max().item() <= 1e-1 * ref.abs().max().item()
+
+
+def test_random_shapes_against_bf16_math():
+    """Seeded sweep over row counts (tile tails), K, hidden widths, gating, biases and the residual: the whole FFN
+    against the same layer in fp32 math on the bf16 operands, within the e4m3 noise floor (about 6e-2 relative)."""
+    g = torch.Generator().manual_seed(77)
+    for case in range(8):
+        m = int(torch.randint(1, 700, (1,), generator=g))
+        k = 128 * int(torch.randint(1, 6, (1,), generator=g))
+        hidden = 256 * int(torch.randint(1, 4, (1,), generator=g))
+        gated = bool(torch.randint(0, 2, (1,), generator=g))
+        x = torch.randn(m, k, generator=g).bfloat16()
+        w_up = (torch.randn((2 if gated else 1) * hidden, k, generator=g) * 0.05).bfloat16()
+        w_down = (torch.randn(256, hidden, generator=g) * 0.05).bfloat16()
+        b_up = (0.1 * torch.randn((2 if gated else 1) * hidden, generator=g)).bfloat16()
+        b_down = (0.1 * torch.randn(256, generator=g)).bfloat16()
+        res = torch.randn(m, 256, generator=g).bfloat16()
+        weights = ops.Fp8FfnWeights(w_up.cuda(), w_down.cuda(), gated=gated, b_up=b_up.cuda(), b_down=b_down.cuda())
+        got = ops.ffn_fp8(x.cuda(), weights, residual=res.cuda(), check=True).float().cpu()
+        up = x.float() @ w_up.float().t() + b_up.float()
+        h = torch.nn.functional.silu(up[:, :hidden]) * up[:, hidden:] if gated else torch.nn.functional.silu(up)
+        want = res.float() + h @ w_down.float().t() + b_down.float()
+        delta = want - res.float()
+        rel = ((got - want).norm() / delta.norm().clamp_min(1e-6)).item()
+        assert rel <= 9e-2, f"case {case}: m{m} k{k} hidden{hidden} gated={gated}: relative error {rel}"
