@@ -447,6 +447,15 @@ def run_e2e(args) -> None:
     ms_e2e = timed(lambda: run_e2e(args.steps), 1, None)
     records: list = []
     ms_recorded = timed(step_resident, args.steps, records)
+    # the same resident steps in the reference's order of operations (every block for every row, then the
+    # pyramid's row selection), for comparison with `value`
+    ms_ref_order = None
+    if model.packed and model.select_early:
+        model.select_early = False
+        for _ in range(2):
+            step_resident()
+        ms_ref_order = timed(step_resident, args.steps, None)
+        model.select_early = True
     clocks = sampler.stop() if rank == 0 else {}
 
     if rank != 0:
@@ -493,6 +502,11 @@ def run_e2e(args) -> None:
                 "d2h_bytes_per_step": host_scores.numel() * 4, "ms_per_step": round(ms_e2e / args.steps, 3)},
         "gpu_launches": launches,
         "kernel_timing_pass_ms_per_step": round(ms_recorded / args.steps, 3),
+        "reference_order": None if ms_ref_order is None else {
+            "value": round(total * args.steps / (ms_ref_order * 1e-3), 2), "unit": "samples/s",
+            "ms_per_step": round(ms_ref_order / args.steps, 3),
+            "note": "same steps with the pyramid's row selection after each whole block, as the reference orders it",
+        },
         "roofline": roofline,
         "kernels": per_op,
         "cpu_baseline": cpu,
