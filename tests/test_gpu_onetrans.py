@@ -178,3 +178,17 @@ def test_early_row_selection_changes_nothing(dtype, tol):
     early = OneTransInference(sd, spec, dtype=dtype, select_early=True).scores(batch)
     late = OneTransInference(sd, spec, dtype=dtype, select_early=False).scores(batch)
     assert (early - late).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("packed", [True, False])
+def test_batch_without_any_behaviour_event(packed):
+    """Every sequence is empty: the forward runs on the NS tokens alone from the first block on."""
+    spec = _mini_spec()
+    sd = random_state_dict(spec, seed=0)
+    batch = synthetic_batch(spec, 40, seq_len=96, min_len=4, seed=11)
+    seq = batch.sequences["seq_a"]
+    batch = ModelInput(batch.user, batch.item, {"seq_a": SequenceInput(seq.values, torch.zeros_like(seq.lengths), seq.timestamps)},
+                       batch.request_timestamp)
+    want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
+    got = OneTransInference(sd, spec, dtype=torch.float32, packed=packed).scores(batch.to("cuda")).cpu().numpy()
+    assert np.abs(got - oracle_model.sigmoid_scores(want_logits).reshape(-1)).max() <= 1e-3
