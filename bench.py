@@ -205,8 +205,12 @@ def launch_work(name: str, meta: dict) -> tuple[str, float]:
         return "hbm", 2.0 * meta["rows"] * meta["cols"] * meta["esize"]
     if name == "add_gathered_rows":  # in place: read + write of the matrix + the ids; the small tables are served by the L2
         return "hbm", 2.0 * meta["rows"] * meta["dim"] * meta["esize"] + 8.0 * meta["tables"] * meta["rows"]
-    if name == "token_tail":         # one read, two writes of the matrix + the ids; the small tables are served by the L2
-        return "hbm", 3.0 * meta["rows"] * meta["cols"] * meta["esize"] + 8.0 * meta["tables"] * meta["rows"]
+    if name == "token_tail":
+        # one read and one write of the matrix, the write of the (possibly compacted) first output, the ids and, with
+        # row selection, one int32 per row; the small tables are served by the L2
+        row_bytes = meta["cols"] * meta["esize"]
+        select = 4.0 * meta["rows"] if meta["rows_out"] != meta["rows"] else 0.0
+        return "hbm", row_bytes * (2.0 * meta["rows"] + meta["rows_out"]) + 8.0 * meta["tables"] * meta["rows"] + select
     if name == "scatter_rows":
         return "hbm", 3.0 * meta["rows"] * meta["dim"] * meta["esize"] + 8.0 * meta["rows"]
     if name in ("rms_norm", "layer_norm"):

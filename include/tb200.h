@@ -99,6 +99,19 @@ int tb200_token_tail_fwd(const void* x, const void* ln_gamma, const void* ln_bet
                          const void* rms_gamma, void* tokens, void* normed, int64_t rows, int32_t cols, float ln_eps,
                          float rms_eps, int dtype, void* stream);
 
+/* `tb200_token_tail_fwd` with the pyramid's row selection of the first block folded in: `normed` still
+ * receives every row (the block projects keys and values from all of them), but `tokens` is written in
+ * compacted form, tokens[row_dst[r], :] = row r for 0 <= row_dst[r] < rows_out, and rows with any other
+ * `row_dst` are not written at all.  That is `tokens = tokens[:, -next_len:, :]` of
+ * `OneTransBlock.forward`'s caller (experiments/onetrans/model.py:176-180) applied to the residual stream before it is stored instead of
+ * after.  row_dst: device int32[rows] or NULL (then identical to `tb200_token_tail_fwd`); tokens:
+ * [rows_out, cols]. */
+int tb200_token_tail_select_fwd(const void* x, const void* ln_gamma, const void* ln_beta, const void* table_a,
+                                int64_t rows_a, const int64_t* ids_a, const void* table_b, int64_t rows_b,
+                                const int64_t* ids_b, const void* rms_gamma, const int32_t* row_dst, int64_t rows_out,
+                                void* tokens, void* normed, int64_t rows, int32_t cols, float ln_eps, float rms_eps,
+                                int dtype, void* stream);
+
 /* ---- (a) sparse-field embedding gather / pool ---------------------------------------------
  * out[b, :] = mean over hot h of table[ids[b, h], :] for ids in (0, vocab_rows); ids equal to 0
  * (padding) or outside the table are skipped; an empty bag gives zeros.  fp32 sum in hot order,

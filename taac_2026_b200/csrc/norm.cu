@@ -53,12 +53,38 @@ template <typename T>
 __device__ __forceinline__ float round_to(float v) {
     return to_float<T>(from_float<T>(v));
 }
+// The same two operations on a pair of values (same bits as the scalar forms, fewer instructions).
+template <typename T>
+__device__ __forceinline__ float2 silu_pair(float2 x) {
+    if (sizeof(T) == 4) return make_float2(silu_f<T>(x.x), silu_f<T>(x.y));
+    const float2 h = __fmul2_rn(x, make_float2(0.5f, 0.5f));
+    float2 t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(h.x));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(h.y));
+    return __ffma2_rn(h, t, h);
+}
+template <typename T>
+__device__ __forceinline__ float2 round_pair(float2 v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ float2 round_pair<__nv_bfloat16>(float2 v) {
+    const __nv_bfloat162 h = __float22bfloat162_rn(v);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+template <>
+__device__ __forceinline__ float2 round_pair<__half>(float2 v) {
+    return __half22float2(__float22half2_rn(v));
+}
 
 // Optional stage behind the normalisation (POST): the normalised row, rounded to T, receives one or two
 // gathered table rows (each sum rounded to T, like tensor additions), is written to y, and is then
 // RMS-normalised with a second weight vector into a second output.  This is the end of the sequence tokenizer
 // and the first norm of the first block in one pass over the token matrix:
 //   tokens = LayerNorm(SiLU(x)) + time_rows + position_rows;   normed = RMSNorm(tokens)
+// With `row_dst` the first output is compacted: row r goes to y[row_dst[r]] when 0 <= row_dst[r] < rows_out and is
+// not written at all otherwise, while `normed` still covers every row.
 struct PostArgs {
     const void* table_a;
     const int64_t* ids_a;
@@ -69,9 +95,11 @@ struct PostArgs {
     const void* gamma2;
     void* normed;
     float eps2;
+    const int32_t* row_dst;   // may be nullptr
+    int64_t rows_out;
 };
 
-template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST = false>
+template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST, bool EXACT>
 __global__ void __launch_bounds__(kMaxThreads, 3)
 norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                 int64_t rows, int cols, float eps, int lanes_per_row, int* __restrict__ status, const PostArgs post) {
@@ -140,6 +168,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     const int group = lane / G;
     const int lane_g = lane % G;
     const float inv_cols = 1.0f / static_cast<float>(cols);
+    const bool compact = POST && post.row_dst != nullptr;
 
     for (int64_t it = 0; it < n_my; ++it) {
         const int s = static_cast<int>(it % kStages);
@@ -154,24 +183,36 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 
         // POST: the table rows of this tile are requested into the L1 now, so that the loads behind the
         // normalisation find them there instead of waiting for the L2 one row at a time
-        int64_t id_a[RU], id_b[RU];
+        //
+        // A lane group whose row lies behind the end of a ragged last tile works on the tile's last row once more:
+        // it reads, computes and writes the same values as that row's own group, which keeps every predicate on
+        // rows out of the code below.
+        int32_t id_a[RU], id_b[RU];   // clamped into tables of fewer than 2^31 rows
+        int32_t dst[RU];
+        int rr[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
             id_a[u] = id_b[u] = 0;
-            if (POST && u * ng + group < rows_here) {
-                const int64_t row = row_begin + it * tile_rows + u * ng + group;
+            dst[u] = -1;
+            rr[u] = min(u * ng + group, rows_here - 1);
+            if (POST) {
+                const int64_t row = row_begin + it * tile_rows + rr[u];
+                if (compact) {
+                    const int32_t d = post.row_dst[row];
+                    dst[u] = (d >= 0 && d < post.rows_out) ? d : -1;
+                }
                 int64_t ia = post.ids_a[row];
-                id_a[u] = ia < 0 ? 0 : (ia > post.rows_a - 1 ? post.rows_a - 1 : ia);
+                id_a[u] = static_cast<int32_t>(ia < 0 ? 0 : (ia > post.rows_a - 1 ? post.rows_a - 1 : ia));
                 if (post.table_b != nullptr) {
                     int64_t ib = post.ids_b[row];
-                    id_b[u] = ib < 0 ? 0 : (ib > post.rows_b - 1 ? post.rows_b - 1 : ib);
+                    id_b[u] = static_cast<int32_t>(ib < 0 ? 0 : (ib > post.rows_b - 1 ? post.rows_b - 1 : ib));
                 }
 #pragma unroll
                 for (int j = 0; j < CPL; ++j) {
                     const int c = lane_g + j * G;
-                    if (c < chunks) {
-                        prefetch_l1(reinterpret_cast<const uint4*>(post.table_a) + id_a[u] * chunks + c);
-                        if (post.table_b != nullptr) prefetch_l1(reinterpret_cast<const uint4*>(post.table_b) + id_b[u] * chunks + c);
+                    if (EXACT || c < chunks) {
+                        prefetch_l1(reinterpret_cast<const uint4*>(post.table_a) + static_cast<int64_t>(id_a[u]) * chunks + c);
+                        if (post.table_b != nullptr) prefetch_l1(reinterpret_cast<const uint4*>(post.table_b) + static_cast<int64_t>(id_b[u]) * chunks + c);
                     }
                 }
             }
@@ -181,17 +222,14 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
         float2 v[RU][CPL][N / 2];
         float sum[RU];
         float sq[RU];
-        bool valid[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
-            const int r = u * ng + group;
-            valid[u] = r < rows_here;
-            const uint4* rowp = tile + static_cast<size_t>(valid[u] ? r : 0) * chunks;
+            const uint4* rowp = tile + static_cast<size_t>(rr[u]) * chunks;
             float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
                 const int c = lane_g + j * G;
-                if (valid[u] && c < chunks) {
+                if (EXACT || c < chunks) {
                     Vec16<T>::unpack2(rowp[c], v[u][j]);
                     if (PRE == kPreBias) {
 #pragma unroll
@@ -203,8 +241,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                     }
                     if (PRE == kPreSilu) {
 #pragma unroll
-                        for (int e = 0; e < N / 2; ++e)
-                            v[u][j][e] = make_float2(round_to<T>(silu_f<T>(v[u][j][e].x)), round_to<T>(silu_f<T>(v[u][j][e].y)));
+                        for (int e = 0; e < N / 2; ++e) v[u][j][e] = round_pair<T>(silu_pair<T>(v[u][j][e]));
                     }
                 } else {
 #pragma unroll
@@ -232,7 +269,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 #pragma unroll
                 for (int j = 0; j < CPL; ++j) {
                     const int c = lane_g + j * G;
-                    if (c < chunks) {
+                    if (EXACT || c < chunks) {
 #pragma unroll
                         for (int e = 0; e < N / 2; ++e) {
                             v[u][j][e] = __fadd2_rn(v[u][j][e], nmean);  // keep the centred value
@@ -247,6 +284,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 #pragma unroll
             for (int u = 0; u < RU; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
         }
+        __syncwarp();   // every lane has read its rows before any lane overwrites the tile (duplicated rows included)
         float2 inv[RU];
 #pragma unroll
         for (int u = 0; u < RU; ++u) {
@@ -256,7 +294,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 #pragma unroll
         for (int j = 0; j < CPL; ++j) {
             const int c = lane_g + j * G;
-            if (c < chunks) {
+            if (EXACT || c < chunks) {
                 float2 g[N / 2];
                 float2 b[N / 2];
 #pragma unroll
@@ -272,7 +310,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                 }
 #pragma unroll
                 for (int u = 0; u < RU; ++u) {
-                    if (valid[u]) {
+                    {
                         float2 o[N / 2];
 #pragma unroll
                         for (int e = 0; e < N / 2; ++e) {
@@ -281,22 +319,16 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                         }
                         uint4 packed = Vec16<T>::pack2(o);
                         if (POST) {
-                            float2 t[N / 2];
-                            Vec16<T>::unpack2(packed, o);   // the normalised row as T stores it
-                            Vec16<T>::unpack2(ld_nc_u4(reinterpret_cast<const uint4*>(post.table_a) + id_a[u] * chunks + c), t);
-#pragma unroll
-                            for (int e = 0; e < N / 2; ++e) o[e] = __fadd2_rn(o[e], t[e]);
-                            packed = Vec16<T>::pack2(o);
-                            if (post.table_b != nullptr) {
-                                Vec16<T>::unpack2(packed, o);
-                                Vec16<T>::unpack2(ld_nc_u4(reinterpret_cast<const uint4*>(post.table_b) + id_b[u] * chunks + c), t);
-#pragma unroll
-                                for (int e = 0; e < N / 2; ++e) o[e] = __fadd2_rn(o[e], t[e]);
-                                packed = Vec16<T>::pack2(o);
-                            }
+                            // each sum rounded to T like a tensor addition: the native packed add of the 16-bit types
+                            // gives those bits directly (fp32 holds more than twice their precision plus two bits, so
+                            // rounding the fp32 sum again changes nothing)
+                            packed = Vec16<T>::add_rn(packed, ld_nc_u4(reinterpret_cast<const uint4*>(post.table_a) + static_cast<int64_t>(id_a[u]) * chunks + c));
+                            if (post.table_b != nullptr)
+                                packed = Vec16<T>::add_rn(packed, ld_nc_u4(reinterpret_cast<const uint4*>(post.table_b) + static_cast<int64_t>(id_b[u]) * chunks + c));
                             Vec16<T>::unpack2(packed, v[u][j]);   // keep the row for the second normalisation
                         }
-                        tile[static_cast<size_t>(u * ng + group) * chunks + c] = packed;
+                        if (!compact) tile[static_cast<size_t>(rr[u]) * chunks + c] = packed;
+                        else if (dst[u] >= 0) reinterpret_cast<uint4*>(y)[static_cast<int64_t>(dst[u]) * chunks + c] = packed;
                     }
                 }
             }
@@ -306,10 +338,10 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
                 float2 acc = make_float2(0.f, 0.f);
-                if (valid[u]) {
+                {
 #pragma unroll
                     for (int j = 0; j < CPL; ++j) {
-                        if (lane_g + j * G < chunks) {
+                        if (EXACT || lane_g + j * G < chunks) {
 #pragma unroll
                             for (int e = 0; e < N / 2; ++e) acc = __ffma2_rn(v[u][j][e], v[u][j][e], acc);
                         }
@@ -324,7 +356,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
 #pragma unroll
             for (int j = 0; j < CPL; ++j) {
                 const int c = lane_g + j * G;
-                if (c < chunks) {
+                if (EXACT || c < chunks) {
                     float2 g2[N / 2];
 #pragma unroll
                     for (int e = 0; e < N / 2; e += 2) {
@@ -334,13 +366,13 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                     }
 #pragma unroll
                     for (int u = 0; u < RU; ++u) {
-                        if (valid[u]) {
+                        {
                             const float i2 = rsqrtf(sq2[u] * inv_cols + post.eps2);
                             const float2 inv2 = make_float2(i2, i2);
                             float2 o[N / 2];
 #pragma unroll
                             for (int e = 0; e < N / 2; ++e) o[e] = __fmul2_rn(__fmul2_rn(v[u][j][e], inv2), g2[e]);
-                            const int64_t row = row_begin + it * tile_rows + u * ng + group;
+                            const int64_t row = row_begin + it * tile_rows + rr[u];
                             reinterpret_cast<uint4*>(post.normed)[row * chunks + c] = Vec16<T>::pack2(o);
                         }
                     }
@@ -351,9 +383,11 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-            bulk_store(reinterpret_cast<uint8_t*>(y) + (row_begin + it * tile_rows) * row_bytes, tile,
-                       static_cast<uint32_t>(rows_here) * row_bytes);
-            bulk_commit();
+            if (!compact) {
+                bulk_store(reinterpret_cast<uint8_t*>(y) + (row_begin + it * tile_rows) * row_bytes, tile,
+                           static_cast<uint32_t>(rows_here) * row_bytes);
+                bulk_commit();
+            }
             // The stage stored one iteration ago is free once its store has read shared memory.
             if (it >= 1 && it - 1 + kStages < n_my) {
                 bulk_wait_read<1>();
@@ -407,9 +441,9 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     }
 }
 
-template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST = false>
-int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
-               int lanes_per_row, cudaStream_t stream, const PostArgs post = PostArgs{}) {
+template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST, bool EXACT>
+int launch_tma_exact(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
+                     int lanes_per_row, cudaStream_t stream, const PostArgs post) {
     const int N = Vec16<T>::N;
     const int chunks = cols / N;
     const int row_bytes = chunks * 16;
@@ -419,7 +453,7 @@ int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int6
     const DeviceInfo& dev = device_info();
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
-        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU, PRE, POST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(norm_tma_kernel<T, LAYER, CPL, RU, PRE, POST, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024);
         attr_set[dev.index] = true;
     }
@@ -430,11 +464,20 @@ int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int6
     const int64_t useful = (rows + static_cast<int64_t>(tile_rows) * kWarps - 1) / (static_cast<int64_t>(tile_rows) * kWarps);
     if (grid > useful) grid = useful;
     if (grid < 1) grid = 1;
-    norm_tma_kernel<T, LAYER, CPL, RU, PRE, POST><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
+    norm_tma_kernel<T, LAYER, CPL, RU, PRE, POST, EXACT><<<static_cast<unsigned>(grid), kMaxThreads, smem, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
         cols, eps, lanes_per_row, nullptr, post);
     count_launch();
     return launch_status();
+}
+
+// EXACT: the lanes of a row group cover the row's 16-byte pieces exactly, so no lane ever idles.
+template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST = false>
+int launch_tma(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
+               int lanes_per_row, cudaStream_t stream, const PostArgs post = PostArgs{}) {
+    if (cols / Vec16<T>::N == CPL * lanes_per_row)
+        return launch_tma_exact<T, LAYER, CPL, RU, PRE, POST, true>(x, gamma, beta, y, rows, cols, eps, lanes_per_row, stream, post);
+    return launch_tma_exact<T, LAYER, CPL, RU, PRE, POST, false>(x, gamma, beta, y, rows, cols, eps, lanes_per_row, stream, post);
 }
 
 template <typename T, bool LAYER, int PRE>
@@ -524,18 +567,23 @@ extern "C" int tb200_layernorm_silu_fwd(const void* x, const void* gamma, const 
     return tb200::norm_entry<true, tb200::kPreSilu>(x, gamma, beta, y, rows, cols, eps, dtype, stream);
 }
 
-extern "C" int tb200_token_tail_fwd(const void* x, const void* ln_gamma, const void* ln_beta, const void* table_a,
-                                    int64_t rows_a, const int64_t* ids_a, const void* table_b, int64_t rows_b,
-                                    const int64_t* ids_b, const void* rms_gamma, void* tokens, void* normed,
-                                    int64_t rows, int32_t cols, float ln_eps, float rms_eps, int dtype, void* stream) {
+extern "C" int tb200_token_tail_select_fwd(const void* x, const void* ln_gamma, const void* ln_beta,
+                                           const void* table_a, int64_t rows_a, const int64_t* ids_a,
+                                           const void* table_b, int64_t rows_b, const int64_t* ids_b,
+                                           const void* rms_gamma, const int32_t* row_dst, int64_t rows_out,
+                                           void* tokens, void* normed, int64_t rows, int32_t cols, float ln_eps,
+                                           float rms_eps, int dtype, void* stream) {
     using namespace tb200;
     if (rows < 0 || cols < 1 || rows_a < 1 || (table_b != nullptr && rows_b < 1)) return TB200_ERR_SHAPE;
+    if (rows_a > INT32_MAX || (table_b != nullptr && rows_b > INT32_MAX)) return TB200_ERR_UNSUPPORTED;
+    if (row_dst != nullptr && (rows_out < 0 || rows_out > INT32_MAX)) return TB200_ERR_SHAPE;
     if (rows == 0) return TB200_OK;
     if (x == nullptr || ln_gamma == nullptr || ln_beta == nullptr || table_a == nullptr || ids_a == nullptr ||
-        (table_b != nullptr && ids_b == nullptr) || rms_gamma == nullptr || tokens == nullptr || normed == nullptr)
+        (table_b != nullptr && ids_b == nullptr) || rms_gamma == nullptr || normed == nullptr ||
+        (tokens == nullptr && !(row_dst != nullptr && rows_out == 0)))
         return TB200_ERR_NULL;
     if (!device_info().valid) return TB200_ERR_DEVICE;
-    PostArgs post{table_a, ids_a, rows_a, table_b, ids_b, rows_b, rms_gamma, normed, rms_eps};
+    PostArgs post{table_a, ids_a, rows_a, table_b, ids_b, rows_b, rms_gamma, normed, rms_eps, row_dst, rows_out};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case TB200_F32: return token_tail_dispatch<float>(x, ln_gamma, ln_beta, tokens, rows, cols, ln_eps, post, s);
@@ -543,4 +591,12 @@ extern "C" int tb200_token_tail_fwd(const void* x, const void* ln_gamma, const v
         case TB200_BF16: return token_tail_dispatch<__nv_bfloat16>(x, ln_gamma, ln_beta, tokens, rows, cols, ln_eps, post, s);
         default: return TB200_ERR_DTYPE;
     }
+}
+
+extern "C" int tb200_token_tail_fwd(const void* x, const void* ln_gamma, const void* ln_beta, const void* table_a,
+                                    int64_t rows_a, const int64_t* ids_a, const void* table_b, int64_t rows_b,
+                                    const int64_t* ids_b, const void* rms_gamma, void* tokens, void* normed,
+                                    int64_t rows, int32_t cols, float ln_eps, float rms_eps, int dtype, void* stream) {
+    return tb200_token_tail_select_fwd(x, ln_gamma, ln_beta, table_a, rows_a, ids_a, table_b, rows_b, ids_b, rms_gamma,
+                                       nullptr, 0, tokens, normed, rows, cols, ln_eps, rms_eps, dtype, stream);
 }

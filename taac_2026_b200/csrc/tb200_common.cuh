@@ -62,6 +62,13 @@ struct Vec16<float> {
         return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x),
                           __float_as_uint(f[1].y));
     }
+    // element-wise a + b, rounded to the element type
+    __device__ static uint4 add_rn(const uint4& a, const uint4& b) {
+        return make_uint4(__float_as_uint(__fadd_rn(__uint_as_float(a.x), __uint_as_float(b.x))),
+                          __float_as_uint(__fadd_rn(__uint_as_float(a.y), __uint_as_float(b.y))),
+                          __float_as_uint(__fadd_rn(__uint_as_float(a.z), __uint_as_float(b.z))),
+                          __float_as_uint(__fadd_rn(__uint_as_float(a.w), __uint_as_float(b.w))));
+    }
 };
 
 template <>
@@ -96,6 +103,17 @@ struct Vec16<__nv_bfloat16> {
         for (int i = 0; i < 4; ++i) {
             __nv_bfloat162 h = __float22bfloat162_rn(f[i]);
             w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static uint4 add_rn(const uint4& a, const uint4& b) {
+        const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&x[i]),
+                                                *reinterpret_cast<const __nv_bfloat162*>(&y[i]));
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -134,6 +152,16 @@ struct Vec16<__half> {
         for (int i = 0; i < 4; ++i) {
             __half2 h = __float22half2_rn(f[i]);
             w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static uint4 add_rn(const uint4& a, const uint4& b) {
+        const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = __hadd2_rn(*reinterpret_cast<const __half2*>(&x[i]), *reinterpret_cast<const __half2*>(&y[i]));
+            w[i] = *reinterpret_cast<const uint32_t*>(&h);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }

@@ -640,8 +640,29 @@ class OneTransInference:
             buckets_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, buckets.long())
             rows_a, rows_b = (self._p(prefix + ".time_embedding.weight"), buckets_full), (pos_table, pos_full)
         first_norm_w = self._p(self.blocks[0]["p"] + ".attn_norm.weight") if self.blocks else None
-        if first_norm_w is not None and projected.shape[1] % (16 // projected.element_size()) == 0:
-            tokens, x_first = ops.token_tail(projected, ln_w, ln_b, rows_a[0], rows_a[1], rows_b[0], rows_b[1], first_norm_w)
+        ns_off = torch.arange(ns, device=dev)[None, :]
+
+        def kept_rows(layer: int) -> tuple[torch.Tensor, torch.Tensor]:
+            """Rows of layer ``layer`` that the pyramid keeps for the next one (in the next layer's order) and
+            the NS rows [B, ns] of the next layer."""
+            owner = torch.repeat_interleave(arange_b, rows[layer + 1], output_size=totals[layer + 1])
+            r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]
+            src = cu[layer][owner] + (counts[layer] - counts[layer + 1])[owner] + r
+            return src, (cu[layer + 1][:-1] + counts[layer + 1])[:, None] + ns_off
+
+        # When the first block is evaluated for the kept rows only, its residual stream is needed for those rows
+        # alone: the fused pass then writes `tokens` already compacted and only `x_first` at full height.
+        first_kept = None
+        fused_tail = first_norm_w is not None and projected.shape[1] % (16 // projected.element_size()) == 0
+        if fused_tail and self.select_early and widths[1] < widths[0] and not (ns > 0 and max_rows[0] == ns) \
+                and totals[1] < 2**31:
+            first_kept = kept_rows(0)
+            row_dst = torch.full((total0,), -1, dtype=torch.int32, device=dev)
+            row_dst[first_kept[0]] = torch.arange(totals[1], dtype=torch.int32, device=dev)
+        if fused_tail:
+            tokens, x_first = ops.token_tail(projected, ln_w, ln_b, rows_a[0], rows_a[1], rows_b[0], rows_b[1], first_norm_w,
+                                             row_dst=None if first_kept is None else row_dst,
+                                             rows_out=None if first_kept is None else totals[1])
         else:
             tokens = ops.layer_norm(projected, ln_w, ln_b, 1e-5, pre_silu=True)
             ops.add_gathered_rows(tokens, rows_a[0], rows_a[1], rows_b[0], rows_b[1])
@@ -649,10 +670,9 @@ class OneTransInference:
 
         # ---- the NS tokens take the rows left for them: [seq rows of b | ns rows of b]
         ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
-        ns_off = torch.arange(ns, device=dev)[None, :]
         ns_rows = (cu[0][:-1] + counts[0])[:, None] + ns_off                       # [B, ns]
         ns_flat = ns_tokens.reshape(batch * ns, self.d).contiguous()
-        ops.scatter_rows(tokens, ns_rows.reshape(-1), ns_flat)
+        ops.scatter_rows(tokens, (ns_rows if first_kept is None else first_kept[1]).reshape(-1), ns_flat)
         if x_first is not None:   # the fused pass normalised placeholder rows there
             ops.scatter_rows(x_first, ns_rows.reshape(-1), ops.rms_norm(ns_flat, first_norm_w, 1e-6))
 
@@ -675,11 +695,7 @@ class OneTransInference:
                 # projected for every row, but queries, the attention rows, the output projection, the residual,
                 # the norm and the FFN only for the rows that survive: the same rows, bit for bit in exact
                 # arithmetic, as "whole block, then selection", without the work whose result would be dropped.
-                new_rows = rows[layer + 1]
-                owner = torch.repeat_interleave(arange_b, new_rows, output_size=totals[layer + 1])
-                r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]
-                src = cu[layer][owner] + (counts[layer] - counts[layer + 1])[owner] + r
-                next_ns_rows = (cu[layer + 1][:-1] + counts[layer + 1])[:, None] + ns_off
+                src, next_ns_rows = first_kept if (layer == 0 and first_kept is not None) else kept_rows(layer)
                 next_flat_ns = next_ns_rows.t().reshape(-1)
                 w_qkv, b_qkv = self._p(p + ".attention.shared_qkv.weight"), self._p(p + ".attention.shared_qkv.bias")
                 kv = F.linear(x, w_qkv[d:], b_qkv[d:])                                              # [N, 2d]
@@ -693,7 +709,8 @@ class OneTransInference:
                 attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
                                             cu_rows_q=cu[layer + 1].to(torch.int32), max_rows_q=max_rows[layer + 1],
                                             kernel=min(self.attention_kernel, 1))
-                tokens = tokens.index_select(0, src)
+                if not (layer == 0 and first_kept is not None):   # else the tokenizer already wrote the kept rows only
+                    tokens = tokens.index_select(0, src)
                 ns_rows, flat_ns = next_ns_rows, next_flat_ns
             else:
                 qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
@@ -722,12 +739,8 @@ class OneTransInference:
             ops.scatter_rows(out, flat_ns, y_ns, bias=ns_b2, residual=tokens)   # tokens + b2 + FFN_ns(x)
             tokens = out
             if not selected and widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
-                new_rows = rows[layer + 1]
-                owner = torch.repeat_interleave(arange_b, new_rows, output_size=totals[layer + 1])
-                r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]
-                src = cu[layer][owner] + (counts[layer] - counts[layer + 1])[owner] + r
+                src, ns_rows = kept_rows(layer)
                 tokens = tokens.index_select(0, src)
-                ns_rows = (cu[layer + 1][:-1] + counts[layer + 1])[:, None] + ns_off
 
         last = len(widths) - 1
         tokens = ops.rms_norm(tokens, self._p("final_norm.weight"), 1e-6).float()

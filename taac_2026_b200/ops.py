@@ -1004,11 +1004,15 @@ def add_gathered_rows(x: torch.Tensor, table_a: torch.Tensor, ids_a: torch.Tenso
 
 def token_tail(x: torch.Tensor, ln_weight: torch.Tensor, ln_bias: torch.Tensor, table_a: torch.Tensor,
                ids_a: torch.Tensor, table_b: torch.Tensor | None, ids_b: torch.Tensor | None,
-               rms_weight: torch.Tensor, *, ln_eps: float = 1e-5, rms_eps: float = 1e-6) -> tuple[torch.Tensor, torch.Tensor]:
+               rms_weight: torch.Tensor, *, ln_eps: float = 1e-5, rms_eps: float = 1e-6,
+               row_dst: torch.Tensor | None = None, rows_out: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """``tokens = layer_norm(silu(x)) + table_a[ids_a] (+ table_b[ids_b])`` and ``rms_norm(tokens)`` in one pass.
 
     Returns ``(tokens, normed)``, both new ``[rows, cols]`` tensors of x's dtype; the values equal
-    ``layer_norm(..., pre_silu=True)`` -> ``add_gathered_rows`` -> ``rms_norm`` run one after the other."""
+    ``layer_norm(..., pre_silu=True)`` -> ``add_gathered_rows`` -> ``rms_norm`` run one after the other.
+    With ``row_dst`` (int32 per row) ``tokens`` is ``[rows_out, cols]`` and holds row r at ``row_dst[r]`` when
+    that lies in ``[0, rows_out)``; the other rows only appear in ``normed``.  Destinations nothing maps to
+    stay uninitialised."""
     _require_backend("token_tail", "cuda")
     _require_cuda_tensors("cuda token_tail", x, ln_weight, ln_bias, table_a, ids_a, table_b, ids_b, rms_weight)
     if x.ndim != 2 or not x.is_contiguous() or not cuda_supported_floating_dtype(x.dtype):
@@ -1026,13 +1030,20 @@ def token_tail(x: torch.Tensor, ln_weight: torch.Tensor, ln_bias: torch.Tensor, 
     vecs = [v.to(device=x.device, dtype=x.dtype).contiguous() for v in (ln_weight, ln_bias, rms_weight)]
     if any(tuple(v.shape) != (cols,) for v in vecs):
         raise ValueError("token_tail weight vectors must have one entry per column")
-    tokens, normed = torch.empty_like(x), torch.empty_like(x)
+    if row_dst is not None:
+        _require_cuda_tensors("cuda token_tail", row_dst)
+        if row_dst.dtype != torch.int32 or row_dst.numel() != rows or not row_dst.is_contiguous():
+            raise ValueError("token_tail row_dst must be contiguous int32 with one entry per row of x")
+        if rows_out is None or rows_out < 0:
+            raise ValueError("token_tail: row_dst needs rows_out")
+    n_out = rows if row_dst is None else int(rows_out)
+    tokens, normed = x.new_empty((n_out, cols)), torch.empty_like(x)
     with torch.cuda.device(x.device), _timed("token_tail", rows=rows, cols=cols, esize=x.element_size(),
-                                            tables=1 if table_b is None else 2):
-        code = _lib.load().tb200_token_tail_fwd(
+                                            tables=1 if table_b is None else 2, rows_out=n_out):
+        code = _lib.load().tb200_token_tail_select_fwd(
             _ptr(x), _ptr(vecs[0]), _ptr(vecs[1]), _ptr(table_a), table_a.shape[0], _ptr(ids_a), _ptr(table_b),
-            0 if table_b is None else table_b.shape[0], _ptr(ids_b), _ptr(vecs[2]), _ptr(tokens), _ptr(normed), rows, cols,
-            float(ln_eps), float(rms_eps), _DTYPE_CODES[x.dtype], _stream_ptr(),
+            0 if table_b is None else table_b.shape[0], _ptr(ids_b), _ptr(vecs[2]), _ptr(row_dst), n_out,
+            _ptr(tokens), _ptr(normed), rows, cols, float(ln_eps), float(rms_eps), _DTYPE_CODES[x.dtype], _stream_ptr(),
         )
     _lib.check(code, "cuda token_tail")
     return tokens, normed

@@ -168,6 +168,37 @@ def test_token_tail_equals_the_separate_kernels(dtype, cols, two):
     assert torch.equal(normed, want_normed)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("cols", [64, 128, 512, 1024])
+def test_token_tail_with_row_selection(dtype, cols):
+    """With `row_dst` the first output only holds the selected rows, at their destinations, and the second
+    output still holds every row; both bit for bit what the unselected call gives."""
+    g = torch.Generator().manual_seed(cols + 1)
+    rows = 2051
+    x = (1.5 * torch.randn(rows, cols, generator=g)).to(dtype).cuda()
+    w1 = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).cuda()
+    b1 = (0.1 * torch.randn(cols, generator=g)).to(dtype).cuda()
+    w2 = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).cuda()
+    ta = torch.randn(65, cols, generator=g).to(dtype).cuda()
+    tb = torch.randn(300, cols, generator=g).to(dtype).cuda()
+    ia = torch.randint(0, 65, (rows,), generator=g).cuda()
+    ib = torch.randint(0, 300, (rows,), generator=g).cuda()
+    want_tokens, want_normed = ops.token_tail(x, w1, b1, ta, ia, tb, ib, w2)
+    kept = torch.randperm(rows, generator=g)[:301].cuda()          # destination i <- row kept[i], any order
+    row_dst = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    row_dst[kept] = torch.arange(kept.numel(), dtype=torch.int32, device="cuda")
+    row_dst[(row_dst < 0).nonzero()[:5, 0]] = torch.tensor([kept.numel(), 2**31 - 1, -7, kept.numel() + 3, -2**31],
+                                                           dtype=torch.int32, device="cuda")   # all skipped
+    tokens, normed = ops.token_tail(x, w1, b1, ta, ia, tb, ib, w2, row_dst=row_dst, rows_out=kept.numel())
+    assert tokens.shape == (kept.numel(), cols)
+    assert torch.equal(tokens, want_tokens[kept])
+    assert torch.equal(normed, want_normed)
+    # nothing selected: no first output at all
+    none = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    tokens, normed = ops.token_tail(x, w1, b1, ta, ia, tb, ib, w2, row_dst=none, rows_out=0)
+    assert tokens.shape == (0, cols) and torch.equal(normed, want_normed)
+
+
 def test_token_tail_rejects_rows_it_cannot_stage():
     """Rows that are not whole 16-byte pieces (or wider than 256 pieces) have no fused kernel: the call fails
     loudly instead of running something else."""
