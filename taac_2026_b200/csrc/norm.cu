@@ -110,9 +110,12 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int chunks = cols / N;  // 16-byte chunks per row
+    // A row wider than one piece per lane always takes the whole warp, and with EXACT its width is then known at
+    // compile time as well: every offset below becomes an immediate and the shuffle loops unroll.
+    constexpr bool kWholeWarp = CPL > 1;
+    const int chunks = (kWholeWarp && EXACT) ? CPL * 32 : cols / N;  // 16-byte chunks per row
     const uint32_t row_bytes = static_cast<uint32_t>(chunks) * 16u;
-    const int G = lanes_per_row;
+    const int G = kWholeWarp ? 32 : lanes_per_row;
     const int ng = 32 / G;           // rows handled side by side by one warp instruction
     const int tile_rows = ng * RU;   // rows per tile
     const uint32_t tile_bytes = row_bytes * static_cast<uint32_t>(tile_rows);
@@ -127,25 +130,26 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     const int64_t w = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
     const int64_t row_begin = (w * rows) / n_warps;
     const int64_t row_end = ((w + 1) * rows) / n_warps;
-    const int64_t n_my = (row_end - row_begin + tile_rows - 1) / tile_rows;
+    const int my_rows = static_cast<int>(row_end - row_begin);   // a warp's span is far below 2^31 rows
+    const int n_my = (my_rows + tile_rows - 1) / tile_rows;
 
-    auto rows_in = [&](int64_t it) -> int {
-        const int64_t left = row_end - (row_begin + it * tile_rows);
-        return left < tile_rows ? static_cast<int>(left) : tile_rows;
+    auto rows_in = [&](int it) -> int {
+        const int left = my_rows - it * tile_rows;
+        return left < tile_rows ? left : tile_rows;
     };
-    auto issue_load = [&](int64_t it) {
-        const int s = static_cast<int>(it % kStages);
+    auto issue_load = [&](int it) {
+        const int s = it % kStages;
         const uint32_t bytes = static_cast<uint32_t>(rows_in(it)) * row_bytes;
         mbar_expect_tx(&full_bar[warp][s], bytes);
         bulk_load(ring + static_cast<size_t>(s) * tile_bytes,
-                  reinterpret_cast<const uint8_t*>(x) + (row_begin + it * tile_rows) * row_bytes, bytes,
+                  reinterpret_cast<const uint8_t*>(x) + (row_begin + static_cast<int64_t>(it) * tile_rows) * row_bytes, bytes,
                   &full_bar[warp][s]);
     };
 
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[warp][s], 1);
         fence_mbar_init();
-        for (int64_t it = 0; it < n_my && it < kStages; ++it) issue_load(it);
+        for (int it = 0; it < n_my && it < kStages; ++it) issue_load(it);
     }
     for (int c = tid; c < chunks; c += kMaxThreads) {
         float2 f[N / 2];
@@ -170,9 +174,10 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     const float inv_cols = 1.0f / static_cast<float>(cols);
     const bool compact = POST && post.row_dst != nullptr;
 
-    for (int64_t it = 0; it < n_my; ++it) {
-        const int s = static_cast<int>(it % kStages);
+    for (int it = 0; it < n_my; ++it) {
+        const int s = it % kStages;
         const uint32_t parity = static_cast<uint32_t>((it / kStages) & 1);
+        const int64_t tile_row0 = row_begin + static_cast<int64_t>(it) * tile_rows;
         const int rows_here = rows_in(it);
         uint4* tile = reinterpret_cast<uint4*>(ring + static_cast<size_t>(s) * tile_bytes);
         const bool ok = mbar_wait(&full_bar[warp][s], parity);
@@ -196,7 +201,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
             dst[u] = -1;
             rr[u] = min(u * ng + group, rows_here - 1);
             if (POST) {
-                const int64_t row = row_begin + it * tile_rows + rr[u];
+                const int64_t row = tile_row0 + rr[u];
                 if (compact) {
                     const int32_t d = post.row_dst[row];
                     dst[u] = (d >= 0 && d < post.rows_out) ? d : -1;
@@ -372,7 +377,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
                             float2 o[N / 2];
 #pragma unroll
                             for (int e = 0; e < N / 2; ++e) o[e] = __fmul2_rn(__fmul2_rn(v[u][j][e], inv2), g2[e]);
-                            const int64_t row = row_begin + it * tile_rows + rr[u];
+                            const int64_t row = tile_row0 + rr[u];
                             reinterpret_cast<uint4*>(post.normed)[row * chunks + c] = Vec16<T>::pack2(o);
                         }
                     }
@@ -384,7 +389,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
         __syncwarp();
         if (lane == 0) {
             if (!compact) {
-                bulk_store(reinterpret_cast<uint8_t*>(y) + (row_begin + it * tile_rows) * row_bytes, tile,
+                bulk_store(reinterpret_cast<uint8_t*>(y) + tile_row0 * row_bytes, tile,
                            static_cast<uint32_t>(rows_here) * row_bytes);
                 bulk_commit();
             }
