@@ -468,6 +468,12 @@ def run_e2e(args) -> None:
         return
 
     roofline, per_op = summarise_kernels(records, peaks, peak_kind)
+    if args.launch_log:
+        with open(args.launch_log, "w") as fh:
+            for name, meta, ev0, ev1 in records:
+                bound, work = launch_work(name, meta)
+                shape = {k: v for k, v in meta.items() if isinstance(v, (int, float, bool, str))}
+                fh.write(json.dumps({"name": name, "ms": round(ev0.elapsed_time(ev1), 4), "bound": bound, "work": work, **shape}) + "\n")
     total = batch_size * world
     value = total * args.steps / (ms_total * 1e-3)
     e2e_value = total * args.steps / (ms_e2e * 1e-3)
@@ -633,12 +639,18 @@ def run_attention_sweep(args) -> None:
 def run_kept_rows_attention(args) -> None:
     """Packed causal attention in which only the last rows of every sample are queries (`cu_rows_q`): the shape of
     a pyramid block evaluated for the rows it keeps.  Samples of 137..579 rows, 9 + U[0, 16] queries each, 8 heads,
-    head_dim 64, bf16.  Bound by the stream over K and V."""
+    head_dim 64, bf16 (`--kind kept`); or the first block's own rule (`--kind kept_pyramid`): samples of 137..604
+    rows whose queries are 9 rows plus every row beyond the 466th, so that most samples have 9 queries and a fifth
+    of them up to 147.  Bound by the stream over K and V."""
     peaks, peak_kind = load_peaks()
     B, H, D = args.batch or 4096, 8, 64
     g = torch.Generator(device="cuda").manual_seed(0)
-    lens = torch.randint(137, 580, (B,), generator=g, device="cuda")
-    keep = 9 + torch.randint(0, 17, (B,), generator=g, device="cuda")
+    if args.kind == "kept_pyramid":
+        lens = torch.randint(137, 605, (B,), generator=g, device="cuda")
+        keep = 9 + (lens - 466).clamp_min(0)
+    else:
+        lens = torch.randint(137, 580, (B,), generator=g, device="cuda")
+        keep = 9 + torch.randint(0, 17, (B,), generator=g, device="cuda")
     cu = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
     cu[1:] = torch.cumsum(lens, 0)
     cu_q = torch.zeros(B + 1, dtype=torch.int32, device="cuda")
@@ -647,7 +659,7 @@ def run_kept_rows_attention(args) -> None:
     kv = torch.randn(rows, 2, H, D, generator=g, device="cuda").div_(8).bfloat16()
     q = torch.randn(q_rows, H, D, generator=g, device="cuda").div_(8).bfloat16()
     fn = lambda: ops.varlen_attention(q, kv[:, 0], kv[:, 1], causal=True, cu_rows=cu, max_rows=int(lens.max()),  # noqa: E731
-                                      cu_rows_q=cu_q, max_rows_q=int(keep.max()))
+                                      cu_rows_q=cu_q, max_rows_q=int(keep.max()), kernel=args.kernel)
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
@@ -662,8 +674,8 @@ def run_kept_rows_attention(args) -> None:
     gbs = nbytes / ms / 1e6
     print(json.dumps({
         "metric": "kept_rows_attention_GBps", "value": round(gbs, 1), "unit": "GB/s",
-        "config": {"workload": f"{B} packed samples of 137..579 rows, 9..25 queries each, H{H} D{D} bf16, causal",
-                   "k_rows": rows, "q_rows": q_rows},
+        "config": {"workload": f"{B} packed samples of {int(lens.min())}..{int(lens.max())} rows, {int(keep.min())}..{int(keep.max())} "
+                               f"queries each, H{H} D{D} bf16, causal", "k_rows": rows, "q_rows": q_rows, "kernel": args.kernel},
         "ms_per_launch": round(ms, 3),
         "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peak_kind},
@@ -778,6 +790,7 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=0, help="per-GPU batch override")
     parser.add_argument("--micro-batch", type=int, default=0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--launch-log", default="", help="write every recorded launch of the timing pass (name, ms, shape) to this file")
     parser.add_argument("--profile", action="store_true",
                         help="run --warmup untimed and --steps plain steps of the main workload and exit (for ncu)")
     parser.add_argument("--ffn", choices=["fp8", "bf16"], default="fp8", help="shared FFN of every block")
@@ -796,7 +809,7 @@ def main() -> None:
         else:
             run_norm_sweep(args)
     elif args.workload == "attention":
-        if args.kind == "kept":
+        if args.kind in ("kept", "kept_pyramid"):
             run_kept_rows_attention(args)
         else:
             run_attention_sweep(args)

@@ -198,14 +198,16 @@ int tb200_bias_act_rows(void* x, int64_t rows, int32_t cols, const void* bias, i
  * sample b's lq = cu_rows_q[b+1] - cu_rows_q[b] queries are the LAST lq of its lk rows, so the causal rule
  * becomes k <= q + (lk - lq).  This is the block of OneTrans's pyramid (experiments/onetrans/model.py:340-348
  * keeps `sequence_part[:, -keep_count:]` after the block) evaluated for the kept rows only; Lq then bounds
- * the query counts, Lk the key counts.  Served by the mma.sync kernel.
+ * the query counts, Lk the key counts.  Served by kernels 1, 3 and 4; the automatic choice is 3 up to 32
+ * rows and 4 beyond (D = 64), else 1.
  * key_valid: device uint8[B, Lk] or NULL; when given it replaces the (seq_len, ns_start) rule by
  * "key k is valid iff key_valid[b, k] != 0" for arbitrary padding patterns (several sequence domains
  * with separators, experiments/onetrans/model.py:287-315); padded queries are the invalid positions.
  * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.
  * kernel: 0 = automatic, 1 = mma.sync kernel (every supported shape), 2 = tcgen05/TMEM kernel (D = 64, bf16,
  * no key_valid map; TB200_ERR_UNSUPPORTED otherwise), 3 = one warp per (sample, head) (D = 64, at most 32
- * rows).  total_rows: row count of the packed matrices when
+ * rows), 4 = one warp per (sample, head) streaming the keys in tiles of 16 against 16 queries in registers
+ * (packed batches, D = 64: few queries, many keys).  total_rows: row count of the packed matrices when
  * cu_rows is given (bounds the TMA tensor maps), ignored otherwise.  status_word: optional device int32 that
  * the tcgen05 kernel sets to 1 if one of its bounded waits gave up. */
 int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,

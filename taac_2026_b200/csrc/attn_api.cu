@@ -8,6 +8,8 @@ bool attn_tc05_supported(const AttnArgs& a, int head_dim, int dtype);
 int attn_tc05_forward(const AttnArgs& a, int max_lq, int64_t total_rows, int32_t* status, cudaStream_t stream);
 bool attn_small_supported(const AttnArgs& a, int head_dim, int max_lq, int max_lk);
 bool attn_tiny_supported(const AttnArgs& a, int head_dim, int max_lq, int max_lk);
+bool attn_fewq_supported(const AttnArgs& a, int head_dim);
+int attn_fewq_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 int attn_tiny_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 int attn_small_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 }  // namespace tb200
@@ -47,16 +49,23 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     a.scale_log2 = scale * 1.4426950408889634f;
     if (cu_rows != nullptr && total_rows < 0) return TB200_ERR_SHAPE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // kernel: 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel, 3 = one-warp-per-(sample, head) kernel
+    // kernel: 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel, 3 = one-warp-per-(sample, head) kernel for
+    // samples of at most 32 rows, 4 = one-warp-per-(sample, head) kernel for few queries against many keys
     const bool tc_ok = attn_tc05_supported(a, D, dtype) && (cu_rows == nullptr || total_rows > 0);
     if (kernel == 2 && !tc_ok) return TB200_ERR_UNSUPPORTED;
-    if (kernel < 0 || kernel > 3) return TB200_ERR_UNSUPPORTED;
-    if (cu_rows_q != nullptr) {   // separate query rows: the mma.sync kernel
-        if (kernel > 1) return TB200_ERR_UNSUPPORTED;
-        return attn_mma_forward(a, D, dtype, Lq, s);
-    }
+    if (kernel < 0 || kernel > 4) return TB200_ERR_UNSUPPORTED;
+    const bool fewq_ok = attn_fewq_supported(a, D);
+    if (kernel == 4) return fewq_ok ? attn_fewq_forward(a, dtype, s) : TB200_ERR_UNSUPPORTED;
     const bool small_ok = attn_small_supported(a, D, Lq, Lk);
     if (kernel == 3 && !small_ok) return TB200_ERR_UNSUPPORTED;
+    if (cu_rows_q != nullptr) {
+        // separate query rows: the scalar kernel up to 32 rows; beyond that the queries are by construction the few
+        // rows a caller kept of long samples, which is the streaming kernel's case (the mma.sync kernel on request)
+        if (kernel == 2) return TB200_ERR_UNSUPPORTED;
+        if (kernel == 3 || (kernel == 0 && small_ok)) return attn_small_forward(a, dtype, s);
+        if (kernel == 0 && fewq_ok) return attn_fewq_forward(a, dtype, s);
+        return attn_mma_forward(a, D, dtype, Lq, s);
+    }
     // samples of at most 32 rows (the non-sequence tokens alone, late in the pyramid): no tensor-core tile pays
     if (kernel == 3 || (kernel == 0 && small_ok)) {
         // up to 16 rows the whole sample is one tensor-core tile per head; 17..32 rows take the scalar kernel

@@ -485,6 +485,210 @@ attn_tiny_kernel(const AttnArgs a) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Packed samples with FEW queries against many keys (head_dim 64): after the pyramid has chosen the rows it
+// keeps, a sample's queries are its last handful of rows, while its keys are all of them.  A 64-row query tile
+// is then almost empty and the launch is a stream over K and V.  Here one warp owns a (sample, head): its 16
+// query rows live in registers as MMA fragments, the keys and values pass through a private ring of 16-row
+// tiles filled by cp.async (no block-wide barrier anywhere), and every tile is 8 MMAs for Q K^T, an online
+// softmax in registers and 8 MMAs for P V.  Samples with more than 16 queries take their query tiles one after
+// the other in the same warp.  Masks: packed batches only (every key valid), causal aligned at the end when
+// the queries have their own offsets.
+// ------------------------------------------------------------------------------------------------
+constexpr int kFqWarps = 4;
+constexpr int kFqStages = 3;
+constexpr int kFqRows = 16;    // keys per tile = queries per tile
+
+template <typename T>
+__global__ void __launch_bounds__(kFqWarps * 32, 4)
+attn_fewq_kernel(const AttnArgs a) {
+    constexpr int D = 64;
+    constexpr int CH = D / 8;
+    extern __shared__ __align__(128) uint8_t fq_smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int mi = lane >> 3;
+    const int64_t pair = static_cast<int64_t>(blockIdx.x) * kFqWarps + warp;
+    if (pair >= static_cast<int64_t>(a.B) * a.H) return;
+    const int b = static_cast<int>(pair / a.H);
+    const int h_own = static_cast<int>(pair - static_cast<int64_t>(b) * a.H);
+
+    const int64_t row_base = a.cu_rows[b];
+    const int lk = a.cu_rows[b + 1] - static_cast<int32_t>(row_base);
+    int64_t q_base = row_base;
+    int lq = lk;
+    if (a.cu_rows_q != nullptr) {
+        q_base = a.cu_rows_q[b];
+        lq = a.cu_rows_q[b + 1] - static_cast<int32_t>(q_base);
+    }
+    if (lq <= 0 || lk <= 0) return;   // uniform over the warp
+    const int off = max(lk - lq, 0);
+    const bool causal = a.causal != 0;
+    // this warp's ring: kFqStages x (K tile, V tile) of 16 rows x 64
+    T* ring = reinterpret_cast<T*>(fq_smem) + static_cast<size_t>(warp) * kFqStages * 2 * kFqRows * D;
+
+    // Work split.  A sample of at most 16 queries: warp w owns head w of the block's heads and its only query tile.
+    // A sample with more: when the block's warps all belong to one sample (H a multiple of the warps per
+    // block), they go through its heads together, warp w taking query tiles w, w + 4, ...; the warps then read
+    // the same keys and values at about the same time, so all but one of them are served by the L2 instead of
+    // re-reading a long sample from HBM once per query tile.
+    const bool together = lq > kFqRows && a.H % kFqWarps == 0;
+    const int h_first = together ? h_own - warp : h_own;
+    const int n_heads = together ? kFqWarps : 1;
+    const int r_first = together ? warp * kFqRows : 0;
+    const int r_step = together ? kFqWarps * kFqRows : kFqRows;
+
+    for (int hh = 0; hh < n_heads; ++hh) {
+    const int h = h_first + hh;
+    const T* q = static_cast<const T*>(a.q) + q_base * a.q_sl + static_cast<int64_t>(h) * a.q_sh;
+    const T* k = static_cast<const T*>(a.k) + row_base * a.k_sl + static_cast<int64_t>(h) * a.k_sh;
+    const T* v = static_cast<const T*>(a.v) + row_base * a.v_sl + static_cast<int64_t>(h) * a.v_sh;
+    T* o = static_cast<T*>(a.o) + q_base * a.o_sl + static_cast<int64_t>(h) * a.o_sh;
+    auto issue = [&](int tile) {   // rows [16 tile, 16 tile + 16) of K and V; rows past the sample are zero
+        T* sK = ring + static_cast<size_t>(tile % kFqStages) * 2 * kFqRows * D;
+        T* sV = sK + kFqRows * D;
+#pragma unroll
+        for (int i = lane; i < kFqRows * CH; i += 32) {
+            const int r = i / CH;
+            const int c = i - r * CH;
+            const int row = tile * kFqRows + r;
+            const bool ok = row < lk;
+            cp_async16(sK + swz<D>(r, c), k + static_cast<int64_t>(ok ? row : 0) * a.k_sl + c * 8, ok);
+            cp_async16(sV + swz<D>(r, c), v + static_cast<int64_t>(ok ? row : 0) * a.v_sl + c * 8, ok);
+        }
+    };
+
+    for (int r0 = r_first; r0 < lq; r0 += r_step) {
+        // keys the tile's last existing query can see
+        const int q_last = min(r0 + kFqRows, lq) - 1;
+        const int kv_end = causal ? min(lk, q_last + off + 1) : lk;
+        const int n_tiles = (kv_end + kFqRows - 1) / kFqRows;
+#pragma unroll
+        for (int s0 = 0; s0 < kFqStages - 1; ++s0) {
+            if (s0 < n_tiles) issue(s0);
+            cp_async_commit();
+        }
+        // Q fragments straight from global memory: rows r0 + g and r0 + g + 8, columns 16 kk + 2 t (+ 8)
+        uint32_t qf[D / 16][4];
+        {
+            const bool ok0 = r0 + g < lq, ok1 = r0 + g + 8 < lq;
+            const T* q0 = q + static_cast<int64_t>(ok0 ? r0 + g : 0) * a.q_sl + 2 * t;
+            const T* q1 = q + static_cast<int64_t>(ok1 ? r0 + g + 8 : 0) * a.q_sl + 2 * t;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                qf[kk][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16) : 0u;
+                qf[kk][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16) : 0u;
+                qf[kk][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8) : 0u;
+                qf[kk][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8) : 0u;
+            }
+        }
+        float acc[D / 8][4];
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+        float m_run[2] = {-INFINITY, -INFINITY};   // running maxima of rows g, g + 8 (raw scores)
+        float l_run[2] = {0.f, 0.f};               // this lane's share of the running sums
+
+        for (int jt = 0; jt < n_tiles; ++jt) {
+            if (jt + kFqStages - 1 < n_tiles) issue(jt + kFqStages - 1);
+            cp_async_commit();
+            cp_async_wait<kFqStages - 1>();
+            __syncwarp();
+            const T* sK = ring + static_cast<size_t>(jt % kFqStages) * 2 * kFqRows * D;
+            const T* sV = sK + kFqRows * D;
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t kb[4];
+                ldsm_x4(kb, sK + swz<D>((mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)));
+                mma16816<T>(s[0], qf[kk], kb[0], kb[1]);
+                mma16816<T>(s[1], qf[kk], kb[2], kb[3]);
+            }
+            const int c0 = jt * kFqRows;
+            // only the tiles on the causal edge and the sample's last tile hold keys a query must not see
+            const bool edge = (causal && c0 + kFqRows - 1 > r0 + off) || c0 + kFqRows > lk;
+            float p_scale[2];
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                const int rg = r0 + g + 8 * hr + off;   // the query's position among the keys
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int c = c0 + j * 8 + 2 * t + e;
+                        if (edge && (c >= lk || (causal && c > rg))) s[j][2 * hr + e] = -INFINITY;
+                        mx = fmaxf(mx, s[j][2 * hr + e]);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run[hr], mx);
+                const float ms = (m_new == -INFINITY ? 0.f : m_new) * a.scale_log2;
+                const float corr = exp2f(m_run[hr] * a.scale_log2 - ms);   // first tile: exp2(-inf) = 0
+                m_run[hr] = m_new;
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float p = exp2f(s[j][2 * hr + e] * a.scale_log2 - ms);
+                        s[j][2 * hr + e] = p;
+                        sum += p;
+                    }
+                l_run[hr] = l_run[hr] * corr + sum;
+                p_scale[hr] = corr;
+            }
+            if (__any_sync(0xffffffffu, p_scale[0] != 1.f || p_scale[1] != 1.f)) {
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j) {
+                    acc[j][0] *= p_scale[0];
+                    acc[j][1] *= p_scale[0];
+                    acc[j][2] *= p_scale[1];
+                    acc[j][3] *= p_scale[1];
+                }
+            }
+            uint32_t pa[4];
+            pa[0] = pack2<T>(s[0][0], s[0][1]);
+            pa[1] = pack2<T>(s[0][2], s[0][3]);
+            pa[2] = pack2<T>(s[1][0], s[1][1]);
+            pa[3] = pack2<T>(s[1][2], s[1][3]);
+#pragma unroll
+            for (int jp = 0; jp < D / 16; ++jp) {
+                uint32_t vb[4];
+                ldsm_x4_t(vb, sV + swz<D>((mi & 1) * 8 + (lane & 7), jp * 2 + (mi >> 1)));
+                mma16816<T>(acc[2 * jp], pa, vb[0], vb[1]);
+                mma16816<T>(acc[2 * jp + 1], pa, vb[2], vb[3]);
+            }
+            __syncwarp();   // the stage is free for the copy issued at the top of the next iteration
+        }
+        cp_async_wait<0>();   // nothing of this query tile is in flight when the next one restarts the ring
+        __syncwarp();
+
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            float l = l_run[hr];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const int r = r0 + g + 8 * hr;
+            if (r < lq) {
+                T* orow = o + static_cast<int64_t>(r) * a.o_sl + 2 * t;
+#pragma unroll
+                for (int j = 0; j < D / 8; ++j)
+                    *reinterpret_cast<uint32_t*>(orow + j * 8) = pack2<T>(acc[j][2 * hr] * inv, acc[j][2 * hr + 1] * inv);
+            }
+        }
+    }
+    }   // heads
+}
+
 template <typename T, int D>
 int launch(const AttnArgs& a, int max_lq, cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(kBM + 2 * kKvStages * kBN) * D * sizeof(T);
@@ -514,6 +718,35 @@ int attn_tiny_forward(const AttnArgs& a, int dtype, cudaStream_t stream) {
     if (grid > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
     if (dtype == TB200_BF16) attn_tiny_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), kTinyWarps * 32, 0, stream>>>(a);
     else attn_tiny_kernel<__half><<<static_cast<unsigned>(grid), kTinyWarps * 32, 0, stream>>>(a);
+    count_launch();
+    return launch_status();
+}
+
+// Packed samples with few queries each (head_dim 64, no key_valid map, 4-byte aligned rows): one warp per
+// (sample, head) streams the keys and values.
+bool attn_fewq_supported(const AttnArgs& a, int head_dim) {
+    auto even = [](int64_t x) { return (x & 1) == 0; };
+    return head_dim == 64 && a.cu_rows != nullptr && a.key_valid == nullptr && a.padded_query_self == 0 &&
+           even(a.q_sl) && even(a.q_sh) && even(a.o_sl) && even(a.o_sh) &&
+           (reinterpret_cast<uintptr_t>(a.q) & 3) == 0 && (reinterpret_cast<uintptr_t>(a.o) & 3) == 0;
+}
+int attn_fewq_forward(const AttnArgs& a, int dtype, cudaStream_t stream) {
+    const int64_t pairs = static_cast<int64_t>(a.B) * a.H;
+    const int64_t grid = (pairs + kFqWarps - 1) / kFqWarps;
+    if (grid > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (grid == 0) return TB200_OK;
+    const size_t smem = static_cast<size_t>(kFqWarps) * kFqStages * 2 * kFqRows * 64 * 2;
+    const DeviceInfo& dev = device_info();
+    static bool attr_set[64] = {};
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(attn_fewq_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaFuncSetAttribute(attn_fewq_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaFuncSetAttribute(attn_fewq_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        cudaFuncSetAttribute(attn_fewq_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        attr_set[dev.index] = true;
+    }
+    if (dtype == TB200_BF16) attn_fewq_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), kFqWarps * 32, smem, stream>>>(a);
+    else attn_fewq_kernel<__half><<<static_cast<unsigned>(grid), kFqWarps * 32, smem, stream>>>(a);
     count_launch();
     return launch_status();
 }

@@ -49,21 +49,27 @@ attn_small_kernel(const AttnArgs a) {
 
     const bool packed = a.cu_rows != nullptr;
     int lq = a.Lq, lk = a.Lk;
-    int64_t row_base = 0;
+    int64_t row_base = 0, q_base = 0;
     if (packed) {
         row_base = a.cu_rows[b];
         lq = lk = a.cu_rows[b + 1] - static_cast<int32_t>(row_base);
+        q_base = row_base;
+        if (a.cu_rows_q != nullptr) {   // q and o hold the sample's last lq rows only, packed by their own offsets
+            q_base = a.cu_rows_q[b];
+            lq = a.cu_rows_q[b + 1] - static_cast<int32_t>(q_base);
+        }
     }
     lq = min(lq, kRows);
-    lk = min(lk, kRows);
+    lk = min(lk, kMaxL);
+    const int off = (packed && a.cu_rows_q != nullptr) ? max(lk - lq, 0) : 0;   // position of query 0 among the keys
     const int valid_len = (a.seq_len != nullptr && !packed) ? min(max(a.seq_len[b], 0), lk) : lk;
     const int ns_start = packed ? lk : min(a.ns_start, lk);
     const bool causal = a.causal != 0;
 
-    const T* qp = static_cast<const T*>(a.q) + (packed ? row_base * a.q_sl : static_cast<int64_t>(b) * a.q_sb) + static_cast<int64_t>(h) * a.q_sh;
+    const T* qp = static_cast<const T*>(a.q) + (packed ? q_base * a.q_sl : static_cast<int64_t>(b) * a.q_sb) + static_cast<int64_t>(h) * a.q_sh;
     const T* kp = static_cast<const T*>(a.k) + (packed ? row_base * a.k_sl : static_cast<int64_t>(b) * a.k_sb) + static_cast<int64_t>(h) * a.k_sh;
     const T* vp = static_cast<const T*>(a.v) + (packed ? row_base * a.v_sl : static_cast<int64_t>(b) * a.v_sb) + static_cast<int64_t>(h) * a.v_sh;
-    T* op = static_cast<T*>(a.o) + (packed ? row_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) + static_cast<int64_t>(h) * a.o_sh;
+    T* op = static_cast<T*>(a.o) + (packed ? q_base * a.o_sl : static_cast<int64_t>(b) * a.o_sb) + static_cast<int64_t>(h) * a.o_sh;
 
     // stage K and V with asynchronous 16-byte copies (piece lane % 8 of rows lane / 8, lane / 8 + 4, ...): all of
     // them are in flight together with the load of the query row, instead of one round trip per four rows
@@ -80,7 +86,8 @@ attn_small_kernel(const AttnArgs a) {
     const int part = lane % P;        // which 64 / P dimensions of the row it holds
     const uint32_t group_mask = (P == 1 ? 1u : ((1u << P) - 1u)) << (lane & ~(P - 1));
     const bool active = r < lq;
-    const bool self_row = active && a.padded_query_self && r >= valid_len && r < ns_start;
+    const int rg = r + off;           // its position in the sample
+    const bool self_row = active && a.padded_query_self && rg >= valid_len && rg < ns_start;
     uint4 qraw[CPL];
     if (active && !self_row) {
 #pragma unroll
@@ -92,7 +99,7 @@ attn_small_kernel(const AttnArgs a) {
     __syncwarp();
     if (!active) return;
     if (self_row) {   // padded query: its own value row
-        const uint4* src = reinterpret_cast<const uint4*>(vp + static_cast<int64_t>(r) * a.v_sl);
+        const uint4* src = reinterpret_cast<const uint4*>(vp + static_cast<int64_t>(rg) * a.v_sl);
         uint4* dst = reinterpret_cast<uint4*>(op + static_cast<int64_t>(r) * a.o_sl);
 #pragma unroll
         for (int c = 0; c < CPL; ++c) dst[part * CPL + c] = src[part * CPL + c];
@@ -111,9 +118,9 @@ attn_small_kernel(const AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < CPL * 4; ++i) acc[i] = make_float2(0.f, 0.f);
     float m = -INFINITY, l = 0.f;
-    const int k_end = causal ? min(lk, r + 1) : lk;
+    const int k_end = causal ? min(lk, rg + 1) : lk;
     for (int j = 0; j < k_end; ++j) {
-        if (!attn_visible(r, j, valid_len, ns_start, lk, causal)) continue;   // same decision in the whole group
+        if (!attn_visible(rg, j, valid_len, ns_start, lk, causal)) continue;   // same decision in the whole group
         float2 dot = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < CPL; ++c) {
@@ -154,7 +161,8 @@ attn_small_kernel(const AttnArgs a) {
 
 template <typename T>
 void launch_small(const AttnArgs& a, int64_t grid, cudaStream_t stream) {
-    const int longest = a.Lq > a.Lk ? a.Lq : a.Lk;   // upper bound of any sample's rows
+    // upper bound of the query rows a warp serves (the keys always fit: kMaxL rows of shared memory per warp)
+    const int longest = a.cu_rows_q != nullptr ? a.Lq : (a.Lq > a.Lk ? a.Lq : a.Lk);
     const unsigned g = static_cast<unsigned>(grid);
     if (longest <= kMaxL / 4) attn_small_kernel<T, 4><<<g, kWarps * 32, 0, stream>>>(a);
     else if (longest <= kMaxL / 2) attn_small_kernel<T, 2><<<g, kWarps * 32, 0, stream>>>(a);

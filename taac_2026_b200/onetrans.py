@@ -708,7 +708,7 @@ class OneTransInference:
                     q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
                 attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
                                             cu_rows_q=cu[layer + 1].to(torch.int32), max_rows_q=max_rows[layer + 1],
-                                            kernel=min(self.attention_kernel, 1))
+                                            kernel=self.attention_kernel if self.attention_kernel in (0, 1, 4) else 0)
                 if not (layer == 0 and first_kept is not None):   # else the tokenizer already wrote the kept rows only
                     tokens = tokens.index_select(0, src)
                 ns_rows, flat_ns = next_ns_rows, next_flat_ns

@@ -564,17 +564,20 @@ def _strided_ok(t: torch.Tensor) -> bool:
     return t.stride(-1) == 1 and all(s % 8 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
 
 
-def _attention_record_name(kernel: int, dtype: torch.dtype, dim: int, lq: int, lk: int, has_key_valid: bool) -> str:
+def _attention_record_name(kernel: int, dtype: torch.dtype, dim: int, lq: int, lk: int, has_key_valid: bool,
+                           separate_queries: bool = False) -> str:
     """Name of the timing record: which of the three kernels ``tb200_attn_fwd`` picks (same rule as its
     automatic choice), so that a benchmark can attribute time to each of them."""
     if kernel == 0:
         if dim == 64 and not has_key_valid and lq <= 32 and lk <= 32:
             kernel = 3
+        elif separate_queries:
+            kernel = 4 if dim == 64 else 1
         elif dim == 64 and dtype == torch.bfloat16 and not has_key_valid and lq >= 128:
             kernel = 2
         else:
             kernel = 1
-    return {1: "attention_mma", 2: "attention_tc05", 3: "attention_small"}.get(int(kernel), "attention")
+    return {1: "attention_mma", 2: "attention_tc05", 3: "attention_small", 4: "attention_fewq"}.get(int(kernel), "attention")
 
 
 def varlen_attention(
@@ -607,7 +610,9 @@ def varlen_attention(
     ``q``, any strides whose rows are 16-byte aligned (e.g. a token-major buffer viewed sample-major).
 
     ``kernel``: 0 picks automatically (the tcgen05/TMEM kernel for head_dim 64 bf16 with at least 128
-    rows, the mma.sync kernel otherwise), 1 / 2 force one of them.  ``check=True`` reads the tcgen05
+    rows, the one-warp kernels for samples of at most 32 rows and for ``cu_rows_q`` batches, the mma.sync kernel
+    otherwise); 1 = mma.sync, 2 = tcgen05, 3 = short samples, 4 = few queries against many keys force one of
+    them.  ``check=True`` reads the tcgen05
     kernel's status word back (one sync) and raises if a bounded wait inside it gave up.
 
     ``key_valid`` (bool / uint8 [B, Lk]) replaces ``seq_len`` / ``ns_start`` for padding patterns that
@@ -676,7 +681,7 @@ def varlen_attention(
         scale = 1.0 / math.sqrt(dim)
     stride_arr = (ctypes.c_int64 * 12)(*strides)
     status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
-    with torch.cuda.device(q.device), _timed(_attention_record_name(1 if cu_q is not None else kernel, q.dtype, dim, lq, lk, kv is not None),
+    with torch.cuda.device(q.device), _timed(_attention_record_name(kernel, q.dtype, dim, lq, lk, kv is not None, cu_q is not None),
                                              seq_len=lens, cu_rows=cu, cu_rows_q=cu_q, key_valid=kv, batch=batch, heads=heads,
                                              lq=lq, lk=lk, dim=dim, ns_start=lk if ns_start is None else int(ns_start),
                                              causal=bool(causal), self_rows=bool(padded_query_self), esize=q.element_size()):

@@ -244,9 +244,79 @@ def test_packed_queries_are_the_last_rows_of_each_sample(causal):
     assert got.shape == q_kept.shape
     want = full.index_select(0, sel)
     assert (got.float() - want.float()).abs().max().item() <= 4e-3
-    with pytest.raises(RuntimeError):   # only the mma.sync kernel serves separate query rows
+    for kernel in (1, 4):   # the automatic choice above is the streaming kernel; both named ones agree as well
+        named = ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()),
+                                     cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()), kernel=kernel)
+        assert (named.float() - want.float()).abs().max().item() <= 4e-3
+    # without separate query rows the streaming kernel computes the whole packed batch
+    whole = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(),
+                                 max_rows=int(lens.max()), kernel=4)
+    assert (whole.float() - full.float()).abs().max().item() <= 4e-3
+    with pytest.raises(RuntimeError):   # the tcgen05 kernel does not serve separate query rows
         ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()),
                              cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()), kernel=2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("max_keep", [4, 9, 16, 32])
+def test_packed_queries_of_short_samples_take_the_small_kernel(causal, max_keep):
+    """Samples of at most 32 rows with separate query rows: the one-warp kernel (explicitly and by the automatic
+    choice) against the mma.sync kernel."""
+    g = torch.Generator().manual_seed(max_keep)
+    B, H, D = 37, 3, 64
+    lens = torch.randint(1, 33, (B,), generator=g)
+    lens[0], lens[1] = 32, 17
+    keep = torch.minimum(torch.randint(0, max_keep + 1, (B,), generator=g), lens)
+    keep[0], keep[1] = max_keep, min(9, max_keep)
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    cu_q = torch.zeros(B + 1, dtype=torch.int32)
+    cu_q[1:] = torch.cumsum(keep, 0)
+    qkv = (torch.randn(int(cu[-1]), 3, H, D, generator=g) * 0.5).bfloat16().cuda()
+    sel = torch.cat([torch.arange(int(cu[b + 1]) - int(keep[b]), int(cu[b + 1])) for b in range(B)]).cuda()
+    q_kept = qkv[:, 0].index_select(0, sel).contiguous()
+    kw = dict(causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()), cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()))
+    ref = ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], kernel=1, **kw).float()
+    small = ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], kernel=3, **kw).float()
+    auto = ops.varlen_attention(q_kept, qkv[:, 1], qkv[:, 2], kernel=0, **kw).float()
+    assert (small - ref).abs().max().item() <= 1e-2
+    assert torch.equal(auto, small)
+    full = ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(), max_rows=int(lens.max()),
+                                kernel=3).float()
+    assert (small - full.index_select(0, sel)).abs().max().item() <= 4e-3   # the same rows of the full computation
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_streaming_kernel_on_views_of_a_fused_projection(dtype):
+    """Kernel 4 with k / v as column slices of one [rows, 2 d] matrix and q from its own matrix, ragged key
+    counts around the 16-row tile edges, against the fp32 oracle of the selected rows."""
+    g = torch.Generator().manual_seed(5)
+    H, D = 8, 64
+    lens = torch.tensor([1, 15, 16, 17, 31, 32, 33, 48, 100, 257, 9, 2])
+    keep = torch.tensor([1, 9, 16, 17, 9, 1, 20, 48, 9, 40, 0, 2])
+    B = lens.numel()
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    cu_q = torch.zeros(B + 1, dtype=torch.int32)
+    cu_q[1:] = torch.cumsum(keep, 0)
+    kv = (torch.randn(int(cu[-1]), 2 * H * D, generator=g) * 0.5).to(dtype).cuda()
+    q = (torch.randn(int(cu_q[-1]), H * D, generator=g) * 0.5).to(dtype).cuda()
+    k3, v3 = kv[:, : H * D].unflatten(-1, (H, D)), kv[:, H * D :].unflatten(-1, (H, D))
+    got = ops.varlen_attention(q.unflatten(-1, (H, D)), k3, v3, causal=True, cu_rows=cu.cuda(), max_rows=int(lens.max()),
+                               cu_rows_q=cu_q.cuda(), max_rows_q=int(keep.max()), kernel=4).float()
+    scale = D ** -0.5
+    for b in range(B):
+        lk, lq = int(lens[b]), int(keep[b])
+        if lq == 0:
+            continue
+        kb = k3[int(cu[b]) : int(cu[b + 1])].float().transpose(0, 1)      # [H, lk, D]
+        vb = v3[int(cu[b]) : int(cu[b + 1])].float().transpose(0, 1)
+        qb = q.unflatten(-1, (H, D))[int(cu_q[b]) : int(cu_q[b + 1])].float().transpose(0, 1)
+        s = qb @ kb.transpose(1, 2) * scale
+        pos = torch.arange(lq, device="cuda")[:, None] + (lk - lq)
+        s = s.masked_fill(torch.arange(lk, device="cuda")[None, :] > pos, float("-inf"))
+        want = (torch.softmax(s, -1) @ vb).transpose(0, 1)
+        assert (got[int(cu_q[b]) : int(cu_q[b + 1])] - want).abs().max().item() <= 2e-2, b
 
 
 def test_random_shapes_against_the_oracle():
