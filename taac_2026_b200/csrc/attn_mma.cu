@@ -495,6 +495,12 @@ attn_tiny_kernel(const AttnArgs a) {
 // the other in the same warp.  Masks: packed batches only (every key valid), causal aligned at the end when
 // the queries have their own offsets.
 // ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float fq_ex2(float x) {   // 2^x, -inf -> 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 constexpr int kFqWarps = 4;
 constexpr int kFqStages = 3;
 constexpr int kFqRows = 16;    // keys per tile = queries per tile
@@ -631,14 +637,14 @@ attn_fewq_kernel(const AttnArgs a) {
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m_run[hr], mx);
                 const float ms = (m_new == -INFINITY ? 0.f : m_new) * a.scale_log2;
-                const float corr = exp2f(m_run[hr] * a.scale_log2 - ms);   // first tile: exp2(-inf) = 0
+                const float corr = fq_ex2(m_run[hr] * a.scale_log2 - ms);   // first tile: exp2(-inf) = 0
                 m_run[hr] = m_new;
                 float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const float p = exp2f(s[j][2 * hr + e] * a.scale_log2 - ms);
+                        const float p = fq_ex2(s[j][2 * hr + e] * a.scale_log2 - ms);
                         s[j][2 * hr + e] = p;
                         sum += p;
                     }
