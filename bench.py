@@ -216,6 +216,8 @@ def launch_work(name: str, meta: dict) -> tuple[str, float]:
     if name in ("rms_norm", "layer_norm"):
         extra = meta["cols"] * meta["esize"] * (2 if name == "layer_norm" else 1)
         return "hbm", 2.0 * meta["rows"] * meta["cols"] * meta["esize"] + extra
+    if name == "gemm_bf16":
+        return "tensor", 2.0 * meta["groups"] * meta["m"] * meta["n"] * meta["k"]
     if name.startswith("fp8_gemm"):
         return "tensor_fp8", 2.0 * meta["m"] * meta["n"] * meta["k"]
     if name == "quant_act":
@@ -780,6 +782,53 @@ def run_ffn_sweep(args) -> None:
         }), flush=True)
 
 
+def run_grouped_gemm_sweep(args) -> None:
+    """The per-token layers of 9 non-sequence tokens x 8192 samples at d_model 512: this library's grouped GEMM
+    with the epilogue inside against the library batched GEMM followed by the separate passes it needs."""
+    peaks, peak_kind = load_peaks()
+    groups, rows = 9, args.rows or 8192
+    g = torch.Generator(device="cuda").manual_seed(0)
+    cases = [("qkv projection + bias", 1536, 512, False, False), ("FFN up + bias + SiLU", 2048, 512, True, False),
+             ("FFN down + bias + residual", 512, 2048, False, True)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def time_ms(fn) -> float:
+        for _ in range(3):
+            fn()
+        total = 0.0
+        for _ in range(args.steps):
+            flush.zero_()                      # 256 MB > L2: operands start in HBM
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            total += start.elapsed_time(end)
+        return total / args.steps
+
+    for name, n, k, silu, with_res in cases:
+        x = torch.randn(groups, rows, k, generator=g, device="cuda").bfloat16()
+        w = (torch.randn(groups, n, k, generator=g, device="cuda") * k ** -0.5).bfloat16()
+        w_t = w.transpose(1, 2).contiguous()
+        bias = torch.randn(groups, n, generator=g, device="cuda")
+        bias_b = bias.bfloat16().unsqueeze(1)
+        res = torch.randn(groups, rows, n, generator=g, device="cuda").bfloat16() if with_res else None
+        ours = lambda: ops.grouped_linear(x, w, bias, silu=silu, residual=res)   # noqa: E731
+        if with_res:
+            lib = lambda: ops.bias_act_rows(torch.baddbmm(res, x, w_t), bias_b, silu=False)   # noqa: E731
+        else:
+            lib = lambda: ops.bias_act_rows(torch.bmm(x, w_t), bias_b, silu=silu)   # noqa: E731
+        ms, ms_lib, ms_bmm = time_ms(ours), time_ms(lib), time_ms(lambda: torch.bmm(x, w_t))
+        tf = 2.0 * groups * rows * n * k / ms / 1e9
+        print(json.dumps({
+            "metric": "grouped_linear_TFLOPs", "value": round(tf, 1), "unit": "TFLOP/s",
+            "config": {"workload": f"{groups} groups x {rows} rows, {k} -> {n}, bf16, {name}", "l2": "256 MB flush between launches"},
+            "ms_per_launch": round(ms, 4), "library_bmm_plus_epilogue_ms": round(ms_lib, 4), "library_bmm_alone_ms": round(ms_bmm, 4),
+            "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": round(tf / peaks["bf16_tflops"], 4), "peak_source": peak_kind},
+        }), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -816,7 +865,10 @@ def main() -> None:
     elif args.workload == "gather":
         run_gather_sweep(args)
     elif args.workload == "ffn":
-        run_ffn_sweep(args)
+        if args.kind == "grouped":
+            run_grouped_gemm_sweep(args)
+        else:
+            run_ffn_sweep(args)
     else:
         run_e2e(args)
 

@@ -255,6 +255,20 @@ int tb200_sequence_prepare(const int64_t* values, const int64_t* lengths, const 
                            const int64_t* request_ts, int64_t batch, int32_t n_feat, int32_t max_len,
                            int64_t* out_len, int32_t* out_src, float* out_stats, void* stream);
 
+/* ---- per-token (grouped) bf16 linear layers with a fused epilogue ----------------------------
+ * out[g] = act(a[g] @ w[g]^T + bias[g]) (+ residual[g]) for g in [0, groups): the token-specific projections
+ * and feed-forward layers of the non-sequence tokens, `nn.ModuleList` of `nn.Linear` / `FeedForward` applied
+ * token by token (experiments/onetrans/model.py:137-147 `_ns_linear`, :160-166 the `ns_specific` FFNs), which
+ * a batched library GEMM plus separate bias / SiLU / residual passes would otherwise serve.
+ * a: [groups, M, K], w: [groups, N, K] (stacked `nn.Linear.weight`), out and residual: [groups, M, N], all
+ * bf16 and contiguous; bias: fp32 [groups, N]; bias and residual may be NULL; residual may be `out` itself.
+ * act: 0 = none, 1 = SiLU.  fp32 accumulation over the whole K, one rounding to bf16 at the end.
+ * N % 256 == 0, K % 64 == 0.  groups = 1 is a plain linear layer.  status_word: optional device int32 that the
+ * kernel sets to 1 if one of its bounded waits gave up (the output is then incomplete). */
+int tb200_gemm_bf16_grouped(const void* a, const void* w, const float* bias, const void* residual, void* out,
+                            int32_t groups, int64_t M, int32_t N, int32_t K, int32_t act, int32_t* status_word,
+                            void* stream);
+
 /* ---- whole FFN without any allocation --------------------------------------------------------
  * No counterpart in the reference (which has neither an FP8 path nor a C interface).
  *

@@ -1,0 +1,342 @@
+// Grouped bf16 GEMM with a fused epilogue for sm_100a:
+//     out[g] = act(a[g] x w[g]^T + bias[g]) (+ residual[g])        g = 0 .. groups - 1
+// a: [groups, M, K], w: [groups, N, K] (the layout of stacked `nn.Linear` weights), out / residual:
+// [groups, M, N], all bf16 and contiguous; bias: [groups, N] fp32.  These are the per-token projections and
+// feed-forward layers of the non-sequence tokens: every token has its own weights, so the batch of one token is
+// one group.  A library batched GEMM leaves the bias, the SiLU and the residual to further passes over the
+// result; here they ride in the epilogue, and the result is written once.
+//
+// One persistent CTA per SM walks the (group, row tile, column tile) list round-robin, column tiles fastest,
+// so that the CTAs working side by side share the activation rows.  Roles in a CTA of 320 threads:
+//   warp 0      TMA producer: ring of {A 128 x 64, W 256 x 64} bf16 tiles, 128-byte swizzle, 3 stages
+//   warp 1      MMA issuer (one lane): tcgen05.mma kind::f16 128 x 256 x 16, the whole K range of a tile
+//               accumulates in one of two 256-column TMEM buffers
+//   warps 2..9  epilogue: a thread owns one row and 128 columns of the tile, reads them from TMEM 16 at a
+//               time, adds the bias, applies the activation and writes bf16 into a 128-byte-swizzled staging
+//               tile that one thread hands to TMA (the residual tile arrives there by TMA as well, during the
+//               K loop); meanwhile the tensor cores fill the other TMEM buffer with the next tile.
+// Every wait on an mbarrier is bounded; a wait that gives up raises the status word and all roles drain out
+// through the final barrier, where the TMEM allocation is released.
+#include <cudaTypedefs.h>
+
+#include "tb200_common.cuh"
+#include "tb200_ptx.cuh"
+
+namespace tb200 {
+void count_launch();
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBKBytes = 128;            // 64 bf16 per stage: one 128-byte swizzle atom
+constexpr int kStages = 3;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
+constexpr uint32_t kABytes = kBM * kBKBytes;   // 16 KB
+constexpr uint32_t kBBytes = kBN * kBKBytes;   // 32 KB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kBoxBytes = kBM * 128;      // staging box: 128 rows x 64 bf16
+constexpr int kBoxes = kBN * 2 / 128;          // 4
+constexpr uint32_t kOutBytes = kBoxes * kBoxBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + kOutBytes + 1024;
+
+struct GArgs {
+    const float* bias;      // [groups, N] or nullptr
+    int32_t* status;
+    int32_t groups, N, K;
+    int64_t M;
+    int32_t act;            // 0 = none, 1 = SiLU
+    int32_t has_residual;
+};
+
+// silu(x) = h * tanh(h) + h, h = x / 2 (the result is rounded to bf16)
+__device__ __forceinline__ float2 silu2(float2 x) {
+    const float2 h = __fmul2_rn(x, make_float2(0.5f, 0.5f));
+    float2 t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(h.x));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(h.y));
+    return __ffma2_rn(h, t, h);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ CUtensorMap tmap_o, const __grid_constant__ CUtensorMap tmap_r, const GArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[kStages];
+    __shared__ uint64_t empty_bar[kStages];
+    __shared__ uint64_t res_full;
+    __shared__ uint64_t tmem_full[2];
+    __shared__ uint64_t tmem_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ __align__(16) float bias_s[kBN];
+    __shared__ int s_abort;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;
+    uint8_t* out_s = smem + static_cast<size_t>(kStages) * kStageBytes;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int64_t m_tiles = (g.M + kBM - 1) / kBM;
+    const int n_tiles = g.N / kBN;
+    const int k_blocks = g.K / (kBKBytes / 2);
+    const int64_t total = static_cast<int64_t>(g.groups) * m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&res_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], kEpiThreads);
+        }
+        s_abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    // tile t -> column tile (fastest), row tile, group
+    auto decode = [&](int64_t t, int& n0, int& m0, int& grp) {
+        const int n = static_cast<int>(t % n_tiles);
+        const int64_t rest = t / n_tiles;
+        n0 = n * kBN;
+        m0 = static_cast<int>(rest % m_tiles) * kBM;
+        grp = static_cast<int>(rest / m_tiles);
+    };
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_w);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                int n0, m0, grp;
+                decode(t, n0, m0, grp);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* dst = ring + static_cast<size_t>(s) * kStageBytes;
+                    mbar_expect_tx(&full_bar[s], kStageBytes);
+                    tma_load_3d(dst, &tmap_a, kb * kBKBytes, m0, grp, &full_bar[s]);
+                    tma_load_3d(dst + kABytes, &tmap_w, kb * kBKBytes, n0, grp, &full_bar[s]);
+                }
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (g.status != nullptr) atomicExch(g.status, 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(1, 1, 0, 0, kBM, kBN);   // bf16 x bf16 -> f32, both K-major
+            const uint64_t desc0 = umma_desc_sw128(0, 1024, 16);
+            const uint32_t ring_lo = (smem_u32(ring) & 0x3FFFFu) >> 4;
+            uint32_t s = 0, ph = 0, buf = 0, aph = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                if (!mbar_wait(&tmem_empty[buf], aph ^ 1)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + buf * kBN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_lo = ring_lo + s * (kStageBytes >> 4);
+                    const uint64_t da = desc0 + a_lo;
+                    const uint64_t db = desc0 + a_lo + (kABytes >> 4);
+#pragma unroll
+                    for (int k = 0; k < kBKBytes / 32; ++k) mma_f16_ss(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    tc_commit(&empty_bar[s]);
+                    if (++s == kStages) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(&tmem_full[buf]);
+                aph ^= buf;
+                buf ^= 1;
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (g.status != nullptr) atomicExch(g.status, 1);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int et = threadIdx.x - 64;          // 0..255
+        const int half = et >> 7;                 // columns [128 half, 128 half + 128) of the tile
+        const int quarter = warp & 3;             // TMEM lanes [32 quarter, +32) are visible to this warp
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const int swz = row_in_tile & 7;
+        uint32_t tile_count = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++tile_count) {
+            int n0, m0, grp;
+            decode(t, n0, m0, grp);
+            const uint32_t buf = tile_count & 1;
+            const uint32_t aph = (tile_count >> 1) & 1;
+            // the staging tile is free once the previous tile's store has read it; the residual tile then lands in
+            // it while the tensor cores work
+            if (et == 0) {
+                bulk_wait_read<0>();
+                if (g.has_residual) {
+                    mbar_expect_tx(&res_full, kOutBytes);
+#pragma unroll
+                    for (int b = 0; b < kBoxes; ++b) tma_load_3d(out_s + b * kBoxBytes, &tmap_r, 2 * n0 + b * 128, m0, grp, &res_full);
+                }
+            }
+            bias_s[et] = g.bias != nullptr ? g.bias[static_cast<int64_t>(grp) * g.N + n0 + et] : 0.f;
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            if (!mbar_wait(&tmem_full[buf], aph)) { ok = false; break; }
+            tc_fence_after_sync();
+            if (g.has_residual && !mbar_wait(&res_full, tile_count & 1)) { ok = false; break; }
+            const uint32_t t0 = tmem_base + buf * kBN + lane_addr + half * 128;
+#pragma unroll 1
+            for (int c = 0; c < 8; c += 2) {      // 32 columns per round: two x16 loads under one wait
+                uint32_t r[32];
+                tmem_ld_2x16(t0 + c * 16, r);
+                tc_wait_ld(r);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {     // four 16-byte pieces of 8 columns
+                    const int col = half * 128 + c * 16 + q * 8;
+                    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + col);
+                    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + col + 4);
+                    float2 v[4];
+                    v[0] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1])), make_float2(b0.x, b0.y));
+                    v[1] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3])), make_float2(b0.z, b0.w));
+                    v[2] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5])), make_float2(b1.x, b1.y));
+                    v[3] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7])), make_float2(b1.z, b1.w));
+                    if (g.act == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = silu2(v[e]);
+                    }
+                    // box col / 64, piece (col % 64) / 8 of this row, 128-byte swizzle
+                    uint4* slot = reinterpret_cast<uint4*>(out_s + (col >> 6) * kBoxBytes + row_in_tile * 128 + ((((col & 63) >> 3) ^ swz) << 4));
+                    if (g.has_residual) {
+                        float2 rr[4];
+                        Vec16<__nv_bfloat16>::unpack2(*slot, rr);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
+                    }
+                    *slot = Vec16<__nv_bfloat16>::pack2(v);
+                }
+            }
+            // this buffer's accumulator has been read: the tensor cores may start the tile after the next in it
+            tc_fence_before_sync();
+            mbar_arrive(&tmem_empty[buf]);
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            if (et == 0) {
+#pragma unroll
+                for (int b = 0; b < kBoxes; ++b) tma_store_3d(&tmap_o, out_s + b * kBoxBytes, 2 * n0 + b * 128, m0, grp);
+                bulk_commit();
+            }
+        }
+        if (et == 0) bulk_wait<0>();
+        if (!ok) {
+            s_abort = 1;
+            if (g.status != nullptr) atomicExch(g.status, 1);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return fn;
+}
+
+// [groups, rows, row_bytes] bytes, boxes of box_rows x 128 bytes inside one group, 128-byte swizzle
+bool make_tmap3(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+    PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[3] = {row_bytes, rows, groups};
+    const cuuint64_t strides[2] = {row_bytes, row_bytes * rows};
+    const cuuint32_t box[3] = {128, box_rows, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float* bias, const void* residual, void* out,
+                                       int32_t groups, int64_t M, int32_t N, int32_t K, int32_t act,
+                                       int32_t* status_word, void* stream) {
+    using namespace tb200;
+    if (groups < 0 || M < 0 || N < kBN || N % kBN != 0 || K < 64 || K % 64 != 0) return TB200_ERR_SHAPE;
+    if (act < 0 || act > 1) return TB200_ERR_UNSUPPORTED;
+    if (groups == 0 || M == 0) return TB200_OK;
+    if (a == nullptr || w == nullptr || out == nullptr) return TB200_ERR_NULL;
+    if (!aligned16(a) || !aligned16(w) || !aligned16(out) || (residual != nullptr && !aligned16(residual)) ||
+        (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3) != 0))
+        return TB200_ERR_ALIGN;
+    if (M > 0x7FFFFF00ll || static_cast<int64_t>(groups) * ((M + kBM - 1) / kBM) * (N / kBN) > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    CUtensorMap ta, tw, to, tr;
+    const uint64_t ug = static_cast<uint64_t>(groups), um = static_cast<uint64_t>(M);
+    if (!make_tmap3(&ta, a, 2ull * K, um, ug, kBM) || !make_tmap3(&tw, w, 2ull * K, static_cast<uint64_t>(N), ug, kBN) ||
+        !make_tmap3(&to, out, 2ull * N, um, ug, kBM) ||
+        !make_tmap3(&tr, residual != nullptr ? residual : out, 2ull * N, um, ug, kBM))
+        return TB200_ERR_DRIVER;
+    GArgs g{};
+    g.bias = bias;
+    g.status = status_word;
+    g.groups = groups;
+    g.N = N;
+    g.K = K;
+    g.M = M;
+    g.act = act;
+    g.has_residual = residual != nullptr ? 1 : 0;
+    const DeviceInfo& dev = device_info();
+    static bool attr_set[64] = {};
+    if (!attr_set[dev.index]) {
+        cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+        attr_set[dev.index] = true;
+    }
+    const int64_t total = static_cast<int64_t>(groups) * ((M + kBM - 1) / kBM) * (N / kBN);
+    const int64_t grid = total < dev.sm_count ? total : dev.sm_count;
+    gemm_bf16_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(ta, tw, to, tr, g);
+    count_launch();
+    return launch_status();
+}

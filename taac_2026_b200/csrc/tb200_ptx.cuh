@@ -157,6 +157,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                  : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(m),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // tcgen05: tensor memory
 // ---------------------------------------------------------------------------

@@ -316,6 +316,17 @@ class OneTransInference:
                 blk["ns_w2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "weight").transpose(1, 2).contiguous()
                 blk["ns_b2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "bias").unsqueeze(1)
                 blk["ns_b2_folded"] = (blk["ns_b2"].float() + blk["out_b"].float()).to(blk["ns_b2"].dtype)
+                # The same layers for the grouped tcgen05 GEMM, which takes stacked `nn.Linear` weights as they are
+                # ([token, out, in]) and adds bias, SiLU and residual in its epilogue (bf16, widths in whole tiles).
+                hidden = blk["ns_w1"].shape[2]
+                if self.dtype == torch.bfloat16 and self.device.type == "cuda" and d_model % 256 == 0 and hidden % 256 == 0:
+                    blk["g_qkv_w"] = torch.cat([wq, wk, wv], dim=1).contiguous()                       # [ns, 3d, d]
+                    blk["g_qkv_b"] = blk["ns_qkv_b"].reshape(ns, 3 * d_model).float().contiguous()
+                    blk["g_w1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "weight").contiguous()       # [ns, hidden, d]
+                    blk["g_b1"] = blk["ns_b1"].reshape(ns, hidden).float().contiguous()
+                    blk["g_w2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "weight").contiguous()       # [ns, d, hidden]
+                    blk["g_b2_folded"] = (blk["ns_b2"].float() + blk["out_b"].float()).reshape(ns, d_model).contiguous()
+                    blk["g_out_w"] = self._p(p + ".attention.out.weight").contiguous()                 # [d, d]
             self.blocks.append(blk)
 
     # ------------------------------------------------------------------ pieces
@@ -734,7 +745,10 @@ class OneTransInference:
                 out = self._shared_ffn_residual(blk, x, tokens)
                 ns_b2 = blk["ns_b2"]
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)
-            h = ops.bias_silu_rows(torch.bmm(x_ns, blk["ns_w1"]), blk["ns_b1"])
+            if "g_w1" in blk:
+                h = ops.grouped_linear(x_ns, blk["g_w1"], blk["g_b1"], silu=True)
+            else:
+                h = ops.bias_silu_rows(torch.bmm(x_ns, blk["ns_w1"]), blk["ns_b1"])
             y_ns = torch.bmm(h, blk["ns_w2"]).view(ns * batch, d)
             ops.scatter_rows(out, flat_ns, y_ns, bias=ns_b2, residual=tokens)   # tokens + b2 + FFN_ns(x)
             tokens = out
@@ -767,7 +781,11 @@ class OneTransInference:
         for blk in self.blocks[first_layer:]:
             p = blk["p"]
             x = ops.rms_norm(flat, self._p(p + ".attn_norm.weight"), 1e-6)
-            qkv = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_qkv_w"]), blk["ns_qkv_b"], silu=False)
+            fused = "g_qkv_w" in blk   # every layer of the block in one tcgen05 GEMM each, epilogues inside
+            if fused:
+                qkv = ops.grouped_linear(x.view(ns, batch, d), blk["g_qkv_w"], blk["g_qkv_b"])
+            else:
+                qkv = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_qkv_w"]), blk["ns_qkv_b"], silu=False)
             # sample-major views of the token-major tensors: (B, L = ns, H, hd) with strides (3d, B * 3d, hd, 1)
             q, k, v = (qkv[:, :, i * d : (i + 1) * d].unflatten(-1, (heads, hd)).permute(1, 0, 2, 3) for i in range(3))
             if q.dtype == torch.float32:
@@ -775,10 +793,19 @@ class OneTransInference:
             attn = torch.empty(ns, batch, heads, hd, dtype=q.dtype, device=q.device)
             ops.varlen_attention(q, k, v, causal=True, layout="blhd", kernel=self.attention_kernel,
                                  out=attn.permute(1, 0, 2, 3))
-            flat.addmm_(attn.view(ns * batch, d).to(self.dtype), blk["out_w_t"])   # bias: added by the norm, kept in ns_b2_folded
+            # attention output projection onto the residual stream; its bias is added by the norm on the fly and
+            # rides on the FFN's output bias into the next residual
+            if fused:
+                ops.grouped_linear(attn.view(ns * batch, d), blk["g_out_w"], None, residual=flat, out=flat)
+            else:
+                flat.addmm_(attn.view(ns * batch, d).to(self.dtype), blk["out_w_t"])
             x = ops.rms_norm(flat, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
-            h = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_w1"]), blk["ns_b1"], silu=True)
-            tok = ops.bias_act_rows(torch.baddbmm(tok, h, blk["ns_w2"]), blk["ns_b2_folded"], silu=False)
+            if fused:
+                h = ops.grouped_linear(x.view(ns, batch, d), blk["g_w1"], blk["g_b1"], silu=True)
+                tok = ops.grouped_linear(h, blk["g_w2"], blk["g_b2_folded"], residual=tok, out=tok)
+            else:
+                h = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_w1"]), blk["ns_b1"], silu=True)
+                tok = ops.bias_act_rows(torch.baddbmm(tok, h, blk["ns_w2"]), blk["ns_b2_folded"], silu=False)
             flat = tok.view(ns * batch, d)
         final = ops.rms_norm(flat, self._p("final_norm.weight"), 1e-6).float()
         return final.view(ns, batch, d).mean(dim=0)

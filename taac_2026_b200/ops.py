@@ -871,6 +871,53 @@ def ffn_fp8(x: torch.Tensor, weights: Fp8FfnWeights, *, residual: torch.Tensor |
 
 
 
+def grouped_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *, silu: bool = False,
+                   residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                   check: bool = False) -> torch.Tensor:
+    """``out[g] = act(x[g] @ weight[g].T + bias[g]) (+ residual[g])`` with everything behind the matrix product
+    inside the GEMM's epilogue (tcgen05 kernel, bf16 in and out, fp32 accumulation).
+
+    x: [G, M, K] (or [M, K] with weight [N, K]: a plain linear layer); weight: [G, N, K], the layout of stacked
+    ``nn.Linear`` weights; bias: [G, N] (any float dtype; used as fp32); residual / out: [G, M, N]; ``out`` may be
+    ``residual`` (accumulate in place).  N must be a multiple of 256 and K of 64.  ``check=True`` reads the
+    kernel's status word back (one sync) and raises if a bounded wait inside it gave up."""
+    _require_backend("grouped_linear", "cuda")
+    _require_cuda_tensors("cuda grouped_linear", x, weight, bias, residual, out)
+    squeeze = x.ndim == 2
+    if squeeze:
+        x, weight = x.unsqueeze(0), weight.unsqueeze(0)
+        bias = None if bias is None else bias.reshape(1, -1)
+        residual = None if residual is None else residual.unsqueeze(0)
+        out = None if out is None else out.unsqueeze(0)
+    if x.ndim != 3 or weight.ndim != 3 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise ValueError("grouped_linear needs bf16 x [G, M, K] and weight [G, N, K]")
+    groups, rows, k = x.shape
+    if weight.shape[0] != groups or weight.shape[2] != k:
+        raise ValueError("grouped_linear: weight must be [G, N, K] with x's G and K")
+    n = weight.shape[1]
+    if n % 256 or k % 64 or n < 256 or k < 64:
+        raise ValueError("grouped_linear needs N % 256 == 0 and K % 64 == 0")
+    if not x.is_contiguous() or not weight.is_contiguous():
+        raise ValueError("grouped_linear needs contiguous x and weight")
+    bias32 = None
+    if bias is not None:
+        bias32 = bias.reshape(groups, n).to(torch.float32).contiguous()
+    if out is None:
+        out = torch.empty(groups, rows, n, dtype=torch.bfloat16, device=x.device)
+    for name, t in (("residual", residual), ("out", out)):
+        if t is not None and (tuple(t.shape) != (groups, rows, n) or t.dtype != torch.bfloat16 or not t.is_contiguous()):
+            raise ValueError(f"grouped_linear: {name} must be a contiguous bf16 [G, M, N] tensor")
+    status = torch.zeros(1, dtype=torch.int32, device=x.device) if check else None
+    with torch.cuda.device(x.device), _timed("gemm_bf16", groups=groups, m=rows, n=n, k=k, silu=bool(silu),
+                                            residual=residual is not None):
+        code = _lib.load().tb200_gemm_bf16_grouped(_ptr(x), _ptr(weight), _ptr(bias32), _ptr(residual), _ptr(out), groups,
+                                                   rows, n, k, 1 if silu else 0, _ptr(status), _stream_ptr())
+    _lib.check(code, "cuda grouped_linear")
+    if status is not None and int(status.item()) != 0:
+        raise RuntimeError("cuda grouped_linear: a bounded wait inside the kernel gave up; the output is incomplete")
+    return out[0] if squeeze else out
+
+
 def ffn_fp8_static_capacity() -> int:
     """Bytes of the fixed in-library scratch array used by ``ffn_fp8_static`` (per GPU)."""
     return int(_lib.load().tb200_ffn_fp8_static_scratch_bytes())
