@@ -30,7 +30,7 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBKBytes = 128;            // 64 bf16 per stage: one 128-byte swizzle atom
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
@@ -38,8 +38,8 @@ constexpr uint32_t kABytes = kBM * kBKBytes;   // 16 KB
 constexpr uint32_t kBBytes = kBN * kBKBytes;   // 32 KB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kBoxBytes = kBM * 128;      // staging box: 128 rows x 64 bf16
-constexpr int kBoxes = kBN * 2 / 128;          // 4
-constexpr uint32_t kOutBytes = kBoxes * kBoxBytes;
+constexpr int kBoxes = kBN * 2 / 128;          // 4 boxes per tile, sent one after the other
+constexpr uint32_t kOutBytes = 2 * kBoxBytes;  // two boxes in shared memory: one is stored while the next is filled
 constexpr uint32_t kTmemCols = 512;
 constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + kOutBytes + 1024;
 
@@ -63,11 +63,10 @@ __device__ __forceinline__ float2 silu2(float2 x) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_o, const __grid_constant__ CUtensorMap tmap_r, const GArgs g) {
+                 const __grid_constant__ CUtensorMap tmap_o, const GArgs g, const __nv_bfloat16* __restrict__ residual) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kStages];
     __shared__ uint64_t empty_bar[kStages];
-    __shared__ uint64_t res_full;
     __shared__ uint64_t tmem_full[2];
     __shared__ uint64_t tmem_empty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -90,7 +89,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&res_full, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], kEpiThreads);
@@ -182,73 +180,76 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ---------------------------------------------------------------- epilogue
         const int et = threadIdx.x - 64;          // 0..255
-        const int half = et >> 7;                 // columns [128 half, 128 half + 128) of the tile
+        const int sub = et >> 7;                  // columns [32 sub, 32 sub + 32) of a round's 64
         const int quarter = warp & 3;             // TMEM lanes [32 quarter, +32) are visible to this warp
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const int swz = row_in_tile & 7;
         uint32_t tile_count = 0;
+        uint32_t round_count = 0;                 // rounds so far: staging box round_count % 2
         bool ok = true;
         for (int64_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++tile_count) {
             int n0, m0, grp;
             decode(t, n0, m0, grp);
             const uint32_t buf = tile_count & 1;
             const uint32_t aph = (tile_count >> 1) & 1;
-            // the staging tile is free once the previous tile's store has read it; the residual tile then lands in
-            // it while the tensor cores work
-            if (et == 0) {
-                bulk_wait_read<0>();
-                if (g.has_residual) {
-                    mbar_expect_tx(&res_full, kOutBytes);
-#pragma unroll
-                    for (int b = 0; b < kBoxes; ++b) tma_load_3d(out_s + b * kBoxBytes, &tmap_r, 2 * n0 + b * 128, m0, grp, &res_full);
-                }
-            }
             bias_s[et] = g.bias != nullptr ? g.bias[static_cast<int64_t>(grp) * g.N + n0 + et] : 0.f;
-            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+            // residual pieces of round r: this thread's row, 32 columns = four 16-byte loads, one round ahead
+            const int64_t row = static_cast<int64_t>(m0) + row_in_tile;
+            const bool has_res = residual != nullptr && row < g.M;
+            const uint4* res_row = reinterpret_cast<const uint4*>(
+                residual + (static_cast<int64_t>(grp) * g.M + (has_res ? row : 0)) * g.N + n0 + sub * 32);
+            uint4 res_cur[4], res_next[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) res_cur[q] = has_res ? res_row[q] : make_uint4(0u, 0u, 0u, 0u);   // plain loads: `out` may be this tensor
             if (!mbar_wait(&tmem_full[buf], aph)) { ok = false; break; }
             tc_fence_after_sync();
-            if (g.has_residual && !mbar_wait(&res_full, tile_count & 1)) { ok = false; break; }
-            const uint32_t t0 = tmem_base + buf * kBN + lane_addr + half * 128;
 #pragma unroll 1
-            for (int c = 0; c < 8; c += 2) {      // 32 columns per round: two x16 loads under one wait
-                uint32_t r[32];
-                tmem_ld_2x16(t0 + c * 16, r);
-                tc_wait_ld(r);
+            for (int r = 0; r < kBoxes; ++r, ++round_count) {
+                const int col = r * 64 + sub * 32;       // first of this thread's 32 columns in the tile
+                uint8_t* box = out_s + (round_count & 1) * kBoxBytes;
+                if (r + 1 < kBoxes) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {     // four 16-byte pieces of 8 columns
-                    const int col = half * 128 + c * 16 + q * 8;
-                    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + col);
-                    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + col + 4);
+                    for (int q = 0; q < 4; ++q) res_next[q] = has_res ? res_row[(r + 1) * 8 + q] : make_uint4(0u, 0u, 0u, 0u);
+                }
+                uint32_t acc[32];
+                tmem_ld_2x16(tmem_base + buf * kBN + lane_addr + col, acc);
+                if (et == 0) bulk_wait_read<1>();   // the store that used this box two rounds ago has read it
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+                tc_wait_ld(acc);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + col + q * 8);
+                    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + col + q * 8 + 4);
                     float2 v[4];
-                    v[0] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1])), make_float2(b0.x, b0.y));
-                    v[1] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3])), make_float2(b0.z, b0.w));
-                    v[2] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5])), make_float2(b1.x, b1.y));
-                    v[3] = __fadd2_rn(make_float2(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7])), make_float2(b1.z, b1.w));
+                    v[0] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 0]), __uint_as_float(acc[8 * q + 1])), make_float2(b0.x, b0.y));
+                    v[1] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3])), make_float2(b0.z, b0.w));
+                    v[2] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5])), make_float2(b1.x, b1.y));
+                    v[3] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7])), make_float2(b1.z, b1.w));
                     if (g.act == 1) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) v[e] = silu2(v[e]);
                     }
-                    // box col / 64, piece (col % 64) / 8 of this row, 128-byte swizzle
-                    uint4* slot = reinterpret_cast<uint4*>(out_s + (col >> 6) * kBoxBytes + row_in_tile * 128 + ((((col & 63) >> 3) ^ swz) << 4));
-                    if (g.has_residual) {
+                    if (residual != nullptr) {
                         float2 rr[4];
-                        Vec16<__nv_bfloat16>::unpack2(*slot, rr);
+                        Vec16<__nv_bfloat16>::unpack2(res_cur[q], rr);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
                     }
-                    *slot = Vec16<__nv_bfloat16>::pack2(v);
+                    *reinterpret_cast<uint4*>(box + row_in_tile * 128 + (((sub * 4 + q) ^ swz) << 4)) = Vec16<__nv_bfloat16>::pack2(v);
                 }
-            }
-            // this buffer's accumulator has been read: the tensor cores may start the tile after the next in it
-            tc_fence_before_sync();
-            mbar_arrive(&tmem_empty[buf]);
-            fence_proxy_async_smem();
-            asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-            if (et == 0) {
+                if (r == kBoxes - 1) {   // every column of this buffer has been read: the tensor cores may reuse it
+                    tc_fence_before_sync();
+                    mbar_arrive(&tmem_empty[buf]);
+                }
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+                if (et == 0) {
+                    tma_store_3d(&tmap_o, box, 2 * n0 + r * 128, m0, grp);
+                    bulk_commit();
+                }
 #pragma unroll
-                for (int b = 0; b < kBoxes; ++b) tma_store_3d(&tmap_o, out_s + b * kBoxBytes, 2 * n0 + b * 128, m0, grp);
-                bulk_commit();
+                for (int q = 0; q < 4; ++q) res_cur[q] = res_next[q];
             }
         }
         if (et == 0) bulk_wait<0>();
@@ -313,11 +314,10 @@ extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float
         return TB200_ERR_ALIGN;
     if (M > 0x7FFFFF00ll || static_cast<int64_t>(groups) * ((M + kBM - 1) / kBM) * (N / kBN) > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
     if (!device_info().valid) return TB200_ERR_DEVICE;
-    CUtensorMap ta, tw, to, tr;
+    CUtensorMap ta, tw, to;
     const uint64_t ug = static_cast<uint64_t>(groups), um = static_cast<uint64_t>(M);
     if (!make_tmap3(&ta, a, 2ull * K, um, ug, kBM) || !make_tmap3(&tw, w, 2ull * K, static_cast<uint64_t>(N), ug, kBN) ||
-        !make_tmap3(&to, out, 2ull * N, um, ug, kBM) ||
-        !make_tmap3(&tr, residual != nullptr ? residual : out, 2ull * N, um, ug, kBM))
+        !make_tmap3(&to, out, 2ull * N, um, ug, kBM))
         return TB200_ERR_DRIVER;
     GArgs g{};
     g.bias = bias;
@@ -336,7 +336,8 @@ extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float
     }
     const int64_t total = static_cast<int64_t>(groups) * ((M + kBM - 1) / kBM) * (N / kBN);
     const int64_t grid = total < dev.sm_count ? total : dev.sm_count;
-    gemm_bf16_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(ta, tw, to, tr, g);
+    gemm_bf16_kernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
+        ta, tw, to, g, static_cast<const __nv_bfloat16*>(residual));
     count_launch();
     return launch_status();
 }
