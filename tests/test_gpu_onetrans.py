@@ -168,6 +168,43 @@ def test_blocks_with_only_ns_tokens_left(dtype, tol):
     assert np.abs(got - want).max() <= tol
 
 
+def test_per_token_layers_on_the_grouped_gemm():
+    """bf16, d_model 256: the per-token layers of the non-sequence tokens run on the grouped tcgen05 GEMM (bias,
+    SiLU and residual in its epilogue), in the mixed blocks and in the NS-only blocks.  The scores match the
+    oracle, and the same model without the fused weights (library batched GEMMs + separate passes) agrees."""
+    from taac_2026_b200 import ops
+
+    spec = OneTransSpec(
+        user_int_specs=[(1000, i, 1) for i in range(12)], item_int_specs=[(1000, i, 1) for i in range(6)],
+        user_dense_dim=16, item_dense_dim=0, seq_vocab_sizes={"seq_a": [5000]}, d_model=256, emb_dim=64,
+        num_blocks=4, num_heads=4, hidden_mult=4, seq_top_k=96, user_ns_tokens=4, item_ns_tokens=2,
+    )
+    sd = random_state_dict(spec, seed=4)
+    batch = synthetic_batch(spec, 200, seq_len=96, min_len=1, seed=8)
+    short = batch.sequences["seq_a"].lengths.clamp(max=9)
+    batch = ModelInput(batch.user, batch.item,
+                       {"seq_a": SequenceInput(batch.sequences["seq_a"].values, short, batch.sequences["seq_a"].timestamps)},
+                       batch.request_timestamp)
+    want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
+    want = oracle_model.sigmoid_scores(want_logits).reshape(-1)
+    model = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn="bf16")
+    assert all("g_w1" in blk for blk in model.blocks)
+    records: list = []
+    ops.set_kernel_timing(records)
+    try:
+        got = model.scores(batch.to("cuda"))
+    finally:
+        ops.set_kernel_timing(None)
+    names = [r[0] for r in records]
+    assert names.count("gemm_bf16") >= 5 and "bias_act_rows" not in names
+    assert np.abs(got.cpu().numpy() - want).max() <= 5e-3
+    for blk in model.blocks:                      # the same weights through the unfused path
+        for key in [k for k in blk if k.startswith("g_")]:
+            del blk[key]
+    unfused = model.scores(batch.to("cuda"))
+    assert (got - unfused).abs().max().item() <= 5e-3
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-3)])
 def test_early_row_selection_changes_nothing(dtype, tol):
     """Selecting the rows the pyramid keeps before the row-wise half of a block (default) or after the whole
