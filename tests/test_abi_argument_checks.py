@@ -95,3 +95,40 @@ def test_fp8_entries(lib):
     assert gemm(P(p), P(p), P(p), P(p), None, None, P(p), None, 4, 256, 128, 1, None, None) == ERR_NULL    # scales out
     assert gemm(P(p), P(p), P(p), P(p), None, P(p), P(p), P(p), 4, 256, 128, 0, None, None) == ERR_UNSUPPORTED  # residual + swiglu
     assert lib.tb200_ffn_fp8_static_scratch_bytes() == 64 << 20
+
+
+def test_grouped_gemm_entry(lib):
+    buf = (ctypes.c_uint8 * 256)()
+    p = ctypes.addressof(buf)
+    gemm = lib.tb200_gemm_bf16_grouped
+    assert gemm(P(p), P(p), None, None, P(p), 0, 8, 256, 64, 0, None, None) == OK            # no group
+    assert gemm(P(p), P(p), None, None, P(p), 3, 0, 256, 64, 0, None, None) == OK            # no row
+    assert gemm(P(p), P(p), None, None, P(p), 3, 8, 200, 64, 0, None, None) == ERR_SHAPE     # N % 256
+    assert gemm(P(p), P(p), None, None, P(p), 3, 8, 256, 48, 0, None, None) == ERR_SHAPE     # K % 64
+    assert gemm(P(p), P(p), None, None, P(p), -1, 8, 256, 64, 0, None, None) == ERR_SHAPE
+    assert gemm(P(p), P(p), None, None, P(p), 3, 8, 256, 64, 2, None, None) == ERR_UNSUPPORTED   # unknown activation
+    assert gemm(None, P(p), None, None, P(p), 3, 8, 256, 64, 0, None, None) == ERR_NULL
+    assert gemm(P(p), P(p), None, None, None, 3, 8, 256, 64, 0, None, None) == ERR_NULL
+    assert gemm(P(p + 8), P(p), None, None, P(p), 3, 8, 256, 64, 0, None, None) == ERR_ALIGN
+
+
+def test_token_tail_entries(lib):
+    buf = (ctypes.c_uint8 * 256)()
+    p = ctypes.addressof(buf)
+    sel = lib.tb200_token_tail_select_fwd
+
+    def call(**kw):
+        a = dict(x=P(p), g=P(p), b=P(p), ta=P(p), rows_a=4, ia=P(p), tb=None, rows_b=0, ib=None, g2=P(p), dst=None, rows_out=0,
+                 tokens=P(p), normed=P(p), rows=4, cols=8)
+        a.update(kw)
+        return sel(a["x"], a["g"], a["b"], a["ta"], a["rows_a"], a["ia"], a["tb"], a["rows_b"], a["ib"], a["g2"], a["dst"],
+                   a["rows_out"], a["tokens"], a["normed"], a["rows"], a["cols"], 1e-5, 1e-6, BF16, None)
+
+    assert call(rows=0) == OK
+    assert call(rows=-1) == ERR_SHAPE and call(rows_a=0) == ERR_SHAPE
+    assert call(x=None) == ERR_NULL and call(normed=None) == ERR_NULL and call(tokens=None) == ERR_NULL
+    assert call(tb=P(p), rows_b=4, ib=None) == ERR_NULL                     # a second table needs its ids
+    assert call(dst=P(p), rows_out=-1) == ERR_SHAPE
+    assert call(rows_a=1 << 31) == ERR_UNSUPPORTED                          # ids are held as 32-bit values
+    assert lib.tb200_token_tail_fwd(P(p), P(p), P(p), P(p), 4, P(p), None, 0, None, P(p), P(p), P(p), 0, 8, 1e-5, 1e-6, BF16,
+                                    None) == OK
