@@ -255,6 +255,23 @@ int tb200_sequence_prepare(const int64_t* values, const int64_t* lengths, const 
                            const int64_t* request_ts, int64_t batch, int32_t n_feat, int32_t max_len,
                            int64_t* out_len, int32_t* out_src, float* out_stats, void* stream);
 
+/* Index vectors of the packed valid-token layout: for every row of the packed token matrix the ids of
+ * `SequenceTokenizer.forward`'s embedding lookups (src/taac2026/infrastructure/modeling/tokenizers.py:156-176;
+ * hashed like `modeling/embeddings.py:74-79` where a table is a compressed one), the position inside the
+ * cropped sequence (`modeling/sequence.py:130-138` indexes the sinusoidal table with it) and the time-gap
+ * bucket (`modeling/time_features.py:31-46`), after duplicate removal and tail crop.
+ * Sample b owns rows [cu_rows[b], cu_rows[b+1]): seq_count[b] sequence tokens, then its non-sequence tokens
+ * (their entries are 0).  Sequence token j is input position src[b, start[b] + j], src = out_src of
+ * tb200_sequence_prepare.  hash_buckets [n_feat]: 0 = raw ids, > 0 = ((v - 1) mod buckets) + 1 for v > 0 else 0,
+ * < 0 = feature without a table (its ids are not written).  ids_out [n_feat, total_rows], pos_out and
+ * bucket_out [total_rows] int64; bucket_out (with timestamps / edges) may be NULL.  All inputs int64 on the
+ * device except src (int32). */
+int tb200_packed_token_index(const int64_t* values, const int64_t* timestamps, const int64_t* request_ts,
+                             const int32_t* src, const int64_t* cu_rows, const int64_t* seq_count, const int64_t* start,
+                             const int64_t* edges, int32_t n_edges, const int64_t* hash_buckets, int64_t batch,
+                             int32_t n_feat, int32_t max_len, int64_t total_rows, int64_t* ids_out, int64_t* pos_out,
+                             int64_t* bucket_out, void* stream);
+
 /* ---- per-token (grouped) bf16 linear layers with a fused epilogue ----------------------------
  * out[g] = act(a[g] @ w[g]^T + bias[g]) (+ residual[g]) for g in [0, groups): the token-specific projections
  * and feed-forward layers of the non-sequence tokens, `nn.ModuleList` of `nn.Linear` / `FeedForward` applied

@@ -48,6 +48,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     ),
     "tb200_quant_act_1x128": (_INT, [_P, _P, _P, _I64, _I32, _P]),
     "tb200_fp8_gemm": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _P]),
+    "tb200_packed_token_index": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I32, _P, _I64, _I32, _I32, _I64, _P, _P, _P, _P]),
     "tb200_gemm_bf16_grouped": (_INT, [_P, _P, _P, _P, _P, _I32, _I64, _I32, _I32, _I32, _P, _P]),
     "tb200_ffn_fp8_fwd_static": (
         _INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _P],

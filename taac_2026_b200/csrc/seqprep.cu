@@ -164,6 +164,60 @@ seqprep_kernel(const int64_t* __restrict__ values, const int64_t* __restrict__ l
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Index vectors of the packed token matrix.  Sample b owns rows [cu_rows[b], cu_rows[b + 1]): first its
+// seq_count[b] sequence tokens, then its non-sequence tokens.  Sequence token j is the event at input position
+// src[b, start[b] + j] (start = first position the tail crop keeps); this kernel looks up, for every row, the
+// feature ids (hashed into buckets where a table is a compressed one), the position j and the time-gap bucket;
+// rows of non-sequence tokens get zeros (the padding rows of the tables).  One CTA per sample.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+token_index_kernel(const int64_t* __restrict__ values, const int64_t* __restrict__ timestamps,
+                   const int64_t* __restrict__ request_ts, const int32_t* __restrict__ src,
+                   const int64_t* __restrict__ cu_rows, const int64_t* __restrict__ seq_count,
+                   const int64_t* __restrict__ start, const int64_t* __restrict__ edges, int n_edges,
+                   const int64_t* __restrict__ hash_buckets, int n_feat, int max_len, int64_t total_rows,
+                   int64_t* __restrict__ ids_out, int64_t* __restrict__ pos_out, int64_t* __restrict__ bucket_out) {
+    const int64_t b = blockIdx.x;
+    const int64_t row0 = cu_rows[b];
+    const int64_t n_rows = cu_rows[b + 1] - row0;
+    const int64_t n_seq = seq_count[b];
+    const int64_t first = start[b];
+    const int64_t req = request_ts[b];
+    for (int64_t j = threadIdx.x; j < n_rows; j += blockDim.x) {
+        const int64_t row = row0 + j;
+        int64_t p = -1;
+        if (j < n_seq && first + j < max_len) p = src[b * max_len + first + j];
+        const bool live = p >= 0 && p < max_len;
+        for (int f = 0; f < n_feat; ++f) {
+            const int64_t buckets = hash_buckets[f];
+            if (buckets < 0) continue;                       // feature without a table: nothing to write
+            int64_t v = live ? values[(b * n_feat + f) * max_len + p] : 0;
+            if (buckets > 0) v = v > 0 ? (v - 1) % buckets + 1 : 0;
+            ids_out[static_cast<int64_t>(f) * total_rows + row] = v;
+        }
+        pos_out[row] = live ? j : 0;
+        if (bucket_out != nullptr) {
+            int64_t bucket = 0;
+            if (live) {
+                const int64_t t = timestamps[b * max_len + p];
+                if (t != 0) {
+                    int64_t gap = req - t;
+                    if (gap < 0) gap = 0;
+                    int lo = 0, hi = n_edges;                  // number of edges < gap
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (edges[mid] < gap) lo = mid + 1;
+                        else hi = mid;
+                    }
+                    bucket = (lo < n_edges - 1 ? lo : n_edges - 1) + 1;
+                }
+            }
+            bucket_out[row] = bucket;
+        }
+    }
+}
+
 }  // namespace
 }  // namespace tb200
 
@@ -189,6 +243,28 @@ extern "C" int tb200_sequence_prepare(const int64_t* values, const int64_t* leng
     }
     seqprep_kernel<<<static_cast<unsigned>(batch), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         values, lengths, timestamps, request_ts, n_feat, max_len, table, out_len, out_src, out_stats);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int tb200_packed_token_index(const int64_t* values, const int64_t* timestamps, const int64_t* request_ts,
+                                        const int32_t* src, const int64_t* cu_rows, const int64_t* seq_count,
+                                        const int64_t* start, const int64_t* edges, int32_t n_edges,
+                                        const int64_t* hash_buckets, int64_t batch, int32_t n_feat, int32_t max_len,
+                                        int64_t total_rows, int64_t* ids_out, int64_t* pos_out, int64_t* bucket_out,
+                                        void* stream) {
+    using namespace tb200;
+    if (batch < 0 || n_feat < 1 || max_len < 1 || total_rows < 0 || n_edges < 0) return TB200_ERR_SHAPE;
+    if (batch == 0 || total_rows == 0) return TB200_OK;
+    if (values == nullptr || request_ts == nullptr || src == nullptr || cu_rows == nullptr || seq_count == nullptr ||
+        start == nullptr || hash_buckets == nullptr || ids_out == nullptr || pos_out == nullptr)
+        return TB200_ERR_NULL;
+    if (bucket_out != nullptr && (timestamps == nullptr || edges == nullptr || n_edges < 1)) return TB200_ERR_NULL;
+    if (batch > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    token_index_kernel<<<static_cast<unsigned>(batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        values, timestamps, request_ts, src, cu_rows, seq_count, start, edges, n_edges, hash_buckets, n_feat, max_len,
+        total_rows, ids_out, pos_out, bucket_out);
     count_launch();
     return launch_status();
 }

@@ -241,6 +241,7 @@ class OneTransInference:
             self.seq_tables[domain] = entries
         self._prepare_blocks()
         self._pos_cache: dict[int, torch.Tensor] = {}
+        self._hash_buckets: dict[str, torch.Tensor] = {}   # per sequence domain: how each feature's ids are hashed
 
     # ------------------------------------------------------------------ weights
     def _p(self, name: str) -> torch.Tensor:
@@ -616,39 +617,35 @@ class OneTransInference:
         # zero padding row) through the projection and are overwritten afterwards, which costs ns / (n + ns)
         # extra rows but saves a full scatter of the token matrix.
         total0 = totals[0]
-        n_seq = total0 - batch * ns
-        sample_of = torch.repeat_interleave(arange_b, n0, output_size=n_seq)
-        seq_cu = offsets(n0)
-        j_idx = torch.arange(n_seq, device=dev) - seq_cu[sample_of]              # position after the tail crop
-        src_pos = src_map[sample_of, start[sample_of] + j_idx].long()             # position in the raw input
-        dest = cu[0][sample_of] + j_idx                                           # row in the packed matrix
         prefix = f"sequence_tokenizers.{domain}"
         entries = self.seq_tables[domain]
         n_feat = values.shape[1]
         emb = self.spec.emb_dim
         live = [f for f in range(n_feat) if f < len(entries) and entries[f][1] is not None]
+        has_time = prefix + ".time_embedding.weight" in self.w
+        # ids of every feature, position and time-gap bucket of every packed row: one kernel instead of a dozen
+        # index operations over the token rows
+        if domain not in self._hash_buckets:
+            self._hash_buckets[domain] = torch.tensor(
+                [(-1 if f not in live else (entries[f][1].shape[0] - 1 if entries[f][0] == "compressed" else 0))
+                 for f in range(n_feat)], dtype=torch.long, device=dev)
+        ids_all, pos_full, buckets_full = ops.packed_token_index(
+            values, ts if has_time else None, request_ts, src_map, cu[0], n0, start, self._hash_buckets[domain], total0,
+            edges=self._edges if has_time else None)
         if live:
             token_input = (torch.empty if len(live) == n_feat else torch.zeros)(
                 (total0, n_feat * emb), dtype=self.dtype, device=dev)
             for f in live:
-                kind, table = entries[f]
-                ids = values[sample_of, f, src_pos]
-                if kind == "compressed":
-                    ids = hash_compress_ids(ids.clamp_min(0), table.shape[0] - 1)
-                ids_full = torch.zeros(total0, dtype=ids.dtype, device=dev).index_copy_(0, dest, ids)
-                ops.gather_rows(table, ids_full, out=token_input, col0=f * emb)
+                ops.gather_rows(entries[f][1], ids_all[f], out=token_input, col0=f * emb)
         else:
             token_input = torch.zeros(total0, max(1, n_feat * emb), dtype=self.dtype, device=dev)
         # Linear -> SiLU -> LayerNorm, the time-bucket and position rows and the first block's RMSNorm in one pass
         # over the token matrix (`token_tail`); the NS rows are filled in afterwards
         projected = self._linear(token_input, prefix + ".project.0")
         ln_w, ln_b = self._p(prefix + ".project.2.weight"), self._p(prefix + ".project.2.bias")
-        pos_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, j_idx)
         pos_table = self._positions(width).to(self.dtype).contiguous()
         rows_a, rows_b = (pos_table, pos_full), (None, None)
-        if prefix + ".time_embedding.weight" in self.w:
-            buckets = sequence_time_buckets(ts[sample_of, src_pos][:, None], request_ts[sample_of], self._edges)[:, 0]
-            buckets_full = torch.zeros(total0, dtype=torch.long, device=dev).index_copy_(0, dest, buckets.long())
+        if has_time:
             rows_a, rows_b = (self._p(prefix + ".time_embedding.weight"), buckets_full), (pos_table, pos_full)
         first_norm_w = self._p(self.blocks[0]["p"] + ".attn_norm.weight") if self.blocks else None
         ns_off = torch.arange(ns, device=dev)[None, :]

@@ -989,6 +989,46 @@ def sequence_prepare(values: torch.Tensor, lengths: torch.Tensor, timestamps: to
 
 
 
+def packed_token_index(values: torch.Tensor, timestamps: torch.Tensor | None, request_ts: torch.Tensor, src: torch.Tensor,
+                       cu_rows: torch.Tensor, seq_count: torch.Tensor, start: torch.Tensor, hash_buckets: torch.Tensor,
+                       total_rows: int, edges: torch.Tensor | None = None,
+                       ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    """Ids, positions and time-gap buckets of every row of the packed token matrix in one kernel.
+
+    ``values`` [B, F, L], ``timestamps`` [B, L], ``request_ts`` [B], ``cu_rows`` [B + 1], ``seq_count`` [B],
+    ``start`` [B], ``hash_buckets`` [F], ``edges`` [E] (all int64), ``src`` [B, L] int32 from ``sequence_prepare``.
+    Returns ``(ids [F, total_rows], positions [total_rows], buckets [total_rows] or None)`` (int64); rows of
+    non-sequence tokens hold zeros.  With ``edges=None`` no buckets are computed."""
+    _require_backend("packed_token_index", "cuda")
+    _require_cuda_tensors("cuda packed_token_index", values, timestamps, request_ts, src, cu_rows, seq_count, start,
+                          hash_buckets, edges)
+    if values.ndim != 3 or src.ndim != 2 or src.dtype != torch.int32:
+        raise ValueError("packed_token_index expects values [B, F, L] and src [B, L] int32")
+    batch, n_feat, max_len = values.shape
+    i64 = lambda t: t.to(torch.int64).contiguous()   # noqa: E731
+    values, request_ts, cu_rows, seq_count, start, hash_buckets = (i64(t) for t in (values, request_ts, cu_rows, seq_count,
+                                                                                    start, hash_buckets))
+    if cu_rows.numel() != batch + 1 or seq_count.numel() != batch or start.numel() != batch or hash_buckets.numel() != n_feat:
+        raise ValueError("packed_token_index: one offset, count and start per sample and one bucket count per feature")
+    src = src.contiguous()
+    dev = values.device
+    ids = torch.zeros(n_feat, total_rows, dtype=torch.int64, device=dev)
+    pos = torch.empty(total_rows, dtype=torch.int64, device=dev)
+    buckets = None
+    if edges is not None:
+        if timestamps is None:
+            raise ValueError("packed_token_index: time buckets need the timestamps")
+        timestamps, edges = i64(timestamps), i64(edges)
+        buckets = torch.empty(total_rows, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev), _timed("packed_token_index", batch=batch, n_feat=n_feat, rows=total_rows):
+        code = _lib.load().tb200_packed_token_index(
+            _ptr(values), _ptr(timestamps), _ptr(request_ts), _ptr(src), _ptr(cu_rows), _ptr(seq_count), _ptr(start),
+            _ptr(edges), 0 if edges is None else edges.numel(), _ptr(hash_buckets), batch, n_feat, max_len, total_rows,
+            _ptr(ids), _ptr(pos), _ptr(buckets), _stream_ptr())
+    _lib.check(code, "cuda packed_token_index")
+    return ids, pos, buckets
+
+
 def scatter_rows(dst: torch.Tensor, ids: torch.Tensor, src: torch.Tensor, *, col0: int = 0,
                  bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
     """``dst[ids[i], col0 : col0 + dim] = src[i] (+ bias[i // rows_per_group]) (+ residual[ids[i]])`` in place.

@@ -185,3 +185,47 @@ def test_row_kernels_edge_cases():
     y = torch.randn(7, 24, device=dev).bfloat16()
     b = torch.randn(24, device=dev).bfloat16()
     assert torch.equal(ops.bias_act_rows(y.clone(), b, silu=False), (y.float() + b.float()).bfloat16())
+
+
+@pytest.mark.parametrize("with_time", [True, False])
+def test_packed_token_index_matches_the_index_arithmetic(with_time):
+    """Ids (raw and hashed), positions and time-gap buckets of every packed row from one kernel, against the
+    same quantities spelled out with tensor indexing."""
+    g = torch.Generator().manual_seed(31)
+    B, F, L, ns = 37, 3, 50, 4
+    values = torch.randint(-2, 5000, (B, F, L), generator=g)
+    ts = torch.randint(0, 3, (B, L), generator=g) * torch.randint(1, 10**9, (B, L), generator=g)   # a third are zero
+    req = torch.randint(5 * 10**8, 2 * 10**9, (B,), generator=g)
+    src = torch.stack([torch.randperm(L, generator=g) for _ in range(B)]).to(torch.int32)
+    n0 = torch.randint(0, 31, (B,), generator=g)
+    n0[0], n0[1] = 0, 30
+    start = torch.randint(0, L - 30, (B,), generator=g)
+    rows = n0 + ns
+    cu = torch.zeros(B + 1, dtype=torch.long)
+    cu[1:] = torch.cumsum(rows, 0)
+    total = int(cu[-1])
+    hash_buckets = torch.tensor([0, 97, -1])
+    edges = torch.tensor(sorted(set(torch.randint(1, 10**9, (20,), generator=g).tolist())))
+    ids, pos, buckets = ops.packed_token_index(values.cuda(), ts.cuda() if with_time else None, req.cuda(), src.cuda(), cu.cuda(),
+                                               n0.cuda(), start.cuda(), hash_buckets.cuda(), total,
+                                               edges=edges.cuda() if with_time else None)
+    want_ids = torch.zeros(F, total, dtype=torch.long)
+    want_pos = torch.zeros(total, dtype=torch.long)
+    want_b = torch.zeros(total, dtype=torch.long)
+    for b in range(B):
+        for j in range(int(n0[b])):
+            p = int(src[b, int(start[b]) + j])
+            r = int(cu[b]) + j
+            want_ids[0, r] = values[b, 0, p]
+            v = int(values[b, 1, p])
+            want_ids[1, r] = (v - 1) % 97 + 1 if v > 0 else 0
+            want_pos[r] = j
+            if ts[b, p] != 0:
+                gap = max(int(req[b]) - int(ts[b, p]), 0)
+                want_b[r] = min(int((edges < gap).sum()), edges.numel() - 1) + 1
+    assert torch.equal(ids.cpu(), want_ids)          # the feature without a table stays zero
+    assert torch.equal(pos.cpu(), want_pos)
+    if with_time:
+        assert torch.equal(buckets.cpu(), want_b)
+    else:
+        assert buckets is None
