@@ -450,7 +450,10 @@ def run_e2e(args) -> None:
     launches_before = _lib.launch_count()
     ms_total = timed(step_resident, args.steps, None)
     launches = _lib.launch_count() - launches_before
-    ms_e2e = timed(lambda: run_e2e(args.steps), 1, None)
+    # the end-to-end pass shares the host's copy bandwidth with other tenants of the machine: two passes of K steps
+    # each, the faster one is reported and both are listed
+    e2e_passes = [timed(lambda: run_e2e(args.steps), 1, None) for _ in range(2)]
+    ms_e2e = min(e2e_passes)
     records: list = []
     ms_recorded = timed(step_resident, args.steps, records)
     # the same resident steps in the reference's order of operations (every block for every row, then the
@@ -511,7 +514,8 @@ def run_e2e(args) -> None:
         },
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 2), "unit": "samples/s", "h2d_bytes_per_step": host_batch.nbytes(),
-                "d2h_bytes_per_step": host_scores.numel() * 4, "ms_per_step": round(ms_e2e / args.steps, 3)},
+                "d2h_bytes_per_step": host_scores.numel() * 4, "ms_per_step": round(ms_e2e / args.steps, 3),
+                "passes_ms_per_step": [round(m / args.steps, 3) for m in e2e_passes]},
         "gpu_launches": launches,
         "kernel_timing_pass_ms_per_step": round(ms_recorded / args.steps, 3),
         "reference_order": None if ms_ref_order is None else {

@@ -19,6 +19,8 @@
 // through the final barrier, where the TMEM allocation is released.
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
+
 #include "tb200_common.cuh"
 #include "tb200_ptx.cuh"
 
@@ -267,6 +269,274 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant (cluster of two CTAs, tcgen05 cta_group::2).  A pair owns a 256 x 256 output tile: each CTA
+// loads its own 128 rows of A and one half (128 rows) of the weight tile, the leader (even rank) issues
+// 256 x 256 x 16 MMAs that read A from each CTA's own shared memory and the weight halves from both, and each
+// CTA's TMEM receives its 128 rows.  A stage is then 32 KB per CTA for the same 512 cycles of tensor-core time,
+// so six stages fit where the single-CTA kernel has four: the ring holds 3072 cycles of work, more than the
+// round trip that the K loop otherwise waits for.  Barriers: the "full" barriers live in the leader and count
+// the bytes of both CTAs' loads; "empty" and "accumulator full" are signalled in both CTAs by multicast
+// commits; "accumulator empty" collects one arrival per epilogue warp of both CTAs in the leader.
+// ------------------------------------------------------------------------------------------------
+constexpr int kStagesP = 6;
+constexpr int kEpiWarpsP = 16;                 // four warps per TMEM lane quarter: the epilogue of a short-K tile is as long as its MMAs
+constexpr int kEpiThreadsP = kEpiWarpsP * 32;
+constexpr int kThreadsP = 64 + kEpiThreadsP;
+constexpr uint32_t kBHalfBytes = kBBytes / 2;                 // 16 KB: this CTA's half of the weight tile
+constexpr uint32_t kStagePBytes = kABytes + kBHalfBytes;      // 32 KB
+constexpr size_t kSmemPBytes = static_cast<size_t>(kStagesP) * kStagePBytes + kOutBytes + 1024;
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;                   // shared::cluster address of the pair's even CTA
+constexpr uint32_t kPairWait = 1u << 18;                      // bounded waits give up early in this variant
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, int32_t c0, int32_t c1, int32_t c2,
+                                                 uint64_t* leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], "
+        "[%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(m), "r"(smem_u32(leader_bar) & kPeerMask), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerMask) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsP, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                      const __grid_constant__ CUtensorMap tmap_o, const GArgs g, const __nv_bfloat16* __restrict__ residual) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[kStagesP];     // used in the leader only
+    __shared__ uint64_t empty_bar[kStagesP];
+    __shared__ uint64_t tmem_full[2];
+    __shared__ uint64_t tmem_empty[2];          // used in the leader only
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ __align__(16) float bias_s[kBN];
+    __shared__ int s_abort;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;
+    uint8_t* out_s = smem + static_cast<size_t>(kStagesP) * kStagePBytes;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();       // 0 = leader
+    const int64_t pair = blockIdx.x >> 1;
+    const int64_t n_pairs = gridDim.x >> 1;
+
+    const int64_t m_tiles = (g.M + 2 * kBM - 1) / (2 * kBM);
+    const int n_tiles = g.N / kBN;
+    const int k_blocks = g.K / (kBKBytes / 2);
+    const int64_t total = static_cast<int64_t>(g.groups) * m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesP; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 2 * kEpiWarpsP);
+        }
+        s_abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                          // both CTAs' barriers exist before anything is signalled remotely
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    auto decode = [&](int64_t t, int& n0, int& m0, int& grp) {
+        const int n = static_cast<int>(t % n_tiles);
+        const int64_t rest = t / n_tiles;
+        n0 = n * kBN;
+        m0 = static_cast<int>(rest % m_tiles) * 2 * kBM + static_cast<int>(rank) * kBM;   // this CTA's 128 rows
+        grp = static_cast<int>(rest / m_tiles);
+    };
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_w);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = pair; t < total && ok; t += n_pairs) {
+                int n0, m0, grp;
+                decode(t, n0, m0, grp);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kStagesP;
+                    const uint32_t ph = (it / kStagesP) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1, kPairWait) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* dst = ring + static_cast<size_t>(s) * kStagePBytes;
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * kStagePBytes);   // the bytes of both CTAs
+                    tma_load_3d_pair(dst, &tmap_a, kb * kBKBytes, m0, grp, &full_bar[s]);
+                    tma_load_3d_pair(dst + kABytes, &tmap_w, kb * kBKBytes, n0 + static_cast<int>(rank) * (kBN / 2), grp, &full_bar[s]);
+                }
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (g.status != nullptr) atomicExch(g.status, 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (leader only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc(1, 1, 0, 0, 2 * kBM, kBN);
+            const uint64_t desc0 = umma_desc_sw128(0, 1024, 16);
+            const uint32_t ring_lo = (smem_u32(ring) & 0x3FFFFu) >> 4;
+            uint32_t s = 0, ph = 0, buf = 0, aph = 0;
+            bool ok = true;
+            for (int64_t t = pair; t < total && ok; t += n_pairs) {
+                if (!mbar_wait(&tmem_empty[buf], aph ^ 1, kPairWait)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * kBN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[s], ph, kPairWait)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_lo = ring_lo + s * (kStagePBytes >> 4);
+                    const uint64_t da = desc0 + a_lo;
+                    const uint64_t db = desc0 + a_lo + (kABytes >> 4);
+#pragma unroll
+                    for (int k = 0; k < kBKBytes / 32; ++k) mma_f16_ss_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    tc_commit_pair(&empty_bar[s]);
+                    if (++s == kStagesP) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!ok) break;
+                tc_commit_pair(&tmem_full[buf]);
+                aph ^= buf;
+                buf ^= 1;
+            }
+            if (!ok) {
+                s_abort = 1;
+                if (g.status != nullptr) atomicExch(g.status, 1);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+        const int et = threadIdx.x - 64;          // 0..511
+        const int sub = et >> 7;                  // columns [16 sub, 16 sub + 16) of a round's 64
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const int swz = row_in_tile & 7;
+        uint32_t tile_count = 0;
+        uint32_t round_count = 0;
+        bool ok = true;
+        for (int64_t t = pair; t < total && ok; t += n_pairs, ++tile_count) {
+            int n0, m0, grp;
+            decode(t, n0, m0, grp);
+            const uint32_t buf = tile_count & 1;
+            const uint32_t aph = (tile_count >> 1) & 1;
+            if (et < kBN) bias_s[et] = g.bias != nullptr ? g.bias[static_cast<int64_t>(grp) * g.N + n0 + et] : 0.f;
+            const int64_t row = static_cast<int64_t>(m0) + row_in_tile;
+            const bool has_res = residual != nullptr && row < g.M;
+            const uint4* res_row = reinterpret_cast<const uint4*>(
+                residual + (static_cast<int64_t>(grp) * g.M + (has_res ? row : 0)) * g.N + n0 + sub * 16);
+            uint4 res_cur[2], res_next[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) res_cur[q] = has_res ? res_row[q] : make_uint4(0u, 0u, 0u, 0u);
+            if (!mbar_wait(&tmem_full[buf], aph, kPairWait)) { ok = false; break; }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int r = 0; r < kBoxes; ++r, ++round_count) {
+                const int col = r * 64 + sub * 16;       // first of this thread's 16 columns in the tile
+                uint8_t* box = out_s + (round_count & 1) * kBoxBytes;
+                if (r + 1 < kBoxes) {
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) res_next[q] = has_res ? res_row[(r + 1) * 8 + q] : make_uint4(0u, 0u, 0u, 0u);
+                }
+                uint32_t acc[16];
+                tmem_ld_x16(tmem_base + buf * kBN + lane_addr + col, acc);
+                if (et == 0) bulk_wait_read<1>();
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreadsP) : "memory");
+                tc_wait_ld();
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + col + q * 8);
+                    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + col + q * 8 + 4);
+                    float2 v[4];
+                    v[0] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 0]), __uint_as_float(acc[8 * q + 1])), make_float2(b0.x, b0.y));
+                    v[1] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3])), make_float2(b0.z, b0.w));
+                    v[2] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5])), make_float2(b1.x, b1.y));
+                    v[3] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7])), make_float2(b1.z, b1.w));
+                    if (g.act == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = silu2(v[e]);
+                    }
+                    if (residual != nullptr) {
+                        float2 rr[4];
+                        Vec16<__nv_bfloat16>::unpack2(res_cur[q], rr);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
+                    }
+                    *reinterpret_cast<uint4*>(box + row_in_tile * 128 + (((sub * 2 + q) ^ swz) << 4)) = Vec16<__nv_bfloat16>::pack2(v);
+                }
+                if (r == kBoxes - 1) {   // this CTA's half of the accumulator has been read: one arrival per warp in the leader
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
+                }
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreadsP) : "memory");
+                if (et == 0) {
+                    if (m0 < g.M) tma_store_3d(&tmap_o, box, 2 * n0 + r * 128, m0, grp);
+                    bulk_commit();
+                }
+#pragma unroll
+                for (int q = 0; q < 2; ++q) res_cur[q] = res_next[q];
+            }
+        }
+        if (et == 0) bulk_wait<0>();
+        if (!ok) {
+            s_abort = 1;
+            if (g.status != nullptr) atomicExch(g.status, 1);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                          // the peer may still read this CTA's shared memory or signal its barriers
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
     static bool tried = false;
@@ -333,6 +603,24 @@ extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float
     if (!attr_set[dev.index]) {
         cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
         attr_set[dev.index] = true;
+    }
+    // CTA pairs by default; TB200_GEMM_PAIR=0 in the environment selects the single-CTA kernel (for comparison)
+    static const bool use_pair = []() { const char* e = getenv("TB200_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+    if (use_pair && M > kBM) {
+        static bool pair_attr[64] = {};
+        if (!pair_attr[dev.index]) {
+            cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPBytes));
+            pair_attr[dev.index] = true;
+        }
+        CUtensorMap twh;
+        if (!make_tmap3(&twh, w, 2ull * K, static_cast<uint64_t>(N), ug, kBN / 2)) return TB200_ERR_DRIVER;
+        const int64_t tiles = static_cast<int64_t>(groups) * ((M + 2 * kBM - 1) / (2 * kBM)) * (N / kBN);
+        int64_t pairs = dev.sm_count / 2;
+        if (pairs > tiles) pairs = tiles;
+        gemm_bf16_pair_kernel<<<static_cast<unsigned>(2 * pairs), kThreadsP, kSmemPBytes, static_cast<cudaStream_t>(stream)>>>(
+            ta, twh, to, g, static_cast<const __nv_bfloat16*>(residual));
+        count_launch();
+        return launch_status();
     }
     const int64_t total = static_cast<int64_t>(groups) * ((M + kBM - 1) / kBM) * (N / kBN);
     const int64_t grid = total < dev.sm_count ? total : dev.sm_count;
