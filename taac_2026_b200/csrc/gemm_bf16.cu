@@ -6,15 +6,18 @@
 // one group.  A library batched GEMM leaves the bias, the SiLU and the residual to further passes over the
 // result; here they ride in the epilogue, and the result is written once.
 //
-// One persistent CTA per SM walks the (group, row tile, column tile) list round-robin, column tiles fastest,
-// so that the CTAs working side by side share the activation rows.  Roles in a CTA of 320 threads:
-//   warp 0      TMA producer: ring of {A 128 x 64, W 256 x 64} bf16 tiles, 128-byte swizzle, 3 stages
+// Two kernels share the file.  `gemm_bf16_pair_kernel` (further down) is the one that normally runs: clusters of
+// two CTAs on 256 x 256 tiles with tcgen05 cta_group::2.  `gemm_bf16_kernel` is its single-CTA form, used for
+// matrices of at most 128 rows and when TB200_GEMM_PAIR=0 is set in the environment (for comparison):
+// one persistent CTA per SM walks the (group, row tile, column tile) list round-robin, column tiles fastest,
+// so that the CTAs working side by side share the activation rows.  Roles in its CTA of 320 threads:
+//   warp 0      TMA producer: ring of {A 128 x 64, W 256 x 64} bf16 tiles, 128-byte swizzle, 4 stages
 //   warp 1      MMA issuer (one lane): tcgen05.mma kind::f16 128 x 256 x 16, the whole K range of a tile
 //               accumulates in one of two 256-column TMEM buffers
-//   warps 2..9  epilogue: a thread owns one row and 128 columns of the tile, reads them from TMEM 16 at a
-//               time, adds the bias, applies the activation and writes bf16 into a 128-byte-swizzled staging
-//               tile that one thread hands to TMA (the residual tile arrives there by TMA as well, during the
-//               K loop); meanwhile the tensor cores fill the other TMEM buffer with the next tile.
+//   warps 2..9  epilogue: a thread owns one row, reads 32 of its columns from TMEM per round, adds the bias, applies
+//               the activation, adds the residual (read from global memory a round ahead) and writes bf16 into one
+//               of two alternating 128-byte-swizzled 16 KB staging boxes that one thread hands to TMA; meanwhile the
+//               tensor cores fill the other TMEM buffer with the next tile.
 // Every wait on an mbarrier is bounded; a wait that gives up raises the status word and all roles drain out
 // through the final barrier, where the TMEM allocation is released.
 #include <cudaTypedefs.h>
