@@ -51,3 +51,28 @@ def test_unavailable_backend_is_runtime_error(monkeypatch):
         ops.rms_norm(torch.ones(2, 4), torch.ones(4))
     with pytest.raises(RuntimeError, match="cuda backend requested but"):
         ops.resolved_embedding_bag_mean_backend(torch.ones(4, 4), torch.ones(2, 2, dtype=torch.long))
+
+
+def test_newer_entry_points_have_no_cpu_path_either(monkeypatch):
+    """The fused tokenizer tail, the packed-layout index kernel, the grouped GEMM and the attention kernels refuse
+    CPU tensors when the backend is available, and say that the backend is missing when it is not."""
+    x = torch.ones(4, 64, dtype=torch.bfloat16)
+    w = torch.ones(1, 256, 64, dtype=torch.bfloat16)
+    ids = torch.zeros(4, dtype=torch.long)
+    calls = [
+        lambda: ops.grouped_linear(x[None], w),
+        lambda: ops.token_tail(x, x[0], x[0], x, ids, None, None, x[0]),
+        lambda: ops.packed_token_index(torch.zeros(1, 1, 4, dtype=torch.long), None, torch.zeros(1, dtype=torch.long),
+                                       torch.zeros(1, 4, dtype=torch.int32), torch.tensor([0, 4]), torch.tensor([2]),
+                                       torch.tensor([0]), torch.tensor([0]), 4),
+        lambda: ops.varlen_attention(x.view(4, 1, 64), x.view(4, 1, 64), x.view(4, 1, 64), cu_rows=torch.tensor([0, 4], dtype=torch.int32),
+                                     max_rows=4, kernel=4),
+    ]
+    monkeypatch.setattr(ops, "cuda_available", lambda: True)
+    for call in calls:
+        with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+            call()
+    monkeypatch.setattr(ops, "cuda_available", lambda: False)
+    for call in calls:
+        with pytest.raises(RuntimeError, match="cuda backend requested but"):
+            call()
