@@ -537,17 +537,18 @@ attn_fewq_kernel(const AttnArgs a) {
 
     // Work split.  A sample of at most 16 queries: warp w owns head w of the block's heads and its only query tile.
     // A sample with more: when the block's warps all belong to one sample (H a multiple of the warps per
-    // block), they go through its heads together, warp w taking query tiles w, w + 4, ...; the warps then read
-    // the same keys and values at about the same time, so all but one of them are served by the L2 instead of
-    // re-reading a long sample from HBM once per query tile.
+    // block), its (head, query tile) pairs are dealt to the warps head by head, warp w taking pairs w, w + 4, ...;
+    // warps that work on the same head then read the same keys and values at about the same time, so all but
+    // one of them are served by the L2 instead of re-reading a long sample from HBM once per query tile, and no
+    // warp idles when a head has fewer query tiles than the block has warps.
     const bool together = lq > kFqRows && a.H % kFqWarps == 0;
     const int h_first = together ? h_own - warp : h_own;
-    const int n_heads = together ? kFqWarps : 1;
-    const int r_first = together ? warp * kFqRows : 0;
-    const int r_step = together ? kFqWarps * kFqRows : kFqRows;
+    const int n_qt = (lq + kFqRows - 1) / kFqRows;
+    const int n_items = together ? kFqWarps * n_qt : n_qt;
 
-    for (int hh = 0; hh < n_heads; ++hh) {
-    const int h = h_first + hh;
+    for (int item = together ? warp : 0; item < n_items; item += together ? kFqWarps : 1) {
+    const int h = h_first + (together ? item / n_qt : 0);
+    const int r0 = (together ? item % n_qt : item) * kFqRows;
     const T* q = static_cast<const T*>(a.q) + q_base * a.q_sl + static_cast<int64_t>(h) * a.q_sh;
     const T* k = static_cast<const T*>(a.k) + row_base * a.k_sl + static_cast<int64_t>(h) * a.k_sh;
     const T* v = static_cast<const T*>(a.v) + row_base * a.v_sl + static_cast<int64_t>(h) * a.v_sh;
@@ -566,7 +567,7 @@ attn_fewq_kernel(const AttnArgs a) {
         }
     };
 
-    for (int r0 = r_first; r0 < lq; r0 += r_step) {
+    {
         // keys the tile's last existing query can see
         const int q_last = min(r0 + kFqRows, lq) - 1;
         const int kv_end = causal ? min(lk, q_last + off + 1) : lk;
@@ -692,7 +693,7 @@ attn_fewq_kernel(const AttnArgs a) {
             }
         }
     }
-    }   // heads
+    }   // (head, query tile) pairs
 }
 
 template <typename T, int D>
