@@ -203,7 +203,10 @@ int tb200_bias_act_rows(void* x, int64_t rows, int32_t cols, const void* bias, i
  * key_valid: device uint8[B, Lk] or NULL; when given it replaces the (seq_len, ns_start) rule by
  * "key k is valid iff key_valid[b, k] != 0" for arbitrary padding patterns (several sequence domains
  * with separators, experiments/onetrans/model.py:287-315); padded queries are the invalid positions.
- * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.
+ * D in {32, 64, 128}; dtype TB200_BF16 or TB200_F16.  dtype TB200_F32 (any D <= 256 that is a multiple of 4, at
+ * most 8192 keys per sample, strides multiples of 4) selects a plain fp32 kernel — every product, the softmax and
+ * the weighted sum in fp32, one warp per query row — for comparing an fp32 model with the reference's fp32 torch
+ * path (`_torch_flash_attention`, flash_attention.py:552-570); it ignores `kernel` and is not a serving kernel.
  * kernel: 0 = automatic, 1 = mma.sync kernel (every supported shape), 2 = tcgen05/TMEM kernel (D = 64, bf16,
  * no key_valid map; TB200_ERR_UNSUPPORTED otherwise), 3 = one warp per (sample, head) (D = 64, at most 32
  * rows), 4 = one warp per (sample, head) streaming the keys in tiles of 16 against 16 queries in registers
@@ -279,7 +282,11 @@ int tb200_packed_token_index(const int64_t* values, const int64_t* timestamps, c
  * a batched library GEMM plus separate bias / SiLU / residual passes would otherwise serve.
  * a: [groups, M, K], w: [groups, N, K] (stacked `nn.Linear.weight`), out and residual: [groups, M, N], all
  * bf16 and contiguous; bias: fp32 [groups, N]; bias and residual may be NULL; residual may be `out` itself.
- * act: 0 = none, 1 = SiLU.  fp32 accumulation over the whole K, one rounding to bf16 at the end.
+ * act: 0 = none, 1 = SiLU, 2 = SiLU-gated: the N rows of w[g] are interleaved per 128 hidden columns as
+ * [128 gate rows | 128 value rows] (the order tb200_fp8_gemm's mode 0 takes, bias likewise), out is
+ * [groups, M, N / 2] = silu(gate) * value — the first half of `down(silu(gate) * value)`
+ * (experiments/tokenformer/model.py:118-128) on the bf16 tensor cores; no residual with act 2.
+ * fp32 accumulation over the whole K, one rounding to bf16 at the end.
  * N % 256 == 0, K % 64 == 0.  groups = 1 is a plain linear layer.  status_word: optional device int32 that the
  * kernel sets to 1 if one of its bounded waits gave up (the output is then incomplete). */
 int tb200_gemm_bf16_grouped(const void* a, const void* w, const float* bias, const void* residual, void* out,
@@ -307,7 +314,12 @@ int tb200_gemm_bf16_grouped(const void* a, const void* w, const float* bias, con
  *  - the entry point calls no cudaMalloc / cudaFree and no allocating library routine;
  *  - every call on a device uses the same array: two calls that overlap on the GPU (different streams,
  *    or graphs replayed concurrently) race on it.  Calls on one stream are ordered and safe.  Nothing
- *    in the array needs clearing between calls: each call overwrites all bytes it later reads.
+ *    in the data part of the array needs clearing between calls: each call overwrites all bytes it later
+ *    reads.  The array's first word is a status word: the call clears it (a 4-byte memset on `stream`) and
+ *    the two GEMM kernels set it to 1 if one of their bounded waits gave up — read it with
+ *    tb200_ffn_fp8_static_status;
+ *  - every argument check of the three steps is made before the first launch: a negative return value
+ *    means that nothing was enqueued.
  * w_up_fp8 / w_up_scales / b_up and w_down_* are exactly what the two tb200_fp8_gemm calls take
  * (for gated != 0 the [gate | value] row interleave of mode 0); b_up, b_down and residual may be NULL.
  * d_in % 128 == 0, hidden % 256 == 0, d_out % 256 == 0. */
@@ -318,6 +330,12 @@ int tb200_ffn_fp8_fwd_static(const void* x_bf16, const void* w_up_fp8, const flo
 
 /* Size in bytes of the fixed array behind tb200_ffn_fp8_fwd_static. */
 int64_t tb200_ffn_fp8_static_scratch_bytes(void);
+
+/* Status word of the calls to tb200_ffn_fp8_fwd_static enqueued on `stream` so far (current device):
+ * *value = 0 if every kernel of the last call ran to completion, 1 if a bounded wait inside one of them
+ * gave up (y is then incomplete).  Copies four bytes to the host and SYNCHRONISES `stream`; allocates
+ * nothing.  No counterpart in the reference. */
+int tb200_ffn_fp8_static_status(void* stream, int32_t* value);
 
 #ifdef __cplusplus
 }

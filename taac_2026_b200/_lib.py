@@ -54,6 +54,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         _INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _P],
     ),
     "tb200_ffn_fp8_static_scratch_bytes": (_I64, []),
+    "tb200_ffn_fp8_static_status": (_INT, [_P, _P]),
     "tb200_sequence_prepare": (_INT, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _P, _P, _P]),
     "tb200_scatter_rows": (_INT, [_P, _I64, _I64, _I32, _P, _P, _I64, _I32, _P, _I64, _P, _I64, _INT, _P]),
     "tb200_gather_rows": (_INT, [_P, _I64, _I32, _P, _INT, _I64, _I64, _I64, _P, _I64, _I32, _INT, _P]),

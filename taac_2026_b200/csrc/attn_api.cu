@@ -12,6 +12,7 @@ bool attn_fewq_supported(const AttnArgs& a, int head_dim);
 int attn_fewq_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 int attn_tiny_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
 int attn_small_forward(const AttnArgs& a, int dtype, cudaStream_t stream);
+int attn_f32_forward(const AttnArgs& a, int head_dim, int max_lq, int max_lk, cudaStream_t stream);
 }  // namespace tb200
 
 extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H, int32_t Lq,
@@ -23,14 +24,14 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     if (B < 0 || H < 1 || Lq < 0 || Lk < 0 || D < 1) return TB200_ERR_SHAPE;
     if (B == 0 || Lq == 0) return TB200_OK;
     if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || strides == nullptr) return TB200_ERR_NULL;
-    if (dtype != TB200_BF16 && dtype != TB200_F16) return TB200_ERR_DTYPE;
-    if (D != 32 && D != 64 && D != 128) return TB200_ERR_UNSUPPORTED;
+    if (dtype != TB200_BF16 && dtype != TB200_F16 && dtype != TB200_F32) return TB200_ERR_DTYPE;
+    if (dtype == TB200_F32 ? (D > 256 || D % 4 != 0) : (D != 32 && D != 64 && D != 128)) return TB200_ERR_UNSUPPORTED;
     if (padded_query_self && cu_rows == nullptr && Lq != Lk) return TB200_ERR_SHAPE;
     if (cu_rows_q != nullptr && (cu_rows == nullptr || key_valid != nullptr)) return TB200_ERR_UNSUPPORTED;
     if (ns_start < 0) return TB200_ERR_SHAPE;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return TB200_ERR_ALIGN;
     for (int i = 0; i < 12; ++i)
-        if (strides[i] % 8 != 0) return TB200_ERR_ALIGN;  // every row must start on a 16-byte boundary
+        if (strides[i] % (dtype == TB200_F32 ? 4 : 8) != 0) return TB200_ERR_ALIGN;  // every row must start on a 16-byte boundary
     if (!device_info().valid) return TB200_ERR_DEVICE;
     AttnArgs a{};
     a.q = q; a.k = k; a.v = v; a.o = o;
@@ -49,6 +50,8 @@ extern "C" int tb200_attn_fwd(const void* q, const void* k, const void* v, void*
     a.scale_log2 = scale * 1.4426950408889634f;
     if (cu_rows != nullptr && total_rows < 0) return TB200_ERR_SHAPE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // fp32 tensors: the plain fp32 kernel of the score-parity mode, whatever `kernel` says
+    if (dtype == TB200_F32) return attn_f32_forward(a, D, Lq, Lk, s);
     // kernel: 0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel, 3 = one-warp-per-(sample, head) kernel for
     // samples of at most 32 rows, 4 = one-warp-per-(sample, head) kernel for few queries against many keys
     const bool tc_ok = attn_tc05_supported(a, D, dtype) && (cu_rows == nullptr || total_rows > 0);

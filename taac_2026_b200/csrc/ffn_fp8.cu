@@ -287,7 +287,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         uint32_t tile_count = 0;
         bool ok = true;
 
-        for (int n = sc.n_first; n < n_tiles && ok && sc.active; n += sc.n_step) {
+        for (int n = sc.n_first; n < n_tiles && sc.active; n += sc.n_step) {
             const int n0 = n * kBN;
             // per-column-tile constants -> shared memory
             asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
@@ -318,7 +318,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             float sa_q0 = next_sa();
             float sa_q1 = next_sa();
 
-            for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G, ++tile_count) {
+            for (int64_t m = sc.j; m < m_tiles; m += sc.G, ++tile_count) {
                 const int64_t row = m * kBM + row_in_tile;
                 const bool row_ok = row < g.M;
                 const int m0 = static_cast<int>(m) * kBM;
@@ -361,11 +361,10 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     const float s_b = sa * sb_s[nb_b][kb];
                     const float2 scale_a = make_float2(s_a, s_a);
                     const float2 scale_b = make_float2(s_b, s_b);
-                    // all epilogue threads wait for the same phase, so they pass or give up together
-                    if (!mbar_wait(&tmem_full[buf], aph)) {
-                        ok = false;
-                        break;
-                    }
+                    // A thread whose wait gives up does not leave the loop: it stops waiting (`ok` stays false) but
+                    // walks the rest of the tile schedule, so it still meets every named barrier the other epilogue
+                    // threads sit in.  Its results are garbage; the status word says so.
+                    if (ok && !mbar_wait(&tmem_full[buf], aph)) ok = false;
                     tc_fence_after_sync();
                     const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
                     // 16 columns at a time: the accumulators already take 64 of the 96 registers a thread may use
@@ -382,8 +381,6 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     tc_fence_before_sync();
                     mbar_arrive(&tmem_empty[buf]);
                 }
-                if (!ok) break;
-
                 // -------------------------------------------------------- tile epilogue
                 // Staging address of this thread's 16-byte piece j of its row (128-byte swizzle: piece ^ row % 8)
                 const int swz = row_in_tile & 7;
@@ -442,10 +439,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     const bool has_res = g.residual != nullptr;
                     if (et == 0) bulk_wait_read<0>();
                     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-                    if (has_res && !mbar_wait(&res_full, tile_count & 1)) {
-                        ok = false;
-                        break;
-                    }
+                    if (has_res && ok && !mbar_wait(&res_full, tile_count & 1)) ok = false;   // keep going, see above
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         uint4* slot = reinterpret_cast<uint4*>(box_row + ((c ^ swz) << 4));
@@ -597,6 +591,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
 // array, which lives in the library's device image: every GPU that loads the library holds these
 // bytes until the process exits, and every call on that GPU shares them.
 constexpr size_t kStaticScratchBytes = size_t(64) << 20;
+constexpr size_t kStaticStatusBytes = 256;   // the array's first bytes: the status word the two GEMMs raise
 static __device__ __align__(256) uint8_t g_ffn_scratch[kStaticScratchBytes];
 
 // In host code `g_ffn_scratch` is only a handle for the runtime, not a device address; the address
@@ -689,33 +684,56 @@ extern "C" int tb200_ffn_fp8_fwd_static(const void* x_bf16, const void* w_up_fp8
                                         const float* b_down, const void* residual, void* y_bf16, int64_t M,
                                         int32_t d_in, int32_t hidden, int32_t d_out, int32_t gated, void* stream) {
     using namespace tb200;
-    if (M < 0 || d_in < 128 || d_in % 128 != 0 || hidden < 256 || hidden % 256 != 0 || d_out < 256 || d_out % 256 != 0)
+    // Every check that one of the three sub-calls would make comes first, so that a negative return
+    // really means "nothing was launched".
+    if (M < 0 || d_in < 128 || d_in % 128 != 0 || d_in > 8192 || hidden < 256 || hidden % 256 != 0 || hidden > 8192 ||
+        d_out < 256 || d_out % 256 != 0)
         return TB200_ERR_SHAPE;
     if (M == 0) return TB200_OK;
+    // the array bounds the rows long before the products below could wrap, or the GEMMs' own row limit is reached
+    if (M > static_cast<int64_t>(kStaticScratchBytes)) return TB200_ERR_SCRATCH;
     if (x_bf16 == nullptr || w_up_fp8 == nullptr || w_up_scales == nullptr || w_down_fp8 == nullptr ||
         w_down_scales == nullptr || y_bf16 == nullptr)
         return TB200_ERR_NULL;
-    // carve the fixed array: [x e4m3 | x scales | hidden e4m3 | hidden scales], each part 256-byte aligned
+    if (!aligned16(x_bf16) || !aligned16(w_up_fp8) || !aligned16(w_down_fp8) || !aligned16(y_bf16) ||
+        (residual != nullptr && !aligned16(residual)))
+        return TB200_ERR_ALIGN;
+    // carve the fixed array: [status word | x e4m3 | x scales | hidden e4m3 | hidden scales], each part 256-byte aligned
     const size_t um = static_cast<size_t>(M);
     const size_t xq_bytes = round256(um * d_in);
     const size_t sx_bytes = round256(um * (d_in / 128) * sizeof(float));
     const size_t h_bytes = round256(um * hidden);
     const size_t sh_bytes = round256(um * (hidden / 128) * sizeof(float));
-    if (xq_bytes + sx_bytes + h_bytes + sh_bytes > kStaticScratchBytes) return TB200_ERR_SCRATCH;
+    if (kStaticStatusBytes + xq_bytes + sx_bytes + h_bytes + sh_bytes > kStaticScratchBytes) return TB200_ERR_SCRATCH;
     uint8_t* base = nullptr;
     const int rc = static_scratch_base(&base);
     if (rc != TB200_OK) return rc;
-    uint8_t* xq = base;
-    float* sx = reinterpret_cast<float*>(base + xq_bytes);
-    uint8_t* h = base + xq_bytes + sx_bytes;
-    float* sh = reinterpret_cast<float*>(base + xq_bytes + sx_bytes + h_bytes);
-    // Nothing in the array has to start at zero: the three kernels below overwrite every byte they later
-    // read (rows [0, M) of each part), so what an earlier call left behind is never seen.
+    int32_t* status = reinterpret_cast<int32_t*>(base);
+    uint8_t* xq = base + kStaticStatusBytes;
+    float* sx = reinterpret_cast<float*>(xq + xq_bytes);
+    uint8_t* h = xq + xq_bytes + sx_bytes;
+    float* sh = reinterpret_cast<float*>(h + h_bytes);
+    // The status word is the one part of the array that must start at zero: the kernels only ever raise it.
+    // The data parts need no clearing, the three kernels overwrite every byte they later read (rows [0, M)).
+    const cudaError_t e = cudaMemsetAsync(status, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return static_cast<int>(e);
     int code = tb200_quant_act_1x128(x_bf16, xq, sx, M, d_in, stream);
     if (code != TB200_OK) return code;
     code = tb200_fp8_gemm(xq, sx, w_up_fp8, w_up_scales, b_up, nullptr, h, sh, M, gated ? 2 * hidden : hidden, d_in,
-                          gated ? 0 : 1, nullptr, stream);
+                          gated ? 0 : 1, status, stream);
     if (code != TB200_OK) return code;
     return tb200_fp8_gemm(h, sh, w_down_fp8, w_down_scales, b_down, residual, y_bf16, nullptr, M, d_out, hidden, 2,
-                          nullptr, stream);
+                          status, stream);
+}
+
+extern "C" int tb200_ffn_fp8_static_status(void* stream, int32_t* value) {
+    using namespace tb200;
+    if (value == nullptr) return TB200_ERR_NULL;
+    uint8_t* base = nullptr;
+    const int rc = static_scratch_base(&base);
+    if (rc != TB200_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(value, base, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return e == cudaSuccess ? TB200_OK : static_cast<int>(e);
 }

@@ -53,7 +53,7 @@ struct GArgs {
     int32_t* status;
     int32_t groups, N, K;
     int64_t M;
-    int32_t act;            // 0 = none, 1 = SiLU
+    int32_t act;            // 0 = none, 1 = SiLU, 2 = SiLU-gated pairs (column c gates column c + 128 of its 256-column tile)
     int32_t has_residual;
 };
 
@@ -185,6 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ---------------------------------------------------------------- epilogue
         const int et = threadIdx.x - 64;          // 0..255
+        const bool gated = g.act == 2;
         const int sub = et >> 7;                  // columns [32 sub, 32 sub + 32) of a round's 64
         const int quarter = warp & 3;             // TMEM lanes [32 quarter, +32) are visible to this warp
         const int row_in_tile = quarter * 32 + lane;
@@ -193,7 +194,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t tile_count = 0;
         uint32_t round_count = 0;                 // rounds so far: staging box round_count % 2
         bool ok = true;
-        for (int64_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++tile_count) {
+        for (int64_t t = blockIdx.x; t < total; t += gridDim.x, ++tile_count) {
             int n0, m0, grp;
             decode(t, n0, m0, grp);
             const uint32_t buf = tile_count & 1;
@@ -207,21 +208,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint4 res_cur[4], res_next[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) res_cur[q] = has_res ? res_row[q] : make_uint4(0u, 0u, 0u, 0u);   // plain loads: `out` may be this tensor
-            if (!mbar_wait(&tmem_full[buf], aph)) { ok = false; break; }
+            // A thread whose wait gives up stops waiting but keeps walking the tile list, so that it still meets
+            // every named barrier the other epilogue threads sit in; what it writes is garbage and the status
+            // word says so.
+            if (ok && !mbar_wait(&tmem_full[buf], aph)) ok = false;
             tc_fence_after_sync();
+            const int n_rounds = gated ? kBoxes / 2 : kBoxes;   // gated: 128 gate + 128 value columns -> 128 outputs
 #pragma unroll 1
-            for (int r = 0; r < kBoxes; ++r, ++round_count) {
+            for (int r = 0; r < n_rounds; ++r, ++round_count) {
                 const int col = r * 64 + sub * 32;       // first of this thread's 32 columns in the tile
                 uint8_t* box = out_s + (round_count & 1) * kBoxBytes;
-                if (r + 1 < kBoxes) {
+                if (r + 1 < n_rounds) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) res_next[q] = has_res ? res_row[(r + 1) * 8 + q] : make_uint4(0u, 0u, 0u, 0u);
                 }
-                uint32_t acc[32];
+                uint32_t acc[32], accv[32];
                 tmem_ld_2x16(tmem_base + buf * kBN + lane_addr + col, acc);
+                if (gated) tmem_ld_2x16(tmem_base + buf * kBN + lane_addr + 128 + col, accv);
                 if (et == 0) bulk_wait_read<1>();   // the store that used this box two rounds ago has read it
                 asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
                 tc_wait_ld(acc);
+                if (gated) tc_wait_ld(accv);   // no second wait in hardware terms; it keeps the uses of accv below the wait
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const float4 b0 = *reinterpret_cast<const float4*>(bias_s + col + q * 8);
@@ -231,9 +238,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     v[1] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3])), make_float2(b0.z, b0.w));
                     v[2] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5])), make_float2(b1.x, b1.y));
                     v[3] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7])), make_float2(b1.z, b1.w));
-                    if (g.act == 1) {
+                    if (g.act >= 1) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) v[e] = silu2(v[e]);
+                    }
+                    if (gated) {   // silu(gate) * value, the value columns sit 128 further right in the accumulator
+                        const float4 c0 = *reinterpret_cast<const float4*>(bias_s + 128 + col + q * 8);
+                        const float4 c1 = *reinterpret_cast<const float4*>(bias_s + 128 + col + q * 8 + 4);
+                        v[0] = __fmul2_rn(v[0], __fadd2_rn(make_float2(__uint_as_float(accv[8 * q + 0]), __uint_as_float(accv[8 * q + 1])), make_float2(c0.x, c0.y)));
+                        v[1] = __fmul2_rn(v[1], __fadd2_rn(make_float2(__uint_as_float(accv[8 * q + 2]), __uint_as_float(accv[8 * q + 3])), make_float2(c0.z, c0.w)));
+                        v[2] = __fmul2_rn(v[2], __fadd2_rn(make_float2(__uint_as_float(accv[8 * q + 4]), __uint_as_float(accv[8 * q + 5])), make_float2(c1.x, c1.y)));
+                        v[3] = __fmul2_rn(v[3], __fadd2_rn(make_float2(__uint_as_float(accv[8 * q + 6]), __uint_as_float(accv[8 * q + 7])), make_float2(c1.z, c1.w)));
                     }
                     if (residual != nullptr) {
                         float2 rr[4];
@@ -243,14 +258,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     *reinterpret_cast<uint4*>(box + row_in_tile * 128 + (((sub * 4 + q) ^ swz) << 4)) = Vec16<__nv_bfloat16>::pack2(v);
                 }
-                if (r == kBoxes - 1) {   // every column of this buffer has been read: the tensor cores may reuse it
+                if (r == n_rounds - 1) {   // every column of this buffer has been read: the tensor cores may reuse it
                     tc_fence_before_sync();
                     mbar_arrive(&tmem_empty[buf]);
                 }
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
                 if (et == 0) {
-                    tma_store_3d(&tmap_o, box, 2 * n0 + r * 128, m0, grp);
+                    tma_store_3d(&tmap_o, box, (gated ? n0 : 2 * n0) + r * 128, m0, grp);
                     bulk_commit();
                 }
 #pragma unroll
@@ -283,12 +298,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // commits; "accumulator empty" collects one arrival per epilogue warp of both CTAs in the leader.
 // ------------------------------------------------------------------------------------------------
 constexpr int kStagesP = 6;
-constexpr int kEpiWarpsP = 16;                 // four warps per TMEM lane quarter: the epilogue of a short-K tile is as long as its MMAs
+constexpr int kEpiWarpsP = 8;                  // two warps per TMEM lane quarter, each with a staging box and TMA stores of its own
 constexpr int kEpiThreadsP = kEpiWarpsP * 32;
 constexpr int kThreadsP = 64 + kEpiThreadsP;
 constexpr uint32_t kBHalfBytes = kBBytes / 2;                 // 16 KB: this CTA's half of the weight tile
 constexpr uint32_t kStagePBytes = kABytes + kBHalfBytes;      // 32 KB
-constexpr size_t kSmemPBytes = static_cast<size_t>(kStagesP) * kStagePBytes + kOutBytes + 1024;
+constexpr uint32_t kWarpBoxBytes = 32 * 128;                  // one epilogue warp's staging box: 32 rows x 64 bf16
+constexpr size_t kSmemPBytes = static_cast<size_t>(kStagesP) * kStagePBytes + kEpiWarpsP * kWarpBoxBytes + 1024;
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;                   // shared::cluster address of the pair's even CTA
 constexpr uint32_t kPairWait = 1u << 18;                      // bounded waits give up early in this variant
 
@@ -329,6 +345,7 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerMask) : "memory");
 }
 
+template <bool GATED, bool RES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsP, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                       const __grid_constant__ CUtensorMap tmap_o, const GArgs g, const __nv_bfloat16* __restrict__ residual) {
@@ -338,7 +355,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     __shared__ uint64_t tmem_full[2];
     __shared__ uint64_t tmem_empty[2];          // used in the leader only
     __shared__ uint32_t tmem_base_slot;
-    __shared__ __align__(16) float bias_s[kBN];
     __shared__ int s_abort;
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -451,80 +467,118 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
     } else {
         // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
-        const int et = threadIdx.x - 64;          // 0..511
-        const int sub = et >> 7;                  // columns [16 sub, 16 sub + 16) of a round's 64
-        const int quarter = warp & 3;
+        // Every warp works alone: it owns the 32 rows of its TMEM lane quarter and 128 of the tile's 256 columns, and
+        // sends them out as two units of 64 columns: 32 columns at a time from TMEM to registers, bias / activation /
+        // residual, bf16 into its private 4 KB staging box (32 rows x 128 bytes, 128-byte swizzle), one TMA store per
+        // unit.  No barrier spans the CTA, so no warp waits for the slowest one or for another warp's store, and the
+        // accumulator buffer is handed back as soon as the warp's last load has landed in registers.  Boxes are 128
+        // bytes wide on purpose: the TMA unit works row by row, and narrower boxes (64-byte rows, 16 warps) doubled
+        // its store requests and slowed the long-K shapes by a tenth, because the loads of the K loop queue behind them.
+        const int ew = warp - 2;                  // 0..7
+        constexpr bool gated = GATED;
+        const int half = ew >> 2;                 // non-gated: columns [128 half, +128); gated: outputs [64 half, +64)
+        const int quarter = warp & 3;             // TMEM lanes [32 quarter, +32) are the ones this warp may read
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        const int swz = row_in_tile & 7;
+        uint8_t* box = out_s + ew * kWarpBoxBytes;
+        const int swz = lane & 7;                 // 128-byte swizzle: 16-byte piece ^ (row % 8)
+        constexpr int kUnits = gated ? 1 : 2;
         uint32_t tile_count = 0;
-        uint32_t round_count = 0;
         bool ok = true;
-        for (int64_t t = pair; t < total && ok; t += n_pairs, ++tile_count) {
+        for (int64_t t = pair; t < total; t += n_pairs, ++tile_count) {
             int n0, m0, grp;
             decode(t, n0, m0, grp);
             const uint32_t buf = tile_count & 1;
             const uint32_t aph = (tile_count >> 1) & 1;
-            if (et < kBN) bias_s[et] = g.bias != nullptr ? g.bias[static_cast<int64_t>(grp) * g.N + n0 + et] : 0.f;
             const int64_t row = static_cast<int64_t>(m0) + row_in_tile;
-            const bool has_res = residual != nullptr && row < g.M;
-            const uint4* res_row = reinterpret_cast<const uint4*>(
-                residual + (static_cast<int64_t>(grp) * g.M + (has_res ? row : 0)) * g.N + n0 + sub * 16);
-            uint4 res_cur[2], res_next[2];
+            const bool has_res = RES && row < g.M;
+            const float* bias_t = g.bias != nullptr ? g.bias + static_cast<int64_t>(grp) * g.N + n0 : nullptr;
+            // this thread's residual row: plain loads (`out` may be this tensor), a 32-column piece ahead of its use
+            const uint4* res_row = RES ? reinterpret_cast<const uint4*>(
+                residual + (static_cast<int64_t>(grp) * g.M + (has_res ? row : 0)) * g.N + n0 + half * 128) : nullptr;
+            uint4 res[RES ? 4 : 1];
+            if (RES) {
 #pragma unroll
-            for (int q = 0; q < 2; ++q) res_cur[q] = has_res ? res_row[q] : make_uint4(0u, 0u, 0u, 0u);
-            if (!mbar_wait(&tmem_full[buf], aph, kPairWait)) { ok = false; break; }
+                for (int q = 0; q < 4; ++q) res[RES ? q : 0] = has_res ? res_row[q] : make_uint4(0u, 0u, 0u, 0u);
+            }
+            // A warp whose wait gives up stops waiting but keeps walking the tile list (it still arrives on the
+            // accumulator barrier, so the other roles are not held up by it); its output is garbage, the status word says so.
+            if (ok) {   // one lane polls, the warp follows
+                int passed = 1;
+                if (lane == 0) passed = mbar_wait(&tmem_full[buf], aph, kPairWait) ? 1 : 0;
+                if (__shfl_sync(0xffffffffu, passed, 0) == 0) ok = false;
+            }
             tc_fence_after_sync();
 #pragma unroll 1
-            for (int r = 0; r < kBoxes; ++r, ++round_count) {
-                const int col = r * 64 + sub * 16;       // first of this thread's 16 columns in the tile
-                uint8_t* box = out_s + (round_count & 1) * kBoxBytes;
-                if (r + 1 < kBoxes) {
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) res_next[q] = has_res ? res_row[(r + 1) * 8 + q] : make_uint4(0u, 0u, 0u, 0u);
+            for (int piece = 0; piece < 2 * kUnits; ++piece) {       // 32 accumulator columns per piece, two pieces per store
+                const int sub = piece & 1;
+                const int col = gated ? half * 64 + piece * 32 : half * 128 + piece * 32;   // first accumulator column
+                uint32_t acc[32], accv[gated ? 32 : 1];
+                tmem_ld_2x16(tmem_base + buf * kBN + lane_addr + col, acc);
+                if (gated) tmem_ld_2x16(tmem_base + buf * kBN + lane_addr + 128 + col, *reinterpret_cast<uint32_t (*)[32]>(&accv[0]));
+                if (sub == 0 && lane == 0) bulk_wait_read<0>();     // this warp's previous store has read the box
+                tc_wait_ld(acc);
+                if (gated) tc_wait_ld(*reinterpret_cast<uint32_t (*)[32]>(&accv[0]));
+                if (piece == 2 * kUnits - 1) {          // the warp holds its share of the buffer in registers: hand it back
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
+                } else {
+                    __syncwarp();
                 }
-                uint32_t acc[16];
-                tmem_ld_x16(tmem_base + buf * kBN + lane_addr + col, acc);
-                if (et == 0) bulk_wait_read<1>();
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreadsP) : "memory");
-                tc_wait_ld();
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const float4 b0 = *reinterpret_cast<const float4*>(bias_s + col + q * 8);
-                    const float4 b1 = *reinterpret_cast<const float4*>(bias_s + col + q * 8 + 4);
+                for (int q = 0; q < 4; ++q) {
+                    float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+                    if (bias_t != nullptr) {
+                        b0 = __ldg(reinterpret_cast<const float4*>(bias_t + col + q * 8));
+                        b1 = __ldg(reinterpret_cast<const float4*>(bias_t + col + q * 8 + 4));
+                    }
                     float2 v[4];
                     v[0] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 0]), __uint_as_float(acc[8 * q + 1])), make_float2(b0.x, b0.y));
                     v[1] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3])), make_float2(b0.z, b0.w));
                     v[2] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5])), make_float2(b1.x, b1.y));
                     v[3] = __fadd2_rn(make_float2(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7])), make_float2(b1.z, b1.w));
-                    if (g.act == 1) {
+                    if (g.act >= 1) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) v[e] = silu2(v[e]);
                     }
-                    if (residual != nullptr) {
+                    if (gated) {   // silu(gate) * value, the value columns sit 128 further right in the accumulator
+                        float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
+                        if (bias_t != nullptr) {
+                            c0 = __ldg(reinterpret_cast<const float4*>(bias_t + 128 + col + q * 8));
+                            c1 = __ldg(reinterpret_cast<const float4*>(bias_t + 128 + col + q * 8 + 4));
+                        }
+                        constexpr int G = gated ? 1 : 0;   // keeps the indices inside accv[1] in the non-gated instantiation
+                        v[0] = __fmul2_rn(v[0], __fadd2_rn(make_float2(__uint_as_float(accv[G * (8 * q + 0)]), __uint_as_float(accv[G * (8 * q + 1)])), make_float2(c0.x, c0.y)));
+                        v[1] = __fmul2_rn(v[1], __fadd2_rn(make_float2(__uint_as_float(accv[G * (8 * q + 2)]), __uint_as_float(accv[G * (8 * q + 3)])), make_float2(c0.z, c0.w)));
+                        v[2] = __fmul2_rn(v[2], __fadd2_rn(make_float2(__uint_as_float(accv[G * (8 * q + 4)]), __uint_as_float(accv[G * (8 * q + 5)])), make_float2(c1.x, c1.y)));
+                        v[3] = __fmul2_rn(v[3], __fadd2_rn(make_float2(__uint_as_float(accv[G * (8 * q + 6)]), __uint_as_float(accv[G * (8 * q + 7)])), make_float2(c1.z, c1.w)));
+                    }
+                    if (RES) {
                         float2 rr[4];
-                        Vec16<__nv_bfloat16>::unpack2(res_cur[q], rr);
+                        Vec16<__nv_bfloat16>::unpack2(res[RES ? q : 0], rr);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) v[e] = __fadd2_rn(v[e], rr[e]);
                     }
-                    *reinterpret_cast<uint4*>(box + row_in_tile * 128 + (((sub * 2 + q) ^ swz) << 4)) = Vec16<__nv_bfloat16>::pack2(v);
+                    *reinterpret_cast<uint4*>(box + lane * 128 + (((sub * 4 + q) ^ swz) << 4)) = Vec16<__nv_bfloat16>::pack2(v);
                 }
-                if (r == kBoxes - 1) {   // this CTA's half of the accumulator has been read: one arrival per warp in the leader
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
-                }
-                fence_proxy_async_smem();
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreadsP) : "memory");
-                if (et == 0) {
-                    if (m0 < g.M) tma_store_3d(&tmap_o, box, 2 * n0 + r * 128, m0, grp);
-                    bulk_commit();
-                }
+                if (RES && piece + 1 < 2 * kUnits) {   // the next piece's residual columns
 #pragma unroll
-                for (int q = 0; q < 2; ++q) res_cur[q] = res_next[q];
+                    for (int q = 0; q < 4; ++q) res[RES ? q : 0] = has_res ? res_row[(piece + 1) * 4 + q] : make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (sub == 1) {
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int32_t x_bytes = gated ? n0 + half * 128 : 2 * n0 + half * 256 + (piece >> 1) * 128;
+                        const int32_t y = m0 + quarter * 32;
+                        if (y < g.M) tma_store_3d(&tmap_o, box, x_bytes, y, grp);   // rows past M are clipped by the tensor map
+                        bulk_commit();
+                    }
+                }
             }
         }
-        if (et == 0) bulk_wait<0>();
+        if (lane == 0) bulk_wait<0>();            // the last store must have left shared memory before the CTA ends
         if (!ok) {
             s_abort = 1;
             if (g.status != nullptr) atomicExch(g.status, 1);
@@ -557,17 +611,18 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return fn;
 }
 
-// [groups, rows, row_bytes] bytes, boxes of box_rows x 128 bytes inside one group, 128-byte swizzle
-bool make_tmap3(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+// [groups, rows, row_bytes] bytes, boxes of box_rows x box_bytes (128 or 64) inside one group, swizzle of the box width
+bool make_tmap3(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t groups, uint32_t box_rows,
+                uint32_t box_bytes = 128) {
     PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
     if (fn == nullptr) return false;
     const cuuint64_t dims[3] = {row_bytes, rows, groups};
     const cuuint64_t strides[2] = {row_bytes, row_bytes * rows};
-    const cuuint32_t box[3] = {128, box_rows, 1};
+    const cuuint32_t box[3] = {box_bytes, box_rows, 1};
     const cuuint32_t elem[3] = {1, 1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
@@ -579,7 +634,7 @@ extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float
                                        int32_t* status_word, void* stream) {
     using namespace tb200;
     if (groups < 0 || M < 0 || N < kBN || N % kBN != 0 || K < 64 || K % 64 != 0) return TB200_ERR_SHAPE;
-    if (act < 0 || act > 1) return TB200_ERR_UNSUPPORTED;
+    if (act < 0 || act > 2 || (act == 2 && residual != nullptr)) return TB200_ERR_UNSUPPORTED;
     if (groups == 0 || M == 0) return TB200_OK;
     if (a == nullptr || w == nullptr || out == nullptr) return TB200_ERR_NULL;
     if (!aligned16(a) || !aligned16(w) || !aligned16(out) || (residual != nullptr && !aligned16(residual)) ||
@@ -590,7 +645,7 @@ extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float
     CUtensorMap ta, tw, to;
     const uint64_t ug = static_cast<uint64_t>(groups), um = static_cast<uint64_t>(M);
     if (!make_tmap3(&ta, a, 2ull * K, um, ug, kBM) || !make_tmap3(&tw, w, 2ull * K, static_cast<uint64_t>(N), ug, kBN) ||
-        !make_tmap3(&to, out, 2ull * N, um, ug, kBM))
+        !make_tmap3(&to, out, act == 2 ? static_cast<uint64_t>(N) : 2ull * N, um, ug, kBM))
         return TB200_ERR_DRIVER;
     GArgs g{};
     g.bias = bias;
@@ -612,16 +667,26 @@ extern "C" int tb200_gemm_bf16_grouped(const void* a, const void* w, const float
     if (use_pair && M > kBM) {
         static bool pair_attr[64] = {};
         if (!pair_attr[dev.index]) {
-            cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPBytes));
+            cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPBytes));
+            cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPBytes));
+            cudaFuncSetAttribute(gemm_bf16_pair_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPBytes));
             pair_attr[dev.index] = true;
         }
-        CUtensorMap twh;
+        CUtensorMap twh, tow;
         if (!make_tmap3(&twh, w, 2ull * K, static_cast<uint64_t>(N), ug, kBN / 2)) return TB200_ERR_DRIVER;
+        if (!make_tmap3(&tow, out, act == 2 ? static_cast<uint64_t>(N) : 2ull * N, um, ug, 32)) return TB200_ERR_DRIVER;
         const int64_t tiles = static_cast<int64_t>(groups) * ((M + 2 * kBM - 1) / (2 * kBM)) * (N / kBN);
         int64_t pairs = dev.sm_count / 2;
         if (pairs > tiles) pairs = tiles;
-        gemm_bf16_pair_kernel<<<static_cast<unsigned>(2 * pairs), kThreadsP, kSmemPBytes, static_cast<cudaStream_t>(stream)>>>(
-            ta, twh, to, g, static_cast<const __nv_bfloat16*>(residual));
+        const unsigned grid = static_cast<unsigned>(2 * pairs);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(residual);
+        if (act == 2)
+            gemm_bf16_pair_kernel<true, false><<<grid, kThreadsP, kSmemPBytes, st>>>(ta, twh, tow, g, res);
+        else if (residual != nullptr)
+            gemm_bf16_pair_kernel<false, true><<<grid, kThreadsP, kSmemPBytes, st>>>(ta, twh, tow, g, res);
+        else
+            gemm_bf16_pair_kernel<false, false><<<grid, kThreadsP, kSmemPBytes, st>>>(ta, twh, tow, g, res);
         count_launch();
         return launch_status();
     }

@@ -16,8 +16,9 @@ re-organised for a B200:
 * duplicate-event removal and the sequence statistics share one stable sort
   (modeling/sequence.py:141-198, modeling/time_features.py:49-105).
 
-Plain dense layers go through cuBLAS (``torch.nn.functional.linear``).  Everything runs on the
-GPU; there is no CPU path.
+Dense layers whose widths are whole tiles run on this library's tcgen05 GEMM with bias, SiLU and
+residual in its epilogue (``ops.grouped_linear``); the fp32 score-parity mode and odd widths use
+``torch.nn.functional.linear``.  Everything runs on the GPU; there is no CPU path.
 """
 
 from __future__ import annotations
@@ -170,10 +171,9 @@ class OneTransInference:
     """Forward-only OneTrans on one GPU.
 
     ``dtype`` is the activation / weight type of the dense path: ``torch.bfloat16`` (serving) or
-    ``torch.float32`` (score-parity runs; attention still takes 16-bit tensor-core inputs — the
-    reference's accelerated backend serves fp32 callers in bf16, accelerators/attention/
-    flash_attention.py:249-252; here fp16, whose three extra mantissa bits keep the scores within 1e-5
-    of the fp32 reference; activations behind an RMSNorm are far inside the fp16 range).
+    ``torch.float32`` (score-parity runs against the reference's fp32 torch path: dense layers in fp32 through
+    the library, attention through this library's plain fp32 kernel, so nothing between the inputs and the
+    scores is rounded to 16 bits).
 
     ``ffn="fp8"`` runs the shared FFN of every block through the e4m3 block-scaled tcgen05 GEMMs
     (bf16 activations only; needs d_model % 256 == 0 and hidden % 256 == 0); ``"bf16"`` uses cuBLAS.
@@ -187,7 +187,7 @@ class OneTransInference:
 
     def __init__(self, state_dict: dict[str, torch.Tensor], spec: OneTransSpec, *, device: torch.device | str = "cuda",
                  dtype: torch.dtype = torch.bfloat16, attention_kernel: int = 0, ffn: str = "bf16",
-                 packed: bool = True, select_early: bool = True) -> None:
+                 packed: bool = True, select_early: bool = True, fused_tokenizer: bool = True) -> None:
         if not ops.cuda_available():
             raise RuntimeError("OneTransInference needs the cuda backend (libtb200 + an sm_100 device)")
         self.spec = spec
@@ -197,6 +197,9 @@ class OneTransInference:
         # packed layout: apply the pyramid's row selection right after attention, before the row-wise half of the
         # block (same rows, same values; False keeps the reference's order: whole block, then selection)
         self.select_early = select_early
+        # packed layout, bf16: gather -> projection -> SiLU / LayerNorm / time and position rows / first RMSNorm of the
+        # sequence tokenizer as ONE kernel (`ops.token_project`); False keeps the separate gather, GEMM and tail kernels
+        self.fused_tokenizer = bool(fused_tokenizer)
         if ffn not in ("bf16", "fp8"):
             raise ValueError(f"unknown ffn mode {ffn}")
         if ffn == "fp8" and (dtype != torch.bfloat16 or spec.d_model % 256 or (spec.d_model * spec.hidden_mult) % 256):
@@ -241,6 +244,10 @@ class OneTransInference:
             self.seq_tables[domain] = entries
         self._prepare_blocks()
         self._pos_cache: dict[int, torch.Tensor] = {}
+        # One persistent device word for every tcgen05 launch of this engine (attention, FP8 and grouped GEMMs):
+        # a kernel whose bounded wait gives up raises it.  Passing it costs nothing per call; it is read back by
+        # `raise_if_incomplete` (one small device-to-host copy), which `score_stream` calls for the caller.
+        self.status_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._hash_buckets: dict[str, torch.Tensor] = {}   # per sequence domain: how each feature's ids are hashed
 
     # ------------------------------------------------------------------ weights
@@ -299,6 +306,15 @@ class OneTransInference:
                 blk["ffn_fp8_folded"] = folded
             blk["out_w_t"] = self._p(p + ".attention.out.weight").t()
             blk["out_b"] = self._p(p + ".attention.out.bias")
+            # shared projections as `nn.Linear` weights ([out, in], contiguous row blocks) with fp32 biases: what the
+            # tcgen05 GEMM takes.  Rows [0, d) of shared_qkv are the queries, [d, 3d) keys and values.
+            d_model = self.d
+            w_qkv, b_qkv = self._p(p + ".attention.shared_qkv.weight"), self.w[p + ".attention.shared_qkv.bias"].float()
+            blk["qkv_w"], blk["qkv_b"] = w_qkv, b_qkv.contiguous()
+            blk["q_w"], blk["q_b"] = w_qkv[:d_model], b_qkv[:d_model].contiguous()
+            blk["kv_w"], blk["kv_b"] = w_qkv[d_model:], b_qkv[d_model:].contiguous()
+            blk["out_w"] = self._p(p + ".attention.out.weight")
+            blk["out_b32"] = self.w[p + ".attention.out.bias"].float().contiguous()
             if ns > 0:
                 def stack(fmt: str, kind: str) -> torch.Tensor:
                     return torch.stack([self._p(fmt.format(i=i) + "." + kind) for i in range(ns)])
@@ -307,7 +323,6 @@ class OneTransInference:
                 bq, bk, bv = (stack(p + f".attention.ns_{n}." + "{i}", "bias") for n in "qkv")
                 blk["ns_qkv_w"] = torch.cat([wq, wk, wv], dim=1).transpose(1, 2).contiguous()  # [ns, d, 3d]
                 blk["ns_qkv_b"] = torch.cat([bq, bk, bv], dim=1).unsqueeze(1)  # [ns, 1, 3d]
-                d_model = self.d
                 blk["ns_q_w"] = blk["ns_qkv_w"][:, :, :d_model].contiguous()     # query / key-value halves for blocks
                 blk["ns_kv_w"] = blk["ns_qkv_w"][:, :, d_model:].contiguous()    # that project fewer queries than keys
                 blk["ns_q_b"] = blk["ns_qkv_b"][:, :, :d_model].contiguous()
@@ -323,6 +338,10 @@ class OneTransInference:
                 if self.dtype == torch.bfloat16 and self.device.type == "cuda" and d_model % 256 == 0 and hidden % 256 == 0:
                     blk["g_qkv_w"] = torch.cat([wq, wk, wv], dim=1).contiguous()                       # [ns, 3d, d]
                     blk["g_qkv_b"] = blk["ns_qkv_b"].reshape(ns, 3 * d_model).float().contiguous()
+                    blk["g_q_w"], blk["g_kv_w"] = wq.contiguous(), torch.cat([wk, wv], dim=1).contiguous()
+                    blk["g_q_b"] = blk["g_qkv_b"][:, :d_model].contiguous()
+                    blk["g_kv_b"] = blk["g_qkv_b"][:, d_model:].contiguous()
+                    blk["g_b2"] = blk["ns_b2"].reshape(ns, d_model).float().contiguous()
                     blk["g_w1"] = stack(p + ".ffn.ns_specific.{i}.net.0", "weight").contiguous()       # [ns, hidden, d]
                     blk["g_b1"] = blk["ns_b1"].reshape(ns, hidden).float().contiguous()
                     blk["g_w2"] = stack(p + ".ffn.ns_specific.{i}.net.3", "weight").contiguous()       # [ns, d, hidden]
@@ -331,11 +350,53 @@ class OneTransInference:
             self.blocks.append(blk)
 
     # ------------------------------------------------------------------ pieces
-    def _linear(self, x: torch.Tensor, prefix: str) -> torch.Tensor:
-        return F.linear(x, self._p(prefix + ".weight"), self._p(prefix + ".bias"))
+    def _linear(self, x: torch.Tensor, prefix: str, *, silu: bool = False, residual: torch.Tensor | None = None) -> torch.Tensor:
+        key = prefix + "#b32"
+        if key not in self._cast_cache:
+            self._cast_cache[key] = self.w[prefix + ".bias"].float().contiguous()
+        return self._proj(x, self._p(prefix + ".weight"), self._cast_cache[key], silu=silu, residual=residual)
 
-    def _layer_norm(self, x: torch.Tensor, prefix: str) -> torch.Tensor:
-        return ops.layer_norm(x, self._p(prefix + ".weight"), self._p(prefix + ".bias"), 1e-5)
+    def _own_gemm(self, n: int, k: int) -> bool:
+        """The tcgen05 GEMM serves bf16 layers whose widths are whole tiles; the fp32 score-parity mode and odd
+        shapes (the 32-wide dense token, d_model below 256) go to the library."""
+        return self.dtype == torch.bfloat16 and self.device.type == "cuda" and n % 256 == 0 and k % 64 == 0
+
+    def _proj(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, *, silu: bool = False,
+              residual: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``act(x @ weight.T + bias) (+ residual)`` for a shared `nn.Linear` ([N, K] weight, fp32 bias): this
+        library's tcgen05 GEMM with the epilogue inside where it applies, the library GEMM otherwise."""
+        n, k = weight.shape
+        lead = x.shape[:-1]
+        if self._own_gemm(n, k):
+            x2 = x.reshape(-1, k)
+            y = ops.grouped_linear(x2 if x2.is_contiguous() else x2.contiguous(), weight, bias, silu=silu,
+                                   residual=None if residual is None else residual.reshape(-1, n),
+                                   out=None if out is None else out.view(-1, n), status=self.status_word)
+            return y.view(*lead, n)
+        with ops.timed("cublas_linear", m=x.numel() // k, n=n, k=k):
+            y = F.linear(x, weight, None if bias is None else bias.to(x.dtype))
+        if silu:
+            y = F.silu(y)
+        if residual is not None:
+            y = y + residual
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def _grouped(self, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, **kw) -> torch.Tensor:
+        return ops.grouped_linear(x, weight, bias, status=self.status_word, **kw)
+
+    def raise_if_incomplete(self) -> None:
+        """Read the engine's status word (a 4-byte device-to-host copy, which waits for the work enqueued so far)
+        and raise if a bounded wait inside one of the tcgen05 kernels gave up since the last call: the scores
+        computed in between are then incomplete."""
+        if int(self.status_word.item()) != 0:
+            self.status_word.zero_()
+            raise RuntimeError("cuda backend: a bounded wait inside a tcgen05 kernel gave up; scores are incomplete")
+
+    def _layer_norm(self, x: torch.Tensor, prefix: str, pre_silu: bool = False) -> torch.Tensor:
+        return ops.layer_norm(x, self._p(prefix + ".weight"), self._p(prefix + ".bias"), 1e-5, pre_silu=pre_silu)
 
     def _bank_tokens(self, bank: _Bank, int_feats: torch.Tensor) -> torch.Tensor:
         if bank.fields is None:
@@ -360,8 +421,8 @@ class OneTransInference:
         groups = [list(g) for g in groups] or [[i] for i in range(bank.n_fields)]
         if self.spec.force_auto_split or n_tokens != len(groups):
             flat = feats.reshape(batch, -1) if feats.shape[1] > 0 else torch.zeros(batch, 1, dtype=self.dtype, device=self.device)
-            h = F.silu(self._linear(flat, prefix + ".project.0"))
-            return self._layer_norm(h, prefix + ".project.2").view(batch, n_tokens, self.d)
+            h = self._linear(flat, prefix + ".project.0")
+            return self._layer_norm(h, prefix + ".project.2", pre_silu=True).view(batch, n_tokens, self.d)
         grouped = []
         for g in groups:
             idx = [i for i in g if 0 <= i < feats.shape[1]]
@@ -374,8 +435,8 @@ class OneTransInference:
             return None
         values = values.to(self.dtype)
         miss = torch.zeros_like(values) if missing is None else missing[:, : values.shape[1]].to(self.dtype)
-        h = F.silu(self._linear(torch.cat([values, miss], dim=-1), prefix + ".project.0"))
-        return self._layer_norm(h, prefix + ".project.2").unsqueeze(1)
+        h = self._linear(torch.cat([values, miss], dim=-1), prefix + ".project.0")
+        return self._layer_norm(h, prefix + ".project.2", pre_silu=True).unsqueeze(1)
 
     def _sequence_tokens(self, domain: str, values: torch.Tensor, timestamps: torch.Tensor, request_ts: torch.Tensor):
         """`SequenceTokenizer.forward` (modeling/tokenizers.py:156-190)."""
@@ -427,9 +488,9 @@ class OneTransInference:
     def _shared_ffn_residual(self, blk: dict, x: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         """tokens + FFN(x) for every row (`FeedForward`, experiments/onetrans/model.py:33-44)."""
         if self.ffn_mode == "fp8":
-            return ops.ffn_fp8(x, blk["ffn_fp8"], residual=tokens)
+            return ops.ffn_fp8(x, blk["ffn_fp8"], residual=tokens, status=self.status_word)
         p = blk["p"]
-        return tokens + self._linear(F.silu(self._linear(x, p + ".ffn.shared.net.0")), p + ".ffn.shared.net.3")
+        return self._linear(self._linear(x, p + ".ffn.shared.net.0", silu=True), p + ".ffn.shared.net.3", residual=tokens)
 
     def _block(self, blk: dict, tokens: torch.Tensor, mask: dict, seq_count: int) -> torch.Tensor:
         """`OneTransBlock.forward` (experiments/onetrans/model.py:97-107)."""
@@ -444,10 +505,8 @@ class OneTransInference:
                 blk["ns_qkv_b"][:ns_here], x_ns, blk["ns_qkv_w"][:ns_here]
             ).transpose(0, 1)
         q, k, v = (qkv[:, :, i * d : (i + 1) * d].unflatten(-1, (self.heads, self.head_dim)) for i in range(3))
-        if q.dtype == torch.float32:  # score-parity mode: 16-bit tensor-core inputs with the most mantissa bits
-            q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
         attn = ops.varlen_attention(q, k, v, causal=True, padded_query_self=True, layout="blhd",
-                                    kernel=self.attention_kernel, **mask)
+                                    kernel=self.attention_kernel, **mask, status=self.status_word)
         attn = attn.view(batch, total, d).to(self.dtype)
         tokens = tokens + self._linear(attn, p + ".attention.out")
 
@@ -487,7 +546,12 @@ class OneTransInference:
 
     def _classify(self, seq_summary: torch.Tensor, ns_summary: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         embeddings = torch.cat([seq_summary, ns_summary], dim=-1)
-        h = F.silu(F.linear(embeddings, self.w["classifier.0.weight"].float(), self.w["classifier.0.bias"].float()))
+        if self._own_gemm(self.d, 2 * self.d):
+            # serving mode: the wide layer on the tcgen05 GEMM (bias + SiLU in its epilogue); its inputs come out of a
+            # bf16 network, so bf16 operands with fp32 accumulation lose nothing that was still there
+            h = self._linear(embeddings.to(self.dtype), "classifier.0", silu=True).float()
+        else:
+            h = F.silu(F.linear(embeddings, self.w["classifier.0.weight"].float(), self.w["classifier.0.bias"].float()))
         logits = F.linear(h, self.w["classifier.3.weight"].float(), self.w["classifier.3.bias"].float())
         return logits, embeddings
 
@@ -705,53 +769,56 @@ class OneTransInference:
                 # arithmetic, as "whole block, then selection", without the work whose result would be dropped.
                 src, next_ns_rows = first_kept if (layer == 0 and first_kept is not None) else kept_rows(layer)
                 next_flat_ns = next_ns_rows.t().reshape(-1)
-                w_qkv, b_qkv = self._p(p + ".attention.shared_qkv.weight"), self._p(p + ".attention.shared_qkv.bias")
-                kv = F.linear(x, w_qkv[d:], b_qkv[d:])                                              # [N, 2d]
-                qm = F.linear(x.index_select(0, src), w_qkv[:d], b_qkv[:d])                         # [N', d]
-                ops.scatter_rows(kv, flat_ns, torch.bmm(x_ns, blk["ns_kv_w"]).view(ns * batch, 2 * d), bias=blk["ns_kv_b"])
-                ops.scatter_rows(qm, next_flat_ns, torch.bmm(x_ns, blk["ns_q_w"]).view(ns * batch, d), bias=blk["ns_q_b"])
+                kv = self._proj(x, blk["kv_w"], blk["kv_b"])                                        # [N, 2d]
+                qm = self._proj(ops.gather_rows(x, src), blk["q_w"], blk["q_b"])                    # [N', d]
+                if "g_kv_w" in blk:   # the per-token overrides of the NS rows: grouped GEMM, bias in its epilogue
+                    ops.scatter_rows(kv, flat_ns, self._grouped(x_ns, blk["g_kv_w"], blk["g_kv_b"]).view(ns * batch, 2 * d))
+                    ops.scatter_rows(qm, next_flat_ns, self._grouped(x_ns, blk["g_q_w"], blk["g_q_b"]).view(ns * batch, d))
+                else:
+                    ops.scatter_rows(kv, flat_ns, torch.bmm(x_ns, blk["ns_kv_w"]).view(ns * batch, 2 * d), bias=blk["ns_kv_b"])
+                    ops.scatter_rows(qm, next_flat_ns, torch.bmm(x_ns, blk["ns_q_w"]).view(ns * batch, d), bias=blk["ns_q_b"])
                 q = qm.unflatten(-1, (heads, hd))
                 k, v = (kv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(2))
-                if q.dtype == torch.float32:
-                    q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
                 attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
                                             cu_rows_q=cu[layer + 1].to(torch.int32), max_rows_q=max_rows[layer + 1],
-                                            kernel=self.attention_kernel if self.attention_kernel in (0, 1, 4) else 0)
+                                            kernel=self.attention_kernel if self.attention_kernel in (0, 1, 4) else 0, status=self.status_word)
                 if not (layer == 0 and first_kept is not None):   # else the tokenizer already wrote the kept rows only
-                    tokens = tokens.index_select(0, src)
+                    tokens = ops.gather_rows(tokens, src)
                 ns_rows, flat_ns = next_ns_rows, next_flat_ns
             else:
-                qkv = self._linear(x, p + ".attention.shared_qkv")                    # [N, 3d]
-                ops.scatter_rows(qkv, flat_ns, torch.bmm(x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d), bias=blk["ns_qkv_b"])
+                qkv = self._proj(x, blk["qkv_w"], blk["qkv_b"])                       # [N, 3d]
+                if "g_qkv_w" in blk:
+                    ops.scatter_rows(qkv, flat_ns, self._grouped(x_ns, blk["g_qkv_w"], blk["g_qkv_b"]).view(ns * batch, 3 * d))
+                else:
+                    ops.scatter_rows(qkv, flat_ns, torch.bmm(x_ns, blk["ns_qkv_w"]).view(ns * batch, 3 * d), bias=blk["ns_qkv_b"])
                 q, k, v = (qkv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(3))
-                if q.dtype == torch.float32:
-                    q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
                 attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
-                                            kernel=self.attention_kernel)
+                                            kernel=self.attention_kernel, status=self.status_word)
             attn2d = attn.view(-1, d).to(self.dtype)
-            if self.ffn_mode == "fp8":
-                # tokens + attention out-projection with the residual inside the GEMM (beta = 1); its bias is
-                # added by the norm on the fly and rides on the FFN output biases into the next residual
-                tokens = tokens.addmm_(attn2d, blk["out_w_t"])   # in place: an out-of-place addmm first copies C
+            folded = self.ffn_mode == "fp8"
+            if folded:
+                # tokens + attention out-projection with the residual inside the GEMM's epilogue, in place; its bias
+                # is added by the norm on the fly and rides on the FFN output biases into the next residual
+                tokens = self._proj(attn2d, blk["out_w"], None, residual=tokens, out=tokens)
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
-                out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens)
-                ns_b2 = blk["ns_b2_folded"]
+                out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens, status=self.status_word)
             else:
-                tokens = tokens + F.linear(attn2d, blk["out_w_t"].t(), blk["out_b"])
+                tokens = self._proj(attn2d, blk["out_w"], blk["out_b32"], residual=tokens)
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
                 out = self._shared_ffn_residual(blk, x, tokens)
-                ns_b2 = blk["ns_b2"]
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)
-            if "g_w1" in blk:
-                h = ops.grouped_linear(x_ns, blk["g_w1"], blk["g_b1"], silu=True)
+            if "g_w1" in blk:   # per-token FeedForward on the grouped GEMM: bias + SiLU, then bias, in the epilogues
+                h = self._grouped(x_ns, blk["g_w1"], blk["g_b1"], silu=True)
+                y_ns = self._grouped(h, blk["g_w2"], blk["g_b2_folded" if folded else "g_b2"]).view(ns * batch, d)
+                ops.scatter_rows(out, flat_ns, y_ns, residual=tokens)              # tokens + b2 + FFN_ns(x)
             else:
                 h = ops.bias_silu_rows(torch.bmm(x_ns, blk["ns_w1"]), blk["ns_b1"])
-            y_ns = torch.bmm(h, blk["ns_w2"]).view(ns * batch, d)
-            ops.scatter_rows(out, flat_ns, y_ns, bias=ns_b2, residual=tokens)   # tokens + b2 + FFN_ns(x)
+                y_ns = torch.bmm(h, blk["ns_w2"]).view(ns * batch, d)
+                ops.scatter_rows(out, flat_ns, y_ns, bias=blk["ns_b2_folded" if folded else "ns_b2"], residual=tokens)
             tokens = out
             if not selected and widths[layer + 1] < widths[layer]:  # pyramid: drop the earliest sequence rows of every sample
                 src, ns_rows = kept_rows(layer)
-                tokens = tokens.index_select(0, src)
+                tokens = ops.gather_rows(tokens, src)
 
         last = len(widths) - 1
         tokens = ops.rms_norm(tokens, self._p("final_norm.weight"), 1e-6).float()
@@ -759,7 +826,9 @@ class OneTransInference:
         total_seq = totals[last] - batch * ns
         owner = torch.repeat_interleave(arange_b, n_last, output_size=total_seq)
         seq_rows = cu[last][owner] + (torch.arange(total_seq, device=dev) - offsets(n_last)[owner])
-        seq_sum = torch.zeros(batch, d, device=dev).index_add_(0, owner, tokens[seq_rows])
+        # rows of a sample are consecutive: a segmented sum in row order (no floating-point atomics, so the scores
+        # of a batch do not depend on which GPU or which run computed them)
+        seq_sum = torch.segment_reduce(tokens[seq_rows], "sum", lengths=n_last, axis=0, unsafe=True)
         seq_summary = seq_sum / n_last.clamp_min(1).to(torch.float32)[:, None]
         ns_summary = tokens[ns_rows.reshape(-1)].view(batch, ns, d).mean(dim=1)
         return self._classify(seq_summary, ns_summary)
@@ -780,26 +849,24 @@ class OneTransInference:
             x = ops.rms_norm(flat, self._p(p + ".attn_norm.weight"), 1e-6)
             fused = "g_qkv_w" in blk   # every layer of the block in one tcgen05 GEMM each, epilogues inside
             if fused:
-                qkv = ops.grouped_linear(x.view(ns, batch, d), blk["g_qkv_w"], blk["g_qkv_b"])
+                qkv = self._grouped(x.view(ns, batch, d), blk["g_qkv_w"], blk["g_qkv_b"])
             else:
                 qkv = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_qkv_w"]), blk["ns_qkv_b"], silu=False)
             # sample-major views of the token-major tensors: (B, L = ns, H, hd) with strides (3d, B * 3d, hd, 1)
             q, k, v = (qkv[:, :, i * d : (i + 1) * d].unflatten(-1, (heads, hd)).permute(1, 0, 2, 3) for i in range(3))
-            if q.dtype == torch.float32:
-                q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
             attn = torch.empty(ns, batch, heads, hd, dtype=q.dtype, device=q.device)
             ops.varlen_attention(q, k, v, causal=True, layout="blhd", kernel=self.attention_kernel,
-                                 out=attn.permute(1, 0, 2, 3))
+                                 out=attn.permute(1, 0, 2, 3), status=self.status_word)
             # attention output projection onto the residual stream; its bias is added by the norm on the fly and
             # rides on the FFN's output bias into the next residual
             if fused:
-                ops.grouped_linear(attn.view(ns * batch, d), blk["g_out_w"], None, residual=flat, out=flat)
+                self._grouped(attn.view(ns * batch, d), blk["g_out_w"], None, residual=flat, out=flat)
             else:
                 flat.addmm_(attn.view(ns * batch, d).to(self.dtype), blk["out_w_t"])
             x = ops.rms_norm(flat, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
             if fused:
-                h = ops.grouped_linear(x.view(ns, batch, d), blk["g_w1"], blk["g_b1"], silu=True)
-                tok = ops.grouped_linear(h, blk["g_w2"], blk["g_b2_folded"], residual=tok, out=tok)
+                h = self._grouped(x.view(ns, batch, d), blk["g_w1"], blk["g_b1"], silu=True)
+                tok = self._grouped(h, blk["g_w2"], blk["g_b2_folded"], residual=tok, out=tok)
             else:
                 h = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_w1"]), blk["ns_b1"], silu=True)
                 tok = ops.bias_act_rows(torch.baddbmm(tok, h, blk["ns_w2"]), blk["ns_b2_folded"], silu=False)
@@ -822,13 +889,17 @@ class OneTransInference:
         return probs.reshape(-1) if probs.shape[1] == 1 else probs
 
 
-def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int | None = None):
+def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int | None = None, check_every: int = 0):
     """Scores for a stream of host-resident batches, one ``scores`` tensor (on the device) per batch.
 
     The serving loop of `evaluation/workflow.py:246-293` with the host-to-device copy taken off the critical
     path: the copy of batch i + 1 runs on a side stream while batch i is scored, so that in steady state a
     step costs max(copy, compute) instead of their sum.  ``host_batches`` should be pinned
-    (``ModelInput.pin_memory()``) for the copies to be asynchronous."""
+    (``ModelInput.pin_memory()``) for the copies to be asynchronous.
+
+    The engine's status word (raised by a tcgen05 kernel whose bounded wait gave up) is read when the stream
+    ends and, with ``check_every=n``, after every n-th batch; a raised word turns into a ``RuntimeError``
+    instead of silently wrong scores."""
     dev = model.device
     compute = torch.cuda.current_stream(dev)
     copier = torch.cuda.Stream(dev)
@@ -846,6 +917,7 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
     if first is None:
         return
     pending = stage(first)
+    served = 0
     while pending is not None:
         staged, done = pending
         nxt = next(it, None)
@@ -854,6 +926,10 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
             t.record_stream(compute)
         pending = stage(nxt) if nxt is not None else None
         yield model.scores(staged, micro_batch=micro_batch)
+        served += 1
+        if check_every > 0 and served % check_every == 0:
+            model.raise_if_incomplete()
+    model.raise_if_incomplete()
 
 
 def random_state_dict(spec: OneTransSpec, *, seed: int = 0, device: torch.device | str = "cpu",

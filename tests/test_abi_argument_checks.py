@@ -73,8 +73,9 @@ def test_attention_entry(lib):
     assert call(B=0) == OK and call(Lq=0) == OK                 # nothing to compute
     assert call(B=-1) == ERR_SHAPE and call(H=0) == ERR_SHAPE
     assert call(q=None) == ERR_NULL and call(strides=None) == ERR_NULL
-    assert call(dtype=0) == ERR_DTYPE                           # fp32 has no kernel (the host casts)
+    assert call(dtype=7) == ERR_DTYPE
     assert call(D=48) == ERR_UNSUPPORTED
+    assert call(dtype=0, D=258) == ERR_UNSUPPORTED              # the fp32 kernel takes head dims up to 256
     assert call(self_rows=1, Lq=4, Lk=8) == ERR_SHAPE           # the self fallback needs a square problem
     assert call(ns=-1) == ERR_SHAPE
     assert call(cu_q=P(p)) == ERR_UNSUPPORTED                   # separate query rows need a packed batch
@@ -106,7 +107,8 @@ def test_grouped_gemm_entry(lib):
     assert gemm(P(p), P(p), None, None, P(p), 3, 8, 200, 64, 0, None, None) == ERR_SHAPE     # N % 256
     assert gemm(P(p), P(p), None, None, P(p), 3, 8, 256, 48, 0, None, None) == ERR_SHAPE     # K % 64
     assert gemm(P(p), P(p), None, None, P(p), -1, 8, 256, 64, 0, None, None) == ERR_SHAPE
-    assert gemm(P(p), P(p), None, None, P(p), 3, 8, 256, 64, 2, None, None) == ERR_UNSUPPORTED   # unknown activation
+    assert gemm(P(p), P(p), None, None, P(p), 3, 8, 256, 64, 3, None, None) == ERR_UNSUPPORTED   # unknown activation
+    assert gemm(P(p), P(p), None, P(p), P(p), 3, 8, 256, 64, 2, None, None) == ERR_UNSUPPORTED   # the gated epilogue takes no residual
     assert gemm(None, P(p), None, None, P(p), 3, 8, 256, 64, 0, None, None) == ERR_NULL
     assert gemm(P(p), P(p), None, None, None, 3, 8, 256, 64, 0, None, None) == ERR_NULL
     assert gemm(P(p + 8), P(p), None, None, P(p), 3, 8, 256, 64, 0, None, None) == ERR_ALIGN
@@ -132,3 +134,31 @@ def test_token_tail_entries(lib):
     assert call(rows_a=1 << 31) == ERR_UNSUPPORTED                          # ids are held as 32-bit values
     assert lib.tb200_token_tail_fwd(P(p), P(p), P(p), P(p), 4, P(p), None, 0, None, P(p), P(p), P(p), 0, 8, 1e-5, 1e-6, BF16,
                                     None) == OK
+
+
+def test_static_ffn_entry_checks_everything_before_it_launches(lib):
+    """A negative status from the no-allocation entry point means that none of its three kernels was enqueued:
+    the checks of all three steps (shapes up to the K limit of the GEMMs, NULL and alignment of every pointer,
+    the row bound) come first.  On a machine without a GPU the valid call itself ends at the device check."""
+    buf = (ctypes.c_uint8 * 512)()
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) & ~15
+    ffn = lib.tb200_ffn_fp8_fwd_static
+    ERR_SCRATCH = -8
+
+    def call(**kw):
+        a = dict(x=P(p16), wu=P(p16), su=P(p16), bu=None, wd=P(p16), sd=P(p16), bd=None, res=None, y=P(p16), M=64, d_in=512,
+                 hidden=2048, d_out=512, gated=0)
+        a.update(kw)
+        return ffn(a["x"], a["wu"], a["su"], a["bu"], a["wd"], a["sd"], a["bd"], a["res"], a["y"], a["M"], a["d_in"],
+                   a["hidden"], a["d_out"], a["gated"], None)
+
+    assert call(M=0) == OK
+    assert call(M=-1) == ERR_SHAPE and call(d_in=100) == ERR_SHAPE and call(hidden=128) == ERR_SHAPE and call(d_out=100) == ERR_SHAPE
+    assert call(d_in=8192 + 128) == ERR_SHAPE and call(hidden=8192 + 256) == ERR_SHAPE   # the GEMMs' K limit, found up front
+    assert call(x=None) == ERR_NULL and call(y=None) == ERR_NULL and call(sd=None) == ERR_NULL
+    assert call(wd=P(p16 + 8)) == ERR_ALIGN and call(res=P(p16 + 4)) == ERR_ALIGN and call(y=P(p16 + 2)) == ERR_ALIGN
+    assert call(M=(64 << 20) // (512 + 2048) + 1) == ERR_SCRATCH
+    assert call(M=1 << 62) == ERR_SCRATCH          # no wrap-around of the size products
+    assert call(M=(1 << 31) + 5) == ERR_SCRATCH
+    assert lib.tb200_ffn_fp8_static_status(None, None) == ERR_NULL

@@ -349,3 +349,45 @@ def test_random_shapes_against_the_oracle():
         outs = [ops.varlen_attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], causal=causal, cu_rows=cu.cuda(),
                                      max_rows=int(rows_per.max()), kernel=kern).float() for kern in (1, 2)]
         assert (outs[0] - outs[1]).abs().max().item() <= 1e-2, f"case {case}: packed kernels disagree"
+
+
+@pytest.mark.parametrize("D", [32, 64, 20])
+@pytest.mark.parametrize("L,ns", [(1, 0), (40, 0), (64, 9), (265, 9)])
+def test_fp32_kernel_every_mask_family(D, L, ns):
+    """fp32 q, k, v take the plain fp32 kernel (score-parity mode): against the fp32 oracle to 1e-5, for the
+    causal-valid family with an always-valid suffix, key padding, an explicit key map, and a packed batch whose
+    queries are the last rows of every sample."""
+    B, H = 5, 2
+    S = L - ns
+    q, k, v = _qkv(B, H, L, D, torch.float32, seed=L + ns + D)
+    lens = torch.tensor([S, 0, min(S, 1), S // 2, max(S - 1, 0)])
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.cuda(), ns_start=S, causal=True, padded_query_self=True)
+    assert got.dtype == torch.float32
+    pos = torch.arange(L)[None]
+    _check(got, q, k, v, R.structured_attention_mask(lens, L, S, True, True), (pos >= lens[:, None]) & (pos < S), tol=1e-5)
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), seq_len=lens.clamp_min(1).cuda())
+    _check(got, q, k, v, R.structured_attention_mask(lens.clamp_min(1), L, L, False, False), tol=1e-5)
+    key_valid = torch.rand(B, L, generator=torch.Generator().manual_seed(L)) < 0.6
+    key_valid[:, 0] = True
+    got = ops.varlen_attention(q.cuda(), k.cuda(), v.cuda(), key_valid=key_valid.cuda())
+    _check(got, q, k, v, key_valid[:, None, :].expand(B, L, L), tol=1e-5)
+    # packed, queries = the last rows of every sample, causal rule aligned at the end
+    lens_p = torch.tensor([L, max(1, L // 2), 1, L, max(1, L - 3)])
+    keep = torch.tensor([min(L, 5), 1, 1, 0, 2]).clamp_max(lens_p)
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens_p, 0)
+    cu_q = torch.zeros(B + 1, dtype=torch.int32)
+    cu_q[1:] = torch.cumsum(keep, 0)
+    g = torch.Generator().manual_seed(9)
+    kv = torch.randn(int(cu[-1]), 2, H, D, generator=g)
+    sel = torch.cat([torch.arange(int(cu[i + 1]) - int(keep[i]), int(cu[i + 1])) for i in range(B)])
+    qp = torch.randn(int(cu[-1]), H, D, generator=g) * D ** -0.25
+    got = ops.varlen_attention(qp[sel].contiguous().cuda(), kv[:, 0].cuda(), kv[:, 1].cuda(), causal=True, cu_rows=cu.cuda(),
+                               max_rows=L, cu_rows_q=cu_q.cuda(), max_rows_q=max(int(keep.max()), 1)).cpu()
+    want = []
+    for i in range(B):
+        lo, hi = int(cu[i]), int(cu[i + 1])
+        qi, ki, vi = (t[lo:hi].permute(1, 0, 2)[None] for t in (qp, kv[:, 0], kv[:, 1]))
+        mask = torch.tril(torch.ones(hi - lo, hi - lo, dtype=torch.bool))[None, None]
+        want.append(R.attention(qi, ki, vi, mask)[0].permute(1, 0, 2)[hi - lo - int(keep[i]):])
+    assert (got - torch.cat(want)).abs().max().item() <= 1e-5

@@ -139,6 +139,52 @@ def test_full_size_block_against_bf16_torch_on_device():
     assert (got - ref).abs().max().item() <= 1e-1 * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("m,d,hidden", [(300, 256, 512), (4100, 512, 2048)])
+def test_precise_mode_meets_the_5e_2_bound(gated, m, d, hidden):
+    """`precise=True`: the up projection runs on the bf16 tensor cores (bias, SiLU and the gate in its epilogue), its
+    bf16 hidden activation is quantised per 1 x 128 block, the down projection is e4m3.  Only the hidden activation
+    and W_down are rounded to e4m3, which leaves 3.5e-2 (gated) / 3.6e-2 (plain) against the bf16 FFN: inside the
+    5e-2 bound that the all-e4m3 mode misses for the gated layer."""
+    g = torch.Generator().manual_seed(d + hidden + m)
+    x = _activations(m, d, 2)
+    w_up = (torch.randn((2 if gated else 1) * hidden, d, generator=g) * 0.02).bfloat16()
+    w_down = (torch.randn(d, hidden, generator=g) * 0.02).bfloat16()
+    b_up = torch.randn((2 if gated else 1) * hidden, generator=g) * 0.05
+    b_down = torch.randn(d, generator=g) * 0.05
+    res = torch.randn(m, d, generator=g).bfloat16()
+    weights = ops.Fp8FfnWeights(w_up.cuda(), w_down.cuda(), gated=gated, b_up=b_up.cuda(), b_down=b_down.cuda(), precise=True)
+    got = ops.ffn_fp8(x.cuda(), weights, residual=res.cuda(), check=True, precise=True).float().cpu()
+    ref = (R.swiglu_ffn(x, w_up, w_down, b_up=b_up, b_down=b_down) if gated else R.silu_ffn(x, w_up, b_up, w_down, b_down))
+    rel = _rel(got - res.float(), ref)
+    assert rel <= 5e-2, rel
+    coarse = ops.ffn_fp8(x.cuda(), weights, residual=res.cuda(), check=True).float().cpu()
+    assert rel < _rel(coarse - res.float(), ref)          # and it is what buys the accuracy
+    with pytest.raises(ValueError):
+        ops.ffn_fp8(x.cuda(), ops.Fp8FfnWeights(w_up.cuda(), w_down.cuda(), gated=gated), precise=True)
+
+
+def test_full_size_block_precise_mode_on_device():
+    """The benchmark shape (262 144 tokens, 512 -> 2 x 2048 -> 512, SiLU-gated) in the precise mode: relative error of
+    the whole output and of every 4 096-row slab against the bf16 torch FFN within 5e-2."""
+    m, d, hidden = 262144, 512, 2048
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(m, d, generator=g, device="cuda")
+    t4 = torch.randn(m, d, generator=g, device="cuda") / torch.sqrt(torch.randn(m, d, 4, generator=g, device="cuda").pow(2).mean(-1))
+    x = torch.where(torch.rand(m, d, generator=g, device="cuda") < 0.01, 3.0 * t4, x).bfloat16()
+    del t4
+    w_up = (torch.randn(2 * hidden, d, generator=g, device="cuda") * 0.02).bfloat16()
+    w_down = (torch.randn(d, hidden, generator=g, device="cuda") * 0.02).bfloat16()
+    weights = ops.Fp8FfnWeights(w_up, w_down, gated=True, precise=True)
+    got = ops.ffn_fp8(x, weights, check=True, precise=True).float()
+    h = torch.nn.functional.linear(x, w_up)
+    ref = torch.nn.functional.linear(torch.nn.functional.silu(h[:, :hidden]) * h[:, hidden:], w_down).float()
+    del h
+    assert ((got - ref).norm() / ref.norm()).item() <= 5e-2
+    slab = ((got - ref).view(64, -1).norm(dim=1) / ref.view(64, -1).norm(dim=1)).max().item()
+    assert slab <= 5e-2
+
+
 def test_random_shapes_against_bf16_math():
     """Seeded sweep over row counts (tile tails), K, hidden widths, gating, biases and the residual: the whole FFN
     against the same layer in fp32 math on the bf16 operands, within the e4m3 noise floor (about 6e-2 relative)."""

@@ -83,3 +83,21 @@ def test_grouped_linear_rejects_unsupported_shapes():
     empty = ops.grouped_linear(torch.zeros(2, 0, 64, dtype=torch.bfloat16, device="cuda"),
                                torch.zeros(2, 256, 64, dtype=torch.bfloat16, device="cuda"))
     assert empty.shape == (2, 0, 256)
+
+
+@pytest.mark.parametrize("groups,rows,n,k", [(1, 100, 256, 64), (1, 128, 512, 128), (2, 300, 1024, 512), (1, 5000, 4096, 512)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gated_epilogue(groups, rows, n, k, with_bias):
+    """act 2: the weight rows of every 256-column tile are [128 gate rows | 128 value rows]; out = silu(gate) * value.
+    Rows up to 128 take the single-CTA kernel, more rows the CTA-pair kernel."""
+    g = torch.Generator().manual_seed(groups * 77 + rows)
+    x = torch.randn(groups, rows, k, generator=g).bfloat16().cuda()
+    w = (torch.randn(groups, n, k, generator=g) * k ** -0.5).bfloat16().cuda()
+    bias = torch.randn(groups, n, generator=g).cuda() if with_bias else None
+    got = ops.grouped_linear(x, w, bias, gated=True, check=True)
+    assert got.shape == (groups, rows, n // 2) and got.dtype == torch.bfloat16
+    full = _reference(x, w, bias, False, None).view(groups, rows, n // 256, 2, 128)
+    want = (torch.nn.functional.silu(full[:, :, :, 0]) * full[:, :, :, 1]).reshape(groups, rows, n // 2)
+    _close(got, want)
+    with pytest.raises(ValueError):
+        ops.grouped_linear(x, w, bias, gated=True, residual=got)

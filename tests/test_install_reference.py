@@ -1,49 +1,22 @@
-"""`install()` against a real checkout of the reference, when one is importable (set
-TAAC2026_REFERENCE=/path/to/TAAC_2026 or have `taac2026` on sys.path); skipped otherwise, e.g. on
-the GPU box.  The CUDA operators are replaced by recording fakes — the pattern the reference's own
+"""`install()` against the reference itself: a checkout named by TAAC2026_REFERENCE or lying beside this
+repository, else the byte-compiled modules under oracle/_ref (`python -m oracle.build_ref`); skipped when
+neither exists.  The CUDA operators are replaced by recording fakes — the pattern the reference's own
 tests use for backends they cannot run (tests/unit/infrastructure/accelerators/test_tilelang_ops.py:222-302)
 — so the routing is checked without a GPU."""
 
 from __future__ import annotations
 
-import json
-import os
-import sys
-import types
-from pathlib import Path
-
 import pytest
 import torch
 
+from oracle import ref_runtime
 
-def _reference_root() -> Path | None:
-    # the checkout named by TAAC2026_REFERENCE, else a sibling `reference/` directory of this repository
-    sibling = Path(__file__).resolve().parents[2] / "reference"
-    for candidate in (os.environ.get("TAAC2026_REFERENCE"), str(sibling)):
-        if candidate and (Path(candidate) / "src" / "taac2026").is_dir():
-            return Path(candidate)
-    return None
-
-
-ROOT = _reference_root()
-pytestmark = pytest.mark.skipif(ROOT is None, reason="no reference checkout available")
+pytestmark = pytest.mark.skipif(not ref_runtime.available(), reason="no reference checkout and no oracle/_ref available")
 
 
 @pytest.fixture()
 def installed(monkeypatch):
-    if "orjson" not in sys.modules:
-        try:
-            import orjson  # noqa: F401
-        except ImportError:
-            shim = types.ModuleType("orjson")
-            shim.OPT_INDENT_2 = shim.OPT_SORT_KEYS = shim.OPT_SERIALIZE_NUMPY = shim.OPT_NON_STR_KEYS = 0
-            shim.dumps = lambda obj, default=None, option=0: json.dumps(obj, default=default).encode()
-            shim.loads = json.loads
-            shim.JSONDecodeError = json.JSONDecodeError
-            monkeypatch.setitem(sys.modules, "orjson", shim)
-    for path in (ROOT / "src", ROOT):
-        if str(path) not in sys.path:
-            monkeypatch.syspath_prepend(str(path))
+    ref_runtime.import_reference()
     from taac_2026_b200 import install as tb
     from taac_2026_b200 import ops
 
@@ -111,3 +84,93 @@ def test_spec_from_reference_matches_fixture_spec(installed):
     spec = tb.spec_from_reference(schema, config)
     assert spec.user_int_specs == [(40, 0, 1), (41, 1, 2)] and spec.item_int_specs == [(30, 0, 1)]
     assert spec.seq_vocab_sizes == {"seq_a": [90]} and spec.num_time_buckets == 64 and spec.user_dense_dim == 4
+
+
+def test_config_layer_accepts_the_literal_only_while_installed(installed):
+    tb, _ = installed
+    from taac2026.domain import config as cfg
+
+    made = cfg.PCVRModelConfig(rms_norm_backend="cuda", flash_attention_backend="cuda")
+    assert (made.rms_norm_backend, made.flash_attention_backend) == ("cuda", "cuda")
+    assert "cuda" in cfg.RMS_NORM_BACKEND_CHOICES and "cuda" in cfg.FLASH_ATTENTION_BACKEND_CHOICES
+    assert cfg.PCVRModelConfig(rms_norm_backend="triton").rms_norm_backend == "triton"   # the reference's own names still pass
+    with pytest.raises(Exception, match="rms_norm"):
+        cfg.PCVRModelConfig(rms_norm_backend="nope")
+    tb.uninstall()
+    with pytest.raises(Exception):
+        cfg.PCVRModelConfig(rms_norm_backend="cuda")
+    assert "cuda" not in cfg.RMS_NORM_BACKEND_CHOICES
+    tb.install()
+
+
+def test_resolvers_answer_cuda_in_every_namespace(installed, monkeypatch):
+    tb, _ = installed
+    from taac2026.infrastructure import accelerators as acc
+    from taac2026.infrastructure.accelerators import attention, embedding, normalization
+    from taac_2026_b200 import ops
+
+    seen = []
+    for name in ("resolved_rms_norm_backend", "resolved_layer_norm_backend", "resolved_flash_attention_backend",
+                 "resolved_embedding_bag_mean_backend"):
+        monkeypatch.setattr(ops, name, lambda *a, _n=name, **k: seen.append((_n, a[-1] if isinstance(a[-1], str) else k)) or "cuda")
+    tb.uninstall()
+    tb.install()      # re-wrap with the recording resolvers in place
+    x = torch.ones(2, 4)
+    q = torch.ones(1, 1, 2, 4)
+    ids = torch.ones(2, 3, dtype=torch.long)
+    for holder in (acc, normalization):
+        assert holder.resolved_rms_norm_backend(x, "cuda", eps=1e-6) == "cuda"
+        assert holder.resolved_layer_norm_backend(x, backend="cuda") == "cuda"
+    for holder in (acc, attention):
+        assert holder.resolved_flash_attention_backend(q, q, q, "cuda", is_causal=True) == "cuda"
+    for holder in (acc, embedding):
+        assert holder.resolved_embedding_bag_mean_backend(x, ids, "cuda") == "cuda"
+    assert len(seen) == 8
+    assert acc.resolved_rms_norm_backend(x, "torch") == "torch"          # other names reach the reference's resolver
+    with pytest.raises(ValueError):
+        acc.resolved_rms_norm_backend(x, "nope")
+
+
+def test_operator_benchmark_cli_takes_the_cuda_backend(installed, monkeypatch):
+    tb, calls = installed
+    from taac2026.application.benchmarking import pcvr_tilelang_ops_benchmark as bench
+    from taac_2026_b200 import ops
+
+    monkeypatch.setattr(ops, "compile_rms_norm_kernel", lambda x, w, eps=1e-6, **kw: (lambda x_, w_: bench._reference_rms_norm(x_, w_, eps)))
+    monkeypatch.setattr(ops, "compile_layer_norm_kernel",
+                        lambda x, w, b, eps=1e-5, **kw: (lambda x_, w_, b_: bench._reference_layer_norm(x_, w_, b_, eps)))
+    for operator in ("rms_norm", "layer_norm"):
+        args = bench.parse_args(["--operator", operator, "--backends", "torch,cuda", "--device", "cpu", "--rows", "16", "--cols", "32",
+                                 "--steps", "2", "--warmup-steps", "1", "--repeats", "1", "--dtype", "float32"])
+        assert args.backends == ("torch", "cuda")
+        summary = bench.run_benchmark(args)
+        by_backend = {r["backend"]: r for r in summary["results"]}
+        assert by_backend["cuda"]["status"] == "ok" and by_backend["cuda"]["resolved_backend"] == "cuda", by_backend["cuda"]
+    tb.uninstall()
+    with pytest.raises(ValueError, match="unsupported backends"):
+        bench.parse_args(["--operator", "rms_norm", "--backends", "cuda"])
+    tb.install()
+
+
+def test_route_all_leaves_training_calls_differentiable(installed):
+    """The kernels are forward-only.  With every backend routed here wholesale, a call that needs gradients goes to
+    the reference's torch path instead of silently cutting the graph; an explicit backend="cuda" is left to the
+    operator, which refuses."""
+    tb, calls = installed
+    from taac2026.infrastructure import accelerators as acc
+    from taac_2026_b200 import ops
+
+    tb.install(route_all=True)
+    x = torch.ones(2, 4, requires_grad=True)
+    w = torch.ones(4, requires_grad=True)
+    out = acc.rms_norm(x, w, backend="torch")
+    out.sum().backward()
+    assert w.grad is not None and calls == []
+    with torch.no_grad():
+        acc.rms_norm(x, w, backend="torch")
+    assert calls == ["rms_norm"]
+    with pytest.raises(RuntimeError, match="forward-only"):
+        ops._refuse_autograd("rms_norm", x, w)
+    with torch.no_grad():
+        ops._refuse_autograd("rms_norm", x, w)      # no gradient is being recorded: nothing to refuse
+    tb.install(route_all=False)

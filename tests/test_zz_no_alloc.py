@@ -69,6 +69,12 @@ def test_static_scratch_ffn_matches_three_call_path(gated):
         assert torch.cuda.memory_allocated() == before  # the torch allocator was not touched
         assert torch.isfinite(out.float()).all()
         assert torch.equal(out, want)
+        # the status word lives in the same fixed array: reading it allocates nothing either
+        value = ctypes.c_int32(-1)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert _lib.load().tb200_ffn_fp8_static_status(stream, ctypes.byref(value)) == 0
+        assert value.value == 0 and torch.cuda.memory_allocated() == before
+    assert ops.ffn_fp8_static_status() == 0
     # the Python wrapper is the same call
     out2 = torch.empty_like(out)
     assert torch.equal(ops.ffn_fp8_static(x, weights, out2), want)
@@ -92,7 +98,7 @@ def test_request_beyond_the_fixed_array_is_refused():
         ops.ffn_fp8_static(x, weights, out)
     # the largest request that fits still runs
     fit = rows - 1
-    while fit * (d + hidden) + 256 * 4 + fit * ((d + hidden) // 128) * 4 > capacity:
+    while fit * (d + hidden) + 256 * 5 + fit * ((d + hidden) // 128) * 4 > capacity:   # four parts and the status word, 256-byte units
         fit -= 64
     assert _call_static(x[:fit], weights, out[:fit]) == 0
     torch.cuda.synchronize()
