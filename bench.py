@@ -217,9 +217,13 @@ def launch_work(name: str, meta: dict) -> tuple[str, float]:
         select = 4.0 * meta["rows"] if meta["rows_out"] != meta["rows"] else 0.0
         return "hbm", row_bytes * (2.0 * meta["rows"] + meta["rows_out"]) + 8.0 * meta["tables"] * meta["rows"] + select
     if name == "token_project":
-        # fused tokenizer: distinct table rows in, the full-height normalised rows and the kept token rows out, ids and
-        # the int32 destination per row
-        return "hbm", float(meta["bytes"])
+        # fused tokenizer: every DISTINCT table row in once (repeats are served by the L2), the full-height normalised
+        # rows and the kept token rows out, the feature ids, the two ids of the added rows and the int32 destination
+        ids = meta["ids"]
+        row_bytes = meta["k"] // ids.shape[0] * 2
+        distinct = sum(int(torch.unique(ids[f]).numel()) for f in range(ids.shape[0]))
+        out_bytes = 2.0 * meta["cols"] * (meta["rows"] + meta["rows_out"])
+        return "hbm", float(distinct * row_bytes) + out_bytes + 8.0 * ids.numel() + 20.0 * meta["rows"]
     if name == "scatter_rows":
         return "hbm", 3.0 * meta["rows"] * meta["dim"] * meta["esize"] + 8.0 * meta["rows"]
     if name in ("rms_norm", "layer_norm"):

@@ -112,6 +112,31 @@ int tb200_token_tail_select_fwd(const void* x, const void* ln_gamma, const void*
                                 void* tokens, void* normed, int64_t rows, int32_t cols, float ln_eps, float rms_eps,
                                 int dtype, void* stream);
 
+/* The whole sequence tokenizer in one kernel: row gather -> projection -> SiLU -> LayerNorm -> time / position rows
+ * -> first RMSNorm,
+ *     x[r, :]      = concat_f tables[f][clamp(ids[f, r]), :]                     (K = n_feat * emb columns)
+ *     tokens[r, :] = layernorm(silu(x[r, :] @ w^T + bias)) + table_a[ids_a[r]] (+ table_b[ids_b[r]])
+ *     normed[r, :] = rmsnorm(tokens[r, :]) * rms_gamma
+ * i.e. `SequenceTokenizer.forward` (src/taac2026/infrastructure/modeling/tokenizers.py:156-190: `nn.Embedding`
+ * lookups, `torch.cat`, `nn.Linear -> nn.SiLU -> nn.LayerNorm`, the time-bucket rows), the sinusoidal position rows and
+ * the `attn_norm` of the first `OneTransBlock` (experiments/onetrans/model.py:106) without the gathered [rows, K]
+ * matrix and the projected [rows, n_cols] matrix ever being written: tb200_gather_rows + a GEMM +
+ * tb200_token_tail_select_fwd in one pass (tcgen05 MMAs on a CTA pair, the row-wise tail in their epilogue).  Values
+ * agree with that three-kernel path to bf16 rounding (the projection is not rounded to bf16 before the SiLU here).
+ * tables / table_rows: HOST arrays of n_feat (<= 8) device table pointers (NULL = a feature without a table: zeros)
+ * and their row counts; every table is [table_rows[f], emb] bf16; emb in {32, 64, 128}, n_feat * emb in {64, 128}.
+ * ids: device int64 [n_feat, rows], clamped into their table.  w: [n_cols, n_feat * emb] bf16 (`nn.Linear.weight`),
+ * bias: fp32 [n_cols] or NULL; ln_gamma, ln_beta, rms_gamma: bf16 [n_cols]; table_a / table_b (NULL allowed):
+ * bf16 [rows_a / rows_b, n_cols] with device int64 ids per row.  n_cols in {256, 512}; bf16 only.
+ * row_dst, rows_out, tokens, normed: as in tb200_token_tail_select_fwd.  status_word: optional device int32 that
+ * the kernel sets to 1 if one of its bounded waits gave up (the outputs are then incomplete). */
+int tb200_token_project_fwd(const void* const* tables, const int64_t* table_rows, int32_t n_feat, int32_t emb,
+                            const int64_t* ids, const void* w, const float* bias, const void* ln_gamma,
+                            const void* ln_beta, const void* table_a, int64_t rows_a, const int64_t* ids_a,
+                            const void* table_b, int64_t rows_b, const int64_t* ids_b, const void* rms_gamma,
+                            const int32_t* row_dst, int64_t rows_out, void* tokens, void* normed, int64_t rows,
+                            int32_t n_cols, float ln_eps, float rms_eps, int32_t* status_word, void* stream);
+
 /* ---- (a) sparse-field embedding gather / pool ---------------------------------------------
  * out[b, :] = mean over hot h of table[ids[b, h], :] for ids in (0, vocab_rows); ids equal to 0
  * (padding) or outside the table are skipped; an empty bag gives zeros.  fp32 sum in hot order,

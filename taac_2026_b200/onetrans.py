@@ -696,16 +696,24 @@ class OneTransInference:
         ids_all, pos_full, buckets_full = ops.packed_token_index(
             values, ts if has_time else None, request_ts, src_map, cu[0], n0, start, self._hash_buckets[domain], total0,
             edges=self._edges if has_time else None)
-        if live:
-            token_input = (torch.empty if len(live) == n_feat else torch.zeros)(
-                (total0, n_feat * emb), dtype=self.dtype, device=dev)
-            for f in live:
-                ops.gather_rows(entries[f][1], ids_all[f], out=token_input, col0=f * emb)
-        else:
-            token_input = torch.zeros(total0, max(1, n_feat * emb), dtype=self.dtype, device=dev)
-        # Linear -> SiLU -> LayerNorm, the time-bucket and position rows and the first block's RMSNorm in one pass
-        # over the token matrix (`token_tail`); the NS rows are filled in afterwards
-        projected = self._linear(token_input, prefix + ".project.0")
+        seq_tables = [entries[f][1] if f in live else None for f in range(n_feat)]
+        proj_w = self._p(prefix + ".project.0.weight")
+        # gather -> projection -> SiLU -> LayerNorm -> time / position rows -> first RMSNorm as ONE kernel where the
+        # shapes allow it (bf16, whole-tile widths); else the row gather, the projection GEMM and the fused tail
+        one_kernel = (self.fused_tokenizer and self.dtype == torch.bfloat16 and bool(self.blocks) and bool(live)
+                      and ops.token_project_supported(seq_tables, proj_w))
+        projected = None
+        if not one_kernel:
+            if live:
+                token_input = (torch.empty if len(live) == n_feat else torch.zeros)(
+                    (total0, n_feat * emb), dtype=self.dtype, device=dev)
+                for f in live:
+                    ops.gather_rows(entries[f][1], ids_all[f], out=token_input, col0=f * emb)
+            else:
+                token_input = torch.zeros(total0, max(1, n_feat * emb), dtype=self.dtype, device=dev)
+            # Linear -> SiLU -> LayerNorm, the time-bucket and position rows and the first block's RMSNorm in one pass
+            # over the token matrix (`token_tail`); the NS rows are filled in afterwards
+            projected = self._linear(token_input, prefix + ".project.0")
         ln_w, ln_b = self._p(prefix + ".project.2.weight"), self._p(prefix + ".project.2.bias")
         pos_table = self._positions(width).to(self.dtype).contiguous()
         rows_a, rows_b = (pos_table, pos_full), (None, None)
@@ -725,13 +733,22 @@ class OneTransInference:
         # When the first block is evaluated for the kept rows only, its residual stream is needed for those rows
         # alone: the fused pass then writes `tokens` already compacted and only `x_first` at full height.
         first_kept = None
-        fused_tail = first_norm_w is not None and projected.shape[1] % (16 // projected.element_size()) == 0
+        fused_tail = one_kernel or (first_norm_w is not None and projected.shape[1] % (16 // projected.element_size()) == 0)
         if fused_tail and self.select_early and widths[1] < widths[0] and not (ns > 0 and max_rows[0] == ns) \
                 and totals[1] < 2**31:
             first_kept = kept_rows(0)
             row_dst = torch.full((total0,), -1, dtype=torch.int32, device=dev)
             row_dst[first_kept[0]] = torch.arange(totals[1], dtype=torch.int32, device=dev)
-        if fused_tail:
+        if one_kernel:
+            key = prefix + ".project.0#b32"
+            if key not in self._cast_cache:
+                self._cast_cache[key] = self.w[prefix + ".project.0.bias"].float().contiguous()
+            tokens, x_first = ops.token_project(seq_tables, ids_all, proj_w, self._cast_cache[key], ln_w, ln_b, rows_a[0],
+                                                rows_a[1], rows_b[0], rows_b[1], first_norm_w,
+                                                row_dst=None if first_kept is None else row_dst,
+                                                rows_out=None if first_kept is None else totals[1],
+                                                status=self.status_word)
+        elif fused_tail:
             tokens, x_first = ops.token_tail(projected, ln_w, ln_b, rows_a[0], rows_a[1], rows_b[0], rows_b[1], first_norm_w,
                                              row_dst=None if first_kept is None else row_dst,
                                              rows_out=None if first_kept is None else totals[1])

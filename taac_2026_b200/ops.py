@@ -1272,6 +1272,83 @@ def token_tail(x: torch.Tensor, ln_weight: torch.Tensor, ln_bias: torch.Tensor, 
     return tokens, normed
 
 
+def token_project_supported(tables: list[torch.Tensor | None], weight: torch.Tensor) -> bool:
+    """True when ``token_project`` serves this tokenizer: bf16, 1..8 features of one width in {32, 64, 128} whose
+    concatenation is 64 or 128 wide, a model width of 256 or 512."""
+    live = [t for t in tables if t is not None]
+    if not live or len(tables) > 8 or weight.dtype != torch.bfloat16 or weight.ndim != 2:
+        return False
+    emb = live[0].shape[1]
+    if any(t.ndim != 2 or t.shape[1] != emb or t.dtype != torch.bfloat16 or not t.is_contiguous() for t in live):
+        return False
+    return emb in (32, 64, 128) and len(tables) * emb in (64, 128) and weight.shape[0] in (256, 512) \
+        and weight.shape[1] == len(tables) * emb
+
+
+def token_project(tables: list[torch.Tensor | None], ids: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                  ln_weight: torch.Tensor, ln_bias: torch.Tensor, table_a: torch.Tensor, ids_a: torch.Tensor,
+                  table_b: torch.Tensor | None, ids_b: torch.Tensor | None, rms_weight: torch.Tensor, *,
+                  ln_eps: float = 1e-5, rms_eps: float = 1e-6, row_dst: torch.Tensor | None = None,
+                  rows_out: int | None = None, check: bool = False, status: torch.Tensor | None = None,
+                  ) -> tuple[torch.Tensor, torch.Tensor]:
+    """The sequence tokenizer in one kernel: ``x = cat_f tables[f][ids[f]]``, ``p = x @ weight.T + bias``,
+    ``tokens = layer_norm(silu(p)) + table_a[ids_a] (+ table_b[ids_b])``, ``normed = rms_norm(tokens)``.
+
+    ``tables``: one bf16 ``[rows_f, emb]`` table (or None: zeros) per feature; ``ids``: int64 ``[n_feat, rows]``;
+    ``weight``: bf16 ``[N, n_feat * emb]``; ``bias``: ``[N]`` (used as fp32).  The rest as in ``token_tail``, of which
+    this is the fused form (``gather_rows`` + the projection GEMM + ``token_tail``): same outputs to bf16 rounding,
+    without the two intermediate matrices.  Returns ``(tokens, normed)``."""
+    _require_backend("token_project", "cuda")
+    live = [t for t in tables if t is not None]
+    _require_cuda_tensors("cuda token_project", *live, ids, weight, bias, ln_weight, ln_bias, table_a, ids_a, table_b, ids_b,
+                          rms_weight, row_dst)
+    if not token_project_supported(tables, weight):
+        raise ValueError("token_project: unsupported tokenizer shape (see token_project_supported)")
+    n_feat, emb = len(tables), live[0].shape[1]
+    n_cols = weight.shape[0]
+    if ids.dtype != torch.int64 or ids.ndim != 2 or ids.shape[0] != n_feat or not ids.is_contiguous():
+        raise ValueError("token_project ids must be a contiguous int64 [n_feat, rows] tensor")
+    rows = ids.shape[1]
+    if (table_b is None) != (ids_b is None):
+        raise ValueError("token_project: table_b and ids_b come together")
+    for table, idv in ((table_a, ids_a), (table_b, ids_b)):
+        if table is None:
+            continue
+        if table.ndim != 2 or table.shape[1] != n_cols or table.dtype != torch.bfloat16 or not table.is_contiguous():
+            raise ValueError("token_project added tables must be contiguous bf16 [rows, N] matrices")
+        if idv.dtype != torch.int64 or idv.numel() != rows or not idv.is_contiguous():
+            raise ValueError("token_project added-row ids must be contiguous int64 with one entry per row")
+    dev = weight.device
+    vecs = [v.to(device=dev, dtype=torch.bfloat16).contiguous() for v in (ln_weight, ln_bias, rms_weight)]
+    if any(tuple(v.shape) != (n_cols,) for v in vecs):
+        raise ValueError("token_project weight vectors must have one entry per column")
+    bias32 = None if bias is None else bias.to(device=dev, dtype=torch.float32).contiguous()
+    if row_dst is not None:
+        if row_dst.dtype != torch.int32 or row_dst.numel() != rows or not row_dst.is_contiguous():
+            raise ValueError("token_project row_dst must be contiguous int32 with one entry per row")
+        if rows_out is None or rows_out < 0:
+            raise ValueError("token_project: row_dst needs rows_out")
+    n_out = rows if row_dst is None else int(rows_out)
+    tokens = torch.empty((n_out, n_cols), dtype=torch.bfloat16, device=dev)
+    normed = torch.empty((rows, n_cols), dtype=torch.bfloat16, device=dev)
+    table_ptrs = (ctypes.c_void_p * n_feat)(*[0 if t is None else t.data_ptr() for t in tables])
+    table_rows = (ctypes.c_int64 * n_feat)(*[1 if t is None else t.shape[0] for t in tables])
+    status = _status_word(check, status, dev)
+    weight = weight.contiguous()
+    with torch.cuda.device(dev), _timed("token_project", rows=rows, cols=n_cols, k=n_feat * emb, rows_out=n_out,
+                                       ids=ids, bytes=0):
+        code = _lib.load().tb200_token_project_fwd(
+            table_ptrs, table_rows, n_feat, emb, _ptr(ids), _ptr(weight), _ptr(bias32), _ptr(vecs[0]), _ptr(vecs[1]),
+            _ptr(table_a), table_a.shape[0], _ptr(ids_a), _ptr(table_b), 0 if table_b is None else table_b.shape[0],
+            _ptr(ids_b), _ptr(vecs[2]), _ptr(row_dst), n_out, _ptr(tokens), _ptr(normed), rows, n_cols, float(ln_eps),
+            float(rms_eps), _ptr(status), _stream_ptr(),
+        )
+    _lib.check(code, "cuda token_project")
+    if check and int(status.item()) != 0:
+        raise RuntimeError("cuda token_project: a bounded wait inside the kernel gave up; the outputs are incomplete")
+    return tokens, normed
+
+
 def bias_act_rows(x: torch.Tensor, bias: torch.Tensor, *, silu: bool) -> torch.Tensor:
     """``x = act(x + bias[group])`` in place for a contiguous ``x`` [groups, rows_per_group, cols] (or
     [rows, cols] with ``bias`` [cols]); ``act`` is SiLU (the sum rounded to the dtype first) or identity."""
@@ -1309,6 +1386,8 @@ __all__ = [
     "timed",
     "add_gathered_rows",
     "token_tail",
+    "token_project",
+    "token_project_supported",
     "bias_act_rows",
     "bias_silu_rows",
     "AttentionMaskPlan",
