@@ -89,6 +89,23 @@ __device__ __forceinline__ void st_cluster_f2(uint32_t addr, float a, float b) {
 __device__ __forceinline__ void st_cluster_f1(uint32_t addr, float a) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
 }
+// bounded wait that also acquires the other CTA's writes made before its arrival
+__device__ __forceinline__ bool wait_cluster(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes) : "memory");
 }
@@ -113,13 +130,7 @@ __device__ __forceinline__ void forget_unpacked(uint32_t (&h)[N]) {
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
     return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
 }
-// Read-only 16-byte loads as volatile statements: the compiler keeps them where they are written instead of hoisting
-// the loads of all sixteen unrolled chunks to the top of a loop (and spilling what they fetched).
-__device__ __forceinline__ uint4 ldg_u4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
+__device__ __forceinline__ uint4 ldg_u4(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint2 ldg_u2(const void* p) {
     uint2 v;
     asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
@@ -130,11 +141,7 @@ __device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
     const __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
-__device__ __forceinline__ float4 ldg_f4(const void* p) {
-    float4 v;
-    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-}
+__device__ __forceinline__ float4 ldg_f4(const void* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
 template <int N_COLS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -149,6 +156,11 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     __shared__ uint64_t w_full;                  // this CTA's rows of W are resident
     __shared__ uint64_t tmem_full[2];            // accumulator buffer complete (tcgen05.commit)
     __shared__ uint64_t tmem_free[2];            // every warp has read its columns of the buffer
+    // Per lane quarter, one barrier for each of the two exchanges of a tile: the eight warps (four here, four in the
+    // other CTA) that share its rows have written their partial statistics.  Two barriers, not one with alternating
+    // phases: a warp of the other CTA may arrive for the next exchange while an arrival for this one is still on its
+    // way, and on a single barrier that early arrival would be counted for the wrong phase.
+    __shared__ uint64_t ex_bar[4][2];
     __shared__ uint32_t tmem_base_slot;
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -157,6 +169,7 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     uint8_t* box_s = a_s + kAStages * kAStageBytes;                    // [16 warps][32 rows][128 B]
     float2* ex1 = reinterpret_cast<float2*>(box_s + kWarps * kBoxBytes);      // [8][128] (local mean, local M2) of the 8 column groups
     float* ex2 = reinterpret_cast<float*>(ex1 + 8 * kRows);            // [8][128] partial sums of squares
+    float* pvec = ex2 + 8 * kRows;                                     // [4][NC] fp32: bias, ln gamma, ln beta, rms gamma of this CTA's columns
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();       // which half of the columns
@@ -174,11 +187,22 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             mbar_init(&tmem_free[s], kWarps);
         }
         mbar_init(&w_full, 1);
+        for (int q = 0; q < 4; ++q) {
+            mbar_init(&ex_bar[q][0], 8);
+            mbar_init(&ex_bar[q][1], 8);
+        }
         fence_mbar_init();
     }
     if (warp == 1) {
         tmem_alloc(&tmem_base_slot, 2 * NC);
         tmem_relinquish();
+    }
+    for (int i = threadIdx.x; i < NC; i += kThreads) {
+        const int col = static_cast<int>(cluster_rank()) * NC + i;
+        pvec[i] = g.bias != nullptr ? g.bias[col] : 0.f;
+        pvec[NC + i] = __bfloat162float(g.ln_gamma[col]);
+        pvec[2 * NC + i] = __bfloat162float(g.ln_beta[col]);
+        pvec[3 * NC + i] = __bfloat162float(g.rms_gamma[col]);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -196,32 +220,50 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
 
     // ---- gather of one 128-row A tile: warp w copies rows [8 w, 8 w + 8); emb / 8 lanes copy one feature row.
     // Both CTAs of the pair gather the same rows (the second read of a table row is served by the L2).
+    // Every thread makes K / 32 copies per tile (at most four).  Their table-row ids are read one tile before the copies
+    // are issued (`load_ids`), so that the copies never wait for an id to arrive from HBM.
+    uint32_t gid[4];
+    auto load_ids = [&](int32_t it_local) {
+        uint32_t tid_v;
+        asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid_v));
+        const int gw = static_cast<int>(tid_v >> 5), gl = static_cast<int>(tid_v & 31);
+        const int chunks_f = g.emb >> 3;                  // 16-byte pieces of one feature's row: 4, 8 or 16
+        const int per_feat = chunks_f >> 2;               // copies per thread and feature: 8 rows / (32 / chunks_f)
+        const int sub_row = gl / chunks_f;
+        const int32_t row0 = (pair + it_local * n_pairs) * kRows;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = q / per_feat;
+            const int i = (q - f * per_feat) * (32 / chunks_f);
+            uint32_t id = 0;
+            if (f < g.n_feat && g.table[f] != nullptr) {
+                const int64_t r = min(row0 + gw * 8 + i + sub_row, n_rows - 1);
+                const int64_t v = g.ids[static_cast<int64_t>(f) * g.rows + r];
+                id = static_cast<uint32_t>(min(max(v, static_cast<int64_t>(0)), g.table_rows[f] - 1));
+            }
+            gid[q] = id;
+        }
+    };
     auto gather = [&](int32_t it_local) {
         // thread and layout constants are derived afresh from a volatile read of the thread id on every call: kept
         // alive across the epilogue they would cost a dozen registers
         uint32_t tid_v;
         asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid_v));
         const int gw = static_cast<int>(tid_v >> 5), gl = static_cast<int>(tid_v & 31);
-        const int chunks_f = g.emb >> 3;                  // 16-byte pieces of one feature's row: 4, 8 or 16
-        const int rows_per_instr = 32 / chunks_f;
+        const int chunks_f = g.emb >> 3;
+        const int per_feat = chunks_f >> 2;
         const int sub_row = gl / chunks_f;
         const int piece = gl - sub_row * chunks_f;
-        const uint32_t a_base = smem_u32(a_s);
-        const int32_t row0 = (pair + it_local * n_pairs) * kRows;
-        const uint32_t s = static_cast<uint32_t>(it_local) & 1u;
-        for (int f = 0; f < g.n_feat; ++f) {
-            const __nv_bfloat16* table = g.table[f];
-            const int64_t last = g.table_rows[f] - 1;
-            const int col_piece = f * chunks_f + piece;          // 16-byte piece inside the K-wide row
-            const uint32_t dst_kb = a_base + s * kAStageBytes + (col_piece >> 3) * kKBlockBytes;
-            const int j = col_piece & 7;
-            for (int i = 0; i < 8; i += rows_per_instr) {
-                const int tile_row = gw * 8 + i + sub_row;
-                const int64_t r = min(row0 + tile_row, n_rows - 1);
-                const int64_t v = table != nullptr ? g.ids[static_cast<int64_t>(f) * g.rows + r] : 0;
-                const int64_t rid = min(max(v, static_cast<int64_t>(0)), last);
-                const uint32_t dst = dst_kb + tile_row * 128 + ((j ^ (tile_row & 7)) << 4);
-                const __nv_bfloat16* src = table != nullptr ? table + rid * g.emb + piece * 8 : g.table_a;
+        const uint32_t stage = smem_u32(a_s) + (static_cast<uint32_t>(it_local) & 1u) * kAStageBytes;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = q / per_feat;
+            if (f < g.n_feat) {
+                const int tile_row = gw * 8 + (q - f * per_feat) * (32 / chunks_f) + sub_row;
+                const int col_piece = f * chunks_f + piece;          // 16-byte piece inside the K-wide row
+                const uint32_t dst = stage + (col_piece >> 3) * kKBlockBytes + tile_row * 128 + (((col_piece & 7) ^ (tile_row & 7)) << 4);
+                const __nv_bfloat16* table = g.table[f];
+                const __nv_bfloat16* src = table != nullptr ? table + static_cast<int64_t>(gid[q]) * g.emb + piece * 8 : g.table_a;
                 cp_async16(dst, src, table != nullptr ? 16u : 0u);
             }
         }
@@ -256,14 +298,32 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const int slot = (static_cast<int>(rank) * 4 + cg) * kRows + row_in_tile;   // this thread's place in the exchange tables
     const uint32_t ex1_peer = map_to_peer(smem_u32(ex1 + slot), rank ^ 1u);
     const uint32_t ex2_peer = map_to_peer(smem_u32(ex2 + slot), rank ^ 1u);
+    const uint32_t exbar_peer = map_to_peer(smem_u32(&ex_bar[quarter][0]), rank ^ 1u);
+    // The eight warps that hold parts of the same 32 rows meet at ex_bar[quarter] twice per tile: every warp writes its
+    // partials here and into the other CTA, then one lane arrives on both CTAs' barriers (release at cluster scope,
+    // after the warp's writes) and the warp waits on its own CTA's.  Warps of other row quarters are not involved, so
+    // the quarters drift apart and fill each other's stalls.
+    auto exchange_arrive = [&](int which) {      // which: 0 = LayerNorm sums, 1 = RMS sum of the tile
+        __syncwarp();                            // the warp's partial writes come before its one arrival
+        if (lane == 0) {
+            asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ex_bar[quarter][which])) : "memory");
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(exbar_peer + 8u * which) : "memory");
+        }
+    };
+    auto exchange_wait = [&](int which, uint32_t tile) -> bool {    // every lane waits (and so acquires the other warps' writes) itself
+        return __all_sync(0xffffffffu, wait_cluster(&ex_bar[quarter][which], tile & 1u, kWait) ? 1 : 0) != 0;
+    };
     constexpr float kInvN = 1.0f / N_COLS;
     bool ok = true;
 
     // ---- prologue: tiles 0 and 1 on their way, tile 0 signalled, its MMAs issued
+    load_ids(0);
     if (my_tiles > 0) gather(0);
     asm volatile("cp.async.commit_group;" ::: "memory");
+    load_ids(1);
     if (my_tiles > 1) gather(1);
     asm volatile("cp.async.commit_group;" ::: "memory");
+    load_ids(2);
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     fence_proxy_async_smem();                 // the copied rows are visible to the tensor core's proxy before the signal
     mbar_arrive(&full_bar[0]);
@@ -276,17 +336,11 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     for (int32_t it = 0; it < my_tiles; ++it) {
         const int32_t m0 = (pair + it * n_pairs) * kRows;
         const uint32_t b = static_cast<uint32_t>(it) & 1u;
-        // ---- the next tile's rows have landed (copies issued a tile ago): signal, and let its MMAs start into the
-        // other accumulator buffer; they run under the whole epilogue of this tile
+        // ---- the next tile's rows have landed (copies issued a tile ago): signal
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (it + 1 < my_tiles) {
             fence_proxy_async_smem();
             mbar_arrive(&full_bar[b ^ 1u]);
-            if (warp == 0) {
-                int passed = 1;
-                if (lane == 0 && ok) passed = issue(it + 1) ? 1 : 0;
-                if (__shfl_sync(0xffffffffu, passed, 0) == 0) ok = false;
-            }
         }
         // A warp whose wait gives up stops waiting but keeps walking the tiles, so that it still meets every barrier
         // and every arrival the others count on; its output is garbage and the status word says so.
@@ -299,6 +353,7 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         // the MMAs of this tile are done: its A stage is free for the tile after the next
         if (it + 2 < my_tiles) gather(it + 2);
         asm volatile("cp.async.commit_group;" ::: "memory");
+        load_ids(it + 3);                        // rows past the end are clamped: the ids are simply not used
 
         const int32_t row = min(m0 + row_in_tile, n_rows - 1);   // rows past the end repeat the last one (nothing of theirs is stored)
         const bool row_ok = m0 + row_in_tile < n_rows;
@@ -306,77 +361,83 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         const int32_t id_b = g.table_b != nullptr ? static_cast<int32_t>(min(max(g.ids_b[row], static_cast<int64_t>(0)), g.rows_b - 1)) : 0;
         int32_t dst_row = g.row_dst != nullptr ? g.row_dst[row] : row;
         if (!row_ok || dst_row >= g.rows_out) dst_row = -1;
+        const __nv_bfloat16* ta = g.table_a + static_cast<int64_t>(id_a) * N_COLS + col0;
+        const __nv_bfloat16* tb = g.table_b != nullptr ? g.table_b + static_cast<int64_t>(id_b) * N_COLS + col0 : nullptr;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(ta));      // this thread's 2 * CPT bytes of the two rows: one line each
+        if (tb != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(tb));
 
         // ---- pass 1: accumulator columns -> bf16 SiLU values in registers
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * NC + cg * CPT;
         uint32_t h[NP];
+        float2 s1 = make_float2(0.f, 0.f), s2 = make_float2(0.f, 0.f);     // sum and sum of squares of the SiLU values
+        {
+            uint32_t acc[CPT / 16][16];
 #pragma unroll
-        for (int c = 0; c < CPT / 16; ++c) {
-            uint32_t acc[16];
-            tmem_ld_x16(taddr + 16 * c, acc);
-            tc_wait_ld(acc);
+            for (int c = 0; c < CPT / 16; ++c) tmem_ld_x16(taddr + 16 * c, acc[c]);     // back to back, one wait
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (g.bias != nullptr) bv = ldg_f4(g.bias + col0 + 16 * c + 4 * j);
-                const float2 v0 = silu2(__fadd2_rn(make_float2(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1])), make_float2(bv.x, bv.y)));
-                const float2 v1 = silu2(__fadd2_rn(make_float2(__uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3])), make_float2(bv.z, bv.w)));
-                h[8 * c + 2 * j] = pack_bf16x2(v0);
-                h[8 * c + 2 * j + 1] = pack_bf16x2(v1);
+            for (int c = 0; c < CPT / 16; ++c) tc_wait_ld(acc[c]);                      // (the first one waits for all of them)
+            const float* bias_s = pvec + cg * CPT;
+#pragma unroll
+            for (int c = 0; c < CPT / 16; ++c) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 bv = *reinterpret_cast<const float4*>(bias_s + 16 * c + 4 * j);
+                    const float2 v0 = silu2(__fadd2_rn(make_float2(__uint_as_float(acc[c][4 * j]), __uint_as_float(acc[c][4 * j + 1])), make_float2(bv.x, bv.y)));
+                    const float2 v1 = silu2(__fadd2_rn(make_float2(__uint_as_float(acc[c][4 * j + 2]), __uint_as_float(acc[c][4 * j + 3])), make_float2(bv.z, bv.w)));
+                    s1 = __fadd2_rn(s1, __fadd2_rn(v0, v1));
+                    s2 = __ffma2_rn(v0, v0, s2);
+                    s2 = __ffma2_rn(v1, v1, s2);
+                    h[8 * c + 2 * j] = pack_bf16x2(v0);
+                    h[8 * c + 2 * j + 1] = pack_bf16x2(v1);
+                }
             }
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_free[b]);   // the MMAs of the tile after the next may overwrite this buffer
-
-        // ---- LayerNorm statistics of the rounded SiLU values: local mean and centred sum of squares, then the
-        // exact combination of the eight column groups of the row (four here, four in the other CTA)
-        float2 acc2 = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < NP; ++i) acc2 = __fadd2_rn(acc2, unpack_bf16x2(h[i]));
-        forget_unpacked(h);
-        const float mean_l = (acc2.x + acc2.y) * (1.0f / CPT);
-        const float2 nmean_l = make_float2(-mean_l, -mean_l);
-        acc2 = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < NP; ++i) {
-            const float2 d = __fadd2_rn(unpack_bf16x2(h[i]), nmean_l);
-            acc2 = __ffma2_rn(d, d, acc2);
+        // the next tile's MMAs go into the other buffer and run under the rest of this epilogue; by now every warp has
+        // signalled that tile's rows, so the issuing warp does not wait for stragglers
+        if (warp == 0 && it + 1 < my_tiles) {
+            int passed = 1;
+            if (lane == 0 && ok) passed = issue(it + 1) ? 1 : 0;
+            if (__shfl_sync(0xffffffffu, passed, 0) == 0) ok = false;
         }
-        forget_unpacked(h);
-        ex1[slot] = make_float2(mean_l, acc2.x + acc2.y);
-        st_cluster_f2(ex1_peer, mean_l, acc2.x + acc2.y);
-        cluster_sync_all();
+
+        // ---- LayerNorm statistics: this thread's sum and sum of squares (fp32, taken in pass 1) meet those of the
+        // row's other seven column groups, four of them in the other CTA
+        ex1[slot] = make_float2(s1.x + s1.y, s2.x + s2.y);
+        st_cluster_f2(ex1_peer, s1.x + s1.y, s2.x + s2.y);
+        exchange_arrive(0);
+        if (!exchange_wait(0, static_cast<uint32_t>(it)) && ok) ok = false;
         float mean = 0.f, m2 = 0.f;
-        float2 part[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-            part[q] = ex1[q * kRows + row_in_tile];
-            mean += part[q].x;
-            m2 += part[q].y;
+            const float2 part = ex1[q * kRows + row_in_tile];
+            mean += part.x;
+            m2 += part.y;
         }
-        mean *= 0.125f;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) m2 = fmaf(static_cast<float>(CPT) * (part[q].x - mean), part[q].x - mean, m2);
-        const float rstd1 = rsqrtf(m2 * kInvN + g.ln_eps);
+        mean *= kInvN;
+        const float rstd1 = rsqrtf(fmaxf(fmaf(-mean, mean, m2 * kInvN), 0.f) + g.ln_eps);
         const float2 nmean = make_float2(-mean, -mean);
         const float2 rstd = make_float2(rstd1, rstd1);
 
         // ---- normalise, add the table rows (one rounding per sum, like tensor additions), RMS partial sum
-        const __nv_bfloat16* ta = g.table_a + static_cast<int64_t>(id_a) * N_COLS + col0;
-        const __nv_bfloat16* tb = g.table_b != nullptr ? g.table_b + static_cast<int64_t>(id_b) * N_COLS + col0 : nullptr;
-        acc2 = make_float2(0.f, 0.f);
+        float2 acc2 = make_float2(0.f, 0.f);
+        const float* gam_s = pvec + NC + cg * CPT;
+        const float* bet_s = pvec + 2 * NC + cg * CPT;
 #pragma unroll
         for (int c = 0; c < CPT / 8; ++c) {
-            const uint4 gw = ldg_u4(g.ln_gamma + col0 + 8 * c);
-            const uint4 bw = ldg_u4(g.ln_beta + col0 + 8 * c);
             const uint4 aw = ldg_u4(ta + 8 * c);
-            const uint32_t gws[4] = {gw.x, gw.y, gw.z, gw.w}, bws[4] = {bw.x, bw.y, bw.z, bw.w}, aws[4] = {aw.x, aw.y, aw.z, aw.w};
+            const uint32_t aws[4] = {aw.x, aw.y, aw.z, aw.w};
             uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                w[e] = pack_bf16x2(__ffma2_rn(__fmul2_rn(__fadd2_rn(unpack_bf16x2(h[4 * c + e]), nmean), rstd), unpack_bf16x2(gws[e]), unpack_bf16x2(bws[e])));
+            for (int e = 0; e < 4; e += 2) {
+                const float4 g4 = *reinterpret_cast<const float4*>(gam_s + 8 * c + 2 * e);
+                const float4 b4 = *reinterpret_cast<const float4*>(bet_s + 8 * c + 2 * e);
+                w[e] = pack_bf16x2(__ffma2_rn(__fmul2_rn(__fadd2_rn(unpack_bf16x2(h[4 * c + e]), nmean), rstd), make_float2(g4.x, g4.y), make_float2(b4.x, b4.y)));
+                w[e + 1] = pack_bf16x2(__ffma2_rn(__fmul2_rn(__fadd2_rn(unpack_bf16x2(h[4 * c + e + 1]), nmean), rstd), make_float2(g4.z, g4.w), make_float2(b4.z, b4.w)));
                 w[e] = add_bf16x2(w[e], aws[e]);
+                w[e + 1] = add_bf16x2(w[e + 1], aws[e + 1]);
             }
             if (tb != nullptr) {
                 const uint4 b2 = ldg_u4(tb + 8 * c);
@@ -395,7 +456,8 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         forget_unpacked(h);
         ex2[slot] = acc2.x + acc2.y;
         st_cluster_f1(ex2_peer, acc2.x + acc2.y);
-        cluster_sync_all();
+        exchange_arrive(1);
+        if (!exchange_wait(1, static_cast<uint32_t>(it)) && ok) ok = false;
         float sq = 0.f;
 #pragma unroll
         for (int q = 0; q < 8; ++q) sq += ex2[q * kRows + row_in_tile];
@@ -412,14 +474,16 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         // ---- `normed`: the warp's 32 rows x CPT columns through its staging box (128-byte rows at CPT = 64)
         if (lane == 0) bulk_wait_read<0>();     // this warp's previous store has read the box
         __syncwarp();
+        const float* rg_s = pvec + 3 * NC + cg * CPT;
 #pragma unroll
         for (int c = 0; c < CPT / 8; ++c) {
-            const uint4 gw = ldg_u4(g.rms_gamma + col0 + 8 * c);
+            const float4 g0 = *reinterpret_cast<const float4*>(rg_s + 8 * c);
+            const float4 g1 = *reinterpret_cast<const float4*>(rg_s + 8 * c + 4);
             uint4 o;
-            o.x = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c]), rms), unpack_bf16x2(gw.x)));
-            o.y = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c + 1]), rms), unpack_bf16x2(gw.y)));
-            o.z = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c + 2]), rms), unpack_bf16x2(gw.z)));
-            o.w = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c + 3]), rms), unpack_bf16x2(gw.w)));
+            o.x = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c]), rms), make_float2(g0.x, g0.y)));
+            o.y = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c + 1]), rms), make_float2(g0.z, g0.w)));
+            o.z = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c + 2]), rms), make_float2(g1.x, g1.y)));
+            o.w = pack_bf16x2(__fmul2_rn(__fmul2_rn(unpack_bf16x2(h[4 * c + 3]), rms), make_float2(g1.z, g1.w)));
             // CPT = 64: eight 16-byte pieces per row, 128-byte swizzle; CPT = 32: four pieces, 64-byte swizzle
             const int pc = CPT == 64 ? (c ^ swz) : (c ^ ((lane >> 1) & 3));
             *reinterpret_cast<uint4*>(box + lane * (2 * CPT) + (pc << 4)) = o;
@@ -479,7 +543,7 @@ bool make_tmap(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t 
 template <int N_COLS>
 int launch(const CUtensorMap& tw, const CUtensorMap& to, const TPArgs& g, cudaStream_t stream) {
     constexpr size_t smem = kMaxKBlocks * (N_COLS / 2) * 128 + kAStages * kAStageBytes + kWarps * kBoxBytes +
-                            8 * kRows * sizeof(float2) + 8 * kRows * sizeof(float) + 1024;
+                            8 * kRows * sizeof(float2) + 8 * kRows * sizeof(float) + 4 * (N_COLS / 2) * sizeof(float) + 1024;
     const DeviceInfo& dev = device_info();
     static bool attr_set[64] = {};
     if (!attr_set[dev.index]) {
@@ -513,7 +577,7 @@ extern "C" int tb200_token_project_fwd(const void* const* tables, const int64_t*
     const int64_t k = static_cast<int64_t>(n_feat) * emb;
     if (k != 64 && k != 128) return TB200_ERR_UNSUPPORTED;
     if (rows == 0) return TB200_OK;
-    if (rows > 0x7FFFFF00ll || rows_a > 0x7FFFFFFFll || rows_b > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (rows > 0x7FF00000ll || rows_a > 0x7FFFFFFFll || rows_b > 0x7FFFFFFFll) return TB200_ERR_SHAPE;   // 32-bit row arithmetic, with room for the ids read three tiles ahead
     if (tables == nullptr || table_rows == nullptr || ids == nullptr || w == nullptr || ln_gamma == nullptr ||
         ln_beta == nullptr || table_a == nullptr || ids_a == nullptr || rms_gamma == nullptr || tokens == nullptr ||
         normed == nullptr || (table_b != nullptr && ids_b == nullptr))

@@ -73,11 +73,14 @@ def test_matches_fp32_math(rows, n_feat, emb, n_cols, missing, second):
     dev = _cuda(case)
     tokens, normed = ops.token_project(*dev, check=True)
     assert tokens.shape == (rows, n_cols) and normed.shape == (rows, n_cols)
-    # one bf16 rounding of values of size <= 8 is 3e-2; the tanh-form SiLU adds about 1e-3 before the LayerNorm
-    assert (tokens.float().cpu() - want_tokens.float()).abs().max().item() <= 4e-2
-    assert (normed.float().cpu() - want_normed.float()).abs().max().item() <= 4e-2
-    assert ((tokens.float().cpu() - want_tokens.float()).abs().mean().item()) <= 2e-3
-    assert ((normed.float().cpu() - want_normed.float()).abs().mean().item()) <= 2e-3
+    # The kernel takes the LayerNorm statistics from the fp32 SiLU values (the reference rounds them to bf16 first) and
+    # uses the tanh form of the SiLU, so a LayerNorm output may sit one bf16 step beside the reference's; the table rows
+    # are added to values of size up to 8 (step 2^-5), whatever the size of the sum.  Hence an absolute bound of two such
+    # steps on every element, and a mean error that shows the differences are rounding, not bias.
+    for got, want in ((tokens, want_tokens), (normed, want_normed)):
+        err = (got.float().cpu() - want.float()).abs()
+        assert err.max().item() <= 7e-2
+        assert err.mean().item() <= 5e-4
 
 
 def test_row_selection_and_three_kernel_path():
