@@ -527,7 +527,7 @@ def run_e2e(args) -> None:
     ffn_mode = args.ffn if spec.d_model % 256 == 0 else "bf16"
     model = OneTransInference(sd, spec, device=dev, dtype=torch.bfloat16, ffn=ffn_mode, packed=not args.padded,
                               select_early=not args.late_select, attention_kernel=args.kernel,
-                              fused_tokenizer=not args.unfused_tokenizer)
+                              fused_tokenizer=args.fused_tokenizer)
     # Distinct batches rotate through both arms (rank r draws seeds r, r + 1000, ...), so that no step meets the ids,
     # lengths or duplicate pattern of the step before it.
     n_rot = max(1, args.rotate)
@@ -756,6 +756,40 @@ def run_norm_sweep(args) -> None:
             print(json.dumps({
                 "metric": f"{name}_fwd_GBps", "value": round(gbs, 1), "unit": "GB/s", "config": {"workload": f"{rows}x{cols} bf16"},
                 "us_per_launch": round(ms * 1e3, 2),
+                "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peak_kind},
+            }), flush=True)
+
+
+def run_norm_backward_sweep(args) -> None:
+    """RMSNorm / LayerNorm backward on 65 536 x {128, 256, 512, 1024} bf16 rows: x and dy in, dx out
+    (3 * rows * cols * 2 bytes of algorithmic HBM traffic); buffers rotate through > 400 MB."""
+    peaks, peak_kind = load_peaks()
+    rows = args.rows or 65536
+    for cols in ([args.cols] if args.cols else [128, 256, 512, 1024]):
+        g = torch.Generator(device="cuda").manual_seed(0)
+        n_buf = max(2, int(400e6 // (rows * cols * 4)) + 1)
+        bufs = [(torch.randn(rows, cols, generator=g, device="cuda").bfloat16(), torch.randn(rows, cols, generator=g, device="cuda").bfloat16())
+                for _ in range(n_buf)]
+        w = (1 + 0.02 * torch.randn(cols, generator=g, device="cuda")).bfloat16()
+        b = (0.02 * torch.randn(cols, generator=g, device="cuda")).bfloat16()
+        for name, fn in (("rms_norm_bwd", lambda p: ops.rms_norm_backward(p[0], w, p[1], 1e-6)),
+                         ("layer_norm_bwd", lambda p: ops.layer_norm_backward(p[0], w, b, p[1], 1e-6))):
+            for p in bufs:
+                fn(p)
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(args.steps):
+                for p in bufs:
+                    fn(p)
+            end.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(end) / (args.steps * n_buf)
+            gbs = 3.0 * rows * cols * 2 / ms / 1e6
+            print(json.dumps({
+                "metric": f"{name}_GBps", "value": round(gbs, 1), "unit": "GB/s", "config": {"workload": f"{rows}x{cols} bf16"},
+                "us_per_call": round(ms * 1e3, 2), "note": "two launches per call (row kernel + reduction of the partial sums)",
                 "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peak_kind},
             }), flush=True)
@@ -1074,8 +1108,8 @@ def main() -> None:
                         help="rows scored by both the GPU and the CPU arm after the timed regions (scores, AUC)")
     parser.add_argument("--no-op-lines", action="store_true", help="skip the standalone attention / FFN lines of the default run")
     parser.add_argument("--no-reference-order", action="store_true", help="skip the pass in the reference's order of operations")
-    parser.add_argument("--unfused-tokenizer", action="store_true",
-                        help="sequence tokenizer as separate gather, projection and tail kernels instead of the fused kernel")
+    parser.add_argument("--fused-tokenizer", action="store_true",
+                        help="sequence tokenizer as the one-kernel form (ops.token_project) instead of gather, projection and tail kernels")
     parser.add_argument("--rows", type=int, default=0)
     parser.add_argument("--cols", type=int, default=0)
     parser.add_argument("--kind", default="")
@@ -1084,6 +1118,8 @@ def main() -> None:
     if args.workload == "norm":
         if args.kind == "token_tail":
             run_token_tail_sweep(args)
+        elif args.kind == "bwd":
+            run_norm_backward_sweep(args)
         else:
             run_norm_sweep(args)
     elif args.workload == "attention":

@@ -112,6 +112,23 @@ int tb200_token_tail_select_fwd(const void* x, const void* ln_gamma, const void*
                                 void* tokens, void* normed, int64_t rows, int32_t cols, float ln_eps, float rms_eps,
                                 int dtype, void* stream);
 
+/* ---- normalisation backward (training side) ----------------------------------------------
+ * Gradients of the two norms above, statistics recomputed from x in fp32:
+ *   RMSNorm    dx = r (dy g) - x r^3 mean(dy g x),   dgamma = sum_rows dy x r              (r = rsqrt(mean(x^2) + eps))
+ *   LayerNorm  dx = rs (dy g - mean(dy g) - xh mean(dy g xh)),  dgamma = sum_rows dy xh,  dbeta = sum_rows dy
+ * Replaces the backward kernels of the reference's accelerated norms
+ * (src/taac2026/infrastructure/accelerators/normalization/kernels/triton.py:83-116, :277-320: dX per row, partial
+ * dW / dB per block, then a reduction).  x, dy, dx: [rows, cols]; gamma, dgamma, dbeta: [cols]; all of `dtype`.
+ * cols must be whole 16-byte pieces and at most 128 of them (1024 columns of a 16-bit type, 512 of fp32);
+ * TB200_ERR_UNSUPPORTED otherwise.  workspace: device floats, tb200_norm_bwd_workspace_bytes(cols, layer_norm) bytes,
+ * holds the per-CTA partial sums between the two kernels of a call (no other state).  Sums run in a fixed order:
+ * the result does not depend on scheduling. */
+int64_t tb200_norm_bwd_workspace_bytes(int32_t cols, int32_t layer_norm);
+int tb200_rmsnorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, void* dgamma, float* workspace,
+                      int64_t rows, int32_t cols, float eps, int dtype, void* stream);
+int tb200_layernorm_bwd(const void* x, const void* gamma, const void* dy, void* dx, void* dgamma, void* dbeta,
+                        float* workspace, int64_t rows, int32_t cols, float eps, int dtype, void* stream);
+
 /* The whole sequence tokenizer in one kernel: row gather -> projection -> SiLU -> LayerNorm -> time / position rows
  * -> first RMSNorm,
  *     x[r, :]      = concat_f tables[f][clamp(ids[f, r]), :]                     (K = n_feat * emb columns)

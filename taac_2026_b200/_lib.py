@@ -38,6 +38,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "tb200_token_tail_select_fwd": (
         _INT, [_P, _P, _P, _P, _I64, _P, _P, _I64, _P, _P, _P, _I64, _P, _P, _I64, _I32, _F, _F, _INT, _P],
     ),
+    "tb200_norm_bwd_workspace_bytes": (_I64, [_I32, _I32]),
+    "tb200_rmsnorm_bwd": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I32, _F, _INT, _P]),
+    "tb200_layernorm_bwd": (_INT, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _F, _INT, _P]),
     "tb200_token_project_fwd": (
         _INT, [_P, _P, _I32, _I32, _P, _P, _P, _P, _P, _P, _I64, _P, _P, _I64, _P, _P, _P, _I64, _P, _P, _I64, _I32, _F, _F, _P, _P],
     ),

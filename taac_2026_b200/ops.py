@@ -169,6 +169,8 @@ def rms_norm(
     """
     matrix, normalized_weight, original_shape = _normalize_rms_norm_inputs(x, weight)
     resolved_rms_norm_backend(matrix, backend, eps=eps, block_rows=block_rows)
+    if in_bias is None and torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad) and norm_backward_supported(matrix):
+        return _RmsNormFunction.apply(x, weight, float(eps))     # differentiable: the backward kernel serves this shape
     _refuse_autograd("rms_norm", x, weight, in_bias)
     out = torch.empty_like(matrix)
     if in_bias is not None and tuple(in_bias.shape) != (matrix.shape[1],):
@@ -187,6 +189,83 @@ def rms_norm(
             )
     _lib.check(code, "cuda rms_norm")
     return out.reshape(original_shape)
+
+
+def norm_backward_supported(x: torch.Tensor) -> bool:
+    """The backward kernels take rows of whole 16-byte pieces, at most 128 of them (1024 columns of a 16-bit type)."""
+    per16 = 16 // x.element_size()
+    return x.dtype in _DTYPE_CODES and x.shape[-1] % per16 == 0 and x.shape[-1] // per16 <= 128
+
+
+def rms_norm_backward(x: torch.Tensor, weight: torch.Tensor, grad_out: torch.Tensor, eps: float = 1e-6
+                      ) -> tuple[torch.Tensor, torch.Tensor]:
+    """(dx, dweight) of ``rms_norm(x, weight, eps)`` for the upstream gradient ``grad_out`` — the gradients of the
+    reference's accelerated RMSNorm (normalization/kernels/triton.py:83-116), statistics recomputed in fp32."""
+    matrix, normalized_weight, original_shape = _normalize_rms_norm_inputs(x, weight)
+    resolved_rms_norm_backend(matrix, "cuda", eps=eps)
+    if not norm_backward_supported(matrix):
+        raise RuntimeError("cuda rms_norm backward needs rows of whole 16-byte pieces, at most 1024 16-bit columns")
+    dy = grad_out.reshape(matrix.shape).to(matrix.dtype).contiguous()
+    dx = torch.empty_like(matrix)
+    dw = torch.empty_like(normalized_weight)
+    lib = _lib.load()
+    work = torch.empty(int(lib.tb200_norm_bwd_workspace_bytes(matrix.shape[1], 0)) // 4, dtype=torch.float32, device=matrix.device)
+    with torch.cuda.device(matrix.device), _timed("rms_norm_bwd", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
+        code = lib.tb200_rmsnorm_bwd(_ptr(matrix), _ptr(normalized_weight), _ptr(dy), _ptr(dx), _ptr(dw), _ptr(work),
+                                     matrix.shape[0], matrix.shape[1], float(eps), _DTYPE_CODES[matrix.dtype], _stream_ptr())
+    _lib.check(code, "cuda rms_norm backward")
+    return dx.reshape(original_shape), dw
+
+
+def layer_norm_backward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, grad_out: torch.Tensor, eps: float = 1e-5
+                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dx, dweight, dbias) of ``layer_norm(x, weight, bias, eps)`` (normalization/kernels/triton.py:277-320)."""
+    matrix, normalized_weight, normalized_bias, original_shape = _normalize_layer_norm_inputs(x, weight, bias)
+    resolved_layer_norm_backend(matrix, "cuda", eps=eps)
+    if not norm_backward_supported(matrix):
+        raise RuntimeError("cuda layer_norm backward needs rows of whole 16-byte pieces, at most 1024 16-bit columns")
+    dy = grad_out.reshape(matrix.shape).to(matrix.dtype).contiguous()
+    dx = torch.empty_like(matrix)
+    dw, db = torch.empty_like(normalized_weight), torch.empty_like(normalized_bias)
+    lib = _lib.load()
+    work = torch.empty(int(lib.tb200_norm_bwd_workspace_bytes(matrix.shape[1], 1)) // 4, dtype=torch.float32, device=matrix.device)
+    with torch.cuda.device(matrix.device), _timed("layer_norm_bwd", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
+        code = lib.tb200_layernorm_bwd(_ptr(matrix), _ptr(normalized_weight), _ptr(dy), _ptr(dx), _ptr(dw), _ptr(db), _ptr(work),
+                                       matrix.shape[0], matrix.shape[1], float(eps), _DTYPE_CODES[matrix.dtype], _stream_ptr())
+    _lib.check(code, "cuda layer_norm backward")
+    return dx.reshape(original_shape), dw, db
+
+
+class _RmsNormFunction(torch.autograd.Function):
+    """Differentiable ``rms_norm``: forward and backward both on this library's kernels."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        ctx.save_for_backward(x, weight)
+        ctx.eps = eps
+        with torch.no_grad():
+            return rms_norm(x, weight, eps, backend="cuda")
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight = ctx.saved_tensors
+        dx, dw = rms_norm_backward(x, weight, grad_out, ctx.eps)
+        return dx, dw.to(weight.dtype), None
+
+
+class _LayerNormFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        ctx.save_for_backward(x, weight, bias)
+        ctx.eps = eps
+        with torch.no_grad():
+            return layer_norm(x, weight, bias, eps, backend="cuda")
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, bias = ctx.saved_tensors
+        dx, dw, db = layer_norm_backward(x, weight, bias, grad_out, ctx.eps)
+        return dx, dw.to(weight.dtype), db.to(bias.dtype), None
 
 
 def _normalize_layer_norm_inputs(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor):
@@ -236,6 +315,9 @@ def layer_norm(
     dtype as a separate activation would leave it: the ``Linear -> SiLU -> LayerNorm`` tail in one pass."""
     matrix, normalized_weight, normalized_bias, original_shape = _normalize_layer_norm_inputs(x, weight, bias)
     resolved_layer_norm_backend(matrix, backend, eps=eps, block_rows=block_rows)
+    if not pre_silu and torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or bias.requires_grad) \
+            and norm_backward_supported(matrix):
+        return _LayerNormFunction.apply(x, weight, bias, float(eps))
     _refuse_autograd("layer_norm", x, weight, bias)
     out = torch.empty_like(matrix)
     with torch.cuda.device(matrix.device), _timed("layer_norm", rows=matrix.shape[0], cols=matrix.shape[1], esize=matrix.element_size()):
@@ -1411,6 +1493,9 @@ __all__ = [
     "fields_bag_mean",
     "gather_rows",
     "layer_norm",
+    "layer_norm_backward",
+    "norm_backward_supported",
+    "rms_norm_backward",
     "resolved_embedding_bag_mean_backend",
     "resolved_layer_norm_backend",
     "resolved_rms_norm_backend",

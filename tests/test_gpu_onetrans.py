@@ -229,3 +229,15 @@ def test_batch_without_any_behaviour_event(packed):
     want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
     got = OneTransInference(sd, spec, dtype=torch.float32, packed=packed).scores(batch.to("cuda")).cpu().numpy()
     assert np.abs(got - oracle_model.sigmoid_scores(want_logits).reshape(-1)).max() <= 1e-3
+
+
+def test_one_kernel_tokenizer_gives_the_same_scores():
+    """`fused_tokenizer=True` replaces gather + projection + tail by `ops.token_project`: same scores to bf16 rounding."""
+    spec = _wide_spec()
+    sd = random_state_dict(spec, seed=5)
+    batch = synthetic_batch(spec, 48, seq_len=260, min_len=0, seed=6).to("cuda")
+    plain = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn="fp8")
+    fused = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn="fp8", fused_tokenizer=True)
+    a, b = plain.scores(batch), fused.scores(batch)
+    fused.raise_if_incomplete()
+    assert (a - b).abs().max().item() <= 2e-3
