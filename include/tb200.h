@@ -166,6 +166,16 @@ int tb200_token_project_fwd(const void* const* tables, const int64_t* table_rows
 int tb200_bag_mean_fwd(const void* table, int64_t vocab_rows, int32_t dim, const void* ids, int ids_dtype,
                        int64_t batch, int32_t bag, void* out, int dtype, void* stream);
 
+/* Sparse gradient of tb200_bag_mean_fwd with respect to the table, in the (row list, value rows) form the reference
+ * hands to its sparse optimizer (`SparseEmbeddingBagMean.backward`,
+ * src/taac2026/infrastructure/modeling/embeddings.py:34-62; dense atomic form: embedding/kernels/triton.py:105-151):
+ *     rows_out[b * bag + h] = ids[b, h],   vals_out[b * bag + h, :] = grad_out[b, :] / (number of valid ids of bag b)
+ * for valid ids (0 < id < vocab_rows); the other positions name row 0 and carry zeros, so that the layout is fixed
+ * ([batch * bag] rows) and coalescing the list gives the reference's gradient.  No atomics.
+ * ids: [batch, bag] of ids_dtype; grad_out: [batch, dim], vals_out: [batch * bag, dim] of `dtype`; rows_out: int64. */
+int tb200_bag_mean_bwd(const void* ids, int ids_dtype, const void* grad_out, int64_t* rows_out, void* vals_out,
+                       int64_t batch, int32_t bag, int32_t dim, int64_t vocab_rows, int dtype, void* stream);
+
 /* All sparse fields of one entity in a single launch: the fused form of the per-field Python
  * loop in `FeatureEmbeddingBank.forward`
  * (src/taac2026/infrastructure/modeling/embeddings.py:137-173), including its

@@ -47,6 +47,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "tb200_add_gathered_rows": (_INT, [_P, _I64, _I32, _P, _I64, _P, _P, _I64, _P, _INT, _P]),
     "tb200_bias_act_rows": (_INT, [_P, _I64, _I32, _P, _I64, _I32, _INT, _P]),
     "tb200_bag_mean_fwd": (_INT, [_P, _I64, _I32, _P, _INT, _I64, _I32, _P, _INT, _P]),
+    "tb200_bag_mean_bwd": (_INT, [_P, _INT, _P, _P, _P, _I64, _I32, _I32, _I64, _INT, _P]),
     "tb200_fields_bag_mean_fwd": (_INT, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _INT, _I64, _I32, _P, _INT, _P]),
     "tb200_attn_fwd": (
         _INT,

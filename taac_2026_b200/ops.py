@@ -384,6 +384,29 @@ def embedding_bag_mean(
     return out
 
 
+def embedding_bag_mean_backward(values: torch.Tensor, grad_out: torch.Tensor, num_embeddings: int) -> torch.Tensor:
+    """Sparse gradient of ``embedding_bag_mean`` with respect to the table: an (uncoalesced) ``torch.sparse_coo_tensor``
+    of shape ``[num_embeddings, dim]`` with one entry per bag position, ``grad_out[b] / valid_count[b]`` at the looked-up
+    row — what `SparseEmbeddingBagMean.backward` returns (modeling/embeddings.py:34-62); padded positions name row 0
+    with zeros instead of being dropped, so the layout is fixed and no compaction pass is needed."""
+    _require_backend("embedding_bag_mean_backward", "cuda")
+    _require_cuda_tensors("cuda embedding_bag_mean_backward", values, grad_out)
+    if values.ndim != 2 or grad_out.ndim != 2 or grad_out.shape[0] != values.shape[0]:
+        raise ValueError("embedding_bag_mean_backward expects values [B, bag] and grad_out [B, dim]")
+    if values.dtype not in _ID_CODES or not cuda_supported_floating_dtype(grad_out.dtype):
+        raise RuntimeError("cuda embedding_bag_mean_backward needs int32 / int64 ids and a fp16, bf16 or fp32 gradient")
+    ids, grad = values.contiguous(), grad_out.contiguous()
+    batch, bag = ids.shape
+    dim = grad.shape[1]
+    rows = torch.empty(batch * bag, dtype=torch.int64, device=grad.device)
+    vals = torch.empty(batch * bag, dim, dtype=grad.dtype, device=grad.device)
+    with torch.cuda.device(grad.device):
+        code = _lib.load().tb200_bag_mean_bwd(_ptr(ids), _ID_CODES[ids.dtype], _ptr(grad), _ptr(rows), _ptr(vals), batch, bag, dim,
+                                              int(num_embeddings), _DTYPE_CODES[grad.dtype], _stream_ptr())
+    _lib.check(code, "cuda embedding_bag_mean_backward")
+    return torch.sparse_coo_tensor(rows.unsqueeze(0), vals, (int(num_embeddings), dim), device=grad.device, dtype=grad.dtype)
+
+
 class FieldTables:
     """Device-side description of the embedding tables of one entity's sparse fields.
 
@@ -1490,6 +1513,7 @@ __all__ = [
     "cuda_available",
     "cuda_supported_floating_dtype",
     "embedding_bag_mean",
+    "embedding_bag_mean_backward",
     "fields_bag_mean",
     "gather_rows",
     "layer_norm",

@@ -229,3 +229,22 @@ def test_packed_token_index_matches_the_index_arithmetic(with_time):
         assert torch.equal(buckets.cpu(), want_b)
     else:
         assert buckets is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("batch,bag,dim,vocab", [(1, 1, 8, 5), (300, 4, 64, 50), (1000, 3, 128, 1000), (77, 9, 32, 20)])
+def test_bag_mean_backward_matches_autograd(dtype, batch, bag, dim, vocab):
+    """The sparse table gradient of the bag mean, coalesced, against torch autograd of `F.embedding_bag(mode="mean",
+    padding_idx=0)` (what the reference's sparse backward reproduces, modeling/embeddings.py:34-62)."""
+    g = torch.Generator().manual_seed(batch + bag + dim)
+    ids = torch.randint(0, vocab + 1, (batch, bag), generator=g)
+    ids[torch.rand(batch, bag, generator=g) < 0.3] = 0          # padding, including all-padding bags
+    grad_out = torch.randn(batch, dim, generator=g).to(dtype)
+    table = torch.randn(vocab + 1, dim, generator=g, requires_grad=True)
+    torch.nn.functional.embedding_bag(ids, table, mode="mean", padding_idx=0).backward(grad_out.float())
+    got = ops.embedding_bag_mean_backward(ids.cuda(), grad_out.cuda(), vocab + 1)
+    assert got.is_sparse and got.shape == (vocab + 1, dim) and got.dtype == dtype
+    dense = torch.zeros(vocab + 1, dim).index_add_(0, got._indices()[0].cpu(), got._values().float().cpu())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (dense - table.grad).abs().max().item() <= tol * max(1.0, table.grad.abs().max().item())
+    assert torch.equal(dense[0], torch.zeros(dim))            # the padding row receives nothing
