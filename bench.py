@@ -9,16 +9,22 @@ in [128, 1024] padded to 1024, 8 blocks, d_model 512, 8 heads, hidden_mult 4; we
 identical on every rank; rank r draws its batch from data seed r (weak scaling).  Rank 0 prints ONE
 JSON line:
 
-* ``value``       samples/s of the whole job with the batch already resident in HBM;
-* ``e2e``         the same through the public call with HOST (pinned) inputs: H2D copy of the batch,
-                  forward, NCCL gather of the scores (N > 1), D2H read of the scores, every step;
+* ``value``       samples/s of the whole job with the batches already resident in HBM (four batches per rank
+                  rotate through the timed steps; a pass of K steps is repeated until about two seconds have been
+                  timed and the median pass is reported);
+* ``e2e``         the same through the public call (``score_stream``) with HOST (pinned) inputs: H2D copy of the
+                  batch, forward, NCCL gather of the scores (N > 1), D2H read of the scores, every step;
 * ``roofline``    algorithmic work / CUDA-event time of the dominant hand-written kernel inside the
-                  timed steps, against the measured peaks in MEASURED_PEAKS.json;
-* ``cpu_baseline`` the vectorised CPU port of the reference's torch path (``oracle/torch_cpu.py``) on a
-                  bounded sample of the same batch, all host threads (rank 0, N = 1 only).
+                  timed steps, against the measured peaks in MEASURED_PEAKS.json; ``kernels`` lists every
+                  timed launch group (library launches included) and ``step_accounting`` the share of the
+                  step they cover;
+* ``cpu_baseline`` the reference's own ``PCVROneTrans`` (compiled form under ``oracle/_ref``, kind
+                  ``"reference"``; the vectorised port ``oracle/torch_cpu.py``, kind ``"port"``, where that
+                  archive is missing) on a bounded sample of the same batch, all host threads (rank 0, N = 1
+                  only), with the score parity of ``--parity-rows`` rows against the GPU outside the timed region.
 
-``--impl reference`` times only that CPU port (same config, bounded sample per step).
-``--workload norm|attention|gather`` run the standalone operator sweeps (also what the ncu
+``--impl reference`` times only that CPU arm (same config, bounded sample per step) and says in its line what ran.
+``--workload norm|attention|gather|ffn`` run the standalone operator sweeps (also what the ncu
 profiles under profiles/ were captured from); they print one JSON line per case.
 """
 
@@ -41,7 +47,7 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 from taac_2026_b200 import _lib, ops  # noqa: E402
-from taac_2026_b200.inputs import OneTransSpec, synthetic_batch  # noqa: E402
+from taac_2026_b200.inputs import OneTransSpec, compact_model_input, synthetic_batch  # noqa: E402
 from taac_2026_b200.onetrans import OneTransInference, random_state_dict, score_stream  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -465,6 +471,82 @@ def score_parity(arm: CpuArm, model, host_batch, rows: int, chunk: int = 256) ->
     }
 
 
+def run_parity_stages(args) -> None:
+    """Score parity by precision stage, outside any timed region: the first ``--parity-rows`` samples of the full-scale
+    batch are scored by the CPU arm in fp32 (the yardstick) and by the GPU engine in four precisions, from the fp32
+    parity mode to the benchmarked one; where the reference can be imported, its own model also runs on the GPU under
+    bf16 autocast (its serving precision, `runtime_autocast_context`, runtime/execution.py:54-60), which shows how far
+    16-bit serving moves the reference itself.  One JSON line per stage: largest score difference and both AUCs."""
+    from oracle import reference_ops as R
+
+    wl = WORKLOADS["full" if args.workload == "parity" else args.workload]
+    spec: OneTransSpec = wl["spec"]()
+    rows = args.parity_rows if args.parity_rows > 256 else 8192
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    batch = synthetic_batch(spec, rows, seq_len=wl["seq_len"], min_len=wl["min_len"], seed=0,
+                            field_exponent=wl["field_exp"], seq_exponent=wl["seq_exp"])
+    sd = random_state_dict(spec, seed=0, device=dev, dtype=torch.bfloat16)
+    arm = CpuArm(spec, sd)
+    chunk = 256
+    t0 = time.perf_counter()
+    want_logits = torch.cat([arm.predict(batch.slice(lo, min(lo + chunk, rows)))[0].reshape(-1).float()
+                             for lo in range(0, rows, chunk)])
+    cpu_seconds = time.perf_counter() - t0
+    want = torch.sigmoid(want_logits)
+    z = (want_logits - want_logits.mean()) / want_logits.std().clamp_min(1e-6)
+    labels = (torch.rand(rows, generator=torch.Generator().manual_seed(2)) < torch.sigmoid(2.0 * z)).numpy()
+    auc_cpu = R.binary_auc(labels, want.numpy())
+    base = {"metric": "score_parity_by_stage", "rows": rows, "yardstick": arm.describe(), "yardstick_seconds": round(cpu_seconds, 1),
+            "auc_yardstick": round(auc_cpu, 6), "config": {"workload": wl["name"]}}
+
+    # the AUC difference of one label draw is a handful of swapped pairs; 32 further draws show its spread
+    draws = [(torch.rand(rows, generator=torch.Generator().manual_seed(100 + i)) < torch.sigmoid(2.0 * z)).numpy() for i in range(32)]
+    auc_cpu_draws = [R.binary_auc(d, want.numpy()) for d in draws]
+
+    def report(stage: str, got: torch.Tensor, **extra) -> None:
+        got = got.detach().float().cpu().reshape(-1)
+        auc = R.binary_auc(labels, got.numpy())
+        deltas = [abs(R.binary_auc(d, got.numpy()) - a) for d, a in zip(draws, auc_cpu_draws)]
+        extra = {**extra, "auc_abs_diff_32_label_draws": {"mean": round(float(sum(deltas) / len(deltas)), 7), "max": round(float(max(deltas)), 7)},
+                 "rank_correlation_with_yardstick": round(float(torch.corrcoef(torch.stack([want.argsort().argsort().float(), got.argsort().argsort().float()]))[0, 1]), 8)}
+        print(json.dumps({**base, "stage": stage, "max_abs_score_diff": round(float((want - got).abs().max()), 7),
+                          "mean_abs_score_diff": round(float((want - got).abs().mean()), 8), "auc": round(auc, 6),
+                          "auc_abs_diff": round(abs(auc - auc_cpu), 7),
+                          "auc_equal_to_4_decimals": round(auc, 4) == round(auc_cpu, 4), **extra}), flush=True)
+
+    dev_batch = batch.to(dev)
+    if arm.kind == "reference":
+        # the reference's own module on the GPU, torch backend, fp32 parameters, bf16 autocast
+        from oracle import ref_runtime
+
+        sd32 = {name: t.float() for name, t in sd.items()}
+        ref_gpu = ref_runtime.build_model(spec.as_dict(), state_dict=sd32, meta_init=True)
+        outs = []
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            for lo in range(0, rows, chunk):
+                outs.append(ref_runtime.predict(ref_gpu, dev_batch.slice(lo, min(lo + chunk, rows)))[0].reshape(-1).float())
+        report("reference model on the GPU, torch backend, bf16 autocast", torch.sigmoid(torch.cat(outs)))
+        outs = []
+        for lo in range(0, rows, chunk):
+            outs.append(ref_runtime.predict(ref_gpu, dev_batch.slice(lo, min(lo + chunk, rows)))[0].reshape(-1).float())
+        report("reference model on the GPU, torch backend, fp32 (TF32 off)", torch.sigmoid(torch.cat(outs)))
+        del ref_gpu, sd32, outs
+        torch.cuda.empty_cache()
+    stages = [("this engine: fp32 dense layers and attention", torch.float32, "bf16"),
+              ("this engine: bf16, bf16 FFN", torch.bfloat16, "bf16"),
+              ("this engine: bf16, FP8 FFN with GEMM 1 in bf16", torch.bfloat16, "fp8_precise"),
+              ("this engine: bf16, FP8 FFN (benchmarked precision)", torch.bfloat16, "fp8")]
+    for name, dtype, ffn in stages:
+        weights = sd if dtype == torch.bfloat16 else {k: v.float() for k, v in sd.items()}
+        model = OneTransInference(weights, spec, device=dev, dtype=dtype, ffn=ffn)
+        got = torch.cat([model.scores(dev_batch.slice(lo, min(lo + 2048, rows))).reshape(-1) for lo in range(0, rows, 2048)])
+        model.raise_if_incomplete()
+        report(name, got)
+        del model, weights, got
+        torch.cuda.empty_cache()
+
+
 # ------------------------------------------------------------------------------------------------
 # main benchmark
 # ------------------------------------------------------------------------------------------------
@@ -533,6 +615,18 @@ def run_e2e(args) -> None:
     n_rot = max(1, args.rotate)
     host_batches = [make_batch(rank + 1000 * i).pin_memory() for i in range(n_rot)]
     dev_batches = [b.to(dev) for b in host_batches]
+    # What the end-to-end arm copies every step.  "compact32": the sequences as 32-bit valid prefixes, written by the
+    # library's host packer (the job of the data loader's batch converter, outside the timed region like the rest of
+    # batch construction; its cost per batch is reported) and expanded to the padded int64 record by one kernel on the
+    # device inside the timed region.  "padded64": the reference's padded int64 record as it is.
+    stream_batches, pack_ms = host_batches, None
+    if args.host_format == "compact32":
+        try:
+            t0 = time.perf_counter()
+            stream_batches = [compact_model_input(b, threads=4, pin=True) for b in host_batches]
+            pack_ms = (time.perf_counter() - t0) * 1e3 / n_rot
+        except OverflowError:
+            args.host_format = "padded64 (a value did not fit the 32-bit format)"
     micro = args.micro_batch or wl["micro"]
     host_scores = torch.empty(world * batch_size if world > 1 else batch_size, dtype=torch.float32).pin_memory()
     counter = {"resident": 0, "e2e": 0}
@@ -548,7 +642,7 @@ def run_e2e(args) -> None:
         of all ranks and reads them back to the host."""
         first = counter["e2e"]
         counter["e2e"] += steps
-        stream = (host_batches[(first + i) % n_rot] for i in range(steps))
+        stream = (stream_batches[(first + i) % n_rot] for i in range(steps))
         for scores in score_stream(model, stream, micro_batch=micro):
             host_scores.copy_(gather_scores(scores), non_blocking=True)
 
@@ -641,7 +735,7 @@ def run_e2e(args) -> None:
             dist.destroy_process_group()
         return
 
-    fp8_peak = measure_fp8_peak() if ffn_mode == "fp8" else None
+    fp8_peak = measure_fp8_peak() if ffn_mode.startswith("fp8") else None
     roofline, per_op, accounting = summarise_kernels(records, peaks, peak_kind, args.steps, fp8_peak, ms_recorded)
     if args.launch_log:
         with open(args.launch_log, "w") as fh:
@@ -671,7 +765,7 @@ def run_e2e(args) -> None:
         "metric": "pcvr_infer_samples_per_s", "value": round(value, 2), "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_total / args.steps, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 activations, e4m3 FFN GEMMs" if ffn_mode == "fp8" else "bf16", "data": "synthetic",
+        "dtype": "bf16 activations, e4m3 FFN GEMMs" if ffn_mode.startswith("fp8") else "bf16", "data": "synthetic",
         "config": {
             "workload": wl["name"], "per_gpu_batch": batch_size, "global_batch": total, "micro_batch": micro,
             "ffn": ffn_mode, "layout": "padded" if args.padded else "packed valid tokens",
@@ -685,7 +779,9 @@ def run_e2e(args) -> None:
                    "timed_region_s": round(sum(resident_passes) * 1e-3, 3),
                    "ms_per_step_passes": [round(m / args.steps, 3) for m in resident_passes]},
         "e2e": {"value": round(e2e_value, 2), "unit": "samples/s",
-                "h2d_bytes_per_step": host_batches[0].nbytes(),
+                "h2d_bytes_per_step": stream_batches[0].nbytes(), "host_format": args.host_format,
+                "padded_int64_record_bytes": host_batches[0].nbytes(),
+                "host_pack_ms_per_batch": None if pack_ms is None else round(pack_ms, 2),
                 "d2h_bytes_per_step": host_scores.numel() * 4, "ms_per_step": round(ms_e2e / args.steps, 3),
                 "passes_ms_per_step": [round(m / args.steps, 3) for m in e2e_passes], "reported": "median pass",
                 "timed_region_s": round(sum(e2e_passes) * 1e-3, 3)},
@@ -853,6 +949,60 @@ def attention_lines(peaks: dict, peak_kind: str, *, batch: int, steps: int, kern
                          "peak_source": peak_kind},
         })
     return out
+
+
+def run_token_project_sweep(args) -> None:
+    """The sequence tokenizer of layer 0 (gather of table rows -> projection 128 -> 512 -> SiLU -> LayerNorm -> position
+    rows -> first RMSNorm, residual stream written for the kept rows only) as ONE kernel (`ops.token_project`) against
+    the three kernels the engine runs by default (`gather_rows`, `grouped_linear`, `token_tail`)."""
+    from taac_2026_b200.inputs import zipf_ids
+
+    peaks, peak_kind = load_peaks()
+    rows = args.rows or 1_000_000
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(1_000_001, 128, generator=g, device="cuda").bfloat16()
+    ids = zipf_ids(rows, 1_000_000, 1.1, torch.Generator().manual_seed(0)).view(1, rows).cuda()
+    w = (torch.randn(512, 128, generator=g, device="cuda") * 128 ** -0.5).bfloat16()
+    b = torch.randn(512, generator=g, device="cuda")
+    lw, lb, rw = ((1 + 0.02 * torch.randn(512, generator=g, device="cuda")).bfloat16() for _ in range(3))
+    pos = torch.randn(1025, 512, generator=g, device="cuda").bfloat16()
+    ip = torch.randint(0, 1025, (rows,), generator=g, device="cuda")
+    keep = torch.rand(rows, generator=g, device="cuda") < 0.05
+    row_dst = torch.where(keep, torch.cumsum(keep, 0) - 1, torch.full_like(ip, -1)).to(torch.int32)
+    n_out = int(keep.sum())
+
+    def fused():
+        return ops.token_project([table], ids, w, b, lw, lb, pos, ip, None, None, rw, row_dst=row_dst, rows_out=n_out)
+
+    def three():
+        x = ops.gather_rows(table, ids[0])
+        p = ops.grouped_linear(x, w, b)
+        return ops.token_tail(p, lw, lb, pos, ip, None, None, rw, row_dst=row_dst, rows_out=n_out)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    # ids + table rows read, normed rows written, kept rows of the residual stream written
+    algo = rows * (8 + 256 + 1024 + 4 + 8) + n_out * 1024
+    for name, fn in (("one kernel (token_project)", fused), ("three kernels (gather_rows, grouped_linear, token_tail)", three)):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(max(args.steps, 3)):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+        ms = statistics.median(times)
+        gbs = algo / ms / 1e6
+        print(json.dumps({
+            "metric": "sequence_tokenizer_rows_per_s", "value": round(rows / ms * 1e3, 1), "unit": "rows/s", "ms": round(ms, 4),
+            "config": {"workload": f"{rows} rows, 1 feature x 128 bf16 -> 512, 5 % of the rows kept, {name}", "l2": "256 MB flush between runs"},
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peak_kind,
+                         "note": "bytes of the one-kernel form: ids + table rows in, normed rows and kept residual rows out"},
+        }), flush=True)
 
 
 def run_attention_sweep(args) -> None:
@@ -1090,14 +1240,17 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=6)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    parser.add_argument("--workload", default="full", choices=[*WORKLOADS, "norm", "attention", "gather", "ffn"])
+    parser.add_argument("--workload", default="full", choices=[*WORKLOADS, "norm", "attention", "gather", "ffn", "parity"])
     parser.add_argument("--batch", type=int, default=0, help="per-GPU batch override")
     parser.add_argument("--micro-batch", type=int, default=0)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--launch-log", default="", help="write every recorded launch of the timing pass (name, ms, shape) to this file")
     parser.add_argument("--profile", action="store_true",
                         help="run --warmup untimed and --steps plain steps of the main workload and exit (for ncu)")
-    parser.add_argument("--ffn", choices=["fp8", "bf16"], default="fp8", help="shared FFN of every block")
+    parser.add_argument("--ffn", choices=["fp8", "fp8_precise", "bf16"], default="fp8", help="shared FFN of every block")
+    parser.add_argument("--host-format", choices=["compact32", "padded64"], default="compact32",
+                        help="what the end-to-end arm copies per step: the compact 32-bit sequence record "
+                             "(inputs.compact_model_input, expanded on the device) or the reference's padded int64 record")
     parser.add_argument("--padded", action="store_true", help="reference [B, T, d] layout instead of packed valid tokens")
     parser.add_argument("--late-select", action="store_true",
                         help="apply the pyramid's row selection after the whole block (the reference's order) instead of "
@@ -1120,6 +1273,8 @@ def main() -> None:
             run_token_tail_sweep(args)
         elif args.kind == "bwd":
             run_norm_backward_sweep(args)
+        elif args.kind == "token_project":
+            run_token_project_sweep(args)
         else:
             run_norm_sweep(args)
     elif args.workload == "attention":
@@ -1134,6 +1289,8 @@ def main() -> None:
             run_grouped_gemm_sweep(args)
         else:
             run_ffn_sweep(args)
+    elif args.workload == "parity":
+        run_parity_stages(args)
     else:
         run_e2e(args)
 

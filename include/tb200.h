@@ -33,6 +33,7 @@ extern "C" {
 #define TB200_ERR_DEVICE (-6)      /* current device is not compute capability 10.x */
 #define TB200_ERR_DRIVER (-7)      /* a driver entry point (tensor-map encode) is unavailable or failed */
 #define TB200_ERR_SCRATCH (-8)     /* the request does not fit the fixed scratch of a no-allocation entry point */
+#define TB200_ERR_RANGE (-9)       /* a value does not fit the 32-bit compact host format: use the padded 64-bit copy */
 
 /* ---- element / index type codes ------------------------------------------------------- */
 #define TB200_F32 0
@@ -175,6 +176,41 @@ int tb200_bag_mean_fwd(const void* table, int64_t vocab_rows, int32_t dim, const
  * ids: [batch, bag] of ids_dtype; grad_out: [batch, dim], vals_out: [batch * bag, dim] of `dtype`; rows_out: int64. */
 int tb200_bag_mean_bwd(const void* ids, int ids_dtype, const void* grad_out, int64_t* rows_out, void* vals_out,
                        int64_t batch, int32_t bag, int32_t dim, int64_t vocab_rows, int dtype, void* stream);
+
+/* ---- compact host format of the behaviour sequences ------------------------------------------------------------
+ * The reference copies padded int64 buffers to the device (ids [B, F, L], timestamps [B, L], lengths [B]; built by
+ * `PCVRRecordBatchConverter._build_sequence_inputs`, src/taac2026/infrastructure/data/batch_converter.py:446-488,
+ * copied in application/evaluation/workflow.py:246-262).  The compact format holds the valid prefix of every sample
+ * in 32 bits:  cu[B + 1] int32 (cu[b] = first event of sample b),  ids[F, ids_stride] int32,  gaps[total] int32 =
+ * request_timestamp[b] - timestamp, INT32_MIN where the timestamp is 0.  The tb200_host_* functions run on the host
+ * (no CUDA call, usable without a GPU; `threads` worker threads, 1..64); a value that does not fit returns
+ * TB200_ERR_RANGE and the caller keeps the padded copy.  tb200_expand_sequence rebuilds the padded int64 tensors on
+ * the device bit for bit (positions beyond the length are zero), so the kernels behind see the reference's layout. */
+
+/* cu from the padded record's lengths: cu[b + 1] = cu[b] + clamp(lengths[b], 0, max_len). */
+int tb200_host_compact_offsets(const int64_t* lengths, int32_t batch, int32_t max_len, int32_t* cu);
+
+/* Padded int64 record -> compact.  gaps may be NULL (timestamps not carried). */
+int tb200_host_compact_sequence(const int64_t* values, const int64_t* timestamps, const int64_t* request_ts,
+                                const int32_t* cu, int32_t batch, int32_t feats, int32_t max_len, int32_t* ids,
+                                int64_t ids_stride, int32_t* gaps, int32_t threads);
+
+/* Arrow list columns (offsets int32, or int64 with offsets_are_int64; values int64) -> compact, without the padded
+ * intermediate: the prefix rule of `pad_list_offsets_values` (batch_converter.py:68-103), length = longest id column
+ * (`_fill_sequence`, :503-538), ids <= 0 -> 0 (:476), and with vocab_sizes the clip_vocab=True rule of
+ * `_clip_sequence_vocab` / `record_oob` (:594-650) with the clipped ids counted per column in oob_counts (may be
+ * NULL).  ts_offsets / ts_values may be NULL (no timestamp column).  Writes cu as well. */
+int tb200_host_compact_from_lists(const void* const* id_offsets, const int64_t* const* id_values, int32_t feats,
+                                  const void* ts_offsets, const int64_t* ts_values, int32_t offsets_are_int64,
+                                  const int64_t* request_ts, const int64_t* vocab_sizes, int64_t* oob_counts,
+                                  int32_t batch, int32_t max_len, int32_t* cu, int32_t* ids, int64_t ids_stride,
+                                  int32_t* gaps, int32_t threads);
+
+/* Device: compact -> values [B, F, L] int64, lengths [B] int64, timestamps [B, L] int64 (NULL: not written).
+ * max_len must be even; values / timestamps 16-byte aligned. */
+int tb200_expand_sequence(const int32_t* ids, const int32_t* gaps, const int32_t* cu, const int64_t* request_ts,
+                          int64_t* values, int64_t* lengths, int64_t* timestamps, int32_t batch, int32_t feats,
+                          int32_t max_len, int64_t ids_stride, void* stream);
 
 /* All sparse fields of one entity in a single launch: the fused form of the per-field Python
  * loop in `FeatureEmbeddingBank.forward`

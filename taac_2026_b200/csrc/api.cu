@@ -54,6 +54,7 @@ extern "C" const char* tb200_strerror(int code) {
         case TB200_ERR_DRIVER: return "tb200: tensor-map driver entry point unavailable or failed";
         case TB200_ERR_SCRATCH:
             return "tb200: request exceeds the 64 MiB fixed scratch of the no-allocation entry point; split the rows";
+        case TB200_ERR_RANGE: return "tb200: a value does not fit the 32-bit compact host format";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

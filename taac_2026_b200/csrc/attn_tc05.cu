@@ -4,17 +4,19 @@
 // (256 TMEM columns and 97 KB of shared memory each), so one runs its softmax while the other owns the
 // tensor cores, and the TMA producer of a CTA already fetches the next item's Q / K / V while the
 // current item is being finished.  Roles (192 threads):
-//   warp 0       TMA producer: Q per item, K and V tiles alternating through one ring of three slots
+//   warp 0       TMA producer: Q per item, K and V tiles alternating through one ring of five slots
 //                (128 keys x 128 bytes each, 128-byte swizzle, no multicast)
 //   warp 1       MMA issuer (one elected lane), owner of the TMEM allocation
 //   warps 2..5   softmax: one thread per query row
-// Per KV tile and half:  S = Q K^T   (tcgen05.mma kind::f16, M 128 x N 128 x K 64, fp32 in TMEM)
-//                        the softmax thread pulls its whole S row into registers (4 x tcgen05.ld of
-//                        32 columns, one wait), frees S at once, takes the row max, writes
-//                        P = exp2(...) as bf16 into swizzled shared memory
-//                        O += P V    (M 128 x N 64 x K 128, V is the MN-major B operand), accumulated
-//                        in TMEM across the key tiles.  The running max is only advanced when it grows
-//                        by more than 2^8 (the exponent stays within fp32 / bf16 range, the final
+// TMEM columns of a CTA: S 0..127 (fp32 scores), O 128..191 (fp32 output), P 192..255 (bf16 probabilities, two per
+// column).  Per KV tile:  S = Q K^T   (tcgen05.mma kind::f16, both operands from shared memory, M 128 x N 128 x K 64)
+//                        the softmax thread reads its S row with x16 tcgen05.ld pairs (32 columns per wait group),
+//                        takes the row maximum, frees S as soon as the row has been read, and writes
+//                        P = exp2(...) as bf16 straight back into TMEM (tcgen05.st): no shared-memory round trip
+//                        O += P V    (P is the TMEM operand, V the MN-major shared-memory operand, M 128 x N 64 x
+//                        K 128, issued in two halves so that the first runs while the softmax finishes the
+//                        second), accumulated in TMEM across the key tiles.  The running max is only advanced
+//                        when it grows by more than 2^8 (the exponent stays within fp32 / bf16 range, the final
 //                        division by the row sum makes the result exact); when it does, the threads
 //                        rescale their O rows in TMEM (tcgen05.ld / tcgen05.st) before P is released.
 // Key tiles without a visible key are skipped; masks come as lengths, never as a matrix.

@@ -296,6 +296,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // round trip that the K loop otherwise waits for.  Barriers: the "full" barriers live in the leader and count
 // the bytes of both CTAs' loads; "empty" and "accumulator full" are signalled in both CTAs by multicast
 // commits; "accumulator empty" collects one arrival per epilogue warp of both CTAs in the leader.
+// Epilogue: eight warps per CTA, two per TMEM lane quarter (one takes the even, one the odd 64-column boxes of
+// its 32 rows).  A warp is self-contained: one lane polls the "accumulator full" barrier and broadcasts the
+// outcome, the warp reads 16 columns per thread and round, arrives on "accumulator empty" right after its last
+// tcgen05.ld (the MMAs of the next tile start while the values are still being converted), and sends its own
+// 32-row x 128-byte box to TMA from a private 4 KB staging tile: no block-wide barrier anywhere in the epilogue.
 // ------------------------------------------------------------------------------------------------
 constexpr int kStagesP = 6;
 constexpr int kEpiWarpsP = 8;                  // two warps per TMEM lane quarter, each with a staging box and TMA stores of its own

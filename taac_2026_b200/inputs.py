@@ -108,6 +108,99 @@ class ModelInput:
         )
 
 
+@dataclass(frozen=True, slots=True)
+class CompactSequence:
+    """One domain in the compact 32-bit host format (``ops.compact_sequence_host``): the valid prefix of every
+    sample back to back instead of the reference's padded int64 buffers (batch_converter.py:446-488)."""
+
+    cu: torch.Tensor  # [B + 1] int32
+    ids: torch.Tensor  # [F, total] int32
+    gaps: torch.Tensor | None  # [total] int32: request timestamp - event timestamp, INT32_MIN = no timestamp
+    max_len: int  # L of the padded layout
+
+    def to(self, device, *, non_blocking: bool = False) -> "CompactSequence":
+        if self.ids.is_contiguous():
+            ids = self.ids.to(device, non_blocking=non_blocking)
+        else:           # rows of a larger host buffer: one copy per feature row, no staging copy on the host
+            ids = torch.empty(self.ids.shape, dtype=self.ids.dtype, device=device)
+            for f in range(self.ids.shape[0]):
+                ids[f].copy_(self.ids[f], non_blocking=non_blocking)
+        return CompactSequence(self.cu.to(device, non_blocking=non_blocking), ids,
+                               None if self.gaps is None else self.gaps.to(device, non_blocking=non_blocking), self.max_len)
+
+    def pin_memory(self) -> "CompactSequence":
+        return CompactSequence(self.cu.pin_memory(), self.ids.contiguous().pin_memory(),
+                               None if self.gaps is None else self.gaps.pin_memory(), self.max_len)
+
+    def tensors(self) -> list[torch.Tensor]:
+        return [t for t in (self.cu, self.ids, self.gaps) if t is not None]
+
+
+@dataclass(frozen=True, slots=True)
+class CompactModelInput:
+    """A ``ModelInput`` whose sequences travel in the compact format.  ``to(device)`` copies it (about a third of
+    the bytes of the padded record at the benchmark's lengths) and ``expand()`` rebuilds the padded ``ModelInput`` on
+    the device, bit for bit, so everything behind it is unchanged."""
+
+    user: EntityInput
+    item: EntityInput
+    sequences: dict[str, CompactSequence]
+    request_timestamp: torch.Tensor  # [B] int64
+
+    def to(self, device, *, non_blocking: bool = False) -> "CompactModelInput":
+        return CompactModelInput(
+            self.user.to(device, non_blocking=non_blocking), self.item.to(device, non_blocking=non_blocking),
+            {name: seq.to(device, non_blocking=non_blocking) for name, seq in self.sequences.items()},
+            self.request_timestamp.to(device, non_blocking=non_blocking),
+        )
+
+    def pin_memory(self) -> "CompactModelInput":
+        return CompactModelInput(self.user.pin_memory(), self.item.pin_memory(),
+                                 {name: seq.pin_memory() for name, seq in self.sequences.items()},
+                                 self.request_timestamp.pin_memory())
+
+    @property
+    def batch_size(self) -> int:
+        return int(self.user.int_values.shape[0])
+
+    def tensors(self) -> list[torch.Tensor]:
+        out = []
+        for entity in (self.user, self.item):
+            out += [entity.int_values, entity.int_missing_mask, entity.dense_values, entity.dense_missing_mask]
+        for seq in self.sequences.values():
+            out += seq.tensors()
+        out.append(self.request_timestamp)
+        return out
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors())
+
+    def expand(self) -> ModelInput:
+        """The padded record, rebuilt by ``ops.expand_sequence`` on the device the tensors live on."""
+        from taac_2026_b200 import ops
+
+        sequences = {}
+        for name, seq in self.sequences.items():
+            values, lengths, timestamps = ops.expand_sequence(seq.cu, seq.ids, seq.gaps, self.request_timestamp, seq.max_len)
+            sequences[name] = SequenceInput(values, lengths, timestamps)
+        return ModelInput(self.user, self.item, sequences, self.request_timestamp)
+
+
+def compact_model_input(batch: ModelInput, *, threads: int = 4, pin: bool = False) -> CompactModelInput:
+    """Host ``ModelInput`` -> ``CompactModelInput`` (native host code, ``threads`` workers).  Raises ``OverflowError``
+    when an id or a timestamp gap needs more than 32 bits; such a batch is copied in its padded form instead.  An
+    all-zero timestamp buffer (a domain without timestamps) is not carried at all."""
+    from taac_2026_b200 import ops
+
+    sequences = {}
+    for name, seq in batch.sequences.items():
+        timed = bool(seq.timestamps.any())
+        cu, ids, gaps = ops.compact_sequence_host(seq.values, seq.lengths, seq.timestamps if timed else None,
+                                                  batch.request_timestamp if timed else None, threads=threads, pin=pin)
+        sequences[name] = CompactSequence(cu, ids, gaps, int(seq.values.shape[2]))
+    return CompactModelInput(batch.user, batch.item, sequences, batch.request_timestamp)
+
+
 @dataclass(frozen=True)
 class OneTransSpec:
     """Everything ``PCVROneTrans._init_specs`` receives that shapes the forward

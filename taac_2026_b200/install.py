@@ -30,8 +30,9 @@ What is wrapped (paths relative to the reference root):
 
 ``install(route_all=True)`` additionally maps every backend the workflows configure
 (evaluation/workflow.py:120-125) to ``"cuda"``: an unmodified CLI run is switched over without touching its
-configuration.  Under autograd the norms and attention go back to the reference's own dispatcher (torch
-backend), because the kernels here are forward-only.
+configuration.  Under autograd the norms stay on this library where its backward kernels take the shape
+(rows of whole 16-byte pieces, at most 1024 16-bit columns); other norm shapes and attention go back to the
+reference's own dispatcher (torch backend), because those kernels are forward-only.
 """
 
 from __future__ import annotations
@@ -89,16 +90,17 @@ def install(*, route_all: bool = False) -> None:
 
     def rms_norm(x, weight, eps=1e-6, *, backend, block_rows=None):
         if pick(backend) == "cuda":
-            # forward-only kernels: a caller that trains gets the reference's differentiable torch path when
-            # everything was routed here wholesale, and the operator's own refusal when it asked for "cuda" itself
-            if backend != "cuda" and wants_grad(x, weight):
+            # the norms are differentiable here for rows the backward kernels take; for other shapes a caller that
+            # trains gets the reference's torch path when everything was routed here wholesale, and the operator's
+            # own refusal when it asked for "cuda" itself
+            if backend != "cuda" and wants_grad(x, weight) and not (x.is_cuda and ops.norm_backward_supported(x)):
                 return ref_rms(x, weight, eps, backend="torch", block_rows=block_rows)
             return ops.rms_norm(x, weight, eps, backend="cuda", block_rows=block_rows)
         return ref_rms(x, weight, eps, backend=backend, block_rows=block_rows)
 
     def layer_norm(x, weight, bias, eps=1e-5, *, backend, block_rows=None):
         if pick(backend) == "cuda":
-            if backend != "cuda" and wants_grad(x, weight, bias):
+            if backend != "cuda" and wants_grad(x, weight, bias) and not (x.is_cuda and ops.norm_backward_supported(x)):
                 return ref_ln(x, weight, bias, eps, backend="torch", block_rows=block_rows)
             return ops.layer_norm(x, weight, bias, eps, backend="cuda", block_rows=block_rows)
         return ref_ln(x, weight, bias, eps, backend=backend, block_rows=block_rows)

@@ -201,8 +201,12 @@ class OneTransInference:
         # sequence tokenizer as ONE kernel (`ops.token_project`) instead of the row gather, the projection GEMM and the
         # fused tail.  Off by default: measured on 1 M rows the one-kernel form takes 1.27 ms against 0.79 ms.
         self.fused_tokenizer = bool(fused_tokenizer)
-        if ffn not in ("bf16", "fp8"):
+        if ffn not in ("bf16", "fp8", "fp8_precise"):
             raise ValueError(f"unknown ffn mode {ffn}")
+        # "fp8_precise": GEMM 1 of the shared FFN on the bf16 tensor cores, only its hidden activation and the down
+        # projection in e4m3 (ops.ffn_fp8(precise=True))
+        self.ffn_precise = ffn == "fp8_precise"
+        ffn = "fp8" if self.ffn_precise else ffn
         if ffn == "fp8" and (dtype != torch.bfloat16 or spec.d_model % 256 or (spec.d_model * spec.hidden_mult) % 256):
             raise RuntimeError("ffn='fp8' needs bf16 activations, d_model % 256 == 0 and hidden % 256 == 0")
         self.ffn_mode = ffn
@@ -299,7 +303,8 @@ class OneTransInference:
             if self.ffn_mode == "fp8":
                 blk["ffn_fp8"] = ops.Fp8FfnWeights(
                     self.w[p + ".ffn.shared.net.0.weight"], self.w[p + ".ffn.shared.net.3.weight"], gated=False,
-                    b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"])
+                    b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"],
+                    precise=self.ffn_precise)
                 # The packed path leaves the attention output bias out of the residual stream it hands to the
                 # FFN (the norm in between adds it on the fly), so the FFN's own output bias carries it.
                 folded = copy.copy(blk["ffn_fp8"])
@@ -489,7 +494,7 @@ class OneTransInference:
     def _shared_ffn_residual(self, blk: dict, x: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         """tokens + FFN(x) for every row (`FeedForward`, experiments/onetrans/model.py:33-44)."""
         if self.ffn_mode == "fp8":
-            return ops.ffn_fp8(x, blk["ffn_fp8"], residual=tokens, status=self.status_word)
+            return ops.ffn_fp8(x, blk["ffn_fp8"], residual=tokens, status=self.status_word, precise=self.ffn_precise)
         p = blk["p"]
         return self._linear(self._linear(x, p + ".ffn.shared.net.0", silu=True), p + ".ffn.shared.net.3", residual=tokens)
 
@@ -819,7 +824,7 @@ class OneTransInference:
                 # is added by the norm on the fly and rides on the FFN output biases into the next residual
                 tokens = self._proj(attn2d, blk["out_w"], None, residual=tokens, out=tokens)
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
-                out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens, status=self.status_word)
+                out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens, status=self.status_word, precise=self.ffn_precise)
             else:
                 tokens = self._proj(attn2d, blk["out_w"], blk["out_b32"], residual=tokens)
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)
@@ -913,7 +918,9 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
     The serving loop of `evaluation/workflow.py:246-293` with the host-to-device copy taken off the critical
     path: the copy of batch i + 1 runs on a side stream while batch i is scored, so that in steady state a
     step costs max(copy, compute) instead of their sum.  ``host_batches`` should be pinned
-    (``ModelInput.pin_memory()``) for the copies to be asynchronous.
+    (``ModelInput.pin_memory()``) for the copies to be asynchronous.  A batch may also be a ``CompactModelInput``
+    (``inputs.compact_model_input``): its sequences cross the link as 32-bit valid prefixes and are expanded to the
+    padded int64 record by one kernel on the device.
 
     The engine's status word (raised by a tcgen05 kernel whose bounded wait gave up) is read when the stream
     ends and, with ``check_every=n``, after every n-th batch; a raised word turns into a ``RuntimeError``
@@ -943,6 +950,8 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
         for t in staged.tensors():           # allocated on the copy stream, consumed on the compute stream
             t.record_stream(compute)
         pending = stage(nxt) if nxt is not None else None
+        if hasattr(staged, "expand"):        # compact host format: rebuild the padded record on the device
+            staged = staged.expand()
         yield model.scores(staged, micro_batch=micro_batch)
         served += 1
         if check_every > 0 and served % check_every == 0:

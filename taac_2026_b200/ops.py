@@ -20,7 +20,7 @@ from __future__ import annotations
 import ctypes
 import math
 from dataclasses import dataclass
-from typing import Literal
+from typing import Any, Literal, Sequence
 
 import torch
 
@@ -1225,6 +1225,125 @@ def sequence_prepare(values: torch.Tensor, lengths: torch.Tensor, timestamps: to
 
 
 
+def compact_sequence_host(values: torch.Tensor, lengths: torch.Tensor, timestamps: torch.Tensor | None,
+                          request_ts: torch.Tensor | None, *, threads: int = 4, pin: bool = False
+                          ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    """Padded int64 host record of one domain -> the compact 32-bit host format ``(cu [B + 1], ids [F, total],
+    gaps [total] or None)``: the valid prefix of every sample back to back, timestamps as gaps to the request
+    timestamp.  Runs on the host inside the native library (no GPU needed).  Raises ``OverflowError`` when a value
+    does not fit 32 bits; the caller then copies the padded record instead."""
+    for t in (values, lengths, timestamps, request_ts):
+        if t is not None and t.is_cuda:
+            raise RuntimeError("compact_sequence_host takes host tensors")
+    if values.ndim != 3 or lengths.ndim != 1 or values.shape[0] != lengths.shape[0]:
+        raise ValueError("compact_sequence_host expects values [B, F, L] and lengths [B]")
+    values, lengths = values.to(torch.int64).contiguous(), lengths.to(torch.int64).contiguous()
+    batch, feats, max_len = values.shape
+    lib = _lib.load()
+    cu = torch.empty(batch + 1, dtype=torch.int32, pin_memory=pin)
+    _lib.check(lib.tb200_host_compact_offsets(_ptr(lengths), batch, max_len, _ptr(cu)), "compact_sequence_host")
+    total = int(cu[-1])
+    ids = torch.empty(feats, max(total, 1), dtype=torch.int32, pin_memory=pin)[:, :total]
+    gaps = None
+    if timestamps is not None:
+        if request_ts is None:
+            raise ValueError("compact_sequence_host needs request_ts with timestamps")
+        timestamps, request_ts = timestamps.to(torch.int64).contiguous(), request_ts.to(torch.int64).contiguous()
+        gaps = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=pin)[:total]
+    code = lib.tb200_host_compact_sequence(_ptr(values), _ptr(timestamps) if gaps is not None else None,
+                                           _ptr(request_ts) if gaps is not None else None, _ptr(cu), batch, feats, max_len,
+                                           _ptr(ids), max(total, 1), _ptr(gaps) if gaps is not None else None, int(threads))
+    _lib.check(code, "compact_sequence_host")
+    return cu, ids, gaps
+
+
+def compact_sequence_from_lists(id_columns: Sequence[tuple[Any, Any]], timestamp_column: tuple[Any, Any] | None,
+                                request_ts: Any, max_len: int, *, vocab_sizes: Sequence[int] | None = None,
+                                threads: int = 4, pin: bool = False):
+    """Arrow list columns -> the compact host format, without the padded intermediate of the reference's converter.
+
+    ``id_columns``: one ``(offsets, values)`` pair of numpy arrays per side column (offsets int32 or int64 of length
+    rows + 1, values int64), ``timestamp_column`` the same pair or None — what ``column.offsets.to_numpy()`` /
+    ``column.values.to_numpy()`` give in `PCVRRecordBatchConverter._sequence_side_arrays` (batch_converter.py:490-500).
+    Returns ``(cu, ids, gaps, oob_counts)`` as torch tensors; ``oob_counts[f]`` is the number of ids of column f that
+    were at or beyond ``vocab_sizes[f]`` and became 0 (the clip_vocab=True rule, batch_converter.py:594-650)."""
+    import numpy as np
+
+    feats = len(id_columns)
+    if feats < 1:
+        raise ValueError("compact_sequence_from_lists needs at least one id column")
+    wide = np.asarray(id_columns[0][0]).dtype == np.int64
+    off_dtype = np.int64 if wide else np.int32
+    keep = []      # arrays whose memory the pointer tables refer to
+
+    def column(pair):
+        offsets = np.ascontiguousarray(np.asarray(pair[0]), dtype=off_dtype)
+        vals = np.ascontiguousarray(np.asarray(pair[1]), dtype=np.int64)
+        keep.extend((offsets, vals))
+        return offsets, vals
+
+    cols = [column(pair) for pair in id_columns]
+    rows = cols[0][0].shape[0] - 1
+    if any(c[0].shape[0] != rows + 1 for c in cols):
+        raise ValueError("every id column needs rows + 1 offsets")
+    off_table = (ctypes.c_void_p * feats)(*[c[0].ctypes.data for c in cols])
+    val_table = (ctypes.c_void_p * feats)(*[c[1].ctypes.data for c in cols])
+    ts = column(timestamp_column) if timestamp_column is not None else None
+    now = np.ascontiguousarray(np.asarray(request_ts), dtype=np.int64)
+    vocab = np.ascontiguousarray(np.asarray(vocab_sizes), dtype=np.int64) if vocab_sizes is not None else None
+    oob = np.zeros(feats, dtype=np.int64)
+    cap = 0
+    for offsets, _ in cols:      # an upper bound of the total for the output buffers
+        cap = max(cap, int(np.minimum(np.maximum(np.diff(offsets.astype(np.int64)), 0), max_len).sum()) if rows > 0 else 0)
+    cap = max(min(cap * feats, rows * max_len), 1)
+    cu = torch.empty(rows + 1, dtype=torch.int32, pin_memory=pin)
+    ids = torch.empty(feats, cap, dtype=torch.int32, pin_memory=pin)
+    gaps = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+    code = _lib.load().tb200_host_compact_from_lists(
+        ctypes.cast(off_table, ctypes.c_void_p), ctypes.cast(val_table, ctypes.c_void_p), feats,
+        ts[0].ctypes.data if ts is not None else None, ts[1].ctypes.data if ts is not None else None, 1 if wide else 0,
+        now.ctypes.data, vocab.ctypes.data if vocab is not None else None, oob.ctypes.data, rows, int(max_len), _ptr(cu),
+        _ptr(ids), cap, _ptr(gaps), int(threads))
+    _lib.check(code, "compact_sequence_from_lists")
+    total = int(cu[-1])
+    return cu, ids[:, :total], gaps[:total], torch.from_numpy(oob)
+
+
+def expand_sequence(cu: torch.Tensor, ids: torch.Tensor, gaps: torch.Tensor | None, request_ts: torch.Tensor | None,
+                    max_len: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Compact device copy -> the padded int64 tensors the reference's model consumes: ``(values [B, F, L],
+    lengths [B], timestamps [B, L])``, bit for bit what was packed (zeros beyond the lengths; all-zero timestamps
+    when the compact record carries none)."""
+    _require_backend("expand_sequence", "cuda")
+    _require_cuda_tensors("cuda expand_sequence", cu, ids, gaps, request_ts)
+    if cu.dtype != torch.int32 or ids.dtype != torch.int32 or ids.ndim != 2 or (gaps is not None and gaps.dtype != torch.int32):
+        raise ValueError("expand_sequence expects int32 cu [B + 1], ids [F, total] and gaps [total]")
+    if max_len < 2 or max_len % 2 != 0:
+        raise ValueError("expand_sequence needs an even max_len")
+    if ids.stride(1) != 1 and ids.shape[1] > 1:
+        raise ValueError("expand_sequence needs ids with unit stride along the events")
+    batch, feats = cu.shape[0] - 1, ids.shape[0]
+    dev = cu.device
+    if ids.shape[1] == 0:            # a batch without a single event: the kernel still wants addresses to ignore
+        ids = ids.new_zeros(feats, 1)
+        gaps = None if gaps is None else gaps.new_zeros(1)
+    values = torch.empty(batch, feats, max_len, dtype=torch.int64, device=dev)
+    lengths = torch.empty(batch, dtype=torch.int64, device=dev)
+    if gaps is not None:
+        timestamps = torch.empty(batch, max_len, dtype=torch.int64, device=dev)
+        request_ts = request_ts.to(torch.int64).contiguous()
+    else:
+        timestamps = torch.zeros(batch, max_len, dtype=torch.int64, device=dev)
+    stride = ids.stride(0) if feats > 1 else max(ids.shape[1], 1)
+    with torch.cuda.device(dev), _timed("expand_sequence", batch=batch, n_feat=feats, max_len=max_len):
+        code = _lib.load().tb200_expand_sequence(_ptr(ids), _ptr(gaps) if gaps is not None else None, _ptr(cu.contiguous()),
+                                                 _ptr(request_ts) if gaps is not None else None, _ptr(values), _ptr(lengths),
+                                                 _ptr(timestamps) if gaps is not None else None, batch, feats, int(max_len),
+                                                 int(stride), _stream_ptr())
+    _lib.check(code, "cuda expand_sequence")
+    return values, lengths, timestamps
+
+
 def packed_token_index(values: torch.Tensor, timestamps: torch.Tensor | None, request_ts: torch.Tensor, src: torch.Tensor,
                        cu_rows: torch.Tensor, seq_count: torch.Tensor, start: torch.Tensor, hash_buckets: torch.Tensor,
                        total_rows: int, edges: torch.Tensor | None = None,
@@ -1514,6 +1633,9 @@ __all__ = [
     "cuda_supported_floating_dtype",
     "embedding_bag_mean",
     "embedding_bag_mean_backward",
+    "compact_sequence_host",
+    "compact_sequence_from_lists",
+    "expand_sequence",
     "fields_bag_mean",
     "gather_rows",
     "layer_norm",
