@@ -643,7 +643,7 @@ def run_e2e(args) -> None:
         first = counter["e2e"]
         counter["e2e"] += steps
         stream = (stream_batches[(first + i) % n_rot] for i in range(steps))
-        for scores in score_stream(model, stream, micro_batch=micro):
+        for scores in score_stream(model, stream, micro_batch=micro, prepare_ahead=not args.no_prepare_ahead):
             host_scores.copy_(gather_scores(scores), non_blocking=True)
 
     def barrier() -> None:
@@ -1263,6 +1263,9 @@ def main() -> None:
     parser.add_argument("--no-reference-order", action="store_true", help="skip the pass in the reference's order of operations")
     parser.add_argument("--fused-tokenizer", action="store_true",
                         help="sequence tokenizer as the one-kernel form (ops.token_project) instead of gather, projection and tail kernels")
+    parser.add_argument("--no-prepare-ahead", action="store_true",
+                        help="end-to-end arm: run duplicate removal and the row plan inside the forward (one device drain per "
+                             "batch) instead of on the copy stream under the previous batch")
     parser.add_argument("--rows", type=int, default=0)
     parser.add_argument("--cols", type=int, default=0)
     parser.add_argument("--kind", default="")

@@ -224,6 +224,18 @@ int tb200_fields_bag_mean_fwd(const void* const* tables, const int64_t* rows, co
                               const int32_t* lengths, int32_t n_fields, int32_t max_bag, int32_t dim, const void* ids,
                               int ids_dtype, int64_t batch, int32_t ids_cols, void* out, int dtype, void* stream);
 
+/* The same with the tokenizer's "missing value" rows folded in (`NonSequentialTokenizer.forward`,
+ * src/taac2026/infrastructure/modeling/tokenizers.py:66-68):
+ *     out[b, f, :] = pooled[b, f, :] + (missing[b, f] ? missing_rows[f, :] : 0)
+ * with the pooled row rounded to `dtype` first and the sum rounded again, i.e. the bits of the two tensor operations
+ * `pooled + mask.unsqueeze(-1) * missing_embeddings`.  missing: uint8 / bool flags [batch, missing_cols], of which
+ * the first n_fields columns are used; missing_rows: [n_fields, dim] of `dtype`, 16-byte aligned. */
+int tb200_fields_bag_mean_missing_fwd(const void* const* tables, const int64_t* rows, const int32_t* offsets,
+                                      const int32_t* lengths, int32_t n_fields, int32_t max_bag, int32_t dim,
+                                      const void* ids, int ids_dtype, int64_t batch, int32_t ids_cols,
+                                      const uint8_t* missing, int32_t missing_cols, const void* missing_rows,
+                                      void* out, int dtype, void* stream);
+
 /* out[i, out_col0 : out_col0 + dim] = table[clamp(id_i, 0, vocab_rows - 1), :]   (bit-exact copy)
  * for i in [0, n), with id_i = ids[(i / seq_len) * ids_batch_stride + (i % seq_len)].
  * The `nn.Embedding` gather of `SequenceTokenizer.forward` fused with its id clamp and with the
@@ -362,6 +374,26 @@ int tb200_packed_token_index(const int64_t* values, const int64_t* timestamps, c
                              const int64_t* edges, int32_t n_edges, const int64_t* hash_buckets, int64_t batch,
                              int32_t n_feat, int32_t max_len, int64_t total_rows, int64_t* ids_out, int64_t* pos_out,
                              int64_t* bucket_out, void* stream);
+
+/* Row plan of the packed valid-token layout for a whole forward, in one launch.  widths[0 .. n_layers] (host array)
+ * is the static pyramid schedule of padded sequence widths (`_pyramid_keep_count`, experiments/onetrans/model.py:
+ * 317-323; widths[0] = min(max_len, seq_top_k)); lengths: [batch] int64 after duplicate removal.  Outputs (device):
+ *   start[b] = max(raw - widths[0], 0), n0[b] = min(raw, widths[0]) with raw = clamp(lengths[b], 0, max_len)
+ *   counts[l, b] = max(n0[b] - (widths[0] - widths[l]), 0)          valid sequence tokens of sample b at layer l
+ *   cu[l, 0 .. batch] / cu32[l, ...]   exclusive prefix sums of counts[l, :] + ns (int64 and int32 copies)
+ *   meta[l] = (total rows, largest rows per sample) of layer l       the one pair of numbers per layer the host reads
+ *   ns_rows0[b, j] = cu[0, b] + counts[0, b] + j                     rows of the non-sequence tokens at layer 0
+ * These are the integers behind `tokens[:, -keep_count:]` (model.py:340-348) when only valid tokens are stored.
+ * n_layers <= 64, (widths[0] + ns) * batch < 2^31. */
+int tb200_pyramid_plan(const int64_t* lengths, int32_t batch, int32_t max_len, const int32_t* widths, int32_t n_layers,
+                       int32_t ns, int64_t* start, int64_t* n0, int64_t* counts, int64_t* cu, int32_t* cu32,
+                       int64_t* meta, int64_t* ns_rows0, void* stream);
+
+/* Rows of layer l kept for layer l + 1, from two consecutive rows of the plan above (cu0 = cu[l], cu1 = cu[l + 1], ...):
+ * src[cu1[b] + r] = cu0[b] + (counts0[b] - counts1[b]) + r;  ns_rows1[b, j] = cu1[b] + counts1[b] + j;  row_dst
+ * (optional, int32 [rows of layer l]) = the destination of every row of layer l, -1 for the dropped ones. */
+int tb200_pyramid_kept_rows(const int64_t* cu0, const int64_t* cu1, const int64_t* counts0, const int64_t* counts1,
+                            int32_t batch, int32_t ns, int64_t* src, int64_t* ns_rows1, int32_t* row_dst, void* stream);
 
 /* ---- per-token (grouped) bf16 linear layers with a fused epilogue ----------------------------
  * out[g] = act(a[g] @ w[g]^T + bias[g]) (+ residual[g]) for g in [0, groups): the token-specific projections

@@ -93,6 +93,9 @@ struct BagArgs {
     int32_t chunks;
     int32_t lanes_per_row;
     int64_t n_bags;  // batch * n_fields
+    const uint8_t* missing;     // [batch, missing_cols] flags or nullptr: out += missing_rows[field] where set
+    const void* missing_rows;   // [n_fields, dim]
+    int32_t missing_cols;
 };
 
 template <typename T, typename I>
@@ -176,6 +179,20 @@ bag_mean_kernel(BagArgs a, const void* __restrict__ ids, T* __restrict__ out) {
 #pragma unroll
                 for (int e = 0; e < N; ++e) acc[e] = __fdiv_rn(acc[e], denom);
                 o = Vec16<T>::pack(acc);
+            }
+            if (a.missing != nullptr) {
+                // the per-field "missing" row, added to the pooled row as stored (one rounding for the mean, one
+                // for the sum: what `pooled + mask[..., None] * missing_embeddings` gives as two tensor operations)
+                const int64_t bidx = q / a.n_fields;
+                const int f = static_cast<int>(q - bidx * a.n_fields);
+                if (a.missing[bidx * a.missing_cols + f] != 0) {
+                    float x[N], m[N];
+                    Vec16<T>::unpack(o, x);
+                    Vec16<T>::unpack(static_cast<const uint4*>(a.missing_rows)[f * chunks + c], m);
+#pragma unroll
+                    for (int e = 0; e < N; ++e) x[e] += m[e];
+                    o = Vec16<T>::pack(x);
+                }
             }
             st_cs_v4(reinterpret_cast<uint4*>(out) + q * chunks + c, o);
         }
@@ -348,10 +365,11 @@ int bag_entry(BagArgs a, int32_t dim, const void* ids, int ids_dtype, int64_t ba
     a.chunks = dim * es / 16;
     a.n_bags = batch * a.n_fields;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (a.max_bag == 0) {  // every bag is empty
+    if (a.max_bag == 0 && a.missing == nullptr) {  // every bag is empty
         cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(a.n_bags) * dim * es, s);
         return e == cudaSuccess ? TB200_OK : static_cast<int>(e);
     }
+    if (a.max_bag == 0) return TB200_ERR_UNSUPPORTED;
     switch (dtype) {
         case TB200_F32: return bag_launch<float>(a, ids, ids_dtype, out, s);
         case TB200_F16: return bag_launch<__half>(a, ids, ids_dtype, out, s);
@@ -395,6 +413,31 @@ extern "C" int tb200_fields_bag_mean_fwd(const void* const* tables, const int64_
     a.max_bag = max_bag;
     a.ids_cols = ids_cols;
     a.clamp = 1;
+    return bag_entry(a, dim, ids, ids_dtype, batch, out, dtype, stream);
+}
+
+extern "C" int tb200_fields_bag_mean_missing_fwd(const void* const* tables, const int64_t* rows, const int32_t* offsets,
+                                                 const int32_t* lengths, int32_t n_fields, int32_t max_bag, int32_t dim,
+                                                 const void* ids, int ids_dtype, int64_t batch, int32_t ids_cols,
+                                                 const uint8_t* missing, int32_t missing_cols, const void* missing_rows,
+                                                 void* out, int dtype, void* stream) {
+    using namespace tb200;
+    if (tables == nullptr || rows == nullptr || offsets == nullptr || lengths == nullptr) return TB200_ERR_NULL;
+    if (missing == nullptr || missing_rows == nullptr) return TB200_ERR_NULL;
+    if (missing_cols < n_fields) return TB200_ERR_SHAPE;
+    if (!aligned16(missing_rows)) return TB200_ERR_ALIGN;
+    BagArgs a{};
+    a.tables = tables;
+    a.rows = rows;
+    a.offsets = offsets;
+    a.lengths = lengths;
+    a.n_fields = n_fields;
+    a.max_bag = max_bag;
+    a.ids_cols = ids_cols;
+    a.clamp = 1;
+    a.missing = missing;
+    a.missing_rows = missing_rows;
+    a.missing_cols = missing_cols;
     return bag_entry(a, dim, ids, ids_dtype, batch, out, dtype, stream);
 }
 

@@ -218,8 +218,153 @@ token_index_kernel(const int64_t* __restrict__ values, const int64_t* __restrict
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Row plan of the packed layout.  The pyramid schedule (padded widths S[0..L], experiments/onetrans/model.py:317-348)
+// is static; what depends on the batch is how many valid sequence tokens every sample still has at each layer:
+//     raw = clamp(len[b], 0, max_len)      start[b] = max(raw - S[0], 0)      n0[b] = min(raw, S[0])
+//     counts[l][b] = max(n0[b] - (S[0] - S[l]), 0)            rows[l][b] = counts[l][b] + ns
+//     cu[l] = exclusive prefix sum of rows[l]   (B + 1 entries, as int64 and as int32)
+//     meta[l] = (sum_b rows[l][b], max_b rows[l][b])          ns_rows0[b][j] = cu[0][b] + counts[0][b] + j
+// One CTA per layer: a thread owns one sample of a 1024-sample tile (coalesced reads), the tile's rows go through a
+// block scan (warp shuffles + one shared array of warp totals) and the running total is carried from tile to tile.
+// It replaces some ninety one-line tensor operations per batch.
+// ---------------------------------------------------------------------------------------
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanMaxLayers = 64;
+
+struct PlanWidths {
+    int32_t w[kPlanMaxLayers + 1];
+};
+
+__global__ void __launch_bounds__(kPlanThreads)
+pyramid_plan_kernel(const int64_t* __restrict__ lengths, int batch, int max_len, PlanWidths widths, int ns,
+                    int64_t* __restrict__ start, int64_t* __restrict__ n0_out, int64_t* __restrict__ counts,
+                    int64_t* __restrict__ cu, int32_t* __restrict__ cu32, int64_t* __restrict__ meta,
+                    int64_t* __restrict__ ns_rows0) {
+    __shared__ int64_t warp_sum[32];
+    __shared__ int64_t warp_max[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int l = blockIdx.x;
+    const int width = widths.w[0];
+    const int64_t drop = width - widths.w[l];
+    int64_t* cu_l = cu + static_cast<int64_t>(l) * (batch + 1);
+    int32_t* cu32_l = cu32 + static_cast<int64_t>(l) * (batch + 1);
+    int64_t running = 0, mx = 0;
+    for (int tile = 0; tile < batch; tile += kPlanThreads) {
+        const int b = tile + tid;
+        int64_t c = 0, r = 0;
+        if (b < batch) {
+            const int64_t len = lengths[b];
+            const int64_t raw = len < 0 ? 0 : (len > max_len ? max_len : len);
+            const int64_t n0 = raw < width ? raw : width;
+            c = n0 > drop ? n0 - drop : 0;
+            r = c + ns;
+            counts[static_cast<int64_t>(l) * batch + b] = c;
+            if (l == 0) {
+                start[b] = raw > width ? raw - width : 0;
+                n0_out[b] = n0;
+            }
+        }
+        mx = max(mx, r);
+        int64_t incl = r;                                   // inclusive scan inside the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int64_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) warp_sum[warp] = incl;
+        __syncthreads();
+        int64_t before = 0, tile_total = 0;
+        for (int w = 0; w < 32; ++w) {                      // 32 shared-memory reads, same address per warp: broadcasts
+            const int64_t v = warp_sum[w];
+            before += w < warp ? v : 0;
+            tile_total += v;
+        }
+        const int64_t first_row = running + before + incl - r;
+        if (b < batch) {
+            cu_l[b] = first_row;
+            cu32_l[b] = static_cast<int32_t>(first_row);
+            if (l == 0)
+                for (int j = 0; j < ns; ++j) ns_rows0[static_cast<int64_t>(b) * ns + j] = first_row + c + j;
+        }
+        running += tile_total;
+        __syncthreads();                                    // warp_sum is rewritten by the next tile
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) warp_max[warp] = mx;
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 32; ++w) mx = max(mx, warp_max[w]);
+        cu_l[batch] = running;
+        cu32_l[batch] = static_cast<int32_t>(running);
+        meta[2 * l] = running;
+        meta[2 * l + 1] = mx;
+    }
+}
+
+// Rows of layer l that the pyramid keeps for layer l + 1 (the last rows of every sample), in the next layer's order:
+//     src[cu1[b] + r] = cu0[b] + (counts0[b] - counts1[b]) + r            r < counts1[b] + ns
+//     ns_rows1[b][j] = cu1[b] + counts1[b] + j
+//     row_dst[cu0[b] + i] = i < dropped ? -1 : cu1[b] + i - dropped        (optional: destination of every row of l)
+__global__ void __launch_bounds__(128)
+pyramid_kept_rows_kernel(const int64_t* __restrict__ cu0, const int64_t* __restrict__ cu1, const int64_t* __restrict__ counts0,
+                         const int64_t* __restrict__ counts1, int ns, int64_t* __restrict__ src, int64_t* __restrict__ ns_rows1,
+                         int32_t* __restrict__ row_dst) {
+    const int b = blockIdx.x;
+    const int64_t base0 = cu0[b], base1 = cu1[b];
+    const int64_t c0 = counts0[b], c1 = counts1[b];
+    const int64_t dropped = c0 - c1;
+    const int64_t rows1 = c1 + ns;
+    for (int64_t r = threadIdx.x; r < rows1; r += blockDim.x) src[base1 + r] = base0 + dropped + r;
+    for (int j = threadIdx.x; j < ns; j += blockDim.x) ns_rows1[static_cast<int64_t>(b) * ns + j] = base1 + c1 + j;
+    if (row_dst != nullptr) {
+        const int64_t rows0 = c0 + ns;
+        for (int64_t i = threadIdx.x; i < rows0; i += blockDim.x)
+            row_dst[base0 + i] = i < dropped ? -1 : static_cast<int32_t>(base1 + i - dropped);
+    }
+}
+
 }  // namespace
 }  // namespace tb200
+
+extern "C" int tb200_pyramid_plan(const int64_t* lengths, int32_t batch, int32_t max_len, const int32_t* widths,
+                                  int32_t n_layers, int32_t ns, int64_t* start, int64_t* n0, int64_t* counts, int64_t* cu,
+                                  int32_t* cu32, int64_t* meta, int64_t* ns_rows0, void* stream) {
+    using namespace tb200;
+    if (batch < 0 || max_len < 0 || n_layers < 0 || n_layers > kPlanMaxLayers || ns < 0) return TB200_ERR_SHAPE;
+    if (widths == nullptr || start == nullptr || n0 == nullptr || counts == nullptr || cu == nullptr || cu32 == nullptr ||
+        meta == nullptr || (batch > 0 && lengths == nullptr) || (ns > 0 && batch > 0 && ns_rows0 == nullptr))
+        return TB200_ERR_NULL;
+    PlanWidths w{};
+    for (int l = 0; l <= n_layers; ++l) {
+        if (widths[l] < 0 || widths[l] > widths[0]) return TB200_ERR_SHAPE;
+        w.w[l] = widths[l];
+    }
+    // the int32 offsets must hold the largest total: every sample at most widths[0] + ns rows
+    if ((static_cast<int64_t>(widths[0]) + ns) * batch > 0x7FFFFFFFll) return TB200_ERR_SHAPE;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    pyramid_plan_kernel<<<static_cast<unsigned>(n_layers + 1), kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        lengths, batch, max_len, w, ns, start, n0, counts, cu, cu32, meta, ns_rows0);
+    count_launch();
+    return launch_status();
+}
+
+extern "C" int tb200_pyramid_kept_rows(const int64_t* cu0, const int64_t* cu1, const int64_t* counts0, const int64_t* counts1,
+                                       int32_t batch, int32_t ns, int64_t* src, int64_t* ns_rows1, int32_t* row_dst,
+                                       void* stream) {
+    using namespace tb200;
+    if (batch < 0 || ns < 0) return TB200_ERR_SHAPE;
+    if (batch == 0) return TB200_OK;
+    if (cu0 == nullptr || cu1 == nullptr || counts0 == nullptr || counts1 == nullptr || src == nullptr ||
+        (ns > 0 && ns_rows1 == nullptr))
+        return TB200_ERR_NULL;
+    if (!device_info().valid) return TB200_ERR_DEVICE;
+    pyramid_kept_rows_kernel<<<static_cast<unsigned>(batch), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        cu0, cu1, counts0, counts1, ns, src, ns_rows1, row_dst);
+    count_launch();
+    return launch_status();
+}
 
 extern "C" int tb200_sequence_prepare(const int64_t* values, const int64_t* lengths, const int64_t* timestamps,
                                       const int64_t* request_ts, int64_t batch, int32_t n_feat, int32_t max_len,

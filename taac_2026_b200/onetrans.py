@@ -201,6 +201,8 @@ class OneTransInference:
         # sequence tokenizer as ONE kernel (`ops.token_project`) instead of the row gather, the projection GEMM and the
         # fused tail.  Off by default: measured on 1 M rows the one-kernel form takes 1.27 ms against 0.79 ms.
         self.fused_tokenizer = bool(fused_tokenizer)
+        self._meta_ring: list[torch.Tensor] = []
+        self._meta_next = 0
         if ffn not in ("bf16", "fp8", "fp8_precise"):
             raise ValueError(f"unknown ffn mode {ffn}")
         # "fp8_precise": GEMM 1 of the shared FFN on the bf16 tensor cores, only its hidden activation and the down
@@ -404,7 +406,8 @@ class OneTransInference:
     def _layer_norm(self, x: torch.Tensor, prefix: str, pre_silu: bool = False) -> torch.Tensor:
         return ops.layer_norm(x, self._p(prefix + ".weight"), self._p(prefix + ".bias"), 1e-5, pre_silu=pre_silu)
 
-    def _bank_tokens(self, bank: _Bank, int_feats: torch.Tensor) -> torch.Tensor:
+    def _bank_tokens(self, bank: _Bank, int_feats: torch.Tensor, missing: torch.Tensor | None = None,
+                     missing_rows: torch.Tensor | None = None) -> torch.Tensor:
         if bank.fields is None:
             return torch.zeros(int_feats.shape[0], 0, self.spec.emb_dim, dtype=self.dtype, device=self.device)
         if bank.hashed:
@@ -412,16 +415,20 @@ class OneTransInference:
             for offset, length, buckets in bank.hashed:
                 cols = int_feats[:, offset : offset + length]
                 int_feats[:, offset : offset + length] = hash_compress_ids(cols.clamp_min(0), buckets)
-        return ops.fields_bag_mean(bank.fields, int_feats)
+        return ops.fields_bag_mean(bank.fields, int_feats, missing, missing_rows)
 
     def _ns_tokenizer(self, prefix: str, bank: _Bank, n_tokens: int, groups, int_feats, missing) -> torch.Tensor:
         """`NonSequentialTokenizer.forward` (modeling/tokenizers.py:63-87)."""
         batch = int_feats.shape[0]
-        feats = self._bank_tokens(bank, int_feats)
         key = prefix + ".missing_embeddings"
-        if key in self.w and missing is not None and feats.shape[1] > 0:
-            m = missing[:, : feats.shape[1]].to(self.dtype)
-            feats = feats + m.unsqueeze(-1) * self._p(key)[: feats.shape[1]].unsqueeze(0)
+        if key in self.w and missing is not None and bank.fields is not None and missing.dtype == torch.bool \
+                and missing.shape[1] >= bank.fields.n_fields:
+            feats = self._bank_tokens(bank, int_feats, missing, self._p(key))     # the missing rows ride in the gather kernel
+        else:
+            feats = self._bank_tokens(bank, int_feats)
+            if key in self.w and missing is not None and feats.shape[1] > 0:
+                m = missing[:, : feats.shape[1]].to(self.dtype)
+                feats = feats + m.unsqueeze(-1) * self._p(key)[: feats.shape[1]].unsqueeze(0)
         if n_tokens <= 0:
             return torch.zeros(batch, 0, self.d, dtype=self.dtype, device=self.device)
         groups = [list(g) for g in groups] or [[i] for i in range(bank.n_fields)]
@@ -562,11 +569,50 @@ class OneTransInference:
         return logits, embeddings
 
     @torch.inference_mode()
-    def predict(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
-        """(logits [B, action_num], pooled embeddings [B, 2 d]) in fp32 — `PCVROneTrans.predict`."""
+    def predict(self, inputs, prepared: dict | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """(logits [B, action_num], pooled embeddings [B, 2 d]) in fp32 — `PCVROneTrans.predict`.  ``prepared`` is
+        what ``prepare(inputs)`` returned for these inputs (the serving loop computes it ahead of time)."""
         if self.packed and len(self.domains) == 1:
-            return self._predict_packed(inputs)
+            return self._predict_packed(inputs, prepared)
         return self._predict_padded(inputs)
+
+    @torch.inference_mode()
+    def prepare(self, inputs) -> dict | None:
+        """Everything of a forward that the host has to wait for, enqueued on the current stream: duplicate removal
+        and statistics of the behaviour sequence, the row plan of the packed layout, and the asynchronous copy of the
+        plan's per-layer totals into pinned host memory (with an event).  A serving loop calls this for batch i + 1 on
+        a side stream while batch i is being scored; the forward of batch i + 1 then finds its buffer sizes on the
+        host already and never drains the device.  None when the engine does not run the packed layout."""
+        if not (self.packed and len(self.domains) == 1):
+            return None
+        seq = inputs.sequences[self.domains[0]]
+        ns = self.num_ns
+        lengths, src_map, stats = ops.sequence_prepare(seq.values, seq.lengths, seq.timestamps, inputs.request_timestamp)
+        max_len = seq.values.shape[2]
+        width = min(max_len, self.seq_keep)            # padded sequence width S[0] after the tail crop
+        widths = [width]                               # static schedule of padded widths
+        for layer in range(self.n_blocks):
+            widths.append(pyramid_keep_count(widths[-1], layer, self.n_blocks, ns))
+        plan = ops.pyramid_plan(lengths.to(torch.long), max_len, widths, ns)
+        # pinned landing buffers are kept in a small ring: allocating pinned memory per batch can stall on the device
+        # when the host runs a batch ahead (a buffer comes round again four batches later, long after its forward
+        # has read it)
+        ring = self._meta_ring
+        if not ring or ring[0].shape != plan["meta"].shape:
+            ring[:] = [torch.empty(plan["meta"].shape, dtype=torch.int64, pin_memory=True) for _ in range(4)]
+        meta_host = ring[self._meta_next % len(ring)]
+        self._meta_next += 1
+        meta_host.copy_(plan["meta"], non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        return {"src_map": src_map, "stats": stats, "plan": plan, "widths": widths, "meta_host": meta_host, "ready": ready,
+                "batch": int(lengths.shape[0])}
+
+    @staticmethod
+    def prepared_tensors(prepared: dict) -> list[torch.Tensor]:
+        """Device tensors of a ``prepare`` result (for ``Tensor.record_stream`` when it was made on another stream)."""
+        plan = prepared["plan"]
+        return [prepared["src_map"], prepared["stats"], plan["start"], plan["cu32"]]   # plan's int64 outputs share one allocation
 
     def _predict_padded(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
         dev = self.device
@@ -639,7 +685,7 @@ class OneTransInference:
         ns_summary = ns_part.mean(dim=1) if ns_part.shape[1] > 0 else torch.zeros(batch, self.d, device=dev)
         return self._classify(seq_summary, ns_summary)
 
-    def _predict_packed(self, inputs) -> tuple[torch.Tensor, torch.Tensor]:
+    def _predict_packed(self, inputs, prepared: dict | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         """Same forward on valid tokens only (one sequence domain).
 
         Sample b owns ``n[b] + ns`` consecutive rows: its valid sequence tokens in order, then its NS
@@ -654,33 +700,24 @@ class OneTransInference:
         seq = inputs.sequences[domain]
         request_ts = inputs.request_timestamp
         # duplicate removal + statistics: one kernel; `src` maps output slots to input positions, so the
-        # compacted [B, F, L] / [B, L] tensors of the reference are never materialised
-        lengths, src_map, stats = ops.sequence_prepare(seq.values, seq.lengths, seq.timestamps, request_ts)
+        # compacted [B, F, L] / [B, L] tensors of the reference are never materialised.  The valid counts, row
+        # offsets and totals that the static pyramid schedule implies come from a second kernel; the totals are the
+        # one host read of the forward (already on the host when the serving loop prepared this batch ahead of time)
+        if prepared is None or prepared["batch"] != batch:
+            prepared = self.prepare(inputs)
+        src_map, stats, plan, widths = prepared["src_map"], prepared["stats"], prepared["plan"], prepared["widths"]
         stat_vectors = [self._stats_vector(stats)]
         values, ts = seq.values, seq.timestamps
         max_len = values.shape[2]
-        raw_len = lengths.clamp(min=0, max=max_len).to(torch.long)
-        width = min(max_len, self.seq_keep)            # padded sequence width S[0] after the tail crop
-        start = (raw_len - width).clamp_min(0)         # first kept position of every row
-        n0 = raw_len.clamp_max(width)                  # valid sequence tokens per sample at layer 0
-
-        # static schedule of padded widths and the valid counts they imply
-        widths = [width]
-        for layer in range(self.n_blocks):
-            widths.append(pyramid_keep_count(widths[-1], layer, self.n_blocks, ns))
-        counts = [(n0 - (width - w)).clamp(min=0) for w in widths]            # [layers + 1] x [B]
-        rows = [c + ns for c in counts]
-        meta = torch.stack([torch.stack([r.sum(), r.max()]) for r in rows]).tolist()  # the one host read
+        width = widths[0]
+        start, n0 = plan["start"], plan["n0"]          # first kept position / valid sequence tokens at layer 0
+        counts = list(plan["counts"].unbind(0))        # [layers + 1] x [B] valid sequence tokens per sample
+        cu = list(plan["cu"].unbind(0))                # [layers + 1] x [B + 1] row offsets
+        cu_i32 = list(plan["cu32"].unbind(0))
+        prepared["ready"].synchronize()
+        meta = prepared["meta_host"].tolist()
         totals = [int(m[0]) for m in meta]
         max_rows = [int(m[1]) for m in meta]
-        arange_b = torch.arange(batch, device=dev)
-
-        def offsets(r: torch.Tensor) -> torch.Tensor:
-            cu = torch.zeros(batch + 1, dtype=torch.long, device=dev)
-            cu[1:] = torch.cumsum(r, dim=0)
-            return cu
-
-        cu = [offsets(r) for r in rows]
 
         # ---- sequence tokenizer on the valid events only (modeling/tokenizers.py:156-190).  It works
         # directly in the packed layout of layer 0: the rows reserved for the NS tokens carry id 0 (the
@@ -726,15 +763,13 @@ class OneTransInference:
         if has_time:
             rows_a, rows_b = (self._p(prefix + ".time_embedding.weight"), buckets_full), (pos_table, pos_full)
         first_norm_w = self._p(self.blocks[0]["p"] + ".attn_norm.weight") if self.blocks else None
-        ns_off = torch.arange(ns, device=dev)[None, :]
 
-        def kept_rows(layer: int) -> tuple[torch.Tensor, torch.Tensor]:
-            """Rows of layer ``layer`` that the pyramid keeps for the next one (in the next layer's order) and
-            the NS rows [B, ns] of the next layer."""
-            owner = torch.repeat_interleave(arange_b, rows[layer + 1], output_size=totals[layer + 1])
-            r = torch.arange(totals[layer + 1], device=dev) - cu[layer + 1][owner]
-            src = cu[layer][owner] + (counts[layer] - counts[layer + 1])[owner] + r
-            return src, (cu[layer + 1][:-1] + counts[layer + 1])[:, None] + ns_off
+        def kept_rows(layer: int, want_row_dst: bool = False):
+            """Rows of layer ``layer`` that the pyramid keeps for the next one (in the next layer's order), the NS
+            rows [B, ns] of the next layer and, on request, the destination of every row of this layer (-1 = dropped)."""
+            src, next_ns, dst = ops.pyramid_kept_rows(cu[layer], cu[layer + 1], counts[layer], counts[layer + 1], ns,
+                                                      totals[layer], totals[layer + 1], want_row_dst=want_row_dst)
+            return (src, next_ns, dst) if want_row_dst else (src, next_ns)
 
         # When the first block is evaluated for the kept rows only, its residual stream is needed for those rows
         # alone: the fused pass then writes `tokens` already compacted and only `x_first` at full height.
@@ -742,9 +777,7 @@ class OneTransInference:
         fused_tail = one_kernel or (first_norm_w is not None and projected.shape[1] % (16 // projected.element_size()) == 0)
         if fused_tail and self.select_early and widths[1] < widths[0] and not (ns > 0 and max_rows[0] == ns) \
                 and totals[1] < 2**31:
-            first_kept = kept_rows(0)
-            row_dst = torch.full((total0,), -1, dtype=torch.int32, device=dev)
-            row_dst[first_kept[0]] = torch.arange(totals[1], dtype=torch.int32, device=dev)
+            *first_kept, row_dst = kept_rows(0, want_row_dst=True)
         if one_kernel:
             key = prefix + ".project.0#b32"
             if key not in self._cast_cache:
@@ -765,7 +798,7 @@ class OneTransInference:
 
         # ---- the NS tokens take the rows left for them: [seq rows of b | ns rows of b]
         ns_tokens = self._ns_tokens(inputs, stat_vectors)                          # [B, ns, d]
-        ns_rows = (cu[0][:-1] + counts[0])[:, None] + ns_off                       # [B, ns]
+        ns_rows = plan["ns_rows0"]                                                 # [B, ns]
         ns_flat = ns_tokens.reshape(batch * ns, self.d).contiguous()
         ops.scatter_rows(tokens, (ns_rows if first_kept is None else first_kept[1]).reshape(-1), ns_flat)
         if x_first is not None:   # the fused pass normalised placeholder rows there
@@ -779,7 +812,7 @@ class OneTransInference:
                 ns_summary = self._ns_only_blocks(tokens, layer, batch)
                 return self._classify(seq_summary, ns_summary)
             p = blk["p"]
-            cu32 = cu[layer].to(torch.int32)
+            cu32 = cu_i32[layer]
             x = x_first if (layer == 0 and x_first is not None) else ops.rms_norm(tokens, self._p(p + ".attn_norm.weight"), 1e-6)
             flat_ns = ns_rows.t().reshape(-1)                                      # token-major: [ns, B] row ids
             x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)                  # [ns, B, d], contiguous
@@ -792,8 +825,14 @@ class OneTransInference:
                 # arithmetic, as "whole block, then selection", without the work whose result would be dropped.
                 src, next_ns_rows = first_kept if (layer == 0 and first_kept is not None) else kept_rows(layer)
                 next_flat_ns = next_ns_rows.t().reshape(-1)
+                # every row the pyramid keeps is an NS row: the shared query projection and the shared FeedForward
+                # would be overwritten row for row by the per-token layers, so they are not run at all
+                only_ns_kept = ns > 0 and max_rows[layer + 1] == ns and "g_w1" in blk
                 kv = self._proj(x, blk["kv_w"], blk["kv_b"])                                        # [N, 2d]
-                qm = self._proj(ops.gather_rows(x, src), blk["q_w"], blk["q_b"])                    # [N', d]
+                if only_ns_kept:
+                    qm = torch.empty(totals[layer + 1], d, dtype=self.dtype, device=dev)
+                else:
+                    qm = self._proj(ops.gather_rows(x, src), blk["q_w"], blk["q_b"])                # [N', d]
                 if "g_kv_w" in blk:   # the per-token overrides of the NS rows: grouped GEMM, bias in its epilogue
                     ops.scatter_rows(kv, flat_ns, self._grouped(x_ns, blk["g_kv_w"], blk["g_kv_b"]).view(ns * batch, 2 * d))
                     ops.scatter_rows(qm, next_flat_ns, self._grouped(x_ns, blk["g_q_w"], blk["g_q_b"]).view(ns * batch, d))
@@ -803,7 +842,7 @@ class OneTransInference:
                 q = qm.unflatten(-1, (heads, hd))
                 k, v = (kv[:, i * d : (i + 1) * d].unflatten(-1, (heads, hd)) for i in range(2))
                 attn = ops.varlen_attention(q, k, v, causal=True, cu_rows=cu32, max_rows=max_rows[layer],
-                                            cu_rows_q=cu[layer + 1].to(torch.int32), max_rows_q=max_rows[layer + 1],
+                                            cu_rows_q=cu_i32[layer + 1], max_rows_q=max_rows[layer + 1],
                                             kernel=self.attention_kernel if self.attention_kernel in (0, 1, 4) else 0, status=self.status_word)
                 if not (layer == 0 and first_kept is not None):   # else the tokenizer already wrote the kept rows only
                     tokens = ops.gather_rows(tokens, src)
@@ -819,6 +858,21 @@ class OneTransInference:
                                             kernel=self.attention_kernel, status=self.status_word)
             attn2d = attn.view(-1, d).to(self.dtype)
             folded = self.ffn_mode == "fp8"
+            if selected and only_ns_kept:
+                # the rest of this block for NS rows only, finishing token-major ([ns, B, d]) as the NS-only blocks
+                # want it: out projection with the residual in its epilogue, norm with the projection's bias added
+                # on the fly, per-token FeedForward with bias (+ that bias) and residual in the epilogues
+                tokens = self._proj(attn2d, blk["out_w"], None, residual=tokens, out=tokens)
+                x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
+                x_ns = ops.gather_rows(x, flat_ns).view(ns, batch, d)
+                tok = ops.gather_rows(tokens, flat_ns).view(ns, batch, d)
+                h = self._grouped(x_ns, blk["g_w1"], blk["g_b1"], silu=True)
+                tok = self._grouped(h, blk["g_w2"], blk["g_b2_folded"], residual=tok, out=tok)
+                seq_summary = torch.zeros(batch, d, device=dev)
+                if layer + 1 == len(self.blocks):
+                    final = ops.rms_norm(tok.view(ns * batch, d), self._p("final_norm.weight"), 1e-6)
+                    return self._classify(seq_summary, final.view(ns, batch, d).mean(dim=0, dtype=torch.float32))
+                return self._classify(seq_summary, self._ns_only_blocks(tok, layer + 1, batch, token_major=True))
             if folded:
                 # tokens + attention out-projection with the residual inside the GEMM's epilogue, in place; its bias
                 # is added by the norm on the fly and rides on the FFN output biases into the next residual
@@ -847,8 +901,10 @@ class OneTransInference:
         tokens = ops.rms_norm(tokens, self._p("final_norm.weight"), 1e-6).float()
         n_last = counts[last]
         total_seq = totals[last] - batch * ns
-        owner = torch.repeat_interleave(arange_b, n_last, output_size=total_seq)
-        seq_rows = cu[last][owner] + (torch.arange(total_seq, device=dev) - offsets(n_last)[owner])
+        owner = torch.repeat_interleave(torch.arange(batch, device=dev), n_last, output_size=total_seq)
+        first_seq = torch.zeros(batch + 1, dtype=torch.long, device=dev)
+        first_seq[1:] = torch.cumsum(n_last, dim=0)
+        seq_rows = cu[last][owner] + (torch.arange(total_seq, device=dev) - first_seq[owner])
         # rows of a sample are consecutive: a segmented sum in row order (no floating-point atomics, so the scores
         # of a batch do not depend on which GPU or which run computed them)
         seq_sum = torch.segment_reduce(tokens[seq_rows], "sum", lengths=n_last, axis=0, unsafe=True)
@@ -856,7 +912,7 @@ class OneTransInference:
         ns_summary = tokens[ns_rows.reshape(-1)].view(batch, ns, d).mean(dim=1)
         return self._classify(seq_summary, ns_summary)
 
-    def _ns_only_blocks(self, tokens: torch.Tensor, first_layer: int, batch: int) -> torch.Tensor:
+    def _ns_only_blocks(self, tokens: torch.Tensor, first_layer: int, batch: int, token_major: bool = False) -> torch.Tensor:
         """Blocks ``first_layer`` .. end for a batch whose samples hold nothing but their NS tokens, then the final
         norm and the NS mean -> [B, d] fp32.
 
@@ -865,7 +921,7 @@ class OneTransInference:
         its ``ns`` tokens.  The block then is six batched or shared matrix products on a token-major
         ``[ns, B, d]`` tensor with no gathers, scatters or shared-weight work that would be overwritten."""
         ns, d, heads, hd = self.num_ns, self.d, self.heads, self.head_dim
-        tok = tokens.view(batch, ns, d).transpose(0, 1).contiguous()            # [ns, B, d]
+        tok = tokens if token_major else tokens.view(batch, ns, d).transpose(0, 1).contiguous()            # [ns, B, d]
         flat = tok.view(ns * batch, d)
         for blk in self.blocks[first_layer:]:
             p = blk["p"]
@@ -894,17 +950,18 @@ class OneTransInference:
                 h = ops.bias_act_rows(torch.bmm(x.view(ns, batch, d), blk["ns_w1"]), blk["ns_b1"], silu=True)
                 tok = ops.bias_act_rows(torch.baddbmm(tok, h, blk["ns_w2"]), blk["ns_b2_folded"], silu=False)
             flat = tok.view(ns * batch, d)
-        final = ops.rms_norm(flat, self._p("final_norm.weight"), 1e-6).float()
-        return final.view(ns, batch, d).mean(dim=0)
+        final = ops.rms_norm(flat, self._p("final_norm.weight"), 1e-6)
+        return final.view(ns, batch, d).mean(dim=0, dtype=torch.float32)     # widened inside the reduction, no fp32 copy
 
     @torch.inference_mode()
-    def scores(self, inputs, micro_batch: int | None = None) -> torch.Tensor:
+    def scores(self, inputs, micro_batch: int | None = None, prepared: dict | None = None) -> torch.Tensor:
         """Sigmoid conversion probabilities (fp32, on the device): [B] for one action, else [B, actions].
         ``micro_batch`` bounds the rows that go through the network at once (samples are independent,
-        so the result does not depend on it); it caps activation memory at large batches."""
+        so the result does not depend on it); it caps activation memory at large batches.  ``prepared``: the
+        result of ``prepare(inputs)`` for a batch that goes through in one piece."""
         batch = inputs.user.int_values.shape[0]
         if micro_batch is None or micro_batch >= batch:
-            logits, _ = self.predict(inputs)
+            logits, _ = self.predict(inputs, prepared)
         else:
             logits = torch.cat([self.predict(inputs.slice(lo, min(lo + micro_batch, batch)))[0]
                                 for lo in range(0, batch, micro_batch)])
@@ -912,7 +969,8 @@ class OneTransInference:
         return probs.reshape(-1) if probs.shape[1] == 1 else probs
 
 
-def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int | None = None, check_every: int = 0):
+def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int | None = None, check_every: int = 0,
+                 prepare_ahead: bool = True):
     """Scores for a stream of host-resident batches, one ``scores`` tensor (on the device) per batch.
 
     The serving loop of `evaluation/workflow.py:246-293` with the host-to-device copy taken off the critical
@@ -920,7 +978,10 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
     step costs max(copy, compute) instead of their sum.  ``host_batches`` should be pinned
     (``ModelInput.pin_memory()``) for the copies to be asynchronous.  A batch may also be a ``CompactModelInput``
     (``inputs.compact_model_input``): its sequences cross the link as 32-bit valid prefixes and are expanded to the
-    padded int64 record by one kernel on the device.
+    padded int64 record by one kernel on the device.  Duplicate removal, sequence statistics and the row plan of
+    batch i + 1 (``model.prepare``) also run on the side stream, and the few integers the host needs from them are
+    in pinned memory before the forward of batch i + 1 starts: the host never drains the device between batches
+    and can enqueue a whole batch ahead.
 
     The engine's status word (raised by a tcgen05 kernel whose bounded wait gave up) is read when the stream
     ends and, with ``check_every=n``, after every n-th batch; a raised word turns into a ``RuntimeError``
@@ -933,9 +994,20 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
         copier.wait_stream(compute)          # pinned source and allocator state are in a known order
         with torch.cuda.stream(copier):
             staged = batch.to(dev, non_blocking=True)
+            held = staged.tensors()
+            if hasattr(staged, "expand"):    # compact host format: rebuild the padded record on the device
+                staged = staged.expand()
+                held = held + staged.tensors()
+            # what the host must read before it can size the forward's buffers (row totals per layer) is computed
+            # here, under the previous batch's kernels, so that the forward itself never waits for the device
+            prepared = None
+            if prepare_ahead and (micro_batch is None or micro_batch >= staged.batch_size):
+                prepared = model.prepare(staged)
+                if prepared is not None:
+                    held = held + model.prepared_tensors(prepared)
             done = torch.cuda.Event()
             done.record(copier)
-        return staged, done
+        return staged, prepared, held, done
 
     it = iter(host_batches)
     first = next(it, None)
@@ -944,15 +1016,13 @@ def score_stream(model: "OneTransInference", host_batches, *, micro_batch: int |
     pending = stage(first)
     served = 0
     while pending is not None:
-        staged, done = pending
+        staged, prepared, held, done = pending
         nxt = next(it, None)
         compute.wait_event(done)
-        for t in staged.tensors():           # allocated on the copy stream, consumed on the compute stream
+        for t in held:                       # allocated on the copy stream, consumed on the compute stream
             t.record_stream(compute)
         pending = stage(nxt) if nxt is not None else None
-        if hasattr(staged, "expand"):        # compact host format: rebuild the padded record on the device
-            staged = staged.expand()
-        yield model.scores(staged, micro_batch=micro_batch)
+        yield model.scores(staged, micro_batch=micro_batch, prepared=prepared)
         served += 1
         if check_every > 0 and served % check_every == 0:
             model.raise_if_incomplete()

@@ -440,23 +440,46 @@ class FieldTables:
         self.lengths = torch.tensor(lengths, dtype=torch.int32, device=self.device)
 
 
-def fields_bag_mean(fields: FieldTables, int_feats: torch.Tensor) -> torch.Tensor:
-    """``[B, ids_cols]`` raw ids -> ``[B, n_fields, dim]`` pooled embeddings, ids clamped per field."""
+def fields_bag_mean(fields: FieldTables, int_feats: torch.Tensor, missing: torch.Tensor | None = None,
+                    missing_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``[B, ids_cols]`` raw ids -> ``[B, n_fields, dim]`` pooled embeddings, ids clamped per field.
+
+    With ``missing`` (bool ``[B, >= n_fields]``) and ``missing_rows`` (``[n_fields, dim]``) the tokenizer's
+    ``pooled + missing[..., None] * missing_rows`` (modeling/tokenizers.py:66-68) happens in the same kernel, with the
+    bits of the two tensor operations."""
     if int_feats.ndim != 2:
         raise ValueError("fields_bag_mean ids must be a 2D tensor")
     _require_backend("fields_bag_mean", "cuda")
-    _require_cuda_tensors("cuda fields_bag_mean", fields.tables[0], int_feats)
+    _require_cuda_tensors("cuda fields_bag_mean", fields.tables[0], int_feats, missing, missing_rows)
     if int_feats.dtype not in _ID_CODES:
         raise RuntimeError(f"cuda fields_bag_mean requires int32 or int64 values, got {int_feats.dtype}")
     ids = int_feats.contiguous()
     out = torch.empty((ids.shape[0], fields.n_fields, fields.dim), dtype=fields.dtype, device=fields.device)
+    lib = _lib.load()
+    if missing is not None and fields.max_bag > 0:
+        if missing_rows is None or missing.dtype != torch.bool or missing.ndim != 2 or missing.shape[0] != ids.shape[0] \
+                or missing.shape[1] < fields.n_fields:
+            raise ValueError("fields_bag_mean: missing must be bool [B, >= n_fields] and comes with missing_rows")
+        if missing_rows.dtype != fields.dtype or missing_rows.shape[0] < fields.n_fields or missing_rows.shape[1] != fields.dim:
+            raise ValueError("fields_bag_mean: missing_rows must be [n_fields, dim] of the tables' dtype")
+        flags, rows = missing.contiguous(), missing_rows[: fields.n_fields].contiguous()
+        with torch.cuda.device(fields.device), _timed("fields_bag_mean", ids=ids, dim=fields.dim, esize=out.element_size(), n_fields=fields.n_fields):
+            code = lib.tb200_fields_bag_mean_missing_fwd(
+                _ptr(fields.ptrs), _ptr(fields.rows), _ptr(fields.offsets), _ptr(fields.lengths), fields.n_fields,
+                fields.max_bag, fields.dim, _ptr(ids), _ID_CODES[ids.dtype], ids.shape[0], ids.shape[1], _ptr(flags),
+                flags.shape[1], _ptr(rows), _ptr(out), _DTYPE_CODES[fields.dtype], _stream_ptr(),
+            )
+        _lib.check(code, "cuda fields_bag_mean")
+        return out
     with torch.cuda.device(fields.device), _timed("fields_bag_mean", ids=ids, dim=fields.dim, esize=out.element_size(), n_fields=fields.n_fields):
-        code = _lib.load().tb200_fields_bag_mean_fwd(
+        code = lib.tb200_fields_bag_mean_fwd(
             _ptr(fields.ptrs), _ptr(fields.rows), _ptr(fields.offsets), _ptr(fields.lengths), fields.n_fields,
             fields.max_bag, fields.dim, _ptr(ids), _ID_CODES[ids.dtype], ids.shape[0], ids.shape[1], _ptr(out),
             _DTYPE_CODES[fields.dtype], _stream_ptr(),
         )
     _lib.check(code, "cuda fields_bag_mean")
+    if missing is not None:
+        out = out + missing[:, : fields.n_fields].to(out.dtype).unsqueeze(-1) * missing_rows[: fields.n_fields].unsqueeze(0)
     return out
 
 
@@ -1225,6 +1248,55 @@ def sequence_prepare(values: torch.Tensor, lengths: torch.Tensor, timestamps: to
 
 
 
+def pyramid_plan(lengths: torch.Tensor, max_len: int, widths: Sequence[int], ns: int) -> dict[str, torch.Tensor]:
+    """Row plan of the packed valid-token layout for one forward, from the per-sample sequence lengths and the static
+    pyramid schedule ``widths`` (padded widths of layers 0 .. L), in one launch.  Returns int64 tensors ``start`` [B],
+    ``n0`` [B], ``counts`` [L + 1, B], ``cu`` [L + 1, B + 1], ``meta`` [L + 1, 2] (total rows, largest rows per
+    sample), ``ns_rows0`` [B, ns] and the int32 copy ``cu32`` of the offsets."""
+    _require_backend("pyramid_plan", "cuda")
+    _require_cuda_tensors("cuda pyramid_plan", lengths)
+    if lengths.ndim != 1 or lengths.dtype != torch.int64:
+        raise ValueError("pyramid_plan expects int64 lengths [B]")
+    lengths = lengths.contiguous()
+    batch, layers, dev = lengths.shape[0], len(widths) - 1, lengths.device
+    if layers < 0 or layers > 64:
+        raise ValueError("pyramid_plan serves 0..64 layers")
+    # one allocation for everything the kernel writes
+    sizes = [batch, batch, (layers + 1) * batch, (layers + 1) * (batch + 1), (layers + 1) * 2, batch * ns]
+    flat = torch.empty(sum(sizes), dtype=torch.int64, device=dev)
+    start, n0, counts, cu, meta, ns_rows0 = flat.split(sizes)
+    cu32 = torch.empty(layers + 1, batch + 1, dtype=torch.int32, device=dev)
+    w = (ctypes.c_int32 * (layers + 1))(*[int(v) for v in widths])
+    with torch.cuda.device(dev), _timed("pyramid_plan", batch=batch, layers=layers):
+        code = _lib.load().tb200_pyramid_plan(_ptr(lengths), batch, int(max_len), ctypes.cast(w, ctypes.c_void_p), layers, int(ns),
+                                              _ptr(start), _ptr(n0), _ptr(counts), _ptr(cu), _ptr(cu32), _ptr(meta),
+                                              _ptr(ns_rows0), _stream_ptr())
+    _lib.check(code, "cuda pyramid_plan")
+    return {"start": start, "n0": n0, "counts": counts.view(layers + 1, batch), "cu": cu.view(layers + 1, batch + 1),
+            "cu32": cu32, "meta": meta.view(layers + 1, 2), "ns_rows0": ns_rows0.view(batch, ns)}
+
+
+def pyramid_kept_rows(cu0: torch.Tensor, cu1: torch.Tensor, counts0: torch.Tensor, counts1: torch.Tensor, ns: int,
+                      total0: int, total1: int, *, want_row_dst: bool = False
+                      ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    """Rows of one layer that the pyramid keeps for the next (``src`` [total1] int64, in the next layer's order), the NS
+    rows of the next layer (``[B, ns]`` int64) and, on request, the int32 destination of every row of this layer
+    (-1 = dropped), from two consecutive rows of ``pyramid_plan``."""
+    _require_backend("pyramid_kept_rows", "cuda")
+    _require_cuda_tensors("cuda pyramid_kept_rows", cu0, cu1, counts0, counts1)
+    batch, dev = counts0.shape[0], cu0.device
+    # at least one element each: an empty tensor has no address to hand over
+    src = torch.empty(max(total1, 1), dtype=torch.int64, device=dev)
+    ns_rows = torch.empty(batch, max(ns, 1), dtype=torch.int64, device=dev)
+    row_dst = torch.empty(max(total0, 1), dtype=torch.int32, device=dev) if want_row_dst else None
+    with torch.cuda.device(dev), _timed("pyramid_kept_rows", batch=batch):
+        code = _lib.load().tb200_pyramid_kept_rows(_ptr(cu0.contiguous()), _ptr(cu1.contiguous()), _ptr(counts0.contiguous()),
+                                                   _ptr(counts1.contiguous()), batch, int(ns), _ptr(src), _ptr(ns_rows),
+                                                   _ptr(row_dst), _stream_ptr())
+    _lib.check(code, "cuda pyramid_kept_rows")
+    return src[:total1], ns_rows[:, :ns], None if row_dst is None else row_dst[:total0]
+
+
 def compact_sequence_host(values: torch.Tensor, lengths: torch.Tensor, timestamps: torch.Tensor | None,
                           request_ts: torch.Tensor | None, *, threads: int = 4, pin: bool = False
                           ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
@@ -1634,6 +1706,8 @@ __all__ = [
     "embedding_bag_mean",
     "embedding_bag_mean_backward",
     "compact_sequence_host",
+    "pyramid_plan",
+    "pyramid_kept_rows",
     "compact_sequence_from_lists",
     "expand_sequence",
     "fields_bag_mean",
