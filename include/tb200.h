@@ -206,6 +206,15 @@ int tb200_host_compact_from_lists(const void* const* id_offsets, const int64_t* 
                                   int32_t batch, int32_t max_len, int32_t* cu, int32_t* ids, int64_t ids_stride,
                                   int32_t* gaps, int32_t threads);
 
+/* The same with the converter's strict time filter (`_fill_strict_sequence`, batch_converter.py:540-592): a row keeps
+ * the positions of its timestamp list with 0 < ts < request_ts (the last max_len of them); id columns contribute their
+ * values at the kept positions below their own length, compacted to the front.  The timestamp column is required. */
+int tb200_host_compact_from_lists_strict(const void* const* id_offsets, const int64_t* const* id_values, int32_t feats,
+                                         const void* ts_offsets, const int64_t* ts_values, int32_t offsets_are_int64,
+                                         const int64_t* request_ts, const int64_t* vocab_sizes, int64_t* oob_counts,
+                                         int32_t batch, int32_t max_len, int32_t* cu, int32_t* ids, int64_t ids_stride,
+                                         int32_t* gaps, int32_t threads);
+
 /* Device: compact -> values [B, F, L] int64, lengths [B] int64, timestamps [B, L] int64 (NULL: not written).
  * max_len must be even; values / timestamps 16-byte aligned. */
 int tb200_expand_sequence(const int32_t* ids, const int32_t* gaps, const int32_t* cu, const int64_t* request_ts,

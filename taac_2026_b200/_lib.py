@@ -53,6 +53,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "tb200_host_compact_offsets": (_INT, [_P, _I32, _I32, _P]),
     "tb200_host_compact_sequence": (_INT, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _I64, _P, _I32]),
     "tb200_host_compact_from_lists": (_INT, [_P, _P, _I32, _P, _P, _I32, _P, _P, _P, _I32, _I32, _P, _P, _I64, _P, _I32]),
+    "tb200_host_compact_from_lists_strict": (_INT, [_P, _P, _I32, _P, _P, _I32, _P, _P, _P, _I32, _I32, _P, _P, _I64, _P, _I32]),
     "tb200_expand_sequence": (_INT, [_P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I64, _P]),
     "tb200_fields_bag_mean_fwd": (_INT, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _INT, _I64, _I32, _P, _INT, _P]),
     "tb200_fields_bag_mean_missing_fwd": (_INT, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _INT, _I64, _I32, _P, _I32, _P, _P, _INT, _P]),

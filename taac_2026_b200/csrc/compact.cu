@@ -252,3 +252,96 @@ extern "C" int tb200_host_compact_from_lists(const void* const* id_offsets, cons
         for (int f = 0; f < feats; ++f) oob_counts[f] = oob[f].load();
     return bad.load() ? TB200_ERR_RANGE : TB200_OK;
 }
+
+// The converter's strict time filter (`_fill_strict_sequence` / `_copy_strict_side_columns`, batch_converter.py:540-592):
+// a row keeps the positions p of its timestamp list with 0 < ts[p] < request_ts, the last max_len of them; its
+// length is their number and its timestamps are theirs.  An id column contributes values[start + p] for the kept
+// positions below its own length, written from slot 0 on (so a short id column is compacted to the front, as the
+// reference does), zeros behind; ids <= 0 -> 0 and the vocabulary rule as above.
+extern "C" int tb200_host_compact_from_lists_strict(const void* const* id_offsets, const int64_t* const* id_values, int32_t feats,
+                                                    const void* ts_offsets, const int64_t* ts_values, int32_t offsets_are_int64,
+                                                    const int64_t* request_ts, const int64_t* vocab_sizes, int64_t* oob_counts,
+                                                    int32_t batch, int32_t max_len, int32_t* cu, int32_t* ids,
+                                                    int64_t ids_stride, int32_t* gaps, int32_t threads) {
+    using namespace tb200;
+    if (batch < 0 || feats < 1 || max_len < 0 || feats > 256) return TB200_ERR_SHAPE;
+    if (cu == nullptr || id_offsets == nullptr || id_values == nullptr || ts_offsets == nullptr || ts_values == nullptr ||
+        request_ts == nullptr)
+        return TB200_ERR_NULL;
+    for (int f = 0; f < feats; ++f)
+        if (id_offsets[f] == nullptr || id_values[f] == nullptr) return TB200_ERR_NULL;
+    auto is_valid = [](int64_t t, int64_t now) { return t > 0 && t < now; };
+    // phase 1: lengths (in parallel, parked in cu[b + 1]), then the prefix sum
+    parallel_rows(batch, threads, [&](int64_t lo, int64_t hi) {
+        for (int64_t b = lo; b < hi; ++b) {
+            const int64_t start = offset_at(ts_offsets, offsets_are_int64, b);
+            const int64_t end = offset_at(ts_offsets, offsets_are_int64, b + 1);
+            int64_t n = 0;
+            for (int64_t p = start; p < end; ++p) n += is_valid(ts_values[p], request_ts[b]) ? 1 : 0;
+            cu[b + 1] = static_cast<int32_t>(std::min<int64_t>(n, max_len));
+        }
+    });
+    int64_t total = 0;
+    cu[0] = 0;
+    for (int32_t b = 0; b < batch; ++b) {
+        total += cu[b + 1];
+        if (total > INT32_MAX) return TB200_ERR_RANGE;
+        cu[b + 1] = static_cast<int32_t>(total);
+    }
+    if (oob_counts != nullptr) std::memset(oob_counts, 0, static_cast<size_t>(feats) * sizeof(int64_t));
+    if (batch == 0 || total == 0) return TB200_OK;
+    if (ids == nullptr) return TB200_ERR_NULL;
+    if (ids_stride < total) return TB200_ERR_SHAPE;
+    std::atomic<int> bad{0};
+    std::vector<std::atomic<int64_t>> oob(feats);
+    for (auto& c : oob) c.store(0);
+    parallel_rows(batch, threads, [&](int64_t lo, int64_t hi) {
+        bool ok = true;
+        int64_t oob_local[256] = {};
+        std::vector<int64_t> kept;           // kept positions of the row, relative to the start of its lists
+        for (int64_t b = lo; b < hi; ++b) {
+            const int64_t first = cu[b];
+            const int64_t len = cu[b + 1] - first;
+            if (len == 0) continue;
+            const int64_t start = offset_at(ts_offsets, offsets_are_int64, b);
+            const int64_t end = offset_at(ts_offsets, offsets_are_int64, b + 1);
+            const int64_t now = request_ts[b];
+            kept.clear();
+            for (int64_t p = start; p < end; ++p)
+                if (is_valid(ts_values[p], now)) kept.push_back(p - start);
+            const int64_t skip = static_cast<int64_t>(kept.size()) - len;      // only the last `len` positions stay
+            for (int64_t j = 0; j < len; ++j) {
+                const int64_t gap = now - ts_values[start + kept[skip + j]];
+                ok &= fits32(gap);
+                if (gaps != nullptr) gaps[first + j] = static_cast<int32_t>(gap);
+            }
+            for (int f = 0; f < feats; ++f) {
+                const int64_t f_start = offset_at(id_offsets[f], offsets_are_int64, b);
+                const int64_t side_len = offset_at(id_offsets[f], offsets_are_int64, b + 1) - f_start;
+                int32_t* dst = ids + f * ids_stride + first;
+                const bool clip = vocab_sizes != nullptr;
+                const int64_t vocab = clip ? vocab_sizes[f] : 0;
+                int64_t n = 0;
+                for (int64_t j = 0; j < len; ++j) {
+                    const int64_t p = kept[skip + j];
+                    if (p >= side_len) break;                                   // positions are increasing
+                    int64_t v = id_values[f][f_start + p];
+                    v = v > 0 ? v : 0;
+                    if (clip && v >= vocab) {
+                        oob_local[f] += vocab > 0 ? 1 : 0;
+                        v = 0;
+                    }
+                    ok &= v <= INT32_MAX;
+                    dst[n++] = static_cast<int32_t>(v);
+                }
+                if (n < len) std::memset(dst + n, 0, static_cast<size_t>(len - n) * sizeof(int32_t));
+            }
+        }
+        for (int f = 0; f < feats; ++f)
+            if (oob_local[f] != 0) oob[f].fetch_add(oob_local[f], std::memory_order_relaxed);
+        if (!ok) bad.store(1, std::memory_order_relaxed);
+    });
+    if (oob_counts != nullptr)
+        for (int f = 0; f < feats; ++f) oob_counts[f] = oob[f].load();
+    return bad.load() ? TB200_ERR_RANGE : TB200_OK;
+}

@@ -1332,14 +1332,16 @@ def compact_sequence_host(values: torch.Tensor, lengths: torch.Tensor, timestamp
 
 def compact_sequence_from_lists(id_columns: Sequence[tuple[Any, Any]], timestamp_column: tuple[Any, Any] | None,
                                 request_ts: Any, max_len: int, *, vocab_sizes: Sequence[int] | None = None,
-                                threads: int = 4, pin: bool = False):
+                                strict_time_filter: bool = False, threads: int = 4, pin: bool = False):
     """Arrow list columns -> the compact host format, without the padded intermediate of the reference's converter.
 
     ``id_columns``: one ``(offsets, values)`` pair of numpy arrays per side column (offsets int32 or int64 of length
     rows + 1, values int64), ``timestamp_column`` the same pair or None — what ``column.offsets.to_numpy()`` /
     ``column.values.to_numpy()`` give in `PCVRRecordBatchConverter._sequence_side_arrays` (batch_converter.py:490-500).
     Returns ``(cu, ids, gaps, oob_counts)`` as torch tensors; ``oob_counts[f]`` is the number of ids of column f that
-    were at or beyond ``vocab_sizes[f]`` and became 0 (the clip_vocab=True rule, batch_converter.py:594-650)."""
+    were at or beyond ``vocab_sizes[f]`` and became 0 (the clip_vocab=True rule, batch_converter.py:594-650).
+    ``strict_time_filter=True`` (needs the timestamp column) keeps only events with ``0 < ts < request_ts``, the last
+    ``max_len`` of them (`_fill_strict_sequence`, batch_converter.py:540-592)."""
     import numpy as np
 
     feats = len(id_columns)
@@ -1372,7 +1374,13 @@ def compact_sequence_from_lists(id_columns: Sequence[tuple[Any, Any]], timestamp
     cu = torch.empty(rows + 1, dtype=torch.int32, pin_memory=pin)
     ids = torch.empty(feats, cap, dtype=torch.int32, pin_memory=pin)
     gaps = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
-    code = _lib.load().tb200_host_compact_from_lists(
+    strict = bool(strict_time_filter) and ts is not None
+    if strict:          # every timestamp event may be kept: size the buffers by that column
+        cap = max(int(np.minimum(np.maximum(np.diff(ts[0].astype(np.int64)), 0), max_len).sum()) if rows > 0 else 0, 1)
+        ids = torch.empty(feats, cap, dtype=torch.int32, pin_memory=pin)
+        gaps = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+    entry = _lib.load().tb200_host_compact_from_lists_strict if strict else _lib.load().tb200_host_compact_from_lists
+    code = entry(
         ctypes.cast(off_table, ctypes.c_void_p), ctypes.cast(val_table, ctypes.c_void_p), feats,
         ts[0].ctypes.data if ts is not None else None, ts[1].ctypes.data if ts is not None else None, 1 if wide else 0,
         now.ctypes.data, vocab.ctypes.data if vocab is not None else None, oob.ctypes.data, rows, int(max_len), _ptr(cu),

@@ -97,3 +97,34 @@ def test_time_features_survive_the_compact_format():
     want, _ = model.predict(batch.to("cuda"))
     got, _ = model.predict(expanded)
     assert torch.equal(got, want)
+
+
+def test_prediction_loop_returns_the_reference_loops_dictionary():
+    """`run_inference_prediction_loop` against plain `model.scores` per batch: same keys (str(user_id), row number
+    where a batch has no ids), same probabilities bit for bit, same counters as
+    `_run_inference_prediction_loop` (application/evaluation/workflow.py:246-293) reports."""
+    from types import SimpleNamespace
+
+    from taac_2026_b200.serving import run_inference_prediction_loop
+
+    spec = OneTransSpec(
+        user_int_specs=[(1000, i, 1) for i in range(8)], item_int_specs=[(1000, i, 1) for i in range(4)],
+        user_dense_dim=16, item_dense_dim=0, seq_vocab_sizes={"seq_a": [5000]}, d_model=128, emb_dim=64,
+        num_blocks=2, num_heads=4, hidden_mult=4, seq_top_k=96, user_ns_tokens=5, item_ns_tokens=2)
+    model = OneTransInference(random_state_dict(spec, seed=0), spec, dtype=torch.bfloat16)
+    batches = []
+    for i, rows in enumerate((64, 64, 40)):
+        inputs = synthetic_batch(spec, rows, seq_len=96, min_len=0, seed=20 + i)
+        ids = [f"u{i}_{r}" for r in range(rows)] if i != 1 else None
+        batches.append(SimpleNamespace(inputs=inputs, user_id=ids))
+    out = run_inference_prediction_loop(model, batches)
+    assert out["batch_count"] == 3 and out["processed_rows"] == 168 and out["loop_elapsed_sec"] > 0
+    want = {}
+    for batch in batches:
+        scores = model.scores(batch.inputs.to("cuda")).cpu().tolist()
+        keys = batch.user_id or list(range(len(scores)))
+        for key, value in zip(keys, scores):
+            want[str(key)] = float(value)
+    assert out["predictions"] == want
+    padded = run_inference_prediction_loop(model, batches, compact=False)
+    assert padded["predictions"] == want
