@@ -327,6 +327,18 @@ int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, int32_t
                    const int32_t* cu_rows_q, const uint8_t* key_valid, int32_t ns_start, int32_t causal, int32_t padded_query_self, float scale, int dtype,
                    int32_t kernel, int64_t total_rows, int32_t* status_word, void* stream);
 
+/* Attention backward for the padded (B, H, L, D) layout: dq, dk, dv from q, k, v, o and the upstream gradient d_o,
+ * under the same mask arguments as tb200_attn_fwd (no packed batches).  First, plain form of the reference's
+ * `flash_attention_backward` (accelerators/attention/kernels/tilelang.py:440-701; preprocess :395-437): fp32 arithmetic,
+ * scores recomputed, two kernels (per query row, per key row), no atomics.  strides: the 12 values of tb200_attn_fwd;
+ * d_o uses o's strides, dq / dk / dv those of q / k / v.  workspace: tb200_attn_bwd_workspace_bytes(B, H, Lq) bytes
+ * of device memory (log-sum-exp and dO.O per query row).  D <= 256, Lq, Lk <= 4096; fp32, fp16 or bf16. */
+int64_t tb200_attn_bwd_workspace_bytes(int32_t B, int32_t H, int32_t Lq);
+int tb200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, void* dq, void* dk,
+                   void* dv, void* workspace, int32_t B, int32_t H, int32_t Lq, int32_t Lk, int32_t D,
+                   const int64_t* strides, const int32_t* seq_len, const uint8_t* key_valid, int32_t ns_start,
+                   int32_t causal, int32_t padded_query_self, float scale, int dtype, void* stream);
+
 /* ---- (d) FP8 e4m3 block-scaled FFN ---------------------------------------------------------
  * The reference has no FP8 path: its FFNs are bf16/fp32 torch modules — the SiLU-gated
  * `down(silu(gate) * value)` of experiments/tokenformer/model.py:118-128 and

@@ -30,9 +30,9 @@ What is wrapped (paths relative to the reference root):
 
 ``install(route_all=True)`` additionally maps every backend the workflows configure
 (evaluation/workflow.py:120-125) to ``"cuda"``: an unmodified CLI run is switched over without touching its
-configuration.  Under autograd the norms stay on this library where its backward kernels take the shape
-(rows of whole 16-byte pieces, at most 1024 16-bit columns); other norm shapes and attention go back to the
-reference's own dispatcher (torch backend), because those kernels are forward-only.
+configuration.  Under autograd the norms and attention stay on this library where its backward kernels take the
+shape (norm rows of whole 16-byte pieces, at most 1024 16-bit columns; attention up to 4096 rows); other shapes go
+back to the reference's own dispatcher (torch backend).
 """
 
 from __future__ import annotations
@@ -107,7 +107,7 @@ def install(*, route_all: bool = False) -> None:
 
     def flash_attention(q, k, v, *, backend, **kwargs):
         if pick(backend) == "cuda":
-            if backend != "cuda" and wants_grad(q, k, v):
+            if backend != "cuda" and wants_grad(q, k, v) and not (q.is_cuda and ops.attention_backward_supported(q, k)):
                 return ref_fa(q, k, v, backend="torch", **kwargs)
             return ops.flash_attention(q, k, v, backend="cuda", **kwargs)
         return ref_fa(q, k, v, backend=backend, **kwargs)

@@ -703,9 +703,70 @@ def resolved_flash_attention_backend(
         raise RuntimeError(f"cuda flash_attention does not support dtype {q.dtype}")
     if q.shape[3] not in (32, 64, 128):
         raise RuntimeError(f"cuda flash_attention supports head_dim 32, 64 or 128, got {q.shape[3]}")
-    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        raise RuntimeError("cuda flash_attention is forward-only; use the torch backend for training")
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad) \
+            and not attention_backward_supported(q, k):
+        raise RuntimeError("cuda flash_attention has no backward kernel for this shape (more than 4096 rows); "
+                           "use the torch backend for training")
     return "cuda"
+
+
+def attention_backward_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
+    """The backward kernels take (B, H, L, D) tensors of at most 4096 rows and head_dim up to 256."""
+    return q.ndim == 4 and k.ndim == 4 and q.shape[2] <= 4096 and k.shape[2] <= 4096 and q.shape[3] <= 256 \
+        and q.shape[1] <= 65535
+
+
+def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, grad_out: torch.Tensor, *,
+                       seq_len: torch.Tensor | None = None, ns_start: int | None = None, causal: bool = False,
+                       padded_query_self: bool = False, key_valid: torch.Tensor | None = None,
+                       scale: float | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dq, dk, dv) of ``varlen_attention(q, k, v, ...)`` in the (B, H, L, D) layout for the upstream gradient
+    ``grad_out`` — the plain fp32-arithmetic form of the reference's flash-attention backward
+    (attention/kernels/tilelang.py:440-701): scores are recomputed, nothing is accumulated with atomics."""
+    _require_backend("attention_backward", "cuda")
+    _require_cuda_tensors("cuda attention_backward", q, k, v, out, grad_out, seq_len, key_valid)
+    if q.dtype not in _DTYPE_CODES or not (q.dtype == k.dtype == v.dtype):
+        raise RuntimeError("cuda attention_backward needs q, k, v of one dtype among fp32, fp16, bf16")
+    if not attention_backward_supported(q, k):
+        raise RuntimeError("cuda attention_backward serves (B, H, L, D) tensors with L <= 4096 and D <= 256")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    out, grad_out = out.to(q.dtype).contiguous(), grad_out.to(q.dtype).contiguous()
+    batch, heads, lq, dim = q.shape
+    lk = k.shape[2]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    lib = _lib.load()
+    work = torch.empty(max(int(lib.tb200_attn_bwd_workspace_bytes(batch, heads, lq)) // 4, 1), dtype=torch.float32, device=q.device)
+    strides = (ctypes.c_int64 * 12)(*[int(s) for t in (q, k, v, out) for s in (t.stride(0), t.stride(1), t.stride(2))])
+    lens = None if seq_len is None else seq_len.to(torch.int32).contiguous()
+    valid = None if key_valid is None else key_valid.to(torch.uint8).contiguous()
+    with torch.cuda.device(q.device), _timed("attention_bwd", batch=batch, heads=heads, lq=lq, lk=lk, dim=dim):
+        code = lib.tb200_attn_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(grad_out), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(work),
+                                  batch, heads, lq, lk, dim, ctypes.cast(strides, ctypes.c_void_p), _ptr(lens), _ptr(valid),
+                                  lk if ns_start is None else int(ns_start), int(bool(causal)), int(bool(padded_query_self)),
+                                  float(dim ** -0.5 if scale is None else scale), _DTYPE_CODES[q.dtype], _stream_ptr())
+    _lib.check(code, "cuda attention_backward")
+    return dq, dk, dv
+
+
+class _FlashAttentionFunction(torch.autograd.Function):
+    """Differentiable ``flash_attention``: forward on the serving kernels, backward on ``attention_backward``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, seq_len, ns_start, causal, padded_query_self):
+        with torch.no_grad():
+            out = varlen_attention(q, k, v, seq_len=seq_len, ns_start=ns_start, causal=causal,
+                                   padded_query_self=padded_query_self, layout="bhld")
+        ctx.save_for_backward(q, k, v, out, seq_len)
+        ctx.mask = (ns_start, causal, padded_query_self)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, seq_len = ctx.saved_tensors
+        ns_start, causal, padded_query_self = ctx.mask
+        dq, dk, dv = attention_backward(q, k, v, out, grad_out, seq_len=seq_len, ns_start=ns_start, causal=causal,
+                                        padded_query_self=padded_query_self)
+        return dq, dk, dv, None, None, None, None
 
 
 def _attn_strides(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
@@ -871,7 +932,8 @@ def flash_attention(
     num_stages: int = 1,
     threads: int = 128,
 ) -> torch.Tensor:
-    """`flash_attention(..., backend="cuda")`: (B, H, L, D) in, (B, H, L, D) out, inference only.
+    """`flash_attention(..., backend="cuda")`: (B, H, L, D) in, (B, H, L, D) out; differentiable for up to 4096 rows
+    (forward on the serving kernels, backward on ``attention_backward``).
 
     fp32 callers are computed in bf16 and cast back, the policy of the reference's accelerated
     backend (accelerators/attention/flash_attention.py:249-252).  The tile-shape arguments are
@@ -884,7 +946,10 @@ def flash_attention(
     plan = plan_attention_mask(q, k, attn_mask, is_causal=is_causal)
     output_dtype = q.dtype
     if output_dtype == torch.float32:
-        q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)     # differentiable casts
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        out = _FlashAttentionFunction.apply(q, k, v, plan.seq_len, plan.ns_start, plan.causal, plan.padded_query_self)
+        return out if out.dtype == output_dtype else out.to(output_dtype)
     out = varlen_attention(
         q, k, v, seq_len=plan.seq_len, ns_start=plan.ns_start, causal=plan.causal,
         padded_query_self=plan.padded_query_self, layout="bhld",
@@ -1714,6 +1779,8 @@ __all__ = [
     "cuda_supported_floating_dtype",
     "embedding_bag_mean",
     "embedding_bag_mean_backward",
+    "attention_backward",
+    "attention_backward_supported",
     "compact_sequence_host",
     "pyramid_plan",
     "pyramid_kept_rows",
