@@ -364,6 +364,26 @@ int tb200_fp8_gemm(const void* a_fp8, const float* a_scales, const void* b_fp8, 
                    const float* bias, const void* residual, void* out, float* out_scales, int64_t M, int32_t N,
                    int32_t K, int32_t mode, int32_t* status_word, void* stream);
 
+/* ---- FP8 FFN with power-of-two (UE8M0) block scales applied by the tensor cores --------------------------------
+ * Same block structure as above (1 x 128 activation blocks, 128 x 128 weight blocks, scales derived from the block's
+ * amax), but the scale is rounded up to a power of two and multiplied in by `tcgen05.mma.kind::mxf8f6f4.block_scale`,
+ * so a tile accumulates over the whole K in tensor memory and the epilogue runs once per tile.  No counterpart in the
+ * reference (it has no FP8 path); serves the FFN modules of experiments/onetrans/model.py:33-44 and
+ * experiments/tokenformer/model.py:118-128.
+ * Scale factors are stored as 512-byte atoms per (128 rows, 128-wide K block): byte (r % 32) * 16 + (r / 32) * 4 + s is
+ * the exponent byte (value 2^(byte - 127)) of row r, 32-wide slice s.  Activations: [ceil(M / 128), K / 128, 512];
+ * weights: [N / 128, K / 128, 512]; tb200_mx_scale_bytes(rows, K) gives the size.  Atom arrays should be zeroed
+ * before first use when M is not a multiple of 128 (rows beyond M are never written). */
+int64_t tb200_mx_scale_bytes(int64_t rows, int32_t K);
+/* bf16 [M, K] -> e4m3 [M, K] + activation scale atoms. */
+int tb200_quant_act_mx(const void* x_bf16, void* x_fp8, uint8_t* scale_atoms, int64_t M, int32_t K, void* stream);
+/* out = epilogue(a @ b^T): mode 0 = SiLU-gated ([128 gate | 128 value] rows per 256-row weight tile) -> e4m3 hidden
+ * [M, N / 2] + its scale atoms; 1 = SiLU -> e4m3 hidden [M, N] + atoms; 2 = bias (+ residual) -> bf16 [M, N].
+ * N % 256 == 0, K % 128 == 0, K <= 8192; every pointer 16-byte aligned. */
+int tb200_mx_gemm(const void* a_fp8, const uint8_t* a_scale_atoms, const void* b_fp8, const uint8_t* b_scale_atoms,
+                  const float* bias, const void* residual, void* out, uint8_t* out_scale_atoms, int64_t M, int32_t N,
+                  int32_t K, int32_t mode, int32_t* status_word, void* stream);
+
 /* ---- integer sequence preprocessing ---------------------------------------------------------
  * Per sample of one sequence domain: which events survive duplicate removal, and the six sequence
  * statistics.  Replaces `deduplicate_sequence_events`

@@ -51,6 +51,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "tb200_attn_bwd_workspace_bytes": (_I64, [_I32, _I32, _I32]),
     "tb200_attn_bwd": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _I32, _I32, _I32,
                               _F, _INT, _P]),
+    "tb200_mx_scale_bytes": (_I64, [_I64, _I32]),
+    "tb200_quant_act_mx": (_INT, [_P, _P, _P, _I64, _I32, _P]),
+    "tb200_mx_gemm": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _P]),
     "tb200_pyramid_plan": (_INT, [_P, _I32, _I32, _P, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
     "tb200_pyramid_kept_rows": (_INT, [_P, _P, _P, _P, _I32, _I32, _P, _P, _P, _P]),
     "tb200_host_compact_offsets": (_INT, [_P, _I32, _I32, _P]),

@@ -251,6 +251,45 @@ __device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// Block-scaled e4m3 MMA (kind::mxf8f6f4): D[m, n] (+)= sum_k A[m, k] B[n, k] * SFA[m, k / 32] * SFB[n, k / 32] with UE8M0
+// (power-of-two) scale factors read from tensor memory; K = 32 per instruction.  sfa_tmem / sfb_tmem are the column
+// addresses of the scale-factor blocks; which byte of their 32-bit columns is used comes from the instruction
+// descriptor (umma_idesc_mx).
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// Shared memory -> tensor memory copy of one scale-factor atom: 32 rows x 16 bytes, written to 32 lanes x 4 columns
+// and repeated in all four lane quarters.  Ordered with the MMAs issued by the same thread.
+__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// Shared-memory matrix descriptor without swizzle (K-major "interleaved" core matrices of 8 rows x 16 bytes):
+// `sbo_bytes` is the distance between 8-row groups, `lbo_bytes` between core matrices along K.
+__device__ __forceinline__ uint64_t umma_desc_noswizzle(uint32_t smem_addr, uint32_t sbo_bytes, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+
+// Instruction descriptor of the block-scaled MMA: e4m3 x e4m3, both K-major, UE8M0 scale factors; sf_id picks the
+// byte of the scale-factor columns (the K / 32 sub-block inside a 128-wide K block).
+__host__ __device__ constexpr uint32_t umma_idesc_mx(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
+    return (b_sf_id << 4) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (a_sf_id << 29);
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle.  `sbo_bytes` is the distance
 // between consecutive groups of eight rows (K-major: eight M/N rows; MN-major: eight
 // K rows); `lbo_bytes` is only read for MN-major operands wider than one 128-byte

@@ -958,6 +958,158 @@ def flash_attention(
 
 
 # --------------------------------------------------------------------------------------------
+# FP8 FFN with power-of-two block scales multiplied in by the tensor cores (tcgen05 block-scaled MMA)
+# --------------------------------------------------------------------------------------------
+def mx_scale_exponents(amax: torch.Tensor) -> torch.Tensor:
+    """amax -> exponent e of the smallest power of two 2^e with amax / 2^e <= 448 (0 for an all-zero block)."""
+    ratio = amax.float() * (1.0 / 448.0)      # the same single-precision product as the kernels
+    mant, exp = torch.frexp(ratio)            # ratio = mant * 2^exp, mant in [0.5, 1)
+    e = torch.where(mant == 0.5, exp - 1, exp)
+    return torch.where(amax > 0, e.clamp(-126, 126), torch.zeros_like(e)).to(torch.int32)
+
+
+def mx_scale_atoms(exponents: torch.Tensor) -> torch.Tensor:
+    """[rows, k_blocks] exponents (one per row and 128-wide K block) -> scale atoms
+    uint8 [ceil(rows / 128), k_blocks, 512] in the layout the kernels copy into tensor memory: byte
+    (r % 32) * 16 + (r / 32) * 4 + s of an atom holds the biased exponent of row r, 32-wide slice s."""
+    rows, k_blocks = exponents.shape
+    tiles = (rows + 127) // 128
+    full = torch.zeros(tiles * 128, k_blocks, dtype=torch.uint8, device=exponents.device)
+    full[:rows] = (exponents + 127).to(torch.uint8)
+    atoms = full.view(tiles, 4, 32, k_blocks, 1).expand(-1, -1, -1, -1, 4)       # [tile, r / 32, r % 32, kb, slice]
+    return atoms.permute(0, 3, 2, 1, 4).reshape(tiles, k_blocks, 512).contiguous()
+
+
+def mx_atoms_to_scales(atoms: torch.Tensor, rows: int) -> torch.Tensor:
+    """Scale atoms -> fp32 scales [rows, k_blocks] (slice 0 of every row; for checking)."""
+    tiles, k_blocks, _ = atoms.shape
+    grid = atoms.view(tiles, k_blocks, 32, 4, 4)[..., 0]                           # [tile, kb, r % 32, r / 32]
+    exps = grid.permute(0, 3, 2, 1).reshape(tiles * 128, k_blocks)[:rows].to(torch.int32) - 127
+    return torch.ldexp(torch.ones_like(exps, dtype=torch.float32), exps)
+
+
+def quantize_activation_mx(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [M, K] -> (e4m3 [M, K], scale atoms uint8 [ceil(M / 128), K / 128, 512]); the scale of a 1 x 128 block is
+    the smallest power of two that brings its amax to at most 448."""
+    _require_backend("quantize_activation_mx", "cuda")
+    _require_cuda_tensors("cuda quantize_activation_mx", x)
+    if x.dtype != torch.bfloat16 or x.ndim != 2:
+        raise RuntimeError("cuda quantize_activation_mx needs a bf16 matrix")
+    if x.shape[1] % 128:
+        raise ValueError("quantize_activation_mx needs K to be a multiple of 128")
+    matrix = x.contiguous()
+    rows, k = matrix.shape
+    q = torch.empty(matrix.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    atoms = torch.zeros((rows + 127) // 128, k // 128, 512, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device), _timed("quant_act", rows=rows, cols=k):
+        code = _lib.load().tb200_quant_act_mx(_ptr(matrix), _ptr(q), _ptr(atoms), rows, k, _stream_ptr())
+    _lib.check(code, "cuda quantize_activation_mx")
+    return q, atoms
+
+
+def quantize_weight_mx(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """[N, K] weight -> (e4m3 [N, K], scale atoms uint8 [N / 128, K / 128, 512]); one power-of-two scale per
+    128 x 128 block, repeated for the block's rows and slices.  Done once at model load with tensor ops."""
+    n, k = weight.shape
+    if n % 128 or k % 128:
+        raise ValueError("quantize_weight_mx needs both dimensions to be multiples of 128")
+    blocks = weight.float().view(n // 128, 128, k // 128, 128)
+    exps = mx_scale_exponents(blocks.abs().amax(dim=(1, 3)))                       # [N / 128, K / 128]
+    scale = torch.ldexp(torch.ones_like(exps, dtype=torch.float32), exps)
+    q = (blocks / scale[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).reshape(n, k).to(torch.float8_e4m3fn)
+    atoms = (exps + 127).to(torch.uint8)[:, :, None].expand(-1, -1, 512).contiguous()
+    return q.contiguous(), atoms
+
+
+def mx_gemm(a: torch.Tensor, a_atoms: torch.Tensor, b: torch.Tensor, b_atoms: torch.Tensor, *, mode: str,
+            bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, check: bool = False,
+            status: torch.Tensor | None = None):
+    """Block-scaled e4m3 GEMM ``a @ b^T`` on the block-scaled tensor-core instruction (see ``tb200_mx_gemm``):
+    ``mode="swiglu"`` / ``"silu"`` return (e4m3 hidden, its scale atoms), ``"linear"`` returns bf16."""
+    modes = {"swiglu": 0, "silu": 1, "linear": 2}
+    if mode not in modes:
+        raise ValueError(f"unknown mx_gemm mode {mode}")
+    _require_backend("mx_gemm", "cuda")
+    _require_cuda_tensors("cuda mx_gemm", a, a_atoms, b, b_atoms, bias, residual)
+    if a.dtype != torch.float8_e4m3fn or b.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("cuda mx_gemm needs float8_e4m3fn operands")
+    if a.ndim != 2 or b.ndim != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError("mx_gemm expects a [M, K] and b [N, K]")
+    m, k = a.shape
+    n = b.shape[0]
+    if n % 256 or k % 128:
+        raise ValueError("mx_gemm needs N % 256 == 0 and K % 128 == 0")
+    if tuple(a_atoms.shape) != ((m + 127) // 128, k // 128, 512) or tuple(b_atoms.shape) != (n // 128, k // 128, 512) \
+            or a_atoms.dtype != torch.uint8 or b_atoms.dtype != torch.uint8:
+        raise ValueError("mx_gemm scale atoms must be uint8 [ceil(M / 128), K / 128, 512] and [N / 128, K / 128, 512]")
+    a, b, a_atoms, b_atoms = a.contiguous(), b.contiguous(), a_atoms.contiguous(), b_atoms.contiguous()
+    bias_f = None if bias is None else bias.float().contiguous()
+    dev = a.device
+    status = _status_word(check, status, dev)
+    out_atoms = None
+    res = None
+    if mode == "linear":
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        res = None if residual is None else residual.to(torch.bfloat16).contiguous()
+        if res is not None and tuple(res.shape) != (m, n):
+            raise ValueError("mx_gemm residual must be [M, N]")
+    else:
+        if residual is not None:
+            raise ValueError("mx_gemm residual is only supported in linear mode")
+        hidden = n // 2 if mode == "swiglu" else n
+        out = torch.empty((m, hidden), dtype=torch.float8_e4m3fn, device=dev)
+        out_atoms = torch.zeros((m + 127) // 128, hidden // 128, 512, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev), _timed("mx_gemm_" + mode, m=m, n=n, k=k):
+        code = _lib.load().tb200_mx_gemm(_ptr(a), _ptr(a_atoms), _ptr(b), _ptr(b_atoms), _ptr(bias_f), _ptr(res), _ptr(out),
+                                         _ptr(out_atoms), m, n, k, modes[mode], _ptr(status), _stream_ptr())
+    _lib.check(code, "cuda mx_gemm")
+    if check and int(status.item()) != 0:
+        raise RuntimeError("cuda mx_gemm: a bounded wait inside the kernel gave up; the output is incomplete")
+    return out if mode == "linear" else (out, out_atoms)
+
+
+class MxFfnWeights:
+    """e4m3 weights of one FFN with power-of-two 128 x 128 block scales, prepared once (row order as in
+    ``Fp8FfnWeights``: gated layers interleave [128 gate rows | 128 value rows] per hidden block)."""
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, *, gated: bool, gate_first: bool = True,
+                 b_up: torch.Tensor | None = None, b_down: torch.Tensor | None = None) -> None:
+        self.gated = gated
+        hidden = w_up.shape[0] // 2 if gated else w_up.shape[0]
+        if w_down.shape[1] != hidden:
+            raise ValueError("MxFfnWeights: w_down must be [d_out, hidden]")
+        if gated:
+            if hidden % 128:
+                raise ValueError("MxFfnWeights: hidden must be a multiple of 128")
+            gate, value = (w_up[:hidden], w_up[hidden:]) if gate_first else (w_up[hidden:], w_up[:hidden])
+            w_up = torch.stack([gate.view(hidden // 128, 128, -1), value.view(hidden // 128, 128, -1)], dim=1).reshape(2 * hidden, -1)
+            if b_up is not None:
+                bg, bv = (b_up[:hidden], b_up[hidden:]) if gate_first else (b_up[hidden:], b_up[:hidden])
+                b_up = torch.stack([bg.view(-1, 128), bv.view(-1, 128)], dim=1).reshape(-1)
+        self.hidden = hidden
+        self.w_up, self.a_up = quantize_weight_mx(w_up)
+        self.w_down, self.a_down = quantize_weight_mx(w_down)
+        self.b_up = None if b_up is None else b_up.float().contiguous()
+        self.b_down = None if b_down is None else b_down.float().contiguous()
+
+
+def ffn_mx(x: torch.Tensor, weights: MxFfnWeights, *, residual: torch.Tensor | None = None, check: bool = False,
+           status: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 [..., d] -> bf16 [..., d_out] like ``ffn_fp8``, with power-of-two block scales applied inside the
+    block-scaled tensor-core instruction: quantise, GEMM 1 with fused (gated) SiLU and re-quantisation, GEMM 2 with
+    fused bias / residual."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    xq, xa = quantize_activation_mx(x2)
+    h, ha = mx_gemm(xq, xa, weights.w_up, weights.a_up, mode="swiglu" if weights.gated else "silu", bias=weights.b_up,
+                    check=check, status=status)
+    res = None if residual is None else residual.reshape(-1, weights.w_down.shape[0])
+    y = mx_gemm(h, ha, weights.w_down, weights.a_down, mode="linear", bias=weights.b_down, residual=res, check=check,
+                status=status)
+    return y.view(*shape[:-1], weights.w_down.shape[0])
+
+
+# --------------------------------------------------------------------------------------------
 # "compiled kernel" handles and cache clearing, as the reference's benchmark CLI expects them
 # --------------------------------------------------------------------------------------------
 # The reference JIT-compiles its TileLang / Triton kernels per shape and hands out callables
@@ -1780,6 +1932,11 @@ __all__ = [
     "embedding_bag_mean",
     "embedding_bag_mean_backward",
     "attention_backward",
+    "MxFfnWeights",
+    "ffn_mx",
+    "mx_gemm",
+    "quantize_activation_mx",
+    "quantize_weight_mx",
     "attention_backward_supported",
     "compact_sequence_host",
     "pyramid_plan",
