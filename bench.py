@@ -237,7 +237,7 @@ def launch_work(name: str, meta: dict) -> tuple[str, float]:
         return "hbm", 2.0 * meta["rows"] * meta["cols"] * meta["esize"] + extra
     if name in ("gemm_bf16", "cublas_linear"):
         return "tensor", 2.0 * meta.get("groups", 1) * meta["m"] * meta["n"] * meta["k"]
-    if name.startswith("fp8_gemm"):
+    if name.startswith("fp8_gemm") or name.startswith("mx_gemm"):
         return "tensor_fp8", 2.0 * meta["m"] * meta["n"] * meta["k"]
     if name == "quant_act":
         return "hbm", meta["rows"] * meta["cols"] * 3.0 + meta["rows"] * (meta["cols"] // 128) * 4.0
@@ -536,6 +536,7 @@ def run_parity_stages(args) -> None:
     stages = [("this engine: fp32 dense layers and attention", torch.float32, "bf16"),
               ("this engine: bf16, bf16 FFN", torch.bfloat16, "bf16"),
               ("this engine: bf16, FP8 FFN with GEMM 1 in bf16", torch.bfloat16, "fp8_precise"),
+              ("this engine: bf16, FP8 FFN with power-of-two scales inside the block-scaled MMA", torch.bfloat16, "fp8_mx"),
               ("this engine: bf16, FP8 FFN (benchmarked precision)", torch.bfloat16, "fp8")]
     for name, dtype, ffn in stages:
         weights = sd if dtype == torch.bfloat16 else {k: v.float() for k, v in sd.items()}
@@ -1115,7 +1116,7 @@ def measure_fp8_peak() -> float | None:
 
 
 def ffn_lines(peaks: dict, peak_kind: str, *, rows: int, steps: int, fp8_peak: float | None,
-              modes=(("gated", False), ("gated", True), ("plain", False))) -> list[dict]:
+              modes=(("gated", False), ("gated", "mx"), ("gated", True), ("plain", False), ("plain", "mx"))) -> list[dict]:
     """`rows` tokens, 512 -> 2 x 2048 (gate, up) -> 512, e4m3 with 1x128 / 128x128 amax scales.  One line per
     (layer kind, precise) pair: the all-e4m3 FFN, and the mode whose up projection runs in bf16 (the one that meets
     5e-2 against the bf16 FFN).  Every line carries its relative error against the bf16 torch FFN on the same data."""
@@ -1131,6 +1132,7 @@ def ffn_lines(peaks: dict, peak_kind: str, *, rows: int, steps: int, fp8_peak: f
     cache: dict[str, tuple] = {}
     for kind, precise in modes:
         gated = kind == "gated"
+        mx = precise == "mx"       # power-of-two scales applied by the block-scaled tensor-core instruction
         if kind not in cache:
             w_up = (torch.randn((2 if gated else 1) * hidden, d, generator=g, device="cuda") * 0.02).bfloat16()
             w_down = (torch.randn(d, hidden, generator=g, device="cuda") * 0.02).bfloat16()
@@ -1138,9 +1140,13 @@ def ffn_lines(peaks: dict, peak_kind: str, *, rows: int, steps: int, fp8_peak: f
             h = torch.nn.functional.silu(h[:, :hidden]) * h[:, hidden:] if gated else torch.nn.functional.silu(h)
             ref = torch.nn.functional.linear(h, w_down).float()
             del h
-            cache[kind] = (ops.Fp8FfnWeights(w_up, w_down, gated=gated, precise=True), ref)
-        weights, ref = cache[kind]
-        run = lambda: ops.ffn_fp8(x, weights, precise=precise)   # noqa: E731
+            cache[kind] = (ops.Fp8FfnWeights(w_up, w_down, gated=gated, precise=True), ref,
+                           ops.MxFfnWeights(w_up, w_down, gated=gated))
+        weights, ref, weights_mx = cache[kind]
+        if mx:
+            run = lambda: ops.ffn_mx(x, weights_mx)   # noqa: E731
+        else:
+            run = lambda: ops.ffn_fp8(x, weights, precise=precise)   # noqa: E731
         for _ in range(3):
             got = run()
         torch.cuda.synchronize()
@@ -1171,7 +1177,8 @@ def ffn_lines(peaks: dict, peak_kind: str, *, rows: int, steps: int, fp8_peak: f
             "metric": "ffn_fp8_TFLOPs", "value": round(tf, 1), "unit": "TFLOP/s",
             "config": {"workload": f"{m} tokens, {d} -> {'2x' if gated else ''}{hidden} -> {d}, e4m3 1x128 / 128x128 scales, "
                                    f"{'SiLU-gated' if gated else 'SiLU'}",
-                       "mode": "up projection in bf16, down projection e4m3" if precise else "both projections e4m3"},
+                       "mode": ("both projections e4m3, power-of-two scales inside the block-scaled MMA" if mx else
+                                "up projection in bf16, down projection e4m3" if precise else "both projections e4m3")},
             "ms_per_step": round(ms, 3), "kernel_ms": {k: round(v, 3) for k, v in per.items()},
             "rel_l2_error_vs_bf16_ffn": round(rel_l2, 5), "max_rel_error_where_ref_above_1e-2": round(max_rel, 3),
             "roofline": {"bound": "tensor", "achieved": round(tf_gemm, 1), "peak": round(fp8_peak, 1) if fp8_peak else nominal,
@@ -1186,7 +1193,7 @@ def run_ffn_sweep(args) -> None:
     """262 144 tokens, 512 -> 2 x 2048 (gate, up) -> 512, e4m3 with 1x128 / 128x128 amax scales."""
     peaks, peak_kind = load_peaks()
     for line in ffn_lines(peaks, peak_kind, rows=args.rows or 262144, steps=args.steps, fp8_peak=None,
-                          modes=(("gated", False), ("gated", True), ("plain", False), ("plain", True))):
+                          modes=(("gated", False), ("gated", "mx"), ("gated", True), ("plain", False), ("plain", "mx"), ("plain", True))):
         print(json.dumps(line), flush=True)
 
 
@@ -1250,7 +1257,7 @@ def main() -> None:
     parser.add_argument("--launch-log", default="", help="write every recorded launch of the timing pass (name, ms, shape) to this file")
     parser.add_argument("--profile", action="store_true",
                         help="run --warmup untimed and --steps plain steps of the main workload and exit (for ncu)")
-    parser.add_argument("--ffn", choices=["fp8", "fp8_precise", "bf16"], default="fp8", help="shared FFN of every block")
+    parser.add_argument("--ffn", choices=["fp8", "fp8_mx", "fp8_precise", "bf16"], default="fp8", help="shared FFN of every block")
     parser.add_argument("--host-format", choices=["compact32", "padded64"], default="compact32",
                         help="what the end-to-end arm copies per step: the compact 32-bit sequence record "
                              "(inputs.compact_model_input, expanded on the device) or the reference's padded int64 record")

@@ -22,7 +22,9 @@
 //                into TMEM (`tcgen05.cp`, alternating between two slots) and issues four 128 x 256 x 32 MMAs
 //   warps 2..17  epilogue: a thread owns one output row and 64 of the 256 columns; it drains its part of the
 //                accumulator into registers and releases the accumulator at once, so the MMAs of the next tile run
-//                under the epilogue's arithmetic and stores
+//                under the epilogue's arithmetic and stores.  The four warps of a TMEM lane quarter work as a group
+//                with their own named barrier, staging rows and TMA stores: nothing inside a tile waits for all
+//                sixteen warps
 // Every wait on an mbarrier is bounded; a wait that gives up raises the status word and all roles drain out through
 // the same final barrier, where the TMEM allocation is released.
 #include <cuda_fp8.h>
@@ -48,7 +50,8 @@ constexpr uint32_t kSfaBytes = kSfAtom;      // A: 128 rows
 constexpr uint32_t kSfbBytes = 2 * kSfAtom;  // B: 256 rows
 constexpr uint32_t kTmemCols = 512;          // accumulator 256 + two scale-factor slots of 12 columns (allocation: power of two)
 constexpr uint32_t kTmemSf = 256;            // first scale-factor column
-constexpr uint32_t kSfSlotCols = 12;         // 4 columns for A, 8 for B
+constexpr uint32_t kSfSlotCols = 12;         // a per-K-block slot: 4 columns for A, 8 for B
+constexpr uint32_t kTmemSfbRes = kTmemSf + 2 * kSfSlotCols;   // resident weight scales (B_RES): 8 columns per K block
 
 enum Mode : int {
     kSwiGLU = 0,  // columns = [128 gate | 128 up] of one hidden block -> e4m3 hidden + scale atoms
@@ -149,7 +152,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __shared__ uint64_t full_bar[kMaxStages];
     __shared__ uint64_t empty_bar[kMaxStages];
     __shared__ uint64_t b_full;
-    __shared__ uint64_t res_full;
+    __shared__ uint64_t res_full[4];   // one per TMEM lane quarter: the residual rows of that quarter have landed
     __shared__ uint64_t tmem_full;
     __shared__ uint64_t tmem_empty;
     __shared__ uint32_t tmem_base_slot;
@@ -183,7 +186,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&b_full, 1);
-        mbar_init(&res_full, 1);
+        for (int q = 0; q < 4; ++q) mbar_init(&res_full[q], 1);
         mbar_init(&tmem_full, 1);
         mbar_init(&tmem_empty, kEpiThreads);
         s_abort = 0;
@@ -263,6 +266,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (B_RES) {
                     if (!mbar_wait(&b_full, b_phase)) { ok = false; break; }
                     b_phase ^= 1;
+                    tc_fence_after_sync();
+                    // the resident weight tile's scale factors go into tensor memory once per column tile
+                    // (ordered behind the MMAs of the previous column tile, which read the same columns)
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        const uint32_t src = sfbres_lo + static_cast<uint32_t>(kb) * (kSfbBytes >> 4);
+                        tc_cp_32x128b_warpx4(tmem_base + kTmemSfbRes + kb * 8, sf_desc0 + src);
+                        tc_cp_32x128b_warpx4(tmem_base + kTmemSfbRes + kb * 8 + 4, sf_desc0 + src + (kSfAtom >> 4));
+                    }
                 }
                 for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G, ++tile) {
                     // the epilogue has read the previous tile out of the accumulator
@@ -277,10 +288,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         const uint32_t sfb_lo = B_RES ? sfbres_lo + static_cast<uint32_t>(kb) * (kSfbBytes >> 4) : a_lo + (kSfbInStage >> 4);
                         // scale factors of this K block -> TMEM slot (it & 1): 4 columns for A, 8 for B
                         const uint32_t t_sfa = tmem_base + kTmemSf + (it & 1) * kSfSlotCols;
-                        const uint32_t t_sfb = t_sfa + 4;
+                        const uint32_t t_sfb = B_RES ? tmem_base + kTmemSfbRes + kb * 8 : t_sfa + 4;
                         tc_cp_32x128b_warpx4(t_sfa, sf_desc0 + sfa_lo);
-                        tc_cp_32x128b_warpx4(t_sfb, sf_desc0 + sfb_lo);
-                        tc_cp_32x128b_warpx4(t_sfb + 4, sf_desc0 + sfb_lo + (kSfAtom >> 4));
+                        if (!B_RES) {
+                            tc_cp_32x128b_warpx4(t_sfb, sf_desc0 + sfb_lo);
+                            tc_cp_32x128b_warpx4(t_sfb + 4, sf_desc0 + sfb_lo + (kSfAtom >> 4));
+                        }
                         const uint64_t da = desc0 + a_lo;
                         const uint64_t db = desc0 + b_lo;
 #pragma unroll
@@ -303,6 +316,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else {
         // ---------------------------------------------------------------- epilogue
+        // The four warps that share a TMEM lane quarter (32 output rows, one 64-column quarter each) form a group of their
+        // own: they exchange the row amax, fill their 32 rows of the staging boxes and send them off with their own TMA
+        // stores, synchronised by a named barrier of 128 threads.  No barrier spans all sixteen warps inside a tile, so
+        // the groups drift apart and one group's conversions overlap another's special-function work.
         const int et = threadIdx.x - 64;          // 0..511
         const int cq = et >> 7;                   // which 64-column quarter of the tile this thread serves
         const int quarter = warp & 3;             // TMEM lanes [32 * quarter, +32) are visible to this warp
@@ -310,6 +327,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
         const int col_a = MODE == kSwiGLU ? cq * 32 : cq * 64;
         const int col_b = MODE == kSwiGLU ? 128 + cq * 32 : cq * 64 + 32;
+        const bool leader = cq == 0 && lane == 0; // issues the group's TMA loads and stores
+        const uint32_t group_bar = 2 + quarter;
+        uint8_t* out_q = out_s + quarter * 4096;  // this group's 32 rows inside every 16 KB staging box
         uint32_t tile_count = 0;
         bool ok = true;
 
@@ -323,12 +343,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int64_t row = m * kBM + row_in_tile;
                 const bool row_ok = row < g.M;
                 const int m0 = static_cast<int>(m) * kBM;
-                if (MODE == kLinear && g.residual != nullptr && et == 0) {
+                if (MODE == kLinear && g.residual != nullptr && leader) {
+                    // the group's staging rows are free once its previous stores have read them; the residual rows
+                    // then land there while the K loop runs
                     bulk_wait_read<0>();
-                    mbar_expect_tx(&res_full, P::kOutBytes);
+                    mbar_expect_tx(&res_full[quarter], P::kOutBoxes * 4096u);
 #pragma unroll
                     for (int b = 0; b < P::kOutBoxes; ++b)
-                        tma_load_2d(out_s + b * kOutBoxBytes, &tmap_r, 2 * n0 + b * 128, m0, &res_full);
+                        tma_load_2d(out_q + b * kOutBoxBytes, &tmap_r, 2 * n0 + b * 128, m0 + quarter * 32, &res_full[quarter]);
                 }
                 // A thread whose wait gives up keeps walking the schedule (it still meets every named barrier); its
                 // results are garbage and the status word says so.
@@ -337,18 +359,29 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // drain this thread's 64 columns into registers (bias added on the way), then release the accumulator
                 float2 acc[32];
                 const uint32_t t0 = tmem_base + lane_addr;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[16];
-                    const int col = c < 2 ? col_a + 16 * c : col_b + 16 * (c - 2);
-                    tmem_ld_x16(t0 + col, r);
-                    tc_wait_ld(r);
-                    const float4* bp = reinterpret_cast<const float4*>(bias_s + col);
+                {
+                    uint32_t r0[16], r1[16], r2[16], r3[16];     // four loads in flight under one wait
+                    tmem_ld_x16(t0 + col_a, r0);
+                    tmem_ld_x16(t0 + col_a + 16, r1);
+                    tmem_ld_x16(t0 + col_b, r2);
+                    tmem_ld_x16(t0 + col_b + 16, r3);
+                    tc_wait_ld(r0);
+                    tc_wait_ld(r1);
+                    tc_wait_ld(r2);
+                    tc_wait_ld(r3);
+                    const float4* ba = reinterpret_cast<const float4*>(bias_s + col_a);
+                    const float4* bb = reinterpret_cast<const float4*>(bias_s + col_b);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float4 bv = bp[i];
-                        acc[8 * c + 2 * i] = make_float2(__uint_as_float(r[4 * i]) + bv.x, __uint_as_float(r[4 * i + 1]) + bv.y);
-                        acc[8 * c + 2 * i + 1] = make_float2(__uint_as_float(r[4 * i + 2]) + bv.z, __uint_as_float(r[4 * i + 3]) + bv.w);
+                        const float4 a0 = ba[i], a1 = ba[4 + i], b0 = bb[i], b1 = bb[4 + i];
+                        acc[2 * i] = make_float2(__uint_as_float(r0[4 * i]) + a0.x, __uint_as_float(r0[4 * i + 1]) + a0.y);
+                        acc[2 * i + 1] = make_float2(__uint_as_float(r0[4 * i + 2]) + a0.z, __uint_as_float(r0[4 * i + 3]) + a0.w);
+                        acc[8 + 2 * i] = make_float2(__uint_as_float(r1[4 * i]) + a1.x, __uint_as_float(r1[4 * i + 1]) + a1.y);
+                        acc[8 + 2 * i + 1] = make_float2(__uint_as_float(r1[4 * i + 2]) + a1.z, __uint_as_float(r1[4 * i + 3]) + a1.w);
+                        acc[16 + 2 * i] = make_float2(__uint_as_float(r2[4 * i]) + b0.x, __uint_as_float(r2[4 * i + 1]) + b0.y);
+                        acc[16 + 2 * i + 1] = make_float2(__uint_as_float(r2[4 * i + 2]) + b0.z, __uint_as_float(r2[4 * i + 3]) + b0.w);
+                        acc[24 + 2 * i] = make_float2(__uint_as_float(r3[4 * i]) + b1.x, __uint_as_float(r3[4 * i + 1]) + b1.y);
+                        acc[24 + 2 * i + 1] = make_float2(__uint_as_float(r3[4 * i + 2]) + b1.z, __uint_as_float(r3[4 * i + 3]) + b1.w);
                     }
                 }
                 tc_fence_before_sync();
@@ -367,8 +400,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                     float (*xchg)[kBM] = amax_xchg[tile_count & 1];
                     xchg[cq][row_in_tile] = amax;
-                    if (et == 0) bulk_wait_read<0>();       // the previous tile's store has read the staging tile
-                    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+                    if (leader) bulk_wait_read<0>();        // the group's previous store has read its staging rows
+                    asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
                     if (MODE == kSwiGLU) {
                         amax = fmaxf(fmaxf(xchg[0][row_in_tile], xchg[1][row_in_tile]),
                                      fmaxf(xchg[2][row_in_tile], xchg[3][row_in_tile]));
@@ -378,7 +411,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     float inv1;
                     const uint32_t sf_byte = pow2_scale(amax, &inv1);
                     const float2 inv = make_float2(inv1, inv1);
-                    uint8_t* box_row = out_s + (MODE == kSiLU ? (cq >> 1) * kOutBoxBytes : 0) + row_in_tile * 128;
+                    uint8_t* box_row = out_q + (MODE == kSiLU ? (cq >> 1) * kOutBoxBytes : 0) + lane * 128;
                     const int piece0 = MODE == kSwiGLU ? cq * 2 : (cq & 1) * 4;
 #pragma unroll
                     for (int c = 0; c < NV / 8; ++c) {
@@ -401,11 +434,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         *reinterpret_cast<uint32_t*>(atom + sf_row_offset(row_in_tile)) = sf_byte * 0x01010101u;
                     }
                 } else {
-                    uint8_t* box_row = out_s + cq * kOutBoxBytes + row_in_tile * 128;
+                    uint8_t* box_row = out_q + cq * kOutBoxBytes + lane * 128;
                     const bool has_res = g.residual != nullptr;
-                    if (et == 0) bulk_wait_read<0>();
-                    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-                    if (has_res && ok && !mbar_wait(&res_full, tile_count & 1)) ok = false;
+                    if (!has_res) {
+                        if (leader) bulk_wait_read<0>();
+                        asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
+                    } else if (ok && !mbar_wait(&res_full[quarter], tile_count & 1)) {
+                        ok = false;
+                    }
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         uint4* slot = reinterpret_cast<uint4*>(box_row + ((c ^ swz) << 4));
@@ -421,17 +457,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         *slot = Vec16<__nv_bfloat16>::pack2(v);
                     }
                 }
+                // the group's rows are staged -> its leader hands them to TMA (rows past M are clipped by the tensor map)
                 fence_proxy_async_smem();
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-                if (et == 0) {
+                asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
+                if (leader) {
                     const int x0 = MODE == kSwiGLU ? (n0 / kBN) * 128 : (MODE == kSiLU ? n0 : 2 * n0);
 #pragma unroll
-                    for (int b = 0; b < P::kOutBoxes; ++b) tma_store_2d(&tmap_o, out_s + b * kOutBoxBytes, x0 + b * 128, m0);
+                    for (int b = 0; b < P::kOutBoxes; ++b)
+                        tma_store_2d(&tmap_o, out_q + b * kOutBoxBytes, x0 + b * 128, m0 + quarter * 32);
                     bulk_commit();
                 }
             }
         }
-        if (et == 0) bulk_wait<0>();
+        if (leader) bulk_wait<0>();
         if (!ok) {
             s_abort = 1;
             if (g.status != nullptr) atomicExch(g.status, 1);
@@ -596,8 +634,9 @@ extern "C" int tb200_mx_gemm(const void* a_fp8, const uint8_t* a_scale_atoms, co
         return TB200_ERR_DRIVER;
     const uint64_t out_row_bytes = mode == kSwiGLU ? static_cast<uint64_t>(N) / 2 : (mode == kSiLU ? static_cast<uint64_t>(N) : 2ull * N);
     CUtensorMap to, tr;
-    if (!make_tmap_bytes(&to, out, out_row_bytes, static_cast<uint64_t>(M), out_row_bytes, kBM)) return TB200_ERR_DRIVER;
-    if (!make_tmap_bytes(&tr, residual != nullptr ? residual : out, out_row_bytes, static_cast<uint64_t>(M), out_row_bytes, kBM))
+    // output and residual move in boxes of 32 rows x 128 bytes: one per epilogue group (a TMEM lane quarter)
+    if (!make_tmap_bytes(&to, out, out_row_bytes, static_cast<uint64_t>(M), out_row_bytes, 32)) return TB200_ERR_DRIVER;
+    if (!make_tmap_bytes(&tr, residual != nullptr ? residual : out, out_row_bytes, static_cast<uint64_t>(M), out_row_bytes, 32))
         return TB200_ERR_DRIVER;
     GemmArgs g{};
     g.sfa = a_scale_atoms;

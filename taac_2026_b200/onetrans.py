@@ -204,8 +204,11 @@ class OneTransInference:
         self._meta_ring: list[torch.Tensor] = []
         self._copy_stream: torch.cuda.Stream | None = None
         self._meta_next = 0
-        if ffn not in ("bf16", "fp8", "fp8_precise"):
+        if ffn not in ("bf16", "fp8", "fp8_precise", "fp8_mx"):
             raise ValueError(f"unknown ffn mode {ffn}")
+        # "fp8_mx": power-of-two block scales applied inside the block-scaled tensor-core instruction (ops.ffn_mx)
+        self.ffn_mx = ffn == "fp8_mx"
+        ffn = "fp8" if self.ffn_mx else ffn
         # "fp8_precise": GEMM 1 of the shared FFN on the bf16 tensor cores, only its hidden activation and the down
         # projection in e4m3 (ops.ffn_fp8(precise=True))
         self.ffn_precise = ffn == "fp8_precise"
@@ -304,10 +307,15 @@ class OneTransInference:
             p = f"blocks.{layer}"
             blk = {"p": p}
             if self.ffn_mode == "fp8":
-                blk["ffn_fp8"] = ops.Fp8FfnWeights(
-                    self.w[p + ".ffn.shared.net.0.weight"], self.w[p + ".ffn.shared.net.3.weight"], gated=False,
-                    b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"],
-                    precise=self.ffn_precise)
+                if self.ffn_mx:
+                    blk["ffn_fp8"] = ops.MxFfnWeights(
+                        self.w[p + ".ffn.shared.net.0.weight"], self.w[p + ".ffn.shared.net.3.weight"], gated=False,
+                        b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"])
+                else:
+                    blk["ffn_fp8"] = ops.Fp8FfnWeights(
+                        self.w[p + ".ffn.shared.net.0.weight"], self.w[p + ".ffn.shared.net.3.weight"], gated=False,
+                        b_up=self.w[p + ".ffn.shared.net.0.bias"], b_down=self.w[p + ".ffn.shared.net.3.bias"],
+                        precise=self.ffn_precise)
                 # The packed path leaves the attention output bias out of the residual stream it hands to the
                 # FFN (the norm in between adds it on the fly), so the FFN's own output bias carries it.
                 folded = copy.copy(blk["ffn_fp8"])
@@ -364,6 +372,11 @@ class OneTransInference:
         if key not in self._cast_cache:
             self._cast_cache[key] = self.w[prefix + ".bias"].float().contiguous()
         return self._proj(x, self._p(prefix + ".weight"), self._cast_cache[key], silu=silu, residual=residual)
+
+    def _ffn_fp8(self, x: torch.Tensor, weights, residual: torch.Tensor) -> torch.Tensor:
+        if self.ffn_mx:
+            return ops.ffn_mx(x, weights, residual=residual, status=self.status_word)
+        return ops.ffn_fp8(x, weights, residual=residual, status=self.status_word, precise=self.ffn_precise)
 
     def _own_gemm(self, n: int, k: int) -> bool:
         """The tcgen05 GEMM serves bf16 layers whose widths are whole tiles; the fp32 score-parity mode and odd
@@ -502,7 +515,7 @@ class OneTransInference:
     def _shared_ffn_residual(self, blk: dict, x: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         """tokens + FFN(x) for every row (`FeedForward`, experiments/onetrans/model.py:33-44)."""
         if self.ffn_mode == "fp8":
-            return ops.ffn_fp8(x, blk["ffn_fp8"], residual=tokens, status=self.status_word, precise=self.ffn_precise)
+            return self._ffn_fp8(x, blk["ffn_fp8"], tokens)
         p = blk["p"]
         return self._linear(self._linear(x, p + ".ffn.shared.net.0", silu=True), p + ".ffn.shared.net.3", residual=tokens)
 
@@ -879,7 +892,7 @@ class OneTransInference:
                 # is added by the norm on the fly and rides on the FFN output biases into the next residual
                 tokens = self._proj(attn2d, blk["out_w"], None, residual=tokens, out=tokens)
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6, in_bias=blk["out_b"])
-                out = ops.ffn_fp8(x, blk["ffn_fp8_folded"], residual=tokens, status=self.status_word, precise=self.ffn_precise)
+                out = self._ffn_fp8(x, blk["ffn_fp8_folded"], tokens)
             else:
                 tokens = self._proj(attn2d, blk["out_w"], blk["out_b32"], residual=tokens)
                 x = ops.rms_norm(tokens, self._p(p + ".ffn_norm.weight"), 1e-6)

@@ -241,3 +241,20 @@ def test_one_kernel_tokenizer_gives_the_same_scores():
     a, b = plain.scores(batch), fused.scores(batch)
     fused.raise_if_incomplete()
     assert (a - b).abs().max().item() <= 2e-3
+
+
+def test_block_scaled_ffn_mode_gives_the_same_scores_as_the_amax_scaled_one():
+    """ffn="fp8_mx" (power-of-two block scales inside the block-scaled tensor-core instruction) against ffn="fp8" on
+    the serving-size backbone: both are e4m3 FFNs, so the scores agree to the e4m3 noise level, and both stay within
+    the bf16-mode tolerance of the oracle."""
+    spec = _wide_spec()
+    sd = random_state_dict(spec, seed=5)
+    batch = synthetic_batch(spec, 48, seq_len=260, min_len=0, seed=6)
+    want_logits, _ = oracle_model.predict(sd, spec.as_dict(), batch)
+    want = oracle_model.sigmoid_scores(want_logits).reshape(-1)
+    base = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn="fp8").scores(batch.to("cuda")).cpu().numpy()
+    model = OneTransInference(sd, spec, dtype=torch.bfloat16, ffn="fp8_mx")
+    got = model.scores(batch.to("cuda")).cpu().numpy()
+    model.raise_if_incomplete()
+    assert np.abs(got - want).max() <= 1e-2
+    assert np.abs(got - base).max() <= 1e-2
