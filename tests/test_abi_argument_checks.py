@@ -162,3 +162,43 @@ def test_static_ffn_entry_checks_everything_before_it_launches(lib):
     assert call(M=1 << 62) == ERR_SCRATCH          # no wrap-around of the size products
     assert call(M=(1 << 31) + 5) == ERR_SCRATCH
     assert lib.tb200_ffn_fp8_static_status(None, None) == ERR_NULL
+
+
+def test_entries_added_for_the_host_loop_and_the_training_slice(lib):
+    buf = (ctypes.c_uint8 * 4096)()
+    p = ctypes.addressof(buf) + (16 - ctypes.addressof(buf) % 16) % 16      # a 16-byte aligned address inside the buffer
+    strides = (ctypes.c_int64 * 12)(*([64] * 12))
+    widths = (ctypes.c_int32 * 3)(8, 4, 2)
+    ERR_RANGE = -9
+    assert lib.tb200_strerror(ERR_RANGE).decode() != lib.tb200_strerror(OK).decode()
+    # compact host format
+    assert lib.tb200_host_compact_offsets(None, 0, 8, P(p)) == OK
+    assert lib.tb200_host_compact_offsets(None, 4, 8, P(p)) == ERR_NULL
+    assert lib.tb200_host_compact_sequence(P(p), None, None, P(p), 0, 1, 8, P(p), 8, None, 1) == OK
+    assert lib.tb200_host_compact_sequence(P(p), None, None, P(p), 2, 0, 8, P(p), 8, None, 1) == ERR_SHAPE   # no feature
+    assert lib.tb200_expand_sequence(P(p), None, P(p), None, P(p), P(p), None, 2, 1, 7, 8, None) == ERR_ALIGN   # odd max_len
+    assert lib.tb200_expand_sequence(P(p), None, P(p), None, P(p), P(p), P(p), 2, 1, 8, 8, None) == ERR_NULL    # timestamps without gaps
+    assert lib.tb200_expand_sequence(None, None, None, None, None, None, None, 0, 1, 8, 8, None) == OK
+    # row plan
+    assert lib.tb200_pyramid_plan(P(p), 4, 8, widths, 65, 2, P(p), P(p), P(p), P(p), P(p), P(p), P(p), None) == ERR_SHAPE
+    assert lib.tb200_pyramid_plan(P(p), 4, 8, None, 2, 2, P(p), P(p), P(p), P(p), P(p), P(p), P(p), None) == ERR_NULL
+    assert lib.tb200_pyramid_kept_rows(None, None, None, None, 0, 2, None, None, None, None) == OK
+    assert lib.tb200_pyramid_kept_rows(P(p), P(p), P(p), P(p), 4, 2, None, P(p), None, None) == ERR_NULL
+    # backward kernels
+    assert lib.tb200_attn_bwd(P(p), P(p), P(p), P(p), P(p), P(p), P(p), P(p), P(p), 1, 1, 8, 8, 300, strides, None, None, 8, 0, 0,
+                              0.125, BF16, None) == ERR_UNSUPPORTED                                   # head_dim above 256
+    assert lib.tb200_attn_bwd(P(p), P(p), P(p), P(p), P(p), P(p), P(p), P(p), None, 1, 1, 8, 8, 64, strides, None, None, 8, 0, 0,
+                              0.125, BF16, None) == ERR_NULL                                          # no workspace
+    assert lib.tb200_attn_bwd(P(p), P(p), P(p), P(p), P(p), P(p), P(p), P(p), P(p), 1, 1, 8, 16, 64, strides, None, None, 16, 0, 1,
+                              0.125, BF16, None) == ERR_SHAPE                                         # padded-self needs Lq == Lk
+    assert lib.tb200_attn_bwd_workspace_bytes(2, 3, 5) == 2 * 3 * 5 * 8
+    assert lib.tb200_bag_mean_bwd(P(p), 1, P(p), P(p), P(p), 4, 2, 12, 10, BF16, None) == ERR_ALIGN      # 24-byte rows
+    assert lib.tb200_bag_mean_bwd(P(p), 1, P(p), P(p), P(p), 0, 2, 8, 10, BF16, None) == OK
+    # block-scaled FFN
+    assert lib.tb200_mx_scale_bytes(300, 512) == 3 * 4 * 512
+    assert lib.tb200_quant_act_mx(P(p), P(p), P(p), 4, 100, None) == ERR_SHAPE
+    assert lib.tb200_quant_act_mx(P(p), P(p), None, 4, 128, None) == ERR_NULL
+    assert lib.tb200_mx_gemm(P(p), P(p), P(p), P(p), None, None, P(p), None, 4, 256, 128, 0, None, None) == ERR_NULL   # no scale output
+    assert lib.tb200_mx_gemm(P(p), P(p), P(p), P(p), None, P(p), P(p), P(p), 4, 256, 128, 1, None, None) == ERR_UNSUPPORTED
+    assert lib.tb200_mx_gemm(P(p), P(p), P(p), P(p), None, None, P(p), None, 4, 200, 128, 2, None, None) == ERR_SHAPE
+    assert lib.tb200_mx_gemm(P(p), P(p), P(p), P(p), None, None, P(p), None, 0, 256, 128, 2, None, None) == OK
