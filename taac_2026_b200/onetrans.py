@@ -596,7 +596,8 @@ class OneTransInference:
         and statistics of the behaviour sequence, the row plan of the packed layout, and the asynchronous copy of the
         plan's per-layer totals into pinned host memory (with an event).  A serving loop calls this for batch i + 1 on
         a side stream while batch i is being scored; the forward of batch i + 1 then finds its buffer sizes on the
-        host already and never drains the device.  None when the engine does not run the packed layout."""
+        host already and never drains the device.  None when the engine does not run the packed layout.  At most
+        three results may be outstanding at a time: the pinned landing buffers are a ring of four."""
         if not (self.packed and len(self.domains) == 1):
             return None
         seq = inputs.sequences[self.domains[0]]
