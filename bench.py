@@ -875,17 +875,7 @@ def run_norm_backward_sweep(args) -> None:
         b = (0.02 * torch.randn(cols, generator=g, device="cuda")).bfloat16()
         for name, fn in (("rms_norm_bwd", lambda p: ops.rms_norm_backward(p[0], w, p[1], 1e-6)),
                          ("layer_norm_bwd", lambda p: ops.layer_norm_backward(p[0], w, b, p[1], 1e-6))):
-            for p in bufs:
-                fn(p)
-            torch.cuda.synchronize()
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            for _ in range(args.steps):
-                for p in bufs:
-                    fn(p)
-            end.record()
-            torch.cuda.synchronize()
-            ms = start.elapsed_time(end) / (args.steps * n_buf)
+            ms = graph_time(fn, bufs, args.steps)      # a CUDA graph over the rotating buffers: device time, not host time
             gbs = 3.0 * rows * cols * 2 / ms / 1e6
             print(json.dumps({
                 "metric": f"{name}_GBps", "value": round(gbs, 1), "unit": "GB/s", "config": {"workload": f"{rows}x{cols} bf16"},

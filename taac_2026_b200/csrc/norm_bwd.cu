@@ -67,21 +67,36 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     // The loop bound is the same for every lane of a warp (the shuffles below name all 32 lanes); a lane whose row
     // lies past the end works on zeros and stores nothing.
     const int64_t row_step = static_cast<int64_t>(gridDim.x) * kWarps * RPW;
-    for (int64_t base = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * RPW; base < rows; base += row_step) {
+    // The pieces of the NEXT row of this lane group are requested before the current row is worked on, so that every
+    // warp always has loads in flight under its shuffle chains (a zero piece stands for "past the end").
+    uint4 nx[CPL], ng[CPL];
+    auto fetch = [&](int64_t row) {
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+            const int c = lg + j * G;
+            if (row < rows && c < chunks) {
+                nx[j] = ld_stream(x + row * cols + static_cast<int64_t>(c) * N);
+                ng[j] = ld_stream(dy + row * cols + static_cast<int64_t>(c) * N);
+            } else {
+                nx[j] = ng[j] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * RPW;
+    fetch(first + sub);
+    for (int64_t base = first; base < rows; base += row_step) {
         const int64_t row = base + sub;
         const bool live = row < rows;
         float xv[CPL][N], gv[CPL][N];
         float s1 = 0.f, s2 = 0.f;            // RMS: s2 = sum x^2;  Layer: s1 = sum x, s2 = centred sum of squares
 #pragma unroll
         for (int j = 0; j < CPL; ++j) {
-            const int c = lg + j * G;
-            if (live && c < chunks) {
-                Vec16<T>::unpack(ld_stream(x + row * cols + static_cast<int64_t>(c) * N), xv[j]);
-                Vec16<T>::unpack(ld_stream(dy + row * cols + static_cast<int64_t>(c) * N), gv[j]);
-            } else {
+            Vec16<T>::unpack(nx[j], xv[j]);
+            Vec16<T>::unpack(ng[j], gv[j]);
+        }
+        fetch(row + row_step);
 #pragma unroll
-                for (int e = 0; e < N; ++e) xv[j][e] = gv[j][e] = 0.f;
-            }
+        for (int j = 0; j < CPL; ++j) {
 #pragma unroll
             for (int e = 0; e < N; ++e) {
                 if (LAYER) s1 += xv[j][e];
