@@ -908,12 +908,12 @@ def run_token_tail_sweep(args) -> None:
     }), flush=True)
 
 
-def attention_lines(peaks: dict, peak_kind: str, *, batch: int, steps: int, kernel: int = 0) -> list[dict]:
+def attention_lines(peaks: dict, peak_kind: str, *, batch: int, steps: int, kernel: int = 0, seed: int = 0) -> list[dict]:
     """Varlen padded-mask attention: `batch` samples (a slice of the 2048), 8 heads, head_dim 64, L 1024, lengths
     uniform in [32, 1024]; non-causal + key padding and causal + key padding.  FLOPs count valid queries x
     visible keys only."""
     B, H, L, D = batch, 8, 1024, 64
-    g = torch.Generator(device="cuda").manual_seed(0)
+    g = torch.Generator(device="cuda").manual_seed(seed)
     q, k, v = (torch.randn(B, H, L, D, generator=g, device="cuda").div_(8).bfloat16() for _ in range(3))
     lens = torch.randint(32, 1025, (B,), generator=g, device="cuda", dtype=torch.int32)
     out = []
@@ -1002,8 +1002,26 @@ def run_token_project_sweep(args) -> None:
 def run_attention_sweep(args) -> None:
     """Batch 2048 (in slices), 8 heads, head_dim 64, L 1024, lengths uniform in [32, 1024]."""
     peaks, peak_kind = load_peaks()
-    for line in attention_lines(peaks, peak_kind, batch=args.batch or 256, steps=args.steps, kernel=args.kernel):
-        print(json.dumps(line), flush=True)
+    batch = args.batch or 256
+    if batch <= 512:
+        for line in attention_lines(peaks, peak_kind, batch=batch, steps=args.steps, kernel=args.kernel):
+            print(json.dumps(line), flush=True)
+        return
+    # the full configuration (batch 2048) in slices of 256 samples with their own seeds: q, k, v of one slice are
+    # 0.8 GB, and the rate of the whole batch is total work over total time
+    slices = [attention_lines(peaks, peak_kind, batch=256, steps=args.steps, kernel=args.kernel, seed=i) for i in range((batch + 255) // 256)]
+    for which in range(2):
+        lines = [sl[which] for sl in slices]
+        ms = sum(line["ms_per_launch"] for line in lines)
+        work = sum(line["value"] * line["ms_per_launch"] for line in lines)      # TFLOP/s x ms
+        tf = work / ms
+        merged = dict(lines[0])
+        merged["value"] = round(tf, 1)
+        merged["ms_per_launch"] = round(ms, 3)
+        merged["config"] = {**lines[0]["config"], "workload": lines[0]["config"]["workload"].replace("B256", f"B{256 * len(lines)} ({len(lines)} slices of 256)"),
+                            "slice_TFLOPs": [line["value"] for line in lines]}
+        merged["roofline"] = {**lines[0]["roofline"], "achieved": round(tf, 1), "frac": round(tf / lines[0]["roofline"]["peak"], 4)}
+        print(json.dumps(merged), flush=True)
 
 
 def run_kept_rows_attention(args) -> None:
