@@ -115,12 +115,26 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 
 // Work items: (query block of 128 rows, head, sample), walked in the same order by every role of a
-// persistent CTA (item w = blockIdx.x + i * gridDim.x).  Later query blocks come first: under a causal
-// mask they own the most key tiles, so the long items start early and the short ones fill the tail.
+// persistent CTA (item w = blockIdx.x + i * gridDim.x).  Two orders of the item list:
+//   block-major (rows of equal length): later query blocks come first; under a causal mask they own the most key
+//     tiles, so the long items start early and the short ones fill the tail;
+//   sample-major (ragged batches: a length vector or packed rows): all blocks and heads of a sample are neighbours in
+//     the list, so the CTAs that run at the same time read the K / V tiles of a few samples and find them in the L2
+//     (measured on 256 samples of 32..1024 keys: 4-5 % faster, causal or not; on equal lengths under a causal mask
+//     the block-major order is the faster one by the same margin).
 struct Work {
     int n_qb, heads, batch;
     int64_t total;
+    bool sample_major;
     __device__ __forceinline__ void decode(int64_t w, int& qb, int& h, int& b) const {
+        if (sample_major) {
+            const int per_b = n_qb * heads;
+            b = static_cast<int>(w / per_b);
+            const int rem = static_cast<int>(w % per_b);
+            qb = n_qb - 1 - rem / heads;
+            h = rem % heads;
+            return;
+        }
         const int64_t per_qb = static_cast<int64_t>(heads) * batch;
         qb = n_qb - 1 - static_cast<int>(w / per_qb);
         const int rem = static_cast<int>(w % per_qb);
@@ -151,6 +165,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     work.heads = a.H;
     work.batch = a.B;
     work.total = static_cast<int64_t>(work.n_qb) * a.H * a.B;
+    work.sample_major = a.seq_len != nullptr || a.cu_rows != nullptr;
 
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
