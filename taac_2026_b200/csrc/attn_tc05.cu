@@ -206,7 +206,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 // TMA coordinates: (d, row, head, batch); packed batches address rows of the whole matrix
                 const int row0 = plan.packed ? static_cast<int>(plan.row_base) : 0;
                 const int bz = plan.packed ? 0 : b;
-                if (!mbar_wait(&q_empty, (qc & 1) ^ 1)) { ok = false; break; }
+                if (!mbar_wait_sleep(&q_empty, (qc & 1) ^ 1)) { ok = false; break; }
                 mbar_expect_tx(&q_full, kTileBytes);
                 tma_load_4d(sQ, &tmap_q, 0, row0 + plan.m0, h_idx, bz, &q_full);
                 ++qc;
@@ -215,7 +215,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     for (int which = 0; which < 2; ++which) {  // K tile, then V tile
                         const uint32_t t = 2 * kc + which;
                         const uint32_t slot = t % kSlots;
-                        if (!mbar_wait(&kv_empty[slot], ((t / kSlots) & 1) ^ 1)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&kv_empty[slot], ((t / kSlots) & 1) ^ 1)) { ok = false; break; }
                         mbar_expect_tx(&kv_full[slot], kTileBytes);
                         tma_load_4d(sKV + slot * kTileBytes, which == 0 ? &tmap_k : &tmap_v, 0, row0 + j * kBN, h_idx, bz,
                                     &kv_full[slot]);
@@ -240,14 +240,14 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 work.decode(w, qb, h_idx, b);
                 const Plan plan = make_plan(a, b, qb * kBM);
                 if (!plan.half_on[0] || plan.n_tiles == 0) continue;
-                if (!mbar_wait(&q_full, qc & 1)) { ok = false; break; }
+                if (!mbar_wait_sleep(&q_full, qc & 1)) { ok = false; break; }
                 ++qc;
                 // S of tile j + 1 is issued before P V of tile j: the softmax of j runs from registers, so the
                 // tensor cores fill the S buffer again while it computes
                 auto issue_s = [&](uint32_t tile_index, bool last_of_item) -> bool {
                     const uint32_t t = 2 * tile_index;
                     const uint32_t slot = t % kSlots;
-                    if (!mbar_wait(&kv_full[slot], (t / kSlots) & 1) || !mbar_wait(&s_free, (tile_index & 1) ^ 1)) return false;
+                    if (!mbar_wait_sleep(&kv_full[slot], (t / kSlots) & 1) || !mbar_wait_sleep(&s_free, (tile_index & 1) ^ 1)) return false;
                     tc_fence_after_sync();
                     const uint32_t k_addr = smem_u32(sKV + slot * kTileBytes);
 #pragma unroll
@@ -274,11 +274,11 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     const uint32_t t = 2 * kc + 1;
                     const uint32_t slot = t % kSlots;
                     const uint32_t v_addr = smem_u32(sKV + slot * kTileBytes);
-                    if (!mbar_wait(&kv_full[slot], (t / kSlots) & 1)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&kv_full[slot], (t / kSlots) & 1)) { ok = false; break; }
 #pragma unroll 1
                     for (int half = 0; half < 2; ++half) {
                         if (half == 1 && i + 1 < n_active && !issue_s(kc + 1, i + 2 == n_active)) { ok = false; break; }
-                        if (!mbar_wait(&p_full[half], kc & 1)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&p_full[half], kc & 1)) { ok = false; break; }
                         tc_fence_after_sync();
 #pragma unroll
                         for (int kk = 0; kk < kBN / 32; ++kk) {
@@ -332,7 +332,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // held in registers did not.
             auto tile = [&](const int n0, auto full_tag) -> bool {
                 constexpr bool FULL = decltype(full_tag)::value;
-                if (!mbar_wait(&s_full, kc & 1)) return false;
+                if (!mbar_wait_sleep(&s_full, kc & 1)) return false;
                 tc_fence_after_sync();
                 // visibility of the 32 columns from `base` on as a bit mask
                 auto chunk_mask = [&](const int base) -> uint32_t {
@@ -383,7 +383,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
                 // the previous P V of this item must be done before P is overwritten or O is rescaled
                 if (tiles_done > 0) {
-                    if (!mbar_wait(&o_full, (kc - 1) & 1)) return false;
+                    if (!mbar_wait_sleep(&o_full, (kc - 1) & 1)) return false;
                     tc_fence_after_sync();
                     if (__any_sync(0xffffffffu, grow)) {  // tcgen05.ld / st are warp-wide: corr = 1 where unchanged
                         const float2 corr2 = make_float2(corr, corr);
@@ -480,7 +480,7 @@ attn_tc05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
             for (int i = 0; i < kD / 2; ++i) o_acc[i] = make_float2(0.f, 0.f);
             if (tiles_done > 0) {
-                if (!mbar_wait(&o_full, (kc - 1) & 1)) { ok = false; break; }
+                if (!mbar_wait_sleep(&o_full, (kc - 1) & 1)) { ok = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {

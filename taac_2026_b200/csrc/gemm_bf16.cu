@@ -419,7 +419,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kStagesP;
                     const uint32_t ph = (it / kStagesP) & 1;
-                    if (!mbar_wait(&empty_bar[s], ph ^ 1, kPairWait) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                    if (!mbar_wait_sleep(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
                         ok = false;
                         break;
                     }
@@ -443,11 +443,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             uint32_t s = 0, ph = 0, buf = 0, aph = 0;
             bool ok = true;
             for (int64_t t = pair; t < total && ok; t += n_pairs) {
-                if (!mbar_wait(&tmem_empty[buf], aph ^ 1, kPairWait)) { ok = false; break; }
+                if (!mbar_wait_sleep(&tmem_empty[buf], aph ^ 1)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * kBN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&full_bar[s], ph, kPairWait)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&full_bar[s], ph)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a_lo = ring_lo + s * (kStagePBytes >> 4);
                     const uint64_t da = desc0 + a_lo;
@@ -510,7 +510,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             // accumulator barrier, so the other roles are not held up by it); its output is garbage, the status word says so.
             if (ok) {   // one lane polls, the warp follows
                 int passed = 1;
-                if (lane == 0) passed = mbar_wait(&tmem_full[buf], aph, kPairWait) ? 1 : 0;
+                if (lane == 0) passed = mbar_wait_sleep(&tmem_full[buf], aph) ? 1 : 0;
                 if (__shfl_sync(0xffffffffu, passed, 0) == 0) ok = false;
             }
             tc_fence_after_sync();

@@ -87,6 +87,33 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     return false;
 }
 
+// Bounded wait for roles that mostly wait (a producer or issuer thread, softmax threads between tiles): try_wait
+// with a suspend-time hint, so that the thread sleeps until the phase completes instead of coming back after the
+// short default time slice and polling again (polling warps take issue slots and power from the warps that work).
+// The bound is a clock, not an iteration count: about two seconds.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity) {
+    constexpr uint32_t kHintNs = 20000;
+    if (mbar_try_wait_hint(bar, parity, kHintNs)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait_hint(bar, parity, kHintNs)) {
+        if (clock64() - t0 > (4ll << 30)) return false;
+    }
+    return true;
+}
+
 // ---------------------------------------------------------------------------
 // proxy fences
 // ---------------------------------------------------------------------------
