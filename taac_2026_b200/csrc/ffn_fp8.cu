@@ -198,7 +198,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 if (B_RES) {
                     if (it > 0) {  // the previous column tile's MMAs must have finished reading b_res
                         const uint32_t last = it - 1;
-                        if (!mbar_wait(&empty_bar[last % STAGES], (last / STAGES) & 1)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&empty_bar[last % STAGES], (last / STAGES) & 1)) { ok = false; break; }
                     }
                     mbar_expect_tx(&b_full, static_cast<uint32_t>(k_blocks) * kBBytes);
                     for (int kb = 0; kb < k_blocks; ++kb)
@@ -209,7 +209,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
-                        if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                        if (!mbar_wait_sleep(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
                             ok = false;
                             break;
                         }
@@ -238,12 +238,12 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             bool ok = true;
             for (int n = sc.n_first; n < n_tiles && ok; n += sc.n_step) {
                 if (B_RES) {
-                    if (!mbar_wait(&b_full, b_phase)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&b_full, b_phase)) { ok = false; break; }
                     b_phase ^= 1;
                 }
                 for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G) {
                     for (int kb = 0; kb < k_blocks; ++kb) {
-                        if (!mbar_wait(&tmem_empty[buf], aph ^ 1) || !mbar_wait(&full_bar[s], ph)) {
+                        if (!mbar_wait_sleep(&tmem_empty[buf], aph ^ 1) || !mbar_wait_sleep(&full_bar[s], ph)) {
                             ok = false;
                             break;
                         }
@@ -364,7 +364,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     // A thread whose wait gives up does not leave the loop: it stops waiting (`ok` stays false) but
                     // walks the rest of the tile schedule, so it still meets every named barrier the other epilogue
                     // threads sit in.  Its results are garbage; the status word says so.
-                    if (ok && !mbar_wait(&tmem_full[buf], aph)) ok = false;
+                    if (ok && !mbar_wait_sleep(&tmem_full[buf], aph)) ok = false;
                     tc_fence_after_sync();
                     const uint32_t t0 = tmem_base + buf * kBN + lane_addr;
                     // 16 columns at a time: the accumulators already take 64 of the 96 registers a thread may use
@@ -439,7 +439,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                     const bool has_res = g.residual != nullptr;
                     if (et == 0) bulk_wait_read<0>();
                     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-                    if (has_res && ok && !mbar_wait(&res_full, tile_count & 1)) ok = false;   // keep going, see above
+                    if (has_res && ok && !mbar_wait_sleep(&res_full, tile_count & 1)) ok = false;   // keep going, see above
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         uint4* slot = reinterpret_cast<uint4*>(box_row + ((c ^ swz) << 4));

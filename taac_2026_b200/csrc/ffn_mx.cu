@@ -216,7 +216,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (B_RES) {
                     if (it > 0) {  // the previous column tile's MMAs must have finished reading the resident tile
                         const uint32_t last = it - 1;
-                        if (!mbar_wait(&empty_bar[last % STAGES], (last / STAGES) & 1)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&empty_bar[last % STAGES], (last / STAGES) & 1)) { ok = false; break; }
                     }
                     mbar_expect_tx(&b_full, static_cast<uint32_t>(k_blocks) * (kBBytes + kSfbBytes));
                     for (int kb = 0; kb < k_blocks; ++kb) {
@@ -232,7 +232,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
-                        if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                        if (!mbar_wait_sleep(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
                             ok = false;
                             break;
                         }
@@ -266,7 +266,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             bool ok = true;
             for (int n = sc.n_first; n < n_tiles && ok; n += sc.n_step) {
                 if (B_RES) {
-                    if (!mbar_wait(&b_full, b_phase)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&b_full, b_phase)) { ok = false; break; }
                     b_phase ^= 1;
                     tc_fence_after_sync();
                     // the resident weight tile's scale factors go into tensor memory once per column tile
@@ -279,10 +279,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 for (int64_t m = sc.j; m < m_tiles && ok; m += sc.G, ++tile) {
                     // the epilogue has read the previous tile out of the accumulator
-                    if (!mbar_wait(&tmem_empty, (tile & 1) ^ 1)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&tmem_empty, (tile & 1) ^ 1)) { ok = false; break; }
                     tc_fence_after_sync();
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                        if (!mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&full_bar[s], ph)) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t a_lo = ring_lo + s * (STAGE_BYTES >> 4);
                         const uint32_t b_lo = B_RES ? bres_lo + static_cast<uint32_t>(kb) * (kBBytes >> 4) : a_lo + (kABytes >> 4);
@@ -356,7 +356,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 // A thread whose wait gives up keeps walking the schedule (it still meets every named barrier); its
                 // results are garbage and the status word says so.
-                if (ok && !mbar_wait(&tmem_full, tile_count & 1)) ok = false;
+                if (ok && !mbar_wait_sleep(&tmem_full, tile_count & 1)) ok = false;
                 tc_fence_after_sync();
                 // drain this thread's 64 columns into registers (bias added on the way), then release the accumulator
                 float2 acc[32];
@@ -441,7 +441,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (!has_res) {
                         if (leader) bulk_wait_read<0>();
                         asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
-                    } else if (ok && !mbar_wait(&res_full[quarter], tile_count & 1)) {
+                    } else if (ok && !mbar_wait_sleep(&res_full[quarter], tile_count & 1)) {
                         ok = false;
                     }
 #pragma unroll
@@ -647,7 +647,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (B_RES) {
                     if (it > 0) {  // the previous column tile's MMAs must have finished reading the resident tiles
                         const uint32_t last = it - 1;
-                        if (!mbar_wait(&empty_bar[last % STAGES], (last / STAGES) & 1, kPairWait)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&empty_bar[last % STAGES], (last / STAGES) & 1)) { ok = false; break; }
                     }
                     if (rank == 0) mbar_expect_tx(&b_full, 2u * static_cast<uint32_t>(k_blocks) * (kBHalfBytes + kSfbBytes));
                     for (int kb = 0; kb < k_blocks; ++kb) {
@@ -662,7 +662,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
-                        if (!mbar_wait(&empty_bar[s], ph ^ 1, kPairWait) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                        if (!mbar_wait_sleep(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
                             ok = false;
                             break;
                         }
@@ -695,7 +695,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             bool ok = true;
             for (int n = n_first; n < n_tiles && ok; n += n_step) {
                 if (B_RES) {
-                    if (!mbar_wait(&b_full, b_phase, kPairWait)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&b_full, b_phase)) { ok = false; break; }
                     b_phase ^= 1;
                     tc_fence_after_sync();
                     for (int kb = 0; kb < k_blocks; ++kb) {
@@ -705,10 +705,10 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
                 for (int64_t m = row_first; m < m_tiles && ok; m += row_step, ++tile) {
-                    if (!mbar_wait(&tmem_empty, (tile & 1) ^ 1, kPairWait)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&tmem_empty, (tile & 1) ^ 1)) { ok = false; break; }
                     tc_fence_after_sync();
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                        if (!mbar_wait(&full_bar[s], ph, kPairWait)) { ok = false; break; }
+                        if (!mbar_wait_sleep(&full_bar[s], ph)) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t a_lo = ring_lo + s * (STAGE_BYTES >> 4);
                         const uint32_t b_lo = B_RES ? bres_lo + static_cast<uint32_t>(kb) * (kBHalfBytes >> 4) : a_lo + (kABytes >> 4);
@@ -781,7 +781,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 if (ok) {   // one lane polls, the warp follows
                     int passed = 1;
-                    if (lane == 0) passed = mbar_wait(&tmem_full, tile_count & 1, kPairWait) ? 1 : 0;
+                    if (lane == 0) passed = mbar_wait_sleep(&tmem_full, tile_count & 1) ? 1 : 0;
                     if (__shfl_sync(0xffffffffu, passed, 0) == 0) ok = false;
                 }
                 tc_fence_after_sync();
@@ -867,7 +867,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (!has_res) {
                         if (leader) bulk_wait_read<0>();
                         asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
-                    } else if (ok && !mbar_wait(&res_full[quarter], tile_count & 1, kPairWait)) {
+                    } else if (ok && !mbar_wait_sleep(&res_full[quarter], tile_count & 1)) {
                         ok = false;
                     }
 #pragma unroll

@@ -180,7 +180,7 @@ norm_tma_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
         const int64_t tile_row0 = row_begin + static_cast<int64_t>(it) * tile_rows;
         const int rows_here = rows_in(it);
         uint4* tile = reinterpret_cast<uint4*>(ring + static_cast<size_t>(s) * tile_bytes);
-        const bool ok = mbar_wait(&full_bar[warp][s], parity);
+        const bool ok = mbar_wait_sleep(&full_bar[warp][s], parity);
         if (__any_sync(0xffffffffu, !ok)) {  // a load never arrived: report and leave
             if (lane == 0 && status != nullptr) atomicExch(status, 1);
             break;

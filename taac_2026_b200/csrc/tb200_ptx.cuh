@@ -105,6 +105,9 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity) {
+#ifdef TB200_POLL_WAITS
+    return mbar_wait(bar, parity);
+#endif
     constexpr uint32_t kHintNs = 20000;
     if (mbar_try_wait_hint(bar, parity, kHintNs)) return true;
     const long long t0 = clock64();
