@@ -499,7 +499,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // ------------------------------------------------------------------------------------------------
 constexpr uint32_t kBHalfBytes = kBBytes / 2;                 // 16 KB: this CTA's half of the weight tile
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;                   // shared::cluster address of the pair's even CTA
-constexpr uint32_t kPairWait = 1u << 18;                      // bounded waits give up early in this variant
 constexpr int kEpiWarps = kEpiThreads / 32;
 
 __device__ __forceinline__ uint32_t cluster_rank() {

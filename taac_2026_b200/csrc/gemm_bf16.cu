@@ -132,7 +132,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
-                    if (!mbar_wait(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
+                    if (!mbar_wait_sleep(&empty_bar[s], ph ^ 1) || *reinterpret_cast<volatile int*>(&s_abort)) {
                         ok = false;
                         break;
                     }
@@ -156,10 +156,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t s = 0, ph = 0, buf = 0, aph = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
-                if (!mbar_wait(&tmem_empty[buf], aph ^ 1)) { ok = false; break; }
+                if (!mbar_wait_sleep(&tmem_empty[buf], aph ^ 1)) { ok = false; break; }
                 const uint32_t d_tmem = tmem_base + buf * kBN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+                    if (!mbar_wait_sleep(&full_bar[s], ph)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a_lo = ring_lo + s * (kStageBytes >> 4);
                     const uint64_t da = desc0 + a_lo;
@@ -211,7 +211,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // A thread whose wait gives up stops waiting but keeps walking the tile list, so that it still meets
             // every named barrier the other epilogue threads sit in; what it writes is garbage and the status
             // word says so.
-            if (ok && !mbar_wait(&tmem_full[buf], aph)) ok = false;
+            if (ok && !mbar_wait_sleep(&tmem_full[buf], aph)) ok = false;
             tc_fence_after_sync();
             const int n_rounds = gated ? kBoxes / 2 : kBoxes;   // gated: 128 gate + 128 value columns -> 128 outputs
 #pragma unroll 1
@@ -311,7 +311,6 @@ constexpr uint32_t kStagePBytes = kABytes + kBHalfBytes;      // 32 KB
 constexpr uint32_t kWarpBoxBytes = 32 * 128;                  // one epilogue warp's staging box: 32 rows x 64 bf16
 constexpr size_t kSmemPBytes = static_cast<size_t>(kStagesP) * kStagePBytes + kEpiWarpsP * kWarpBoxBytes + 1024;
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;                   // shared::cluster address of the pair's even CTA
-constexpr uint32_t kPairWait = 1u << 18;                      // bounded waits give up early in this variant
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;

@@ -272,8 +272,8 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     auto issue = [&](int32_t it_local) -> bool {
         const uint32_t b = static_cast<uint32_t>(it_local) & 1u;
         const uint32_t use = static_cast<uint32_t>(it_local >> 1) & 1u;
-        if (it_local == 0 && !mbar_wait(&w_full, 0, kWait)) return false;
-        if (!mbar_wait(&tmem_free[b], use ^ 1u, kWait) || !mbar_wait(&full_bar[b], use, kWait)) return false;
+        if (it_local == 0 && !mbar_wait_sleep(&w_full, 0)) return false;
+        if (!mbar_wait_sleep(&tmem_free[b], use ^ 1u) || !mbar_wait_sleep(&full_bar[b], use)) return false;
         tc_fence_after_sync();
         const uint32_t idesc = umma_idesc(1, 1, 0, 0, kRows, NC);
         const uint64_t desc0 = umma_desc_sw128(0, 1024, 16);
@@ -346,7 +346,7 @@ token_project_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         // and every arrival the others count on; its output is garbage and the status word says so.
         if (ok) {   // one lane polls, the warp follows
             int passed = 1;
-            if (lane == 0) passed = mbar_wait(&tmem_full[b], static_cast<uint32_t>(it >> 1) & 1u, kWait) ? 1 : 0;
+            if (lane == 0) passed = mbar_wait_sleep(&tmem_full[b], static_cast<uint32_t>(it >> 1) & 1u) ? 1 : 0;
             if (__shfl_sync(0xffffffffu, passed, 0) == 0) ok = false;
         }
         tc_fence_after_sync();
