@@ -188,20 +188,37 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* _
     }
 }
 
-// dgamma[i] = sum over the partial rows (in row order), rounded to T; the same for dbeta
+// dgamma[i] = sum over the partial rows, rounded to T; the same for dbeta.  A block owns 32 columns: thread (ty, tx)
+// adds the partial rows ty, ty + 32, ... of column tx (coalesced across tx), thread (0, tx) then adds the 32 sums in
+// the order of ty.  The order is fixed, so the result does not depend on scheduling; one thread per column walking
+// all ~600 partial rows was a chain of dependent loads that cost 25-30 us per call whatever the width.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 norm_bwd_reduce_kernel(const float* __restrict__ partial_w, const float* __restrict__ partial_b, T* __restrict__ dgamma,
                        T* __restrict__ dbeta, int n_partials, int cols) {
-    const int i = blockIdx.x * 256 + threadIdx.x;
-    if (i >= cols) return;
+    __shared__ float sw[32][33], sb[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + tx;
     float w = 0.f, b = 0.f;
-    for (int p = 0; p < n_partials; ++p) {
-        w += partial_w[static_cast<int64_t>(p) * cols + i];
-        if (partial_b != nullptr) b += partial_b[static_cast<int64_t>(p) * cols + i];
+    if (i < cols) {
+        for (int p = ty; p < n_partials; p += 32) {
+            w += partial_w[static_cast<int64_t>(p) * cols + i];
+            if (partial_b != nullptr) b += partial_b[static_cast<int64_t>(p) * cols + i];
+        }
     }
-    dgamma[i] = from_float<T>(w);
-    if (dbeta != nullptr) dbeta[i] = from_float<T>(b);
+    sw[ty][tx] = w;
+    sb[ty][tx] = b;
+    __syncthreads();
+    if (ty == 0 && i < cols) {
+        float ws = 0.f, bs = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            ws += sw[k][tx];
+            bs += sb[k][tx];
+        }
+        dgamma[i] = from_float<T>(ws);
+        if (dbeta != nullptr) dbeta[i] = from_float<T>(bs);
+    }
 }
 
 int grid_for(int64_t rows, int rows_per_cta) {
@@ -287,16 +304,16 @@ int norm_bwd(const void* x, const void* gamma, const void* dy, void* dx, void* d
         }
         if (code != TB200_OK) return code;
     }
-    const int rgrid = (cols + 255) / 256;
+    const int rgrid = (cols + 31) / 32;
     switch (dtype) {
         case TB200_F32:
-            norm_bwd_reduce_kernel<float><<<rgrid, 256, 0, s>>>(pw, pb, static_cast<float*>(dgamma), static_cast<float*>(dbeta), grid, cols);
+            norm_bwd_reduce_kernel<float><<<rgrid, 1024, 0, s>>>(pw, pb, static_cast<float*>(dgamma), static_cast<float*>(dbeta), grid, cols);
             break;
         case TB200_F16:
-            norm_bwd_reduce_kernel<__half><<<rgrid, 256, 0, s>>>(pw, pb, static_cast<__half*>(dgamma), static_cast<__half*>(dbeta), grid, cols);
+            norm_bwd_reduce_kernel<__half><<<rgrid, 1024, 0, s>>>(pw, pb, static_cast<__half*>(dgamma), static_cast<__half*>(dbeta), grid, cols);
             break;
         default:
-            norm_bwd_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, s>>>(pw, pb, static_cast<__nv_bfloat16*>(dgamma),
+            norm_bwd_reduce_kernel<__nv_bfloat16><<<rgrid, 1024, 0, s>>>(pw, pb, static_cast<__nv_bfloat16*>(dgamma),
                                                                           static_cast<__nv_bfloat16*>(dbeta), grid, cols);
             break;
     }
