@@ -138,6 +138,51 @@ bag_mean_kernel(BagArgs a, const void* __restrict__ ids, T* __restrict__ out) {
     const int chunks = a.chunks;
     constexpr int U = 4;  // table rows in flight per lane
 
+    if (a.max_bag == 1) {
+        // One id per bag (the field bank of single-valued features): the pooled row is the table row itself, so a lane
+        // group keeps the rows of four bags in flight instead of walking one bag after the other.
+        constexpr int B4 = 4;
+        for (int ql0 = group; ql0 < here; ql0 += B4 * n_groups) {
+            for (int c = lane_g; c < chunks; c += G) {
+                uint4 v[B4];
+                int id[B4];
+#pragma unroll
+                for (int u = 0; u < B4; ++u) {
+                    const int ql = ql0 + u * n_groups;
+                    id[u] = ql < here ? bag_ids[ql] : 0;
+                    v[u] = make_uint4(0, 0, 0, 0);
+                    if (id[u] != 0) {
+                        const int64_t q = q_base + ql;
+                        const uint4* table = a.tables != nullptr ? static_cast<const uint4*>(a.tables[q % a.n_fields])
+                                                                 : static_cast<const uint4*>(a.table0);
+                        v[u] = ld_nc_v4(table + static_cast<int64_t>(id[u]) * chunks + c);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < B4; ++u) {
+                    const int ql = ql0 + u * n_groups;
+                    if (ql >= here) continue;
+                    const int64_t q = q_base + ql;
+                    uint4 o = v[u];
+                    if (a.missing != nullptr) {
+                        const int64_t bidx = q / a.n_fields;
+                        const int f = static_cast<int>(q - bidx * a.n_fields);
+                        if (a.missing[bidx * a.missing_cols + f] != 0) {
+                            float x[N], m[N];
+                            Vec16<T>::unpack(o, x);
+                            Vec16<T>::unpack(static_cast<const uint4*>(a.missing_rows)[f * chunks + c], m);
+#pragma unroll
+                            for (int e = 0; e < N; ++e) x[e] += m[e];
+                            o = Vec16<T>::pack(x);
+                        }
+                    }
+                    st_cs_v4(reinterpret_cast<uint4*>(out) + q * chunks + c, o);
+                }
+            }
+        }
+        return;
+    }
+
     for (int ql = group; ql < here; ql += n_groups) {
         const int64_t q = q_base + ql;
         const uint4* table = static_cast<const uint4*>(a.table0);

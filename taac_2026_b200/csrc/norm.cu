@@ -446,6 +446,89 @@ norm_rowwarp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const 
     }
 }
 
+// Warp per row for rows wider than the TMA-staged kernel takes (more than 256 16-byte pieces), whole pieces and
+// 16-byte aligned bases: a lane walks the pieces lane, lane + 32, ... three times (sum, centred squares, output) and
+// keeps them, after the bias / SiLU step, in a shared-memory row of the warp between the passes.  Every lane only
+// reads back the pieces it wrote itself, so the passes need no barrier.
+template <typename T, bool LAYER, int PRE>
+__global__ void __launch_bounds__(kMaxThreads)
+norm_rowwarp_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                        T* __restrict__ y, int64_t rows, int cols, float eps) {
+    constexpr int N = Vec16<T>::N;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int lane = threadIdx.x & 31;
+    const int warp_in_cta = threadIdx.x >> 5;
+    const int chunks = cols / N;
+    uint4* srow = reinterpret_cast<uint4*>(smem) + static_cast<size_t>(warp_in_cta) * chunks;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kMaxThreads + threadIdx.x) >> 5;
+    const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * kMaxThreads) >> 5;
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+    const uint4* b4 = reinterpret_cast<const uint4*>(beta);
+    for (int64_t row = warp; row < rows; row += n_warps) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+        uint4* yr = reinterpret_cast<uint4*>(y + row * cols);
+        float acc = 0.f;   // LayerNorm: sum of the row; RMSNorm: sum of squares
+        for (int c = lane; c < chunks; c += 32) {
+            uint4 p = ld_nc_u4(xr + c);
+            float f[N];
+            Vec16<T>::unpack(p, f);
+            if (PRE == kPreBias) {
+                float b[N];
+                Vec16<T>::unpack(b4[c], b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) f[e] += b[e];
+            }
+            if (PRE == kPreSilu) {
+#pragma unroll
+                for (int e = 0; e < N; ++e) f[e] = round_to<T>(silu_f<T>(f[e]));
+                p = Vec16<T>::pack(f);
+            }
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc = LAYER ? acc + f[e] : fmaf(f[e], f[e], acc);
+            srow[c] = p;   // with a bias: x as it came (x + bias in fp32 does not fit a 16-bit row; the output pass adds it again)
+        }
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        float mean = 0.f, sq = acc;
+        if (LAYER) {
+            mean = acc * inv_cols;
+            sq = 0.f;
+            for (int c = lane; c < chunks; c += 32) {
+                float f[N];
+                Vec16<T>::unpack(srow[c], f);
+#pragma unroll
+                for (int e = 0; e < N; ++e) {
+                    const float d = f[e] - mean;
+                    sq = fmaf(d, d, sq);
+                }
+            }
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        }
+        const float inv = rsqrtf(sq * inv_cols + eps);
+        for (int c = lane; c < chunks; c += 32) {
+            float f[N], g[N], o[N];
+            Vec16<T>::unpack(srow[c], f);
+            Vec16<T>::unpack(g4[c], g);
+            if (PRE == kPreBias) {
+                float b[N];
+                Vec16<T>::unpack(b4[c], b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) f[e] += b[e];
+            }
+            if (LAYER) {
+                float b[N];
+                Vec16<T>::unpack(b4[c], b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) o[e] = fmaf((f[e] - mean) * inv, g[e], b[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < N; ++e) o[e] = (f[e] * inv) * g[e];
+            }
+            yr[c] = Vec16<T>::pack(o);
+        }
+    }
+}
+
 template <typename T, bool LAYER, int CPL, int RU, int PRE, bool POST, bool EXACT>
 int launch_tma_exact(const void* x, const void* gamma, const void* beta, void* y, int64_t rows, int cols, float eps,
                      int lanes_per_row, cudaStream_t stream, const PostArgs post) {
@@ -507,6 +590,22 @@ int norm_dispatch(const void* x, const void* gamma, const void* beta, void* y, i
     const int64_t cap = static_cast<int64_t>(dev.sm_count) * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
+    const bool wide_vec = (cols % N == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) &&
+                          ((!LAYER && PRE != kPreBias) || aligned16(beta)) && (cols / N) <= 640;
+    if (wide_vec) {   // up to 10 KB of row per warp, 80 KB per block
+        const size_t smem = static_cast<size_t>(kMaxThreads / 32) * (cols / N) * 16;
+        static bool attr_set[64] = {};
+        if (!attr_set[dev.index]) {
+            cudaFuncSetAttribute(norm_rowwarp_vec_kernel<T, LAYER, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
+            attr_set[dev.index] = true;
+        }
+        const int64_t cap_vec = static_cast<int64_t>(dev.sm_count) * (smem > 56 * 1024 ? 2 : (smem > 36 * 1024 ? 4 : 6));
+        if (blocks > cap_vec) blocks = cap_vec;
+        norm_rowwarp_vec_kernel<T, LAYER, PRE><<<static_cast<unsigned>(blocks), kMaxThreads, smem, stream>>>(
+            static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows, cols, eps);
+        count_launch();
+        return launch_status();
+    }
     norm_rowwarp_kernel<T, LAYER, PRE><<<static_cast<unsigned>(blocks), kMaxThreads, 0, stream>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), rows,
         cols, eps);

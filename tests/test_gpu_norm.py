@@ -37,7 +37,7 @@ def _inputs(rows, cols, dtype, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("cols", [1, 7, 8, 96, 127, 128, 256, 384, 385, 400, 512, 1024, 2048, 4096])
+@pytest.mark.parametrize("cols", [1, 7, 8, 96, 127, 128, 256, 384, 385, 400, 512, 1024, 2048, 2560, 4096])
 def test_norms_match_oracle(dtype, cols):
     rows = 333
     x, w, b = _inputs(rows, cols, dtype, seed=cols)
@@ -108,7 +108,7 @@ def test_full_size_sweep_properties(cols):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("cols", [7, 128, 384, 512, 1024, 4096])
+@pytest.mark.parametrize("cols", [7, 128, 384, 512, 1024, 2560, 4096])
 def test_rms_norm_with_input_bias(dtype, cols):
     """rms_norm(x, in_bias=b) == rms_norm of the fp32 sum x + b (the bias never rounds on its own)."""
     x, w, b = _inputs(257, cols, dtype, seed=cols + 1)
@@ -118,7 +118,7 @@ def test_rms_norm_with_input_bias(dtype, cols):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("cols", [7, 128, 384, 512, 1024, 4096])
+@pytest.mark.parametrize("cols", [7, 128, 384, 512, 1024, 2560, 4096])
 def test_layer_norm_of_silu(dtype, cols):
     """layer_norm(x, pre_silu=True) == layer_norm(silu(x)) with the activation rounded to the dtype."""
     x, w, b = _inputs(257, cols, dtype, seed=cols + 2)
